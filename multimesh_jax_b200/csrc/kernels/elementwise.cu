@@ -1,0 +1,638 @@
+// Memory-bound transformer kernels for sm_100a: RMSNorm, RoPE, SwiGLU, fused
+// softmax cross-entropy, embedding gather / scatter-add, residual add,
+// gradient accumulation, and the fused AdamW update over flat buffers.
+// All use 16-byte vector accesses and keep each row resident in registers so
+// every tensor is read once and written once.
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace mm {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < THREADS / 32) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+template <int THREADS>
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < THREADS / 32) ? red[l] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per row; each thread keeps VPT 8-element vectors in registers.
+// THREADS x VPT x 8 >= hidden size; instantiated for hidden sizes up to 16384.
+template <int RN_THREADS, int RN_MAX_VEC>
+__global__ void __launch_bounds__(RN_THREADS)
+    rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int D, float eps) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+  const int nvec = D / 8;
+  uint4 xv[RN_MAX_VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      xv[i] = xr[v];
+      float2 a = unpack_bf16(xv[i].x), b = unpack_bf16(xv[i].y), c = unpack_bf16(xv[i].z),
+             d = unpack_bf16(xv[i].w);
+      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x +
+            d.y * d.y;
+    }
+  }
+  ss = block_sum<RN_THREADS>(ss, red);
+  const float r = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      uint4 wv = wr[v];
+      uint4 o;
+      float2 a, g;
+      a = unpack_bf16(xv[i].x); g = unpack_bf16(wv.x); o.x = pack_bf16(a.x * r * g.x, a.y * r * g.y);
+      a = unpack_bf16(xv[i].y); g = unpack_bf16(wv.y); o.y = pack_bf16(a.x * r * g.x, a.y * r * g.y);
+      a = unpack_bf16(xv[i].z); g = unpack_bf16(wv.z); o.z = pack_bf16(a.x * r * g.x, a.y * r * g.y);
+      a = unpack_bf16(xv[i].w); g = unpack_bf16(wv.w); o.w = pack_bf16(a.x * r * g.x, a.y * r * g.y);
+      yr[v] = o;
+    }
+  }
+}
+
+// Backward. dx = rstd * (dy*w) - x * rstd^3 * mean(dy*w*x).  Weight-gradient
+// partial sums go to a scratch buffer `dw_partial` [gridDim.x, D] (fp32) that a
+// second kernel reduces. Blocks stride over rows so the partial count is small.
+template <int RN_THREADS, int RN_MAX_VEC>
+__global__ void __launch_bounds__(RN_THREADS)
+    rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows,
+                       int D, int add_to_dx) {
+  __shared__ float red[32];
+  const int nvec = D / 8;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  float wreg[RN_MAX_VEC][8];
+  float dwacc[RN_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (v < nvec) {
+      uint4 wv = wr[v];
+      float2 a = unpack_bf16(wv.x), b = unpack_bf16(wv.y), c = unpack_bf16(wv.z),
+             d = unpack_bf16(wv.w);
+      wreg[i][0] = a.x; wreg[i][1] = a.y; wreg[i][2] = b.x; wreg[i][3] = b.y;
+      wreg[i][4] = c.x; wreg[i][5] = c.y; wreg[i][6] = d.x; wreg[i][7] = d.y;
+    }
+  }
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
+    const float r = rstd[row];
+    float xf[RN_MAX_VEC][8], gf[RN_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RN_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * RN_THREADS;
+      if (v < nvec) {
+        uint4 xv = xr[v], gv = gr[v];
+        float2 a;
+        a = unpack_bf16(xv.x); xf[i][0] = a.x; xf[i][1] = a.y;
+        a = unpack_bf16(xv.y); xf[i][2] = a.x; xf[i][3] = a.y;
+        a = unpack_bf16(xv.z); xf[i][4] = a.x; xf[i][5] = a.y;
+        a = unpack_bf16(xv.w); xf[i][6] = a.x; xf[i][7] = a.y;
+        a = unpack_bf16(gv.x); gf[i][0] = a.x; gf[i][1] = a.y;
+        a = unpack_bf16(gv.y); gf[i][2] = a.x; gf[i][3] = a.y;
+        a = unpack_bf16(gv.z); gf[i][4] = a.x; gf[i][5] = a.y;
+        a = unpack_bf16(gv.w); gf[i][6] = a.x; gf[i][7] = a.y;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          dwacc[i][j] += gf[i][j] * xf[i][j] * r;
+          gf[i][j] *= wreg[i][j];
+          dot += gf[i][j] * xf[i][j];
+        }
+      }
+    }
+    dot = block_sum<RN_THREADS>(dot, red);
+    const float c = dot * r * r * r / D;
+#pragma unroll
+    for (int i = 0; i < RN_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * RN_THREADS;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gf[i][j] * r - xf[i][j] * c;
+        if (add_to_dx) {
+          uint4 old = dxr[v];
+          float2 a;
+          a = unpack_bf16(old.x); o[0] += a.x; o[1] += a.y;
+          a = unpack_bf16(old.y); o[2] += a.x; o[3] += a.y;
+          a = unpack_bf16(old.z); o[4] += a.x; o[5] += a.y;
+          a = unpack_bf16(old.w); o[6] += a.x; o[7] += a.y;
+        }
+        uint4 ov;
+        ov.x = pack_bf16(o[0], o[1]); ov.y = pack_bf16(o[2], o[3]);
+        ov.z = pack_bf16(o[4], o[5]); ov.w = pack_bf16(o[6], o[7]);
+        dxr[v] = ov;
+      }
+    }
+  }
+  float* out = dw_partial + static_cast<int64_t>(blockIdx.x) * D;
+#pragma unroll
+  for (int i = 0; i < RN_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      float4* o4 = reinterpret_cast<float4*>(out + v * 8);
+      o4[0] = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      o4[1] = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
+  }
+}
+
+// dw[j] (+)= sum_p partial[p, j]
+__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                       int parts, int D, int accumulate) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= D) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[static_cast<int64_t>(p) * D + j];
+  dw[j] = accumulate ? dw[j] + s : s;
+}
+
+// --------------------------------------------------------------------- RoPE
+// In-place rotate-half rotary embedding on a [T, H, Dh] view with row stride
+// `stride_t` elements (lets q and k be slices of one fused QKV buffer).
+// cos/sin tables are fp32 [S, Dh/2]; position of token t is t % S.
+// `sign` = +1 forward, -1 backward (inverse rotation).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cs,
+                            const float* __restrict__ sn, int64_t T, int S, int H, int Dh,
+                            int64_t stride_t, float sign) {
+  const int half = Dh / 2;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per_tok = H * (half / 2);  // each thread handles 2 adjacent pairs (bf162)
+  const int64_t total = T * per_tok;
+  if (idx >= total) return;
+  const int64_t t = idx / per_tok;
+  const int rem = static_cast<int>(idx - t * per_tok);
+  const int h = rem / (half / 2);
+  const int i = (rem - h * (half / 2)) * 2;
+  const int pos = static_cast<int>(t % S);
+  __nv_bfloat16* base = qk + t * stride_t + static_cast<int64_t>(h) * Dh;
+  __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(base + i);
+  __nv_bfloat162 hi = *reinterpret_cast<__nv_bfloat162*>(base + i + half);
+  const float2 c = *reinterpret_cast<const float2*>(cs + static_cast<int64_t>(pos) * half + i);
+  float2 s = *reinterpret_cast<const float2*>(sn + static_cast<int64_t>(pos) * half + i);
+  s.x *= sign; s.y *= sign;
+  const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+  float2 olo, ohi;
+  olo.x = a.x * c.x - b.x * s.x; olo.y = a.y * c.y - b.y * s.y;
+  ohi.x = b.x * c.x + a.x * s.x; ohi.y = b.y * c.y + a.y * s.y;
+  *reinterpret_cast<__nv_bfloat162*>(base + i) = __floats2bfloat162_rn(olo.x, olo.y);
+  *reinterpret_cast<__nv_bfloat162*>(base + i + half) = __floats2bfloat162_rn(ohi.x, ohi.y);
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  h = silu(gate) * up.
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ h, int64_t T, int F) {
+  const int fv = F / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * fv) return;
+  const int64_t t = idx / fv;
+  const int v = static_cast<int>(idx - t * fv);
+  const uint4 g = reinterpret_cast<const uint4*>(gu + t * 2 * F)[v];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + t * 2 * F + F)[v];
+  const uint32_t gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w};
+  uint32_t oo[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 a = unpack_bf16(gg[j]), b = unpack_bf16(uu[j]);
+    float s0 = a.x / (1.f + __expf(-a.x)), s1 = a.y / (1.f + __expf(-a.y));
+    oo[j] = pack_bf16(s0 * b.x, s1 * b.y);
+  }
+  reinterpret_cast<uint4*>(h + t * F)[v] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+}
+
+// dgu[:, :F] = dh * up * silu'(gate),  dgu[:, F:] = dh * silu(gate)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
+                                  const __nv_bfloat16* __restrict__ dh,
+                                  __nv_bfloat16* __restrict__ dgu, int64_t T, int F) {
+  const int fv = F / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * fv) return;
+  const int64_t t = idx / fv;
+  const int v = static_cast<int>(idx - t * fv);
+  const uint4 g = reinterpret_cast<const uint4*>(gu + t * 2 * F)[v];
+  const uint4 u = reinterpret_cast<const uint4*>(gu + t * 2 * F + F)[v];
+  const uint4 d = reinterpret_cast<const uint4*>(dh + t * F)[v];
+  const uint32_t gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w},
+                 dd[4] = {d.x, d.y, d.z, d.w};
+  uint32_t og[4], ou[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 a = unpack_bf16(gg[j]), b = unpack_bf16(uu[j]), e = unpack_bf16(dd[j]);
+    float sg0 = 1.f / (1.f + __expf(-a.x)), sg1 = 1.f / (1.f + __expf(-a.y));
+    float si0 = a.x * sg0, si1 = a.y * sg1;
+    float ds0 = sg0 * (1.f + a.x * (1.f - sg0)), ds1 = sg1 * (1.f + a.y * (1.f - sg1));
+    og[j] = pack_bf16(e.x * b.x * ds0, e.y * b.y * ds1);
+    ou[j] = pack_bf16(e.x * si0, e.y * si1);
+  }
+  reinterpret_cast<uint4*>(dgu + t * 2 * F)[v] = make_uint4(og[0], og[1], og[2], og[3]);
+  reinterpret_cast<uint4*>(dgu + t * 2 * F + F)[v] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+}
+
+// ----------------------------------------------------------- cross-entropy
+// One block per row. Pass 1: online max / sum-exp. Pass 2 (optional): write
+// dlogits = (softmax - onehot) * grad_scale in place of the logits.
+// loss[row] = logsumexp - logit[target]; rows with target < 0 are ignored.
+// For a vocabulary sharded over ranks, `vocab_start` is this shard's first id
+// and stats_out receives (max, sumexp, target_logit) for a later combine.
+constexpr int CE_THREADS = 256;
+__global__ void __launch_bounds__(CE_THREADS)
+    cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const int64_t* __restrict__ targets,
+                         float* __restrict__ loss, float* __restrict__ stats_out,
+                         const float* __restrict__ stats_in, int V, int64_t ld, int vocab_start,
+                         float grad_scale, int write_grad) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const int64_t tgt = targets[row];
+  const int nvec = V / 8;
+  float mx, se;
+  if (stats_in) {
+    mx = stats_in[row * 2];
+    se = stats_in[row * 2 + 1];
+  } else {
+    float m = -INFINITY, s = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+      uint4 x = reinterpret_cast<const uint4*>(lr)[v];
+      const uint32_t xx[4] = {x.x, x.y, x.z, x.w};
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 a = unpack_bf16(xx[j]); f[2 * j] = a.x; f[2 * j + 1] = a.y; }
+      float lm = f[0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) lm = fmaxf(lm, f[j]);
+      const float nm = fmaxf(m, lm);
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += __expf(f[j] - nm);
+      s = s * __expf(m - nm) + acc;
+      m = nm;
+    }
+    for (int j = nvec * 8 + threadIdx.x; j < V; j += CE_THREADS) {
+      const float f = __bfloat162float(lr[j]);
+      const float nm = fmaxf(m, f);
+      s = s * __expf(m - nm) + __expf(f - nm);
+      m = nm;
+    }
+    mx = block_max<CE_THREADS>(m, red);
+    const float contrib = (m == -INFINITY) ? 0.f : s * __expf(m - mx);
+    se = block_sum<CE_THREADS>(contrib, red);
+  }
+  const int64_t local_t = tgt - vocab_start;
+  const bool has_t = tgt >= 0 && local_t >= 0 && local_t < V;
+  if (threadIdx.x == 0) {
+    const float tl = has_t ? __bfloat162float(lr[local_t]) : 0.f;
+    if (stats_out) {
+      stats_out[row * 3] = mx;
+      stats_out[row * 3 + 1] = se;
+      stats_out[row * 3 + 2] = tl;
+    }
+    if (loss) loss[row] = (tgt >= 0) ? (logf(se) + mx - tl) : 0.f;
+  }
+  if (!write_grad) return;
+  const float inv = (tgt >= 0) ? grad_scale / se : 0.f;
+  const float gs = (tgt >= 0) ? grad_scale : 0.f;
+  for (int v = threadIdx.x; v < nvec; v += CE_THREADS) {
+    uint4 x = reinterpret_cast<const uint4*>(lr)[v];
+    const uint32_t xx[4] = {x.x, x.y, x.z, x.w};
+    uint32_t oo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = unpack_bf16(xx[j]);
+      float g0 = __expf(a.x - mx) * inv, g1 = __expf(a.y - mx) * inv;
+      const int c = v * 8 + 2 * j;
+      if (has_t && c == local_t) g0 -= gs;
+      if (has_t && c + 1 == local_t) g1 -= gs;
+      oo[j] = pack_bf16(g0, g1);
+    }
+    reinterpret_cast<uint4*>(lr)[v] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+  }
+  for (int j = nvec * 8 + threadIdx.x; j < V; j += CE_THREADS) {
+    float g = __expf(__bfloat162float(lr[j]) - mx) * inv;
+    if (has_t && j == local_t) g -= gs;
+    lr[j] = __float2bfloat16(g);
+  }
+}
+
+// ---------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
+                                     const int64_t* __restrict__ ids, __nv_bfloat16* __restrict__ out,
+                                     int64_t T, int D, int vocab_start, int vocab_size) {
+  const int dv = D / 8;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * dv) return;
+  const int64_t t = idx / dv;
+  const int v = static_cast<int>(idx - t * dv);
+  const int64_t id = ids[t] - vocab_start;
+  uint4 val = make_uint4(0, 0, 0, 0);
+  if (id >= 0 && id < vocab_size) val = reinterpret_cast<const uint4*>(table + id * D)[v];
+  reinterpret_cast<uint4*>(out + t * D)[v] = val;
+}
+// grad_table (fp32) [V, D] += scatter of dout rows.
+__global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                     const int64_t* __restrict__ ids, float* __restrict__ grad,
+                                     int64_t T, int D, int vocab_start, int vocab_size) {
+  const int dv = D / 2;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * dv) return;
+  const int64_t t = idx / dv;
+  const int v = static_cast<int>(idx - t * dv);
+  const int64_t id = ids[t] - vocab_start;
+  if (id < 0 || id >= vocab_size) return;
+  const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dout + t * D)[v]);
+  float* dst = grad + id * D + v * 2;
+  atomicAdd(dst, g.x);
+  atomicAdd(dst + 1, g.y);
+}
+
+// ------------------------------------------------------- adds / accumulation
+// out = a + b (bf16); out may alias a.
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, int64_t n8) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 x = reinterpret_cast<const uint4*>(a)[i], y = reinterpret_cast<const uint4*>(b)[i];
+  const uint32_t xx[4] = {x.x, x.y, x.z, x.w}, yy[4] = {y.x, y.y, y.z, y.w};
+  uint32_t oo[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 p = unpack_bf16(xx[j]), q = unpack_bf16(yy[j]);
+    oo[j] = pack_bf16(p.x + q.x, p.y + q.y);
+  }
+  reinterpret_cast<uint4*>(out)[i] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+}
+// acc(fp32) += src(bf16)
+__global__ void accumulate_f32_bf16_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ src,
+                                           int64_t n8) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 x = reinterpret_cast<const uint4*>(src)[i];
+  float4* a4 = reinterpret_cast<float4*>(acc) + i * 2;
+  float4 a0 = a4[0], a1 = a4[1];
+  float2 p;
+  p = unpack_bf16(x.x); a0.x += p.x; a0.y += p.y;
+  p = unpack_bf16(x.y); a0.z += p.x; a0.w += p.y;
+  p = unpack_bf16(x.z); a1.x += p.x; a1.y += p.y;
+  p = unpack_bf16(x.w); a1.z += p.x; a1.w += p.y;
+  a4[0] = a0;
+  a4[1] = a1;
+}
+
+// --------------------------------------------------------------------- AdamW
+// Flat-buffer update: fp32 master weights, moments and gradients; writes the
+// bf16 working copy in the same pass. grad is multiplied by grad_scale first
+// (1/num_microbatches, loss scaling or clip coefficient).
+__global__ void adamw_kernel(float* __restrict__ master, __nv_bfloat16* __restrict__ param,
+                             float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ grad, int64_t n4, float lr, float beta1,
+                             float beta2, float eps, float wd, float bc1, float bc2,
+                             float grad_scale) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 p = reinterpret_cast<float4*>(master)[i];
+  float4 mm_ = reinterpret_cast<float4*>(m)[i];
+  float4 vv = reinterpret_cast<float4*>(v)[i];
+  const float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+  float pa[4] = {p.x, p.y, p.z, p.w}, ma[4] = {mm_.x, mm_.y, mm_.z, mm_.w},
+        va[4] = {vv.x, vv.y, vv.z, vv.w}, ga[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float g = ga[j] * grad_scale;
+    ma[j] = beta1 * ma[j] + (1.f - beta1) * g;
+    va[j] = beta2 * va[j] + (1.f - beta2) * g * g;
+    const float mh = ma[j] / bc1, vh = va[j] / bc2;
+    pa[j] = pa[j] * (1.f - lr * wd) - lr * mh / (sqrtf(vh) + eps);
+  }
+  reinterpret_cast<float4*>(master)[i] = make_float4(pa[0], pa[1], pa[2], pa[3]);
+  reinterpret_cast<float4*>(m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+  reinterpret_cast<float4*>(v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+  uint2 o;
+  o.x = pack_bf16(pa[0], pa[1]);
+  o.y = pack_bf16(pa[2], pa[3]);
+  reinterpret_cast<uint2*>(param)[i] = o;
+}
+
+// sum of squares of an fp32 buffer into out[0] (atomic), for gradient clipping.
+__global__ void sumsq_f32_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float f = x[i];
+    s += f * f;
+  }
+  s = block_sum<256>(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+}  // namespace mm
+
+// -------------------------------------------------------------------- C API
+extern "C" {
+using namespace mm;
+
+static inline unsigned blocks_for(int64_t n, int threads) {
+  return static_cast<unsigned>((n + threads - 1) / threads);
+}
+
+int mm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t rows, int D,
+                   float eps, cudaStream_t stream) {
+  if (D % 8 || D > 16384) return -2;
+  if (rows == 0) return 0;
+#define MM_RN_FWD(TH, VPT)                                                              \
+  rmsnorm_fwd_kernel<TH, VPT><<<static_cast<unsigned>(rows), TH, 0, stream>>>(          \
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),       \
+      static_cast<__nv_bfloat16*>(y), rstd, D, eps)
+  if (D <= 1024) MM_RN_FWD(128, 1);
+  else if (D <= 2048) MM_RN_FWD(128, 2);
+  else if (D <= 4096) MM_RN_FWD(128, 4);
+  else if (D <= 8192) MM_RN_FWD(256, 4);
+  else MM_RN_FWD(512, 4);
+#undef MM_RN_FWD
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Number of row-partials the backward kernel produces for `rows` rows; the
+// scratch buffer must hold mm_rmsnorm_bwd_parts(rows) * D floats.
+int mm_rmsnorm_bwd_parts(int64_t rows) {
+  DeviceState* ds = device_state();
+  const int cap = ds ? ds->sm_count * 2 : 296;
+  return static_cast<int>(rows < cap ? rows : cap);
+}
+
+// dw_out is fp32 [D]; accumulate_dw != 0 adds into it. add_to_dx != 0 adds
+// the result into dx (fuses the residual-branch gradient add).
+int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, void* dx,
+                   float* dw_out, float* scratch, int64_t rows, int D, int accumulate_dw,
+                   int add_to_dx, cudaStream_t stream) {
+  if (D % 8 || D > 16384) return -2;
+  if (rows == 0) return 0;
+  const int parts = mm_rmsnorm_bwd_parts(rows);
+#define MM_RN_BWD(TH, VPT)                                                                   \
+  rmsnorm_bwd_kernel<TH, VPT><<<parts, TH, 0, stream>>>(                                     \
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),            \
+      static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), scratch, \
+      static_cast<int>(rows), D, add_to_dx)
+  if (D <= 1024) MM_RN_BWD(128, 1);
+  else if (D <= 2048) MM_RN_BWD(128, 2);
+  else if (D <= 4096) MM_RN_BWD(128, 4);
+  else if (D <= 8192) MM_RN_BWD(256, 4);
+  else MM_RN_BWD(512, 4);
+#undef MM_RN_BWD
+  MM_CUDA_TRY(cudaGetLastError());
+  colsum_partials_kernel<<<blocks_for(D, 128), 128, 0, stream>>>(scratch, dw_out, parts, D,
+                                                               accumulate_dw);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_rope(void* qk, const float* cos_t, const float* sin_t, int64_t T, int S, int H, int Dh,
+            int64_t stride_t, int backward, cudaStream_t stream) {
+  if (Dh % 4) return -2;
+  const int64_t total = T * H * (Dh / 4);
+  if (total == 0) return 0;
+  rope_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(qk), cos_t,
+                                                         sin_t, T, S, H, Dh, stride_t,
+                                                         backward ? -1.f : 1.f);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_swiglu_fwd(const void* gu, void* h, int64_t T, int F, cudaStream_t stream) {
+  if (F % 8) return -2;
+  const int64_t total = T * (F / 8);
+  if (total == 0) return 0;
+  swiglu_fwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), T, F);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+int mm_swiglu_bwd(const void* gu, const void* dh, void* dgu, int64_t T, int F, cudaStream_t stream) {
+  if (F % 8) return -2;
+  const int64_t total = T * (F / 8);
+  if (total == 0) return 0;
+  swiglu_bwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh),
+      static_cast<__nv_bfloat16*>(dgu), T, F);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_cross_entropy(void* logits, const int64_t* targets, float* loss, float* stats_out,
+                     const float* stats_in, int64_t rows, int V, int64_t ld, int vocab_start,
+                     float grad_scale, int write_grad, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (ld % 8) return -2;
+  cross_entropy_kernel<<<static_cast<unsigned>(rows), CE_THREADS, 0, stream>>>(
+      static_cast<__nv_bfloat16*>(logits), targets, loss, stats_out, stats_in, V, ld, vocab_start,
+      grad_scale, write_grad);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t T, int D,
+                     int vocab_start, int vocab_size, cudaStream_t stream) {
+  if (D % 8) return -2;
+  const int64_t total = T * (D / 8);
+  if (total == 0) return 0;
+  embedding_fwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), T, D,
+      vocab_start, vocab_size);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+int mm_embedding_bwd(const void* dout, const int64_t* ids, float* grad, int64_t T, int D,
+                     int vocab_start, int vocab_size, cudaStream_t stream) {
+  if (D % 2) return -2;
+  const int64_t total = T * (D / 2);
+  if (total == 0) return 0;
+  embedding_bwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dout), ids, grad, T, D, vocab_start, vocab_size);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_add_bf16(const void* a, const void* b, void* out, int64_t n, cudaStream_t stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  add_bf16_kernel<<<blocks_for(n / 8, 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b),
+      static_cast<__nv_bfloat16*>(out), n / 8);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+int mm_accumulate_f32_bf16(float* acc, const void* src, int64_t n, cudaStream_t stream) {
+  if (n % 8) return -2;
+  if (n == 0) return 0;
+  accumulate_f32_bf16_kernel<<<blocks_for(n / 8, 256), 256, 0, stream>>>(
+      acc, static_cast<const __nv_bfloat16*>(src), n / 8);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_adamw(float* master, void* param, float* m, float* v, const float* grad, int64_t n, float lr,
+             float beta1, float beta2, float eps, float wd, int step, float grad_scale,
+             cudaStream_t stream) {
+  if (n % 4) return -2;
+  if (n == 0) return 0;
+  const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
+  const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
+  adamw_kernel<<<blocks_for(n / 4, 256), 256, 0, stream>>>(master, static_cast<__nv_bfloat16*>(param),
+                                                         m, v, grad, n / 4, lr, beta1, beta2, eps,
+                                                         wd, bc1, bc2, grad_scale);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_sumsq_f32(const float* x, int64_t n, float* out, cudaStream_t stream) {
+  if (n == 0) return 0;
+  DeviceState* ds = device_state();
+  const int grid = ds ? ds->sm_count * 4 : 592;
+  sumsq_f32_kernel<<<grid, 256, 0, stream>>>(x, n, out);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

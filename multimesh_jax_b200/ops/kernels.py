@@ -1,0 +1,365 @@
+"""Functional layer over the CUDA kernel library.
+
+Every function takes ``torch.Tensor`` arguments. CUDA tensors are handed to
+the hand-written sm_100a kernels on the current stream; CPU tensors run an
+equivalent PyTorch implementation so the framework can be exercised (and the
+kernels' numerics checked) without a GPU. A CUDA tensor never falls back to a
+PyTorch op silently: if the kernel library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+bf16 = torch.bfloat16
+
+# Number of kernel launches issued through this module (for benchmarks).
+launch_count = 0
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def read_status(clear: bool = True) -> int:
+    """Device status word: 0 when no kernel has recorded a bounded-wait expiry."""
+    return _lib.load().mm_read_status(1 if clear else 0)
+
+
+# --------------------------------------------------------------------- GEMM
+_OUT_MODE = {(bf16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2, (bf16, True): 3}
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = bf16,
+         accumulate: bool = False) -> torch.Tensor:
+    """``C[M,N] (+)= A[M,K] @ B[N,K]^T`` with bf16 inputs and fp32 accumulation.
+
+    ``a_mn`` / ``b_mn`` say that the operand is stored transposed (``[K, M]`` /
+    ``[K, N]`` in memory, i.e. contiguous along M / N). Operands must be 2-D
+    with unit stride in the last dimension.
+    """
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        assert not accumulate
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == (M, N) and out.stride(1) == 1
+    if not a.is_cuda:
+        af = (a.t() if a_mn else a).float()
+        bf = (b.t() if b_mn else b).float()
+        res = af @ bf.t()
+        if accumulate:
+            out.add_(res.to(out.dtype))
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+    assert a.dtype == bf16 and b.dtype == bf16
+    mode = _OUT_MODE[(out.dtype, accumulate)]
+    lib = _lib.load()
+    rc = lib.mm_gemm_bf16(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn),
+                          b.stride(0), out.data_ptr(), mode, out.stride(0), M, N, K, _stream())
+    _lib.check(rc, "mm_gemm_bf16")
+    _count()
+    return out
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[T, N] = x[T, K] @ w[N, K]^T."""
+    return gemm(x, w, out=out)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """dx[T, K] = dy[T, N] @ w[N, K]."""
+    return gemm(dy, w, b_mn=True, out=out, accumulate=accumulate)
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 accumulate: bool = False, out_dtype: torch.dtype = bf16) -> torch.Tensor:
+    """dw[N, K] (+)= dy[T, N]^T @ x[T, K]."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------------ RMSNorm
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    D = x.shape[-1]
+    rows = x.numel() // D
+    if not x.is_cuda:
+        xf = x.float()
+        rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        y = (xf * rstd * w.float()).to(x.dtype)
+        return y, rstd.reshape(rows)
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rc = _lib.load().mm_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, D,
+                                    eps, _stream())
+    _lib.check(rc, "mm_rmsnorm_fwd")
+    _count()
+    return y, rstd
+
+
+_scratch = {}
+
+
+def _get_scratch(device, nfloats: int) -> torch.Tensor:
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < nfloats:
+        buf = torch.empty(max(nfloats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, rstd: torch.Tensor,
+                dw_out: Optional[torch.Tensor] = None, accumulate_dw: bool = False,
+                dx_inout: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns (dx, dw). ``dw`` is fp32. With ``dx_inout`` the input gradient is
+    added into that tensor (fusing the residual-stream add)."""
+    D = x.shape[-1]
+    rows = x.numel() // D
+    if not x.is_cuda:
+        xf, gf, wf = x.float().reshape(rows, D), dy.float().reshape(rows, D), w.float()
+        r = rstd.reshape(rows, 1)
+        gw = gf * wf
+        dx = gw * r - xf * (r ** 3) * (gw * xf).sum(-1, keepdim=True) / D
+        dw = (gf * xf * r).sum(0)
+        if dx_inout is not None:
+            dx_inout.add_(dx.reshape(x.shape).to(x.dtype))
+            dx_t = dx_inout
+        else:
+            dx_t = dx.reshape(x.shape).to(x.dtype)
+        if dw_out is None:
+            dw_out = dw
+        elif accumulate_dw:
+            dw_out.add_(dw)
+        else:
+            dw_out.copy_(dw)
+        return dx_t, dw_out
+    lib = _lib.load()
+    x = x.contiguous()
+    dy = dy.contiguous()
+    dx = dx_inout if dx_inout is not None else torch.empty_like(x)
+    if dw_out is None:
+        dw_out = torch.empty(D, dtype=torch.float32, device=x.device)
+        accumulate_dw = False
+    parts = lib.mm_rmsnorm_bwd_parts(rows)
+    scratch = _get_scratch(x.device, parts * D)
+    rc = lib.mm_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                            dw_out.data_ptr(), scratch.data_ptr(), rows, D, int(accumulate_dw),
+                            int(dx_inout is not None), _stream())
+    _lib.check(rc, "mm_rmsnorm_bwd")
+    _count(2)
+    return dx, dw_out
+
+
+# --------------------------------------------------------------------- RoPE
+def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float64), inv)
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+def rope_(qk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, backward: bool = False) -> torch.Tensor:
+    """In-place rotate-half RoPE on ``qk`` of shape [T, H, Dh] (token stride may
+    exceed H*Dh, e.g. a slice of a fused QKV buffer). Position = t % S."""
+    T, H, Dh = qk.shape
+    S = cos.shape[0]
+    assert qk.stride(2) == 1 and qk.stride(1) == Dh
+    if not qk.is_cuda:
+        pos = torch.arange(T) % S
+        c = cos[pos].unsqueeze(1)
+        s = sin[pos].unsqueeze(1) * (-1.0 if backward else 1.0)
+        a, b = qk[..., : Dh // 2].float(), qk[..., Dh // 2:].float()
+        lo, hi = a * c - b * s, b * c + a * s
+        qk[..., : Dh // 2] = lo.to(qk.dtype)
+        qk[..., Dh // 2:] = hi.to(qk.dtype)
+        return qk
+    rc = _lib.load().mm_rope(qk.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, S, H, Dh, qk.stride(0),
+                             int(backward), _stream())
+    _lib.check(rc, "mm_rope")
+    _count()
+    return qk
+
+
+# ------------------------------------------------------------------- SwiGLU
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    T, F2 = gu.shape
+    F = F2 // 2
+    if not gu.is_cuda:
+        g, u = gu[:, :F].float(), gu[:, F:].float()
+        return (torch.nn.functional.silu(g) * u).to(gu.dtype)
+    h = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
+    rc = _lib.load().mm_swiglu_fwd(gu.data_ptr(), h.data_ptr(), T, F, _stream())
+    _lib.check(rc, "mm_swiglu_fwd")
+    _count()
+    return h
+
+
+def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
+    T, F2 = gu.shape
+    F = F2 // 2
+    if not gu.is_cuda:
+        g, u, d = gu[:, :F].float(), gu[:, F:].float(), dh.float()
+        sg = torch.sigmoid(g)
+        dg = d * u * sg * (1 + g * (1 - sg))
+        du = d * g * sg
+        return torch.cat([dg, du], dim=1).to(gu.dtype)
+    dgu = torch.empty_like(gu)
+    rc = _lib.load().mm_swiglu_bwd(gu.data_ptr(), dh.contiguous().data_ptr(), dgu.data_ptr(), T, F, _stream())
+    _lib.check(rc, "mm_swiglu_bwd")
+    _count()
+    return dgu
+
+
+# ------------------------------------------------------------ cross-entropy
+def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, grad_scale: float,
+                          write_grad: bool = True) -> torch.Tensor:
+    """Per-row loss (fp32). When ``write_grad`` the logits buffer is overwritten
+    with d(loss_sum * grad_scale)/dlogits. Rows whose target is negative are skipped."""
+    rows, V = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        lse = torch.logsumexp(lf, dim=-1)
+        valid = targets >= 0
+        tsafe = targets.clamp(min=0)
+        loss = torch.where(valid, lse - lf.gather(1, tsafe[:, None]).squeeze(1), torch.zeros_like(lse))
+        if write_grad:
+            g = torch.softmax(lf, dim=-1)
+            g.scatter_add_(1, tsafe[:, None], -torch.ones(rows, 1))
+            g = g * grad_scale * valid[:, None]
+            logits.copy_(g.to(logits.dtype))
+        return loss
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    rc = _lib.load().mm_cross_entropy(logits.data_ptr(), targets.data_ptr(), loss.data_ptr(), None, None,
+                                      rows, V, logits.stride(0), 0, grad_scale, int(write_grad), _stream())
+    _lib.check(rc, "mm_cross_entropy")
+    _count()
+    return loss
+
+
+# ---------------------------------------------------------------- embedding
+def embedding_fwd(table: torch.Tensor, ids: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    V, D = table.shape
+    flat = ids.reshape(-1)
+    if not table.is_cuda:
+        local = flat - vocab_start
+        ok = (local >= 0) & (local < V)
+        out = table[local.clamp(0, V - 1)] * ok[:, None].to(table.dtype)
+        return out
+    out = torch.empty((flat.numel(), D), dtype=table.dtype, device=table.device)
+    rc = _lib.load().mm_embedding_fwd(table.data_ptr(), flat.data_ptr(), out.data_ptr(), flat.numel(), D,
+                                      vocab_start, V, _stream())
+    _lib.check(rc, "mm_embedding_fwd")
+    _count()
+    return out
+
+
+def embedding_bwd(dout: torch.Tensor, ids: torch.Tensor, grad: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    """grad[V, D] (fp32) += scatter-add of dout rows."""
+    V, D = grad.shape
+    flat = ids.reshape(-1)
+    if not dout.is_cuda:
+        local = flat - vocab_start
+        ok = (local >= 0) & (local < V)
+        grad.index_add_(0, local[ok], dout.reshape(-1, D)[ok].to(grad.dtype))
+        return grad
+    rc = _lib.load().mm_embedding_bwd(dout.contiguous().data_ptr(), flat.data_ptr(), grad.data_ptr(),
+                                      flat.numel(), D, vocab_start, V, _stream())
+    _lib.check(rc, "mm_embedding_bwd")
+    _count()
+    return grad
+
+
+# -------------------------------------------------------------- misc adds
+def add_(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a += b for contiguous bf16 tensors."""
+    if not a.is_cuda or a.numel() % 8 or a.dtype != bf16 or not (a.is_contiguous() and b.is_contiguous()):
+        return a.add_(b)
+    rc = _lib.load().mm_add_bf16(a.data_ptr(), b.data_ptr(), a.data_ptr(), a.numel(), _stream())
+    _lib.check(rc, "mm_add_bf16")
+    _count()
+    return a
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    if not a.is_cuda or a.numel() % 8 or a.dtype != bf16 or not (a.is_contiguous() and b.is_contiguous()):
+        return a + b
+    out = torch.empty_like(a)
+    rc = _lib.load().mm_add_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream())
+    _lib.check(rc, "mm_add_bf16")
+    _count()
+    return out
+
+
+def accumulate_(acc: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """acc(fp32) += src(bf16)."""
+    if not acc.is_cuda or acc.numel() % 8 or src.dtype != bf16 or acc.dtype != torch.float32:
+        return acc.add_(src.to(acc.dtype))
+    rc = _lib.load().mm_accumulate_f32_bf16(acc.data_ptr(), src.contiguous().data_ptr(), acc.numel(), _stream())
+    _lib.check(rc, "mm_accumulate_f32_bf16")
+    _count()
+    return acc
+
+
+# --------------------------------------------------------------------- AdamW
+def adamw_step_(master: torch.Tensor, param: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+                grad: torch.Tensor, *, lr: float, beta1: float, beta2: float, eps: float,
+                weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
+    """Fused AdamW on flat buffers (fp32 master/m/v/grad, bf16 working copy)."""
+    n = master.numel()
+    if not master.is_cuda:
+        g = grad * grad_scale
+        m.mul_(beta1).add_(g, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        mh = m / (1 - beta1 ** step)
+        vh = v / (1 - beta2 ** step)
+        master.mul_(1 - lr * weight_decay).addcdiv_(mh, vh.sqrt() + eps, value=-lr)
+        param.copy_(master.to(param.dtype))
+        return
+    assert n % 4 == 0
+    rc = _lib.load().mm_adamw(master.data_ptr(), param.data_ptr(), m.data_ptr(), v.data_ptr(),
+                              grad.data_ptr(), n, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
+                              _stream())
+    _lib.check(rc, "mm_adamw")
+    _count()
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[0] += sum(x*x) for an fp32 buffer (gradient-norm clipping)."""
+    if not x.is_cuda:
+        out[0] += (x.double() ** 2).sum().float()
+        return out
+    rc = _lib.load().mm_sumsq_f32(x.data_ptr(), x.numel(), out.data_ptr(), _stream())
+    _lib.check(rc, "mm_sumsq_f32")
+    _count()
+    return out
+
+
+# ---------------------------------------------------------------- attention
+def attention_ref(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """fp32 reference: q [B,S,Hq,D], k/v [B,S,Hkv,D] -> [B,S,Hq,D]."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    rep = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(D)
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    o = torch.softmax(s, dim=-1) @ vf
+    return o.permute(0, 2, 1, 3).contiguous()

@@ -1,0 +1,184 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from multimesh_jax_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(out, ref, rtol=2e-2, atol=None):
+    ref = ref.float()
+    if atol is None:
+        atol = 2e-2 * max(ref.abs().max().item(), 1e-6)
+    torch.testing.assert_close(out.float(), ref, rtol=rtol, atol=atol)
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 320), (200, 264, 72), (1024, 1024, 1024),
+               (4096, 5504, 4096), (100, 8, 8)]
+
+
+@pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_layouts(M, N, K_, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = _rand(K_, M) if a_mn else _rand(M, K_)
+    b = _rand(K_, N) if b_mn else _rand(N, K_)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert K.read_status() == 0
+    _close(out, ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_accumulate(dtype):
+    torch.manual_seed(1)
+    M, N, K_ = 512, 768, 256
+    a, b = _rand(M, K_), _rand(N, K_)
+    c0 = torch.randn(M, N, device=DEV).to(dtype)
+    c = c0.clone()
+    K.gemm(a, b, out=c, accumulate=True)
+    ref = c0.float() + a.float() @ b.float().t()
+    assert K.read_status() == 0
+    _close(c, ref)
+    c2 = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    K.gemm(a, b, out=c2)
+    _close(c2, a.float() @ b.float().t(), rtol=1e-3)
+
+
+def test_gemm_strided_operands():
+    torch.manual_seed(2)
+    big = _rand(512, 3 * 256)
+    x = big[:, 256:512]          # row stride 768, unit inner stride
+    w = _rand(384, 256)
+    out = K.linear_fwd(x, w)
+    _close(out, x.float() @ w.float().t())
+    outbuf = torch.zeros(512, 1024, device=DEV, dtype=torch.bfloat16)
+    K.linear_fwd(x, w, out=outbuf[:, 128:512])
+    _close(outbuf[:, 128:512], x.float() @ w.float().t())
+    assert outbuf[:, :128].abs().max().item() == 0 and outbuf[:, 512:].abs().max().item() == 0
+
+
+def test_linear_grads():
+    torch.manual_seed(3)
+    T, Kd, N = 1024, 512, 768
+    x, w, dy = _rand(T, Kd), _rand(N, Kd, scale=0.05), _rand(T, N)
+    _close(K.linear_dgrad(dy, w), dy.float() @ w.float())
+    dw = torch.zeros(N, Kd, device=DEV, dtype=torch.float32)
+    K.linear_wgrad(dy, x, out=dw, accumulate=True)
+    K.linear_wgrad(dy, x, out=dw, accumulate=True)
+    _close(dw, 2 * dy.float().t() @ x.float(), rtol=1e-3)
+    assert K.read_status() == 0
+
+
+@pytest.mark.parametrize("D", [512, 4096, 8192])
+def test_rmsnorm(D):
+    torch.manual_seed(4)
+    rows = 333
+    x, w, dy = _rand(rows, D), _rand(D, scale=0.5) + 1, _rand(rows, D)
+    y, rstd = K.rmsnorm_fwd(x, w, 1e-5)
+    xf = x.float().requires_grad_(True)
+    wf = w.float().requires_grad_(True)
+    ref = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    _close(y, ref.detach())
+    ref.backward(dy.float())
+    dx, dw = K.rmsnorm_bwd(x, w, dy, rstd)
+    _close(dx, xf.grad)
+    _close(dw, wf.grad, rtol=1e-2)
+    base = _rand(rows, D)
+    acc = base.clone()
+    K.rmsnorm_bwd(x, w, dy, rstd, dx_inout=acc)
+    _close(acc, base.float() + xf.grad)
+
+
+def test_rope_roundtrip_and_reference():
+    torch.manual_seed(5)
+    B, S, H, Dh = 2, 128, 4, 128
+    cos, sin = K.rope_tables(S, Dh, 1e4, DEV)
+    qkv = _rand(B * S, 3 * H * Dh)
+    q = qkv[:, : H * Dh].view(B * S, H, Dh)
+    q0 = q.clone()
+    ref = K.rope_(q0.cpu().clone(), cos.cpu(), sin.cpu())
+    K.rope_(q, cos, sin)
+    _close(q, ref.to(DEV))
+    K.rope_(q, cos, sin, backward=True)
+    _close(q, q0, rtol=3e-2)
+
+
+def test_swiglu():
+    torch.manual_seed(6)
+    T, F = 257, 1376
+    gu, dh = _rand(T, 2 * F), _rand(T, F)
+    guf = gu.float().requires_grad_(True)
+    ref = torch.nn.functional.silu(guf[:, :F]) * guf[:, F:]
+    _close(K.swiglu_fwd(gu), ref.detach())
+    ref.backward(dh.float())
+    _close(K.swiglu_bwd(gu, dh), guf.grad)
+
+
+@pytest.mark.parametrize("V", [32000, 1000, 1003])
+def test_cross_entropy(V):
+    torch.manual_seed(7)
+    rows = 64
+    ld = (V + 7) // 8 * 8
+    buf = _rand(rows, ld, scale=2.0)
+    logits = buf[:, :V]
+    tgt = torch.randint(0, V, (rows,), device=DEV)
+    tgt[3] = -100
+    lf = logits.float().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(lf, tgt, ignore_index=-100, reduction="none")
+    (ref.sum() * 0.5).backward()
+    loss = K.cross_entropy_fwd_bwd(logits, tgt, 0.5)
+    _close(loss, ref.detach(), rtol=1e-3, atol=1e-3)
+    _close(logits, lf.grad, atol=2e-3)
+
+
+def test_embedding():
+    torch.manual_seed(8)
+    V, D, T = 1000, 256, 777
+    table = _rand(V, D)
+    ids = torch.randint(0, V, (T,), device=DEV)
+    out = K.embedding_fwd(table, ids)
+    assert torch.equal(out, table[ids])
+    dout = _rand(T, D)
+    grad = torch.zeros(V, D, device=DEV)
+    K.embedding_bwd(dout, ids, grad)
+    ref = torch.zeros(V, D, device=DEV).index_add_(0, ids, dout.float())
+    _close(grad, ref, rtol=1e-3)
+
+
+def test_adamw_matches_torch():
+    torch.manual_seed(9)
+    n = 4096 * 3
+    p = torch.randn(n, device=DEV)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    master, m, v = p.clone(), torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    work = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    for step in range(1, 4):
+        g = torch.randn(n, device=DEV)
+        ref_p.grad = g.clone()
+        opt.step()
+        K.adamw_step_(master, work, m, v, g, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,
+                      weight_decay=0.1, step=step)
+    torch.testing.assert_close(master, ref_p.data, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(work.float(), master, rtol=1e-2, atol=1e-2)
+
+
+def test_add_and_accumulate():
+    a, b = _rand(1000, 64), _rand(1000, 64)
+    _close(K.add(a, b), a.float() + b.float())
+    acc = torch.randn(1000, 64, device=DEV)
+    ref = acc + b.float()
+    K.accumulate_(acc, b)
+    torch.testing.assert_close(acc, ref)
+    s = torch.zeros(1, device=DEV)
+    K.sumsq(acc, s)
+    torch.testing.assert_close(s[0], (acc.double() ** 2).sum().float(), rtol=1e-4, atol=1e-3)
