@@ -1,0 +1,137 @@
+"""Compile entry points: ``compile_function`` (ahead of time) and ``JitFunction``.
+
+Compilation = capture with torch.fx -> native graph -> native MPMD pipeline ->
+plan -> per-task programs -> :class:`Executable`. Small single-task programs
+take the *fast path* and run the captured graph directly, bypassing the MPMD
+runtime, as the reference does for programs under 20 instructions
+(``src/pjrt_client/mm_pjrt_client.cc:51, 587-617``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable, Dict, Optional, Sequence
+
+import torch
+from torch.utils import _pytree as pytree
+
+from .. import state
+from ..runtime.collectives import Topology
+from ..runtime.executable import Executable, ShardedTensor
+from ..task import MultiMesh
+from .capture import Captured, capture, make_partition
+
+FAST_PATH_MAX_NODES = 20
+
+
+def _partition_config(**overrides):
+    from .. import _mm_C
+    cfg = _mm_C.PartitionConfig.from_env()
+    cfg.replicated_parameter_num_elements_cutoff = state.knobs["replicated_parameter_num_elements_cutoff"]
+    cfg.recompute_from_arguments_if_cost_less_than = state.knobs["recompute_from_arguments_if_cost_less_than"]
+    cfg.enable_recomputation = bool(state.flags.recomputation)
+    if state.startup.dump:
+        os.makedirs(state.startup.dump, exist_ok=True)
+        cfg.dump_dir = state.startup.dump
+        cfg.dump_all_passes = bool(state.startup.dump_all_passes)
+    for k, v in overrides.items():
+        setattr(cfg, k, v)
+    return cfg
+
+
+def _apply_shardings(cap: Captured, in_shardings, example_args) -> None:
+    """Attaches user-given axis names to graph inputs (mesh-axis names unless autoshard)."""
+    if in_shardings is None:
+        return
+    flat_args, _ = pytree.tree_flatten(tuple(example_args))
+    specs = pytree.tree_leaves(in_shardings, is_leaf=lambda x: x is None or (
+        isinstance(x, (tuple, list)) and all(e is None or isinstance(e, (str, tuple, list)) for e in x)))
+    tensor_pos = [i for i, a in enumerate(flat_args) if isinstance(a, torch.Tensor)]
+    if len(specs) != len(tensor_pos):
+        return
+    from ..lib import _canonical_axes
+    for k, spec in enumerate(specs):
+        if spec is None:
+            continue
+        vid = cap.graph.inputs[k]
+        ndim = len(cap.graph.value(vid)["shape"])
+        cap.graph.set_value_axes(vid, _canonical_axes(spec, ndim), bool(state.flags.autoshard))
+
+
+def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optional[MultiMesh] = None,
+                     num_devices: Optional[int] = None, donate_argnums: Sequence[int] = (),
+                     backend: Optional[str] = None, in_shardings=None, context=None, topology: Optional[Topology] = None,
+                     name: Optional[str] = None, config_overrides: Optional[Dict[str, Any]] = None) -> Executable:
+    from .. import _mm_C
+    mesh = mesh or MultiMesh.current()
+    if num_devices is None:
+        if mesh is not None:
+            num_devices = mesh.size
+        else:
+            num_devices = max(1, state.startup.gpus or state.startup.cpus or 1)
+    if topology is None:
+        topology = Topology.auto(num_devices, backend)
+    device = topology.torch_device(topology.local_devices[0])
+    cap = capture(fn, example_args, device=device, mesh=mesh)
+    _apply_shardings(cap, in_shardings, example_args)
+    if donate_argnums:
+        flat_idx = pytree.tree_unflatten(list(range(len(cap.input_is_tensor))), cap.in_spec)
+        donated = []
+        tensor_rank = {}
+        k = 0
+        for i, ok in enumerate(cap.input_is_tensor):
+            if ok:
+                tensor_rank[i] = k
+                k += 1
+        for a in donate_argnums:
+            for pos in pytree.tree_leaves(flat_idx[a]):
+                if pos in tensor_rank:
+                    donated.append(tensor_rank[pos])
+        cap.graph.set_donated_inputs(donated)
+    nmb = cap.loop_configs[0]["num_microbatches"] if cap.loop_configs else 0
+    part = make_partition(num_devices, mesh, nmb)
+    cfg = _partition_config(**(config_overrides or {}))
+    plan = _mm_C.mpmd_partition(cap.graph, part, cfg)
+    exe = Executable(cap, plan, topology, context=context, name=name or getattr(fn, "__name__", "step"))
+    exe.partition = part
+    return exe
+
+
+class JitFunction:
+    """Lazily compiled step (``mjit``): compiled on first call per input signature."""
+
+    def __init__(self, fn, *, mesh=None, in_shardings=None, out_shardings=None, donate_argnums=(),
+                 static_argnums=(), backend=None):
+        self.fn = fn
+        self.mesh = mesh
+        self.in_shardings = in_shardings
+        self.out_shardings = out_shardings
+        self.donate_argnums = donate_argnums
+        self.static_argnums = static_argnums
+        self.backend = backend
+        self._cache: Dict[Any, Executable] = {}
+        self.__name__ = getattr(fn, "__name__", "mjit")
+
+    def _signature(self, args):
+        leaves, spec = pytree.tree_flatten(args)
+        sig = []
+        for l in leaves:
+            if isinstance(l, (torch.Tensor, ShardedTensor)):
+                sig.append((tuple(l.shape), str(l.dtype)))
+            else:
+                sig.append(("const", repr(l)))
+        return (str(spec), tuple(sig))
+
+    def lower(self, *args) -> Executable:
+        key = self._signature(args)
+        if key not in self._cache:
+            example = pytree.tree_map(
+                lambda l: torch.empty(l.shape, dtype=l.dtype, device="meta") if isinstance(l, ShardedTensor) else l, args,
+                is_leaf=lambda x: isinstance(x, ShardedTensor))
+            self._cache[key] = compile_function(self.fn, example, mesh=self.mesh, donate_argnums=self.donate_argnums,
+                                                backend=self.backend, in_shardings=self.in_shardings, name=self.__name__)
+        return self._cache[key]
+
+    def __call__(self, *args):
+        if state.flags.ignore_transforms:
+            return self.fn(*args)
+        return self.lower(*args)(*args)

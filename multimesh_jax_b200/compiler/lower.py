@@ -1,0 +1,284 @@
+"""Lowering of task templates to executable programs.
+
+Each task template of the plan (a list of IR node ids) becomes a
+:class:`TemplateProgram`: a flat instruction list interpreted per launch. Nodes
+that came from the fx capture call their original operator (custom ``mm_ops``
+operators dispatch to the hand-written CUDA kernels on CUDA tensors); nodes
+created by the compiler (``mm.copy``, ``mm.dynamic_slice``, ``mm.all_reduce``,
+``mm.spmd_reshard``, ``mm.accumulate``) are implemented here. One program is
+built per unique task and shared by all of its microbatch instances - the
+analogue of the reference compiling each unique task body once
+(``src/pjrt_client/executable_cache.cc:14-28``).
+"""
+from __future__ import annotations
+
+import json
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.fx as fx
+
+from .capture import Captured, DTYPE_FROM_NAME
+
+_SIZE_ARG_OPS = {
+    "aten.view.default", "aten.reshape.default", "aten._unsafe_view.default", "aten.expand.default",
+    "aten.new_zeros.default", "aten.new_empty.default", "aten.new_ones.default", "aten.new_full.default",
+    "aten.zeros.default", "aten.ones.default", "aten.empty.memory_format", "aten.full.default",
+    "aten.broadcast_to.default",
+}
+
+
+class _V:
+    """Placeholder for an IR value inside an argument structure."""
+    __slots__ = ("vid",)
+
+    def __init__(self, vid: int):
+        self.vid = vid
+
+
+class _Dev:
+    """Placeholder for 'the device this task runs on'."""
+
+
+def _materialize(spec, env, ctx):
+    if isinstance(spec, _V):
+        return env[spec.vid]
+    if isinstance(spec, _Dev):
+        return ctx.torch_device
+    if isinstance(spec, tuple):
+        return tuple(_materialize(s, env, ctx) for s in spec)
+    if isinstance(spec, list):
+        return [_materialize(s, env, ctx) for s in spec]
+    if isinstance(spec, dict):
+        return {k: _materialize(v, env, ctx) for k, v in spec.items()}
+    return spec
+
+
+def _has_placeholder(spec) -> bool:
+    if isinstance(spec, (_V, _Dev)):
+        return True
+    if isinstance(spec, (tuple, list)):
+        return any(_has_placeholder(s) for s in spec)
+    if isinstance(spec, dict):
+        return any(_has_placeholder(v) for v in spec.values())
+    return False
+
+
+class Instr:
+    __slots__ = ("kind", "fn", "args", "kwargs", "outs", "slots", "node_id", "extra", "static")
+
+    def __init__(self, kind, fn, args, kwargs, outs, slots, node_id, extra=None):
+        self.kind = kind
+        self.fn = fn
+        self.args = args
+        self.kwargs = kwargs
+        self.outs = outs
+        self.slots = slots
+        self.node_id = node_id
+        self.extra = extra
+        self.static = not (_has_placeholder(args) or _has_placeholder(kwargs))
+
+
+class TemplateProgram:
+    def __init__(self, template: dict, instrs: List[Instr], inputs: List[int], outputs: List[int],
+                 last_use: Dict[int, int]):
+        self.template = template
+        self.instrs = instrs
+        self.inputs = inputs
+        self.outputs = outputs
+        self.name = template["name"]
+        self.mesh_dims = template["mesh_dims"]
+        self.device_start = template["device_start"]
+        self._last_use = last_use
+
+    def run(self, ctx, scalars: Sequence[int], inputs: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        env: Dict[int, Any] = dict(zip(self.inputs, inputs))
+        for idx, ins in enumerate(self.instrs):
+            kind = ins.kind
+            if kind == 0:  # captured operator
+                args = ins.args if ins.static else _materialize(ins.args, env, ctx)
+                kwargs = ins.kwargs if ins.static else _materialize(ins.kwargs, env, ctx)
+                res = ins.fn(*args, **kwargs)
+                if ins.slots is None:
+                    env[ins.outs[0]] = res
+                else:
+                    for pos, slot in enumerate(ins.slots):
+                        if slot is not None:
+                            env[ins.outs[slot]] = res[pos]
+            elif kind == 1:  # identity-like
+                env[ins.outs[0]] = env[ins.args]
+            elif kind == 2:  # copy
+                env[ins.outs[0]] = env[ins.args].clone()
+            elif kind == 3:  # dynamic slice at a host-provided offset
+                dim, size, shards = ins.extra
+                x = env[ins.args]
+                env[ins.outs[0]] = x.narrow(dim, scalars[0] // shards, size // shards)
+            elif kind == 4:  # all-reduce over mesh axes
+                axes, scale = ins.extra
+                y = ctx.all_reduce(env[ins.args], axes, ins.node_id)
+                env[ins.outs[0]] = y if scale == 1.0 else y * scale
+            elif kind == 5:  # local reshard
+                src, dst = ins.extra
+                env[ins.outs[0]] = ctx.spmd_reshard(env[ins.args], src, dst, ins.node_id)
+            # free values whose last use was this instruction (keeps peak memory low)
+            dead = self._last_use.get(idx)
+            if dead:
+                for v in dead:
+                    env.pop(v, None)
+        return [env[v] for v in self.outputs]
+
+
+def _local_shape(value: dict) -> List[int]:
+    sh = value.get("sharding")
+    return list(sh["shard_size"]) if sh else list(value["shape"])
+
+
+def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[Dict[str, Callable]] = None
+                  ) -> TemplateProgram:
+    g = cap.graph
+    instrs: List[Instr] = []
+    single_device = template["num_devices"] == 1
+    fx_by_name = getattr(cap, "_fx_by_name", None)
+    if fx_by_name is None:
+        fx_by_name = {n.name: n for n in cap.gm.graph.nodes}
+        cap._fx_by_name = fx_by_name
+    for nid in template["nodes"]:
+        n = g.node(nid)
+        op = n["op"]
+        # nodes cloned by the compiler (recompute / replication) carry the name of their fx origin
+        fxn = cap.fx_of_node.get(nid) or fx_by_name.get(n["attrs"].get("fx", ""))
+        if fxn is not None and not op.startswith("mm."):
+            # argument structure: fx nodes -> current IR inputs (passes may have rewired them)
+            tensor_inputs = iter(n["inputs"])
+            orig_inputs: Dict[fx.Node, int] = {}
+
+            def conv(a):
+                if isinstance(a, fx.Node):
+                    key = a
+                    if key not in orig_inputs:
+                        vid = _ir_value_of(cap, a)
+                        if vid is None:
+                            raise NotImplementedError(f"non-tensor fx value {a} used by {fxn}")
+                        orig_inputs[key] = vid
+                    return _V(orig_inputs[key])
+                if isinstance(a, torch.device):
+                    return _Dev()
+                if isinstance(a, (list, tuple)):
+                    return type(a)(conv(e) for e in a) if isinstance(a, tuple) else [conv(e) for e in a]
+                if isinstance(a, dict):
+                    return {k: conv(v) for k, v in a.items()}
+                return a
+
+            args = tuple(conv(a) for a in fxn.args)
+            kwargs = {k: conv(v) for k, v in fxn.kwargs.items()}
+            # inputs may have been rewired by passes (e.g. reductions inserted): map old -> new positionally
+            old_ids = _tensor_ids_in_order(args, kwargs)
+            if len(old_ids) == len(n["inputs"]):
+                remap = {o: nw for o, nw in zip(old_ids, n["inputs"]) if o != nw}
+                if remap:
+                    args = _remap(args, remap)
+                    kwargs = _remap(kwargs, remap)
+            # global -> local shapes in size arguments of sharded results
+            if not single_device and op in _SIZE_ARG_OPS and n["outputs"]:
+                outv = g.value(n["outputs"][0])
+                gshape, lshape = list(outv["shape"]), _local_shape(outv)
+                if gshape != lshape:
+                    args = tuple(_fix_sizes(a, gshape, lshape) for a in args)
+            fn = fxn.target
+            if fast_ops and op in fast_ops:
+                fn = fast_ops[op]
+            val = fxn.meta.get("val")
+            single = isinstance(val, torch.Tensor)
+            slots = None
+            if not single:
+                slots, k = [], 0
+                for e in val:
+                    if isinstance(e, torch.Tensor):
+                        slots.append(k)
+                        k += 1
+                    else:
+                        slots.append(None)
+            instrs.append(Instr(0, fn, args, kwargs, n["outputs"], None if single else slots, nid))
+            continue
+        attrs = n["attrs"]
+        if op in ("mm.accumulate",) or op.startswith("mm.marker"):
+            instrs.append(Instr(1, None, n["inputs"][0], None, n["outputs"], None, nid))
+        elif op == "mm.copy":
+            instrs.append(Instr(2, None, n["inputs"][0], None, n["outputs"], None, nid))
+        elif op == "mm.dynamic_slice":
+            dim, size = int(attrs["dim"]), int(attrs["size"])
+            shards = 1
+            sh = g.value(n["outputs"][0]).get("sharding")
+            if sh and not single_device:
+                for a in sh["dim_axes"][dim]:
+                    shards *= sh["mesh_dims"][a]
+            instrs.append(Instr(3, None, n["inputs"][0], None, n["outputs"], None, nid, (dim, size, shards)))
+        elif op == "mm.all_reduce":
+            axes = json.loads(attrs["axes"])
+            instrs.append(Instr(4, None, n["inputs"][0], None, n["outputs"], None, nid, (axes, float(attrs["scale"]))))
+        elif op == "mm.spmd_reshard":
+            from .. import _mm_C
+            src = _mm_C.sharded_shape_from_json(attrs["from"])
+            dst = _mm_C.sharded_shape_from_json(attrs["to"])
+            instrs.append(Instr(5, None, n["inputs"][0], None, n["outputs"], None, nid, (src, dst)))
+        else:
+            raise NotImplementedError(f"no lowering for compiler-generated op {op}")
+    # liveness inside the program
+    last: Dict[int, int] = {}
+    keep = set(template["outputs"])
+    for idx, ins in enumerate(instrs):
+        for v in _reads(ins):
+            last[v] = idx
+    last_use: Dict[int, List[int]] = {}
+    for v, idx in last.items():
+        if v not in keep:
+            last_use.setdefault(idx, []).append(v)
+    return TemplateProgram(template, instrs, list(template["inputs"]), list(template["outputs"]), last_use)
+
+
+def _ir_value_of(cap: Captured, node: fx.Node) -> Optional[int]:
+    return cap.value_of_fx.get((node, None))
+
+
+def _tensor_ids_in_order(args, kwargs) -> List[int]:
+    out: List[int] = []
+
+    def walk(s):
+        if isinstance(s, _V):
+            out.append(s.vid)
+        elif isinstance(s, (tuple, list)):
+            for e in s:
+                walk(e)
+        elif isinstance(s, dict):
+            for e in s.values():
+                walk(e)
+
+    walk(args)
+    walk(kwargs)
+    return out
+
+
+def _remap(spec, remap):
+    if isinstance(spec, _V):
+        return _V(remap.get(spec.vid, spec.vid))
+    if isinstance(spec, tuple):
+        return tuple(_remap(s, remap) for s in spec)
+    if isinstance(spec, list):
+        return [_remap(s, remap) for s in spec]
+    if isinstance(spec, dict):
+        return {k: _remap(v, remap) for k, v in spec.items()}
+    return spec
+
+
+def _fix_sizes(arg, gshape, lshape):
+    if isinstance(arg, (list, tuple)) and len(arg) == len(gshape) and all(isinstance(e, int) for e in arg):
+        if all(a == b or a == -1 for a, b in zip(arg, gshape)):
+            fixed = [l if a != -1 else -1 for a, l in zip(arg, lshape)]
+            return type(arg)(fixed) if isinstance(arg, tuple) else fixed
+    return arg
+
+
+def _reads(ins: Instr) -> List[int]:
+    if ins.kind == 0:
+        return _tensor_ids_in_order(ins.args, ins.kwargs)
+    return [ins.args]

@@ -107,7 +107,9 @@ def build_host(force: bool = False) -> Path:
     if not force and not _newer(srcs + hdrs, target):
         return target
     cuda = _cuda_home()
-    cxx = os.environ.get("CXX", "g++")
+    # $CXX is ignored on purpose: a toolchain that links libstdc++ statically would give this
+    # module a second copy of the C++ runtime next to the one PyTorch loads.
+    cxx = os.environ.get("MM_CXX") or ("/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
     inc = ["-I", str(HERE), "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
            "-I", str(cuda / "include")]
     flags = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wno-sign-compare",

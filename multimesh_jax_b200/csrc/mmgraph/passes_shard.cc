@@ -1,0 +1,755 @@
+// Per-task sharding: logical -> physical mapping, propagation through an
+// index-class ("einsum-like") rule table, SPMD lowering (insert local
+// reshards and reductions of partial results) and hoisting of gradient
+// reductions out of the microbatch loop.
+//
+// The reference delegates propagation and partitioning to XLA
+// (src/pjrt_client/mpmd_sharding_propagation.cc:198-206,
+//  src/pjrt_client/mpmd_shard_map_loop_reduce.cc:137-147); here the rule table is ours.
+#include <algorithm>
+#include <map>
+#include <set>
+#include <stdexcept>
+
+#include "passes.h"
+
+namespace mmg {
+
+namespace {
+
+std::string BaseOp(const std::string& op) {
+  size_t first = op.find('.');
+  if (first == std::string::npos) return op;
+  size_t second = op.find('.', first + 1);
+  return second == std::string::npos ? op : op.substr(0, second);
+}
+
+// One tensor index shared by several operand / result dimensions.
+struct IndexClass {
+  std::vector<std::pair<int, int>> members;  // (slot, dim); slot < #inputs: input, else output
+  bool no_shard = false;                     // must stay unsharded (softmax dim, conv window ...)
+  std::set<int> reduced_outputs;             // outputs (by index) in which this index is summed away
+};
+
+struct Rule {
+  std::vector<IndexClass> classes;
+  bool known = true;
+  double partial_scale = 1.0;  // e.g. mean: multiply after the reduction
+};
+
+Json ArgsOf(const Node& n) {
+  try { return Json::parse(n.Attr("args", "[]")); } catch (...) { return Json::array(); }
+}
+int NormDim(int64_t d, size_t rank) { return static_cast<int>(d < 0 ? d + static_cast<int64_t>(rank) : d); }
+
+void AddIdentity(Rule& r, const Graph& g, const Node& n, int in_slot, int out_idx) {
+  const auto& a = g.value(n.inputs[in_slot]).shape;
+  const auto& o = g.value(n.outputs[out_idx]).shape;
+  const int nin = static_cast<int>(n.inputs.size());
+  // right-aligned broadcasting
+  for (size_t k = 0; k < o.size(); ++k) {
+    const int od = static_cast<int>(o.size() - 1 - k);
+    if (k >= a.size()) continue;
+    const int ad = static_cast<int>(a.size() - 1 - k);
+    if (a[ad] != o[od] || a[ad] == 1) continue;
+    // find the class that already holds (out, od)
+    IndexClass* found = nullptr;
+    for (auto& c : r.classes)
+      for (auto& m : c.members) if (m.first == nin + out_idx && m.second == od) found = &c;
+    if (!found) { r.classes.emplace_back(); found = &r.classes.back(); found->members.emplace_back(nin + out_idx, od); }
+    found->members.emplace_back(in_slot, ad);
+  }
+}
+
+Rule ElementwiseRule(const Graph& g, const Node& n) {
+  Rule r;
+  for (size_t o = 0; o < n.outputs.size(); ++o)
+    for (size_t i = 0; i < n.inputs.size(); ++i) AddIdentity(r, g, n, static_cast<int>(i), static_cast<int>(o));
+  // several same-shaped outputs share classes through their common inputs only; merge by dim
+  return r;
+}
+
+IndexClass Cls(std::initializer_list<std::pair<int, int>> m) { IndexClass c; c.members.assign(m.begin(), m.end()); return c; }
+
+Rule GetRule(const Graph& g, const Node& n) {
+  Rule r;
+  const std::string b = BaseOp(n.op);
+  const int nin = static_cast<int>(n.inputs.size());
+  auto in_rank = [&](int i) { return static_cast<int>(g.value(n.inputs[i]).shape.size()); };
+  auto out_rank = [&](int i) { return static_cast<int>(g.value(n.outputs[i]).shape.size()); };
+  const Json args = ArgsOf(n);
+
+  if (IsElementwise(n) || b == "aten.detach" || b == "aten.alias" || b == "aten.contiguous" ||
+      b == "aten.lift_fresh" || n.op == "mm.all_reduce") {
+    return ElementwiseRule(g, n);
+  }
+  if (b == "aten.mm" && nin == 2) {
+    r.classes = {Cls({{0, 0}, {2, 0}}), Cls({{1, 1}, {2, 1}})};
+    IndexClass k = Cls({{0, 1}, {1, 0}});
+    k.reduced_outputs = {0};
+    r.classes.push_back(k);
+    return r;
+  }
+  if (b == "aten.addmm" && nin == 3) {
+    r.classes = {Cls({{1, 0}, {3, 0}}), Cls({{2, 1}, {3, 1}})};
+    IndexClass k = Cls({{1, 1}, {2, 0}});
+    k.reduced_outputs = {0};
+    r.classes.push_back(k);
+    const auto& bias = g.value(n.inputs[0]).shape;
+    if (bias.size() == 1 && bias[0] != 1) r.classes[1].members.emplace_back(0, 0);
+    return r;
+  }
+  if (b == "aten.bmm" && nin == 2) {
+    r.classes = {Cls({{0, 0}, {1, 0}, {2, 0}}), Cls({{0, 1}, {2, 1}}), Cls({{1, 2}, {2, 2}})};
+    IndexClass k = Cls({{0, 2}, {1, 1}});
+    k.reduced_outputs = {0};
+    r.classes.push_back(k);
+    return r;
+  }
+  if (b == "mm_ops.linear" && nin >= 2) {  // x[..., K], w[N, K] -> [..., N]
+    const int xr = in_rank(0);
+    for (int d = 0; d + 1 < xr; ++d) r.classes.push_back(Cls({{0, d}, {nin, d}}));
+    r.classes.push_back(Cls({{1, 0}, {nin, xr - 1}}));
+    IndexClass k = Cls({{0, xr - 1}, {1, 1}});
+    k.reduced_outputs = {0};
+    r.classes.push_back(k);
+    return r;
+  }
+  if (b == "mm_ops.linear_dgrad" && nin >= 2) {  // dy[..., N], w[N, K] -> [..., K]
+    const int xr = in_rank(0);
+    for (int d = 0; d + 1 < xr; ++d) r.classes.push_back(Cls({{0, d}, {nin, d}}));
+    r.classes.push_back(Cls({{1, 1}, {nin, xr - 1}}));
+    IndexClass k = Cls({{0, xr - 1}, {1, 0}});
+    k.reduced_outputs = {0};
+    r.classes.push_back(k);
+    return r;
+  }
+  if (b == "mm_ops.linear_wgrad" && nin >= 2) {  // dy[..., N], x[..., K] -> [N, K]
+    const int xr = in_rank(0);
+    for (int d = 0; d + 1 < xr; ++d) {
+      IndexClass k = Cls({{0, d}, {1, d}});
+      k.reduced_outputs = {0};
+      r.classes.push_back(k);
+    }
+    r.classes.push_back(Cls({{0, xr - 1}, {nin, 0}}));
+    r.classes.push_back(Cls({{1, xr - 1}, {nin, 1}}));
+    return r;
+  }
+  if (b == "aten.t" && in_rank(0) == 2) {
+    r.classes = {Cls({{0, 0}, {1, 1}}), Cls({{0, 1}, {1, 0}})};
+    return r;
+  }
+  if (b == "aten.transpose" && args.arr.size() >= 2) {
+    const int rank = in_rank(0);
+    const int d0 = NormDim(args.arr[0].as_int(), rank), d1 = NormDim(args.arr[1].as_int(), rank);
+    for (int d = 0; d < rank; ++d) r.classes.push_back(Cls({{0, d}, {1, d == d0 ? d1 : (d == d1 ? d0 : d)}}));
+    return r;
+  }
+  if (b == "aten.permute" && args.arr.size() >= 1 && args.arr[0].is_array()) {
+    const auto perm = args.arr[0].as_int_vector();
+    const int rank = in_rank(0);
+    for (size_t od = 0; od < perm.size(); ++od)
+      r.classes.push_back(Cls({{0, NormDim(perm[od], rank)}, {1, static_cast<int>(od)}}));
+    return r;
+  }
+  if (b == "aten.view" || b == "aten.reshape" || b == "aten._unsafe_view" || b == "aten.flatten" ||
+      b == "aten.unflatten") {
+    // match groups of dims with equal products; only the major dim of a group carries sharding
+    const auto& a = g.value(n.inputs[0]).shape;
+    const auto& o = g.value(n.outputs[0]).shape;
+    size_t i = 0, j = 0;
+    while (i < a.size() && j < o.size()) {
+      size_t i0 = i, j0 = j;
+      int64_t pa = a[i++], po = o[j++];
+      while (pa != po) {
+        if (pa < po) { if (i >= a.size()) break; pa *= a[i++]; }
+        else { if (j >= o.size()) break; po *= o[j++]; }
+      }
+      if (pa != po) { r.known = false; return r; }
+      // skip leading size-1 dims on either side
+      size_t ia = i0, jo = j0;
+      while (ia + 1 < i && a[ia] == 1) ++ia;
+      while (jo + 1 < j && o[jo] == 1) ++jo;
+      IndexClass c = Cls({{0, static_cast<int>(ia)}, {1, static_cast<int>(jo)}});
+      // If the group is not 1:1, the shard count must divide both major dims; checked when assigning.
+      r.classes.push_back(c);
+      for (size_t d = i0; d < i; ++d) if (d != ia) { IndexClass z = Cls({{0, static_cast<int>(d)}}); z.no_shard = true; r.classes.push_back(z); }
+      for (size_t d = j0; d < j; ++d) if (d != jo) { IndexClass z = Cls({{1, static_cast<int>(d)}}); z.no_shard = true; r.classes.push_back(z); }
+    }
+    return r;
+  }
+  if (b == "aten.unsqueeze" && args.arr.size() >= 1) {
+    const int rank = out_rank(0);
+    const int at = NormDim(args.arr[0].as_int(), rank);
+    for (int d = 0, s = 0; d < rank; ++d) { if (d == at) continue; r.classes.push_back(Cls({{0, s}, {1, d}})); ++s; }
+    return r;
+  }
+  if (b == "aten.squeeze") {
+    const auto& a = g.value(n.inputs[0]).shape;
+    const auto& o = g.value(n.outputs[0]).shape;
+    size_t j = 0;
+    for (size_t d = 0; d < a.size(); ++d) {
+      if (j < o.size() && a[d] == o[j]) { r.classes.push_back(Cls({{0, static_cast<int>(d)}, {1, static_cast<int>(j)}})); ++j; }
+    }
+    return r;
+  }
+  if (b == "aten.expand") { AddIdentity(r, g, n, 0, 0); return r; }
+  if ((b == "aten.sum" || b == "aten.mean") ) {
+    const int rank = in_rank(0);
+    std::set<int> red;
+    bool keepdim = false;
+    if (args.arr.size() >= 1 && args.arr[0].is_array()) {
+      for (auto d : args.arr[0].as_int_vector()) red.insert(NormDim(d, rank));
+      if (args.arr.size() >= 2 && args.arr[1].kind == Json::Bool) keepdim = args.arr[1].b;
+    } else {
+      for (int d = 0; d < rank; ++d) red.insert(d);
+    }
+    int od = 0;
+    for (int d = 0; d < rank; ++d) {
+      if (red.count(d)) {
+        IndexClass k = Cls({{0, d}});
+        k.reduced_outputs = {0};
+        r.classes.push_back(k);
+        if (keepdim) ++od;
+      } else {
+        r.classes.push_back(Cls({{0, d}, {1, od}}));
+        ++od;
+      }
+    }
+    if (b == "aten.mean") r.partial_scale = -1.0;  // scale by 1/#shards after the reduction
+    return r;
+  }
+  if (b == "aten._softmax" || b == "aten._log_softmax" || b == "aten._softmax_backward_data" ||
+      b == "aten._log_softmax_backward_data" || b == "aten.softmax" || b == "aten.log_softmax") {
+    Rule e = ElementwiseRule(g, n);
+    const int rank = out_rank(0);
+    int dim = rank - 1;
+    for (auto& a : args.arr) if (a.is_number()) { dim = NormDim(a.as_int(), rank); break; }
+    for (auto& c : e.classes) for (auto& m : c.members) if (m.first == nin && m.second == dim) c.no_shard = true;
+    return e;
+  }
+  if (b == "aten.slice" || b == "aten.narrow" || b == "aten.select" || b == "aten.cat" || b == "aten.index_select") {
+    if (b == "aten.cat") { r.known = false; return r; }
+    const int rank = in_rank(0);
+    const int dim = args.arr.size() >= 1 && args.arr[0].is_number() ? NormDim(args.arr[0].as_int(), rank) : 0;
+    int od = 0;
+    for (int d = 0; d < rank; ++d) {
+      if (d == dim) {
+        IndexClass z = Cls({{0, d}});
+        z.no_shard = true;
+        if (b != "aten.select") { z.members.emplace_back(1, od); ++od; }
+        r.classes.push_back(z);
+      } else {
+        r.classes.push_back(Cls({{0, d}, {1, od}}));
+        ++od;
+      }
+    }
+    return r;
+  }
+  if (n.op == "mm.dynamic_slice" || n.op == "mm.copy" || n.op == "mm.accumulate") {
+    // same rank, dimension by dimension; a sliced dimension keeps its sharding (every
+    // shard contributes its own rows to each microbatch)
+    const int rank = in_rank(0);
+    for (int d = 0; d < rank; ++d) r.classes.push_back(Cls({{0, d}, {nin, d}}));
+    return r;
+  }
+  r.known = false;
+  return r;
+}
+
+// Rules supplied by the front end for custom operators: attrs["shard_rule"] =
+// {"classes":[{"members":[[slot,dim],...],"no_shard":bool,"reduced_outputs":[i,...]}], "partial_scale": x}
+bool RuleFromAttr(const Node& n, Rule* out) {
+  auto it = n.attrs.find("shard_rule");
+  if (it == n.attrs.end()) return false;
+  const Json j = Json::parse(it->second);
+  Rule r;
+  for (auto& c : j.at("classes").arr) {
+    IndexClass ic;
+    for (auto& m : c.at("members").arr)
+      ic.members.emplace_back(static_cast<int>(m.arr[0].as_int()), static_cast<int>(m.arr[1].as_int()));
+    if (c.has("no_shard")) ic.no_shard = c.at("no_shard").as_bool();
+    if (c.has("reduced_outputs"))
+      for (auto v : c.at("reduced_outputs").as_int_vector()) ic.reduced_outputs.insert(static_cast<int>(v));
+    r.classes.push_back(ic);
+  }
+  if (j.has("partial_scale")) r.partial_scale = j.at("partial_scale").num;
+  *out = r;
+  return true;
+}
+
+Rule RuleFor(const Graph& g, const Node& n) {
+  Rule r;
+  if (RuleFromAttr(n, &r)) return r;
+  return GetRule(g, n);
+}
+
+struct TaskMeshInfo {
+  std::vector<int> dims;
+  std::vector<std::string> names;
+  std::vector<std::pair<std::string, std::string>> logical_axes;
+  DeviceRange devices;
+};
+
+TaskMeshInfo MeshOf(const Partition& part, const std::string& color) {
+  const ColorConfig& c = part.Get(color);
+  TaskMeshInfo m;
+  m.dims = c.options.dims.empty() ? std::vector<int>{c.devices.n} : c.options.dims;
+  m.names = c.options.device_axes;
+  while (m.names.size() < m.dims.size()) m.names.push_back("axis" + std::to_string(m.names.size()));
+  m.logical_axes = c.options.logical_axes;
+  m.devices = c.devices;
+  return m;
+}
+
+ShardedShape ReplicatedOn(const Value& v, const TaskMeshInfo& m) {
+  ShardedShape s;
+  s.dtype = v.dtype;
+  s.sizes = v.shape;
+  s.dim_axes.assign(v.shape.size(), {});
+  s.mesh_dims = m.dims;
+  s.devices = m.devices;
+  return s;
+}
+
+// Sharding implied by the value's axis-name annotation on mesh `m`.
+ShardedShape FromAxes(const Value& v, const TaskMeshInfo& m) {
+  if (v.axes_logical)
+    return LogicalToPhysical(v.dtype, v.shape, v.axes, m.logical_axes, m.names, m.dims, m.devices);
+  ShardedShape s = ReplicatedOn(v, m);
+  std::vector<bool> used(m.dims.size(), false);
+  for (size_t d = 0; d < v.axes.size(); ++d)
+    for (auto& name : v.axes[d])
+      for (size_t a = 0; a < m.names.size(); ++a)
+        if (m.names[a] == name && !used[a] && v.shape[d] % (static_cast<int64_t>(s.Shards(static_cast<int>(d))) * m.dims[a]) == 0) {
+          s.dim_axes[d].push_back(static_cast<int>(a));
+          used[a] = true;
+        }
+  return s;
+}
+
+// Re-expresses `src` (sharded on another submesh) on mesh `m`: equal meshes copy the
+// assignment; otherwise shard counts are matched to mesh axes, with the first sharded
+// dimension rescaled when the device counts differ (ResizeSharding semantics).
+ShardedShape AdoptSharding(const ShardedShape& src, const Value& v, const TaskMeshInfo& m) {
+  if (src.mesh_dims == m.dims) {
+    ShardedShape s = src;
+    s.devices = m.devices;
+    return s;
+  }
+  bool ok = true;
+  ShardedShape resized = src.devices.n == m.devices.n ? src : ResizeSharding(src, m.devices, &ok);
+  ShardedShape s = ReplicatedOn(v, m);
+  if (!ok) return s;
+  std::vector<bool> used(m.dims.size(), false);
+  for (int d = 0; d < resized.rank(); ++d) {
+    int want = resized.Shards(d);
+    if (want == 1) continue;
+    // greedily take unused mesh axes, major first, whose product equals the shard count
+    std::vector<int> pick;
+    int prod = 1;
+    for (size_t a = 0; a < m.dims.size() && prod < want; ++a) {
+      if (used[a] || m.dims[a] == 1) continue;
+      if (want % (prod * m.dims[a]) == 0) { pick.push_back(static_cast<int>(a)); prod *= m.dims[a]; }
+    }
+    if (prod == want) {
+      for (int a : pick) used[a] = true;
+      s.dim_axes[d] = pick;
+    }
+  }
+  return s;
+}
+
+int AxesProduct(const std::vector<int>& axes, const std::vector<int>& dims) {
+  int p = 1;
+  for (int a : axes) p *= dims[a];
+  return p;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Shared state of the sharding passes, kept on the side of CompileState
+// ---------------------------------------------------------------------------
+struct ShardingTables {
+  // sharding with which task `group` reads external value `value`
+  std::map<std::pair<int, int>, ShardedShape> input_sharding;
+  std::set<int> fixed_values;  // values whose sharding comes from an annotation
+};
+static std::map<const CompileState*, ShardingTables> g_tables;
+ShardingTables& TablesOf(const CompileState& s) { return g_tables[&s]; }
+void ReleaseShardingTables(const CompileState& s) { g_tables.erase(&s); }
+const ShardedShape* InputShardingOf(const CompileState& s, int group, int value) {
+  auto& t = TablesOf(s);
+  auto it = t.input_sharding.find({group, value});
+  return it == t.input_sharding.end() ? nullptr : &it->second;
+}
+
+namespace {
+
+const ShardedShape* Available(CompileState& s, const TaskGroup& grp, int value) {
+  const Graph& g = *s.graph;
+  const int p = g.value(value).producer;
+  if (p >= 0 && g.node(p).task == grp.id) return g.value(value).has_sharding ? &g.value(value).sharding : nullptr;
+  return InputShardingOf(s, grp.id, value);
+}
+
+void SetAvailable(CompileState& s, const TaskGroup& grp, int value, const ShardedShape& sh) {
+  Graph& g = *s.graph;
+  const int p = g.value(value).producer;
+  if (p >= 0 && g.node(p).task == grp.id) {
+    g.value(value).sharding = sh;
+    g.value(value).has_sharding = true;
+  } else {
+    TablesOf(s).input_sharding[{grp.id, value}] = sh;
+  }
+}
+
+// Evaluates one node: derives per-class mesh axes from the shardings that are known and
+// writes them to members that have none. Returns true when something was assigned.
+bool EvalNode(CompileState& s, const TaskGroup& grp, const TaskMeshInfo& mesh, Node& n, bool to_outputs,
+              bool to_inputs, bool assign_trivial) {
+  Graph& g = *s.graph;
+  const int nin = static_cast<int>(n.inputs.size());
+  auto slot_value = [&](int slot) { return slot < nin ? n.inputs[slot] : n.outputs[slot - nin]; };
+  Rule rule = RuleFor(g, n);
+  bool changed = false;
+  if (!rule.known) {
+    if (assign_trivial) {
+      for (int slot = 0; slot < nin + static_cast<int>(n.outputs.size()); ++slot) {
+        const int v = slot_value(slot);
+        if ((slot < nin ? to_inputs : to_outputs) && !Available(s, grp, v)) {
+          SetAvailable(s, grp, v, ReplicatedOn(g.value(v), mesh));
+          changed = true;
+        }
+      }
+    }
+    return changed;
+  }
+  // candidate axes per class
+  std::vector<std::vector<int>> class_axes(rule.classes.size());
+  for (size_t c = 0; c < rule.classes.size(); ++c) {
+    const IndexClass& ic = rule.classes[c];
+    if (ic.no_shard) continue;
+    int best = 1;
+    for (auto& m : ic.members) {
+      const ShardedShape* sh = Available(s, grp, slot_value(m.first));
+      if (!sh || sh->mesh_dims != mesh.dims || m.second >= sh->rank()) continue;
+      const int prod = AxesProduct(sh->dim_axes[m.second], mesh.dims);
+      if (prod > best) { best = prod; class_axes[c] = sh->dim_axes[m.second]; }
+    }
+    // every member must be divisible
+    for (auto& m : ic.members) {
+      const Value& v = g.value(slot_value(m.first));
+      if (m.second >= static_cast<int>(v.shape.size()) || v.shape[m.second] % best) { class_axes[c].clear(); break; }
+    }
+  }
+  // a mesh axis may serve only one class of a node
+  std::set<int> used;
+  for (auto& ax : class_axes) {
+    std::vector<int> keep;
+    for (int a : ax) if (used.insert(a).second) keep.push_back(a);
+    ax = keep;
+  }
+  // write to members without sharding
+  const int nslots = nin + static_cast<int>(n.outputs.size());
+  for (int slot = 0; slot < nslots; ++slot) {
+    const bool is_in = slot < nin;
+    if (is_in ? !to_inputs : !to_outputs) continue;
+    const int v = slot_value(slot);
+    if (Available(s, grp, v)) continue;
+    ShardedShape sh = ReplicatedOn(g.value(v), mesh);
+    bool nontrivial = false;
+    for (size_t c = 0; c < rule.classes.size(); ++c)
+      for (auto& m : rule.classes[c].members)
+        if (m.first == slot && m.second < sh.rank() && !class_axes[c].empty()) {
+          sh.dim_axes[m.second] = class_axes[c];
+          nontrivial = true;
+        }
+    if (!nontrivial && !assign_trivial) continue;
+    SetAvailable(s, grp, v, sh);
+    changed = true;
+  }
+  return changed;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Logical -> physical
+// ---------------------------------------------------------------------------
+bool LogicalToPhysicalSharding(CompileState& s) {
+  Graph& g = *s.graph;
+  Partition& part = *s.partition;
+  ShardingTables& tables = TablesOf(s);
+  tables.input_sharding.clear();
+  tables.fixed_values.clear();
+  for (auto& v : g.values) { v.has_sharding = false; v.partial = false; v.partial_axes.clear(); }
+  bool changed = false;
+  for (auto& grp : s.groups) {
+    const TaskMeshInfo mesh = MeshOf(part, grp.color);
+    if (mesh.devices.n == 1) continue;  // single-device tasks carry no sharding at all
+    for (int id : grp.nodes) {
+      const Node& n = g.node(id);
+      for (int o : n.outputs) {
+        Value& v = g.value(o);
+        if (!v.has_axes) continue;
+        v.sharding = FromAxes(v, mesh);
+        v.has_sharding = true;
+        tables.fixed_values.insert(o);
+        changed = true;
+      }
+      for (int in : n.inputs) {
+        const Value& v = g.value(in);
+        const int p = v.producer;
+        if ((p >= 0 && g.node(p).task == grp.id) || !v.has_axes) continue;
+        tables.input_sharding[{grp.id, in}] = FromAxes(v, mesh);
+        changed = true;
+      }
+    }
+  }
+  return changed;
+}
+
+// ---------------------------------------------------------------------------
+// Propagation
+// ---------------------------------------------------------------------------
+bool ShardingPropagation(CompileState& s, PropagationMode mode) {
+  Graph& g = *s.graph;
+  Partition& part = *s.partition;
+  bool changed_any = false;
+  const bool full = mode == PropagationMode::kForwardFull;
+  const bool forward = mode != PropagationMode::kBackwardInputOutput;
+  for (int round = 0; round < 4; ++round) {
+    bool changed = false;
+    auto do_group = [&](TaskGroup& grp) {
+      const TaskMeshInfo mesh = MeshOf(part, grp.color);
+      if (mesh.devices.n == 1) return;
+      if (forward) {
+        // adopt producer shardings for external inputs
+        for (int id : grp.nodes)
+          for (int in : g.node(id).inputs) {
+            const Value& v = g.value(in);
+            const int p = v.producer;
+            if (p < 0 || g.node(p).task == grp.id || !v.has_sharding) continue;
+            if (InputShardingOf(s, grp.id, in)) continue;
+            ShardedShape adopted = AdoptSharding(v.sharding, v, mesh);
+            if (adopted.IsReplicated() && !full) continue;
+            TablesOf(s).input_sharding[{grp.id, in}] = adopted;
+            changed = true;
+          }
+        for (int id : grp.nodes) changed |= EvalNode(s, grp, mesh, g.node(id), true, full, full);
+      } else {
+        for (auto it = grp.nodes.rbegin(); it != grp.nodes.rend(); ++it)
+          changed |= EvalNode(s, grp, mesh, g.node(*it), false, true, false);
+        // hand input shardings back to producers that have none (same mesh only)
+        for (int id : grp.nodes)
+          for (int in : g.node(id).inputs) {
+            Value& v = g.value(in);
+            const int p = v.producer;
+            if (p < 0 || g.node(p).task == grp.id || v.has_sharding) continue;
+            const ShardedShape* want = InputShardingOf(s, grp.id, in);
+            if (!want || want->IsReplicated()) continue;
+            const TaskMeshInfo pm = MeshOf(part, g.node(p).color);
+            if (pm.devices.n == 1) continue;
+            v.sharding = AdoptSharding(*want, v, pm);
+            v.has_sharding = true;
+            changed = true;
+          }
+      }
+    };
+    if (forward) for (auto& grp : s.groups) do_group(grp);
+    else for (auto it = s.groups.rbegin(); it != s.groups.rend(); ++it) do_group(*it);
+    changed_any |= changed;
+    if (!changed) break;
+  }
+  return changed_any;
+}
+
+// ---------------------------------------------------------------------------
+// SPMD lowering
+// ---------------------------------------------------------------------------
+bool SpmdLowering(CompileState& s) {
+  Graph& g = *s.graph;
+  Partition& part = *s.partition;
+  bool changed = false;
+  for (auto& grp : s.groups) {
+    const TaskMeshInfo mesh = MeshOf(part, grp.color);
+    if (mesh.devices.n == 1) continue;
+    std::vector<int> new_nodes;
+    for (int id : std::vector<int>(grp.nodes)) {
+      Node& n0 = g.node(id);
+      const int nin = static_cast<int>(n0.inputs.size());
+      Rule rule = RuleFor(g, n0);
+      auto slot_value = [&](int slot) { return slot < nin ? g.node(id).inputs[slot] : g.node(id).outputs[slot - nin]; };
+      // class axes: from outputs first (they are final), else from the most-sharded input
+      std::vector<std::vector<int>> class_axes(rule.classes.size());
+      if (rule.known) {
+        std::set<int> used;
+        for (int pass = 0; pass < 2; ++pass)
+          for (size_t c = 0; c < rule.classes.size(); ++c) {
+            if (rule.classes[c].no_shard || !class_axes[c].empty()) continue;
+            std::vector<int> best;
+            int best_p = 1;
+            for (auto& m : rule.classes[c].members) {
+              const bool is_out = m.first >= nin;
+              if ((pass == 0) != is_out) continue;
+              const ShardedShape* sh = Available(s, grp, slot_value(m.first));
+              if (!sh || m.second >= sh->rank()) continue;
+              const int p = AxesProduct(sh->dim_axes[m.second], mesh.dims);
+              if (p > best_p) { best_p = p; best = sh->dim_axes[m.second]; }
+            }
+            bool ok = !best.empty();
+            for (int a : best) ok = ok && !used.count(a);
+            for (auto& m : rule.classes[c].members) {
+              const Value& v = g.value(slot_value(m.first));
+              if (m.second >= static_cast<int>(v.shape.size()) || v.shape[m.second] % best_p) ok = false;
+            }
+            if (ok) { class_axes[c] = best; for (int a : best) used.insert(a); }
+          }
+      }
+      // required sharding of every input
+      for (int slot = 0; slot < nin; ++slot) {
+        const int v = g.node(id).inputs[slot];
+        ShardedShape want = ReplicatedOn(g.value(v), mesh);
+        if (rule.known)
+          for (size_t c = 0; c < rule.classes.size(); ++c)
+            for (auto& m : rule.classes[c].members)
+              if (m.first == slot && m.second < want.rank()) want.dim_axes[m.second] = class_axes[c];
+        const ShardedShape* have = Available(s, grp, v);
+        if (!have) { SetAvailable(s, grp, v, want); continue; }
+        if (have->mesh_dims == want.mesh_dims && have->dim_axes == want.dim_axes) continue;
+        const int prod = g.value(v).producer;
+        if (prod < 0 || g.node(prod).task != grp.id) {
+          // external input: ask for it in the wanted layout unless another node of this task
+          // already fixed a different one; then convert locally
+          bool conflicting = TablesOf(s).fixed_values.count(v) > 0;
+          if (!conflicting) { TablesOf(s).input_sharding[{grp.id, v}] = want; continue; }
+        }
+        const int rid = g.AddNode("mm.spmd_reshard", {v}, {g.value(v).shape}, {g.value(v).dtype},
+                                  {{"from", have->ToJson().dump()}, {"to", want.ToJson().dump()}});
+        Node& rn = g.node(rid);
+        rn.color = grp.color;
+        rn.task = grp.id;
+        rn.loop = g.node(id).loop;
+        rn.backprop = g.node(id).backprop;
+        g.value(rn.outputs[0]).sharding = want;
+        g.value(rn.outputs[0]).has_sharding = true;
+        g.node(id).inputs[slot] = rn.outputs[0];
+        new_nodes.push_back(rid);
+        changed = true;
+      }
+      // final sharding and partial-sum state of every output
+      for (size_t o = 0; o < g.node(id).outputs.size(); ++o) {
+        const int v = g.node(id).outputs[o];
+        ShardedShape sh = ReplicatedOn(g.value(v), mesh);
+        std::vector<int> partial;
+        if (rule.known)
+          for (size_t c = 0; c < rule.classes.size(); ++c) {
+            for (auto& m : rule.classes[c].members)
+              if (m.first == nin + static_cast<int>(o) && m.second < sh.rank()) sh.dim_axes[m.second] = class_axes[c];
+            if (rule.classes[c].reduced_outputs.count(static_cast<int>(o)))
+              partial.insert(partial.end(), class_axes[c].begin(), class_axes[c].end());
+          }
+        g.value(v).sharding = sh;
+        g.value(v).has_sharding = true;
+        if (partial.empty()) continue;
+        std::sort(partial.begin(), partial.end());
+        Json axes = Json::array();
+        int shards = 1;
+        for (int a : partial) { axes.push(Json::number(a)); shards *= mesh.dims[a]; }
+        const double scale = rule.partial_scale < 0 ? 1.0 / shards : rule.partial_scale;
+        const int rid = g.AddNode("mm.all_reduce", {v}, {g.value(v).shape}, {g.value(v).dtype},
+                                  {{"axes", axes.dump()}, {"scale", std::to_string(scale)}});
+        Node& rn = g.node(rid);
+        rn.color = grp.color;
+        rn.task = grp.id;
+        rn.loop = g.node(id).loop;
+        rn.backprop = g.node(id).backprop;
+        const int reduced = rn.outputs[0];
+        g.value(reduced).sharding = sh;
+        g.value(reduced).has_sharding = true;
+        g.value(reduced).axes = g.value(v).axes;
+        g.value(reduced).has_axes = g.value(v).has_axes;
+        g.value(v).partial = true;
+        g.value(v).partial_axes = partial;
+        // every other user reads the reduced value
+        for (auto& m : g.nodes) {
+          if (m.dead || m.id == rid) continue;
+          for (int& in : m.inputs) if (in == v) in = reduced;
+        }
+        for (int& out : g.outputs) if (out == v) out = reduced;
+        new_nodes.push_back(rid);
+        changed = true;
+      }
+    }
+    grp.nodes.insert(grp.nodes.end(), new_nodes.begin(), new_nodes.end());
+  }
+  if (changed) {
+    g.Toposort();
+    std::vector<int> pos(g.nodes.size(), 0);
+    for (size_t i = 0; i < g.order.size(); ++i) pos[g.order[i]] = static_cast<int>(i);
+    std::vector<int> order;
+    for (auto& grp : s.groups) {
+      std::sort(grp.nodes.begin(), grp.nodes.end(), [&](int a, int b) { return pos[a] < pos[b]; });
+      order.insert(order.end(), grp.nodes.begin(), grp.nodes.end());
+    }
+    g.order = order;
+  }
+  return changed;
+}
+
+// ---------------------------------------------------------------------------
+// Hoist reductions of gradient accumulators out of the loop
+// (src/pjrt_client/mpmd_hoist_shard_map_reduce.cc:49-189): an all-reduce whose only
+// consumer is the loop-carried sum runs once after the loop on the accumulated value.
+// ---------------------------------------------------------------------------
+bool HoistShardMapReduce(CompileState& s) {
+  Graph& g = *s.graph;
+  const auto users = g.ComputeUsers();
+  bool changed = false;
+  for (int id : std::vector<int>(g.order)) {
+    Node& ar = g.node(id);
+    if (ar.dead || ar.op != "mm.all_reduce" || ar.loop < 0) continue;
+    const auto& us = users[ar.outputs[0]];
+    if (us.size() != 1 || g.node(us[0]).op != "mm.accumulate") continue;
+    const int acc_id = us[0];
+    // accumulate the partial value; reduce its sum once, after the loop
+    g.node(acc_id).inputs[0] = ar.inputs[0];
+    const int acc_out = g.node(acc_id).outputs[0];
+    if (s.config.remove_hoisted_reduces) {  // performance upper-bound experiment: drop it entirely
+      ar.dead = true;
+      changed = true;
+      continue;
+    }
+    const std::map<std::string, std::string> ar_attrs = ar.attrs;
+    const std::string acc_color = g.node(acc_id).color;
+    const bool acc_backprop = g.node(acc_id).backprop;
+    const int rid = g.AddNode("mm.all_reduce", {acc_out}, {g.value(acc_out).shape}, {g.value(acc_out).dtype}, ar_attrs);
+    Node& rn = g.node(rid);
+    rn.color = acc_color;
+    rn.loop = -1;
+    rn.backprop = acc_backprop;
+    rn.attrs["hoisted"] = "1";
+    g.value(rn.outputs[0]).sharding = g.value(acc_out).sharding;
+    g.value(rn.outputs[0]).has_sharding = g.value(acc_out).has_sharding;
+    const int reduced = rn.outputs[0];
+    for (auto& m : g.nodes) {
+      if (m.dead || m.id == rid) continue;
+      for (int& in : m.inputs) if (in == acc_out) in = reduced;
+    }
+    for (int& out : g.outputs) if (out == acc_out) out = reduced;
+    g.node(id).dead = true;
+    changed = true;
+  }
+  if (changed) {
+    std::vector<int> keep;
+    for (int id : g.order) if (!g.node(id).dead) keep.push_back(id);
+    g.order = keep;
+    g.Toposort();
+    s.Note("hoisted gradient reductions out of the microbatch loop");
+  }
+  return changed;
+}
+
+}  // namespace mmg

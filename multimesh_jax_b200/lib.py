@@ -1,0 +1,130 @@
+"""Context managers, sharding annotations and ``mjit``.
+
+Counterpart of the reference's ``multimesh/jax/lib.py``: ``ignore_transforms``
+(:50-74), ``enable_fast_path`` (:77-94), ``enable_recomputation`` (:97-115),
+``autoshard`` (:118-132), ``with_sharding_constraint`` (:144-230), ``tasks``
+/ ``context`` (:255-310) and ``mjit`` (:313-351).
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+from typing import Any, Callable, Iterable, Optional, Sequence, Union
+
+import torch
+
+from . import no_op as _no_op
+from . import state
+from .task import Context, MultiMesh, Task, register_task
+
+_auto_sharding = _no_op.no_op(_no_op.AUTO_SHARDING)
+
+
+def ignore_transforms(enabled: bool = True):
+    """Debug aid: ``task`` / ``microbatch`` / sharding annotations become no-ops."""
+    return state._flag("ignore_transforms", enabled)
+
+
+def should_ignore_transforms() -> bool:
+    return state.flags.ignore_transforms or not state.trace.active
+
+
+def enable_fast_path(enabled: bool = True):
+    """Small single-task programs bypass the MPMD runtime when enabled."""
+    return state._flag("fast_path", enabled)
+
+
+def enable_recomputation(enabled: bool = True):
+    """Allows the compiler to recompute cheap producer trees in the consumer
+    task instead of sending their result across submeshes."""
+    return state._flag("recomputation", enabled)
+
+
+def autoshard(enabled: bool = True):
+    """In autoshard mode ``with_sharding_constraint`` records *logical* axis
+    names and the compiler maps them to mesh axes per task."""
+    return state._flag("autoshard", enabled)
+
+
+def replicate_parameters_smaller_than_num_elements(n: int) -> None:
+    state.knobs["replicated_parameter_num_elements_cutoff"] = int(n)
+
+
+def recompute_from_arguments_if_cost_less_than(cost: int) -> None:
+    state.knobs["recompute_from_arguments_if_cost_less_than"] = int(cost)
+
+
+AxisSpec = Union[None, str, Sequence[str]]
+
+
+def _canonical_axes(spec: Sequence[AxisSpec], ndim: int):
+    """``None`` -> [], ``"a"`` -> ["a"], trailing dims padded with []."""
+    if len(spec) > ndim:
+        raise ValueError(f"sharding spec {spec} has more entries than the tensor has dims ({ndim})")
+    axes = []
+    for s in spec:
+        if s is None:
+            axes.append([])
+        elif isinstance(s, str):
+            axes.append([s])
+        else:
+            axes.append([str(x) for x in s])
+    axes.extend([] for _ in range(ndim - len(axes)))
+    return axes
+
+
+def with_sharding_constraint(x: Any, spec: Sequence[AxisSpec]):
+    """Annotates ``x`` (a tensor or a pytree of tensors) with one tuple of axis
+    names per dimension. In autoshard mode the names are logical and resolved
+    per task through ``Task.logical_axes``; otherwise they are mesh axis names
+    and fix the physical sharding directly."""
+    if should_ignore_transforms():
+        return x
+    from torch.utils import _pytree as pytree
+
+    def one(t):
+        if not isinstance(t, torch.Tensor):
+            return t
+        payload = {"axes": _canonical_axes(spec, t.dim()), "logical": bool(state.flags.autoshard)}
+        return _auto_sharding(t, payload)
+
+    return pytree.tree_map(one, x)
+
+
+@contextlib.contextmanager
+def tasks(configurable: Any):
+    """Registers every ``(matcher, Task | factory)`` pair produced by
+    ``configurable`` (an iterable, a mapping or a zero-argument callable) for
+    the duration of the block."""
+    items = configurable() if callable(configurable) else configurable
+    if isinstance(items, dict):
+        items = items.items()
+    ctx = Context()
+    for matcher, t in items:
+        if isinstance(t, Task):
+            ctx.register_task(matcher, task=t)
+        else:
+            ctx.register_task(matcher, factory=t)
+    with ctx:
+        yield ctx
+
+
+@contextlib.contextmanager
+def context(*managers):
+    """Enters several context managers at once."""
+    with contextlib.ExitStack() as stack:
+        for m in managers:
+            stack.enter_context(m)
+        yield
+
+
+def mjit(fun: Callable, *, mesh: Optional[MultiMesh] = None, in_shardings: Any = None,
+         out_shardings: Any = None, donate_argnums: Sequence[int] = (), static_argnums: Sequence[int] = (),
+         backend: Optional[str] = None):
+    """Just-in-time MPMD compilation: the function is captured and compiled on
+    first call for the given argument shapes; ``in_shardings`` / ``out_shardings``
+    are pytrees of per-dimension axis-name tuples (or ``None`` for "compiler's choice")."""
+    from .compiler.api import JitFunction
+    return JitFunction(fun, mesh=mesh, in_shardings=in_shardings, out_shardings=out_shardings,
+                       donate_argnums=tuple(donate_argnums), static_argnums=tuple(static_argnums),
+                       backend=backend)

@@ -1,0 +1,176 @@
+"""Device topology and in-task collectives.
+
+A compiled step addresses ``num_devices`` devices by ordinal. Three kinds of
+topology carry them:
+
+* ``cpu``  - every ordinal is a *virtual* CPU device of this process (the
+  stand-in for GPUs that the reference gets from
+  ``--xla_force_host_platform_device_count``); collectives are rendezvous
+  between the runtime's worker threads.
+* ``cuda`` - every ordinal is a CUDA device of this process.
+* ``dist`` - one process per device (``torch.distributed``; NCCL on GPUs,
+  gloo on CPUs): ordinal ``r`` lives in rank ``r``; collectives are
+  ``torch.distributed`` calls on sub-groups created once per device list.
+"""
+from __future__ import annotations
+
+import threading
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+class Topology:
+    def __init__(self, kind: str, num_devices: int, rank: int = 0, device: Optional[torch.device] = None):
+        assert kind in ("cpu", "cuda", "dist")
+        self.kind = kind
+        self.num_devices = num_devices
+        self.rank = rank
+        self._dist_device = device
+        if kind == "dist":
+            self.local_devices = [rank]
+        else:
+            self.local_devices = list(range(num_devices))
+        self._groups: Dict[Tuple[int, ...], object] = {}
+
+    @staticmethod
+    def auto(num_devices: int, backend: Optional[str] = None) -> "Topology":
+        import torch.distributed as dist
+        if backend in (None, "dist") and dist.is_available() and dist.is_initialized() and \
+                dist.get_world_size() >= num_devices and (backend == "dist" or num_devices > 1 or dist.get_world_size() == 1):
+            if backend == "dist" or dist.get_world_size() == num_devices:
+                dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+                return Topology("dist", num_devices, rank=dist.get_rank(), device=dev)
+        if backend in (None, "cuda") and torch.cuda.is_available() and torch.cuda.device_count() >= num_devices:
+            return Topology("cuda", num_devices)
+        if backend == "cuda":
+            raise RuntimeError(f"backend 'cuda' needs {num_devices} CUDA devices in this process")
+        return Topology("cpu", num_devices)
+
+    def torch_device(self, ordinal: int) -> torch.device:
+        if self.kind == "cpu":
+            return torch.device("cpu")
+        if self.kind == "cuda":
+            return torch.device("cuda", ordinal)
+        return self._dist_device
+
+    def is_local(self, ordinal: int) -> bool:
+        return ordinal in self.local_devices
+
+    def process_group(self, ranks: Sequence[int]):
+        """The ``torch.distributed`` group of ``ranks`` (created collectively on
+        first use: every rank must ask for the same groups in the same order)."""
+        import torch.distributed as dist
+        key = tuple(ranks)
+        if key not in self._groups:
+            if len(key) == dist.get_world_size():
+                self._groups[key] = dist.group.WORLD
+            else:
+                self._groups[key] = dist.new_group(list(key))
+        return self._groups[key]
+
+
+class Rendezvous:
+    """Exchange of one object per participant between threads of a process."""
+
+    def __init__(self):
+        self._cv = threading.Condition()
+        self._slots: Dict[object, Dict[int, object]] = {}
+        self._taken: Dict[object, int] = {}
+        self.timeout_s = 120.0
+
+    def exchange(self, key, group: Sequence[int], me: int, obj) -> List[object]:
+        with self._cv:
+            slot = self._slots.setdefault(key, {})
+            slot[me] = obj
+            self._cv.notify_all()
+            ok = self._cv.wait_for(lambda: len(slot) == len(group), timeout=self.timeout_s)
+            if not ok:
+                raise TimeoutError(f"collective {key!r}: only {len(slot)} of {len(group)} participants arrived")
+            out = [slot[r] for r in group]
+            self._taken[key] = self._taken.get(key, 0) + 1
+            if self._taken[key] == len(group):
+                del self._slots[key]
+                del self._taken[key]
+            return out
+
+
+def mesh_group(ordinal: int, mesh_dims: Sequence[int], axes: Sequence[int]) -> List[int]:
+    """Ordinals (within the task's device list) that differ from ``ordinal``
+    only in the coordinates of ``axes``; row-major mesh."""
+    strides = []
+    acc = 1
+    for s in reversed(mesh_dims):
+        strides.append(acc)
+        acc *= s
+    strides = list(reversed(strides))
+    coord = [(ordinal // st) % sz for st, sz in zip(strides, mesh_dims)]
+    group = [0]
+    base = sum(c * st for i, (c, st) in enumerate(zip(coord, strides)) if i not in axes)
+    group = [base]
+    for a in sorted(axes):
+        group = [g + k * strides[a] for g in group for k in range(mesh_dims[a])]
+    return sorted(group)
+
+
+def tile_box(shape_dict: dict, ordinal: int) -> Tuple[List[int], List[int]]:
+    from .. import _mm_C
+    return _mm_C.tile_box(shape_dict, ordinal)
+
+
+class DeviceCtx:
+    """What a task body sees of the device it runs on."""
+
+    def __init__(self, topology: Topology, device: int, rendezvous: Rendezvous):
+        self.topology = topology
+        self.device = device
+        self.torch_device = topology.torch_device(device)
+        self.rendezvous = rendezvous
+        # set per task launch
+        self.device_start = 0
+        self.mesh_dims: Sequence[int] = (1,)
+        self.key_prefix: Tuple = ()
+
+    # ------------------------------------------------------------------
+    def _exchange(self, key, group_ordinals: List[int], tensor: torch.Tensor) -> List[torch.Tensor]:
+        me = self.device - self.device_start
+        topo = self.topology
+        if topo.kind == "dist":
+            import torch.distributed as dist
+            pg = topo.process_group([self.device_start + o for o in group_ordinals])
+            outs = [torch.empty_like(tensor) for _ in group_ordinals]
+            dist.all_gather(outs, tensor.contiguous(), group=pg)
+            return outs
+        parts = self.rendezvous.exchange((self.key_prefix, key, tuple(group_ordinals)), group_ordinals, me, tensor)
+        return [p.to(self.torch_device) if p.device != self.torch_device else p for p in parts]
+
+    def all_reduce(self, x: torch.Tensor, axes: Sequence[int], key) -> torch.Tensor:
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        if len(group) == 1:
+            return x
+        if self.topology.kind == "dist":
+            import torch.distributed as dist
+            pg = self.topology.process_group([self.device_start + o for o in group])
+            out = x.contiguous().clone()
+            dist.all_reduce(out, group=pg)
+            return out
+        parts = self._exchange(("ar", key), group, x)
+        acc = parts[0].float() if x.dtype in (torch.bfloat16, torch.float16) else parts[0].clone()
+        for p in parts[1:]:
+            acc = acc + (p.float() if acc.dtype != p.dtype else p)
+        return acc.to(x.dtype)
+
+    def spmd_reshard(self, x: torch.Tensor, src: dict, dst: dict, key) -> torch.Tensor:
+        """Local tile of layout ``dst`` from tiles in layout ``src`` (same
+        devices): gather every tile, assemble the global array, slice."""
+        n = src["num_devices"]
+        me = self.device - self.device_start
+        group = list(range(n))
+        parts = self._exchange(("rs", key), group, x)
+        full = torch.empty(src["sizes"], dtype=x.dtype, device=x.device)
+        for o, p in zip(group, parts):
+            lo, hi = tile_box(src, o)
+            full[tuple(slice(a, b) for a, b in zip(lo, hi))] = p
+        lo, hi = tile_box(dst, me)
+        return full[tuple(slice(a, b) for a, b in zip(lo, hi))].contiguous()

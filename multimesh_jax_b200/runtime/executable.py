@@ -1,0 +1,359 @@
+"""The compiled step: per-step dispatch loop over the plan.
+
+``Executable.__call__`` mirrors ``MultiMeshPjRtExecutable::Execute``
+(``src/pjrt_client/mm_pjrt_executable.cc:271-708``): open a window, bind
+parameter stores (reusing the tiles of sharded inputs, or slicing global
+tensors into tiles), then walk the linear operation list and *submit* every
+task and reshard for each local device to the native task-graph runtime, which
+orders them by their store accesses; results are handed back as
+:class:`ShardedTensor` objects whose tiles become valid when the step's tasks
+have run (reading one blocks, nothing else does).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+from torch.utils import _pytree as pytree
+
+from ..compiler.capture import Captured, DTYPE_FROM_NAME
+from ..compiler.lower import TemplateProgram, build_program
+from .collectives import DeviceCtx, Rendezvous, Topology, tile_box
+
+
+import weakref
+
+live_executables: "weakref.WeakSet" = weakref.WeakSet()
+
+
+class StepFailed(RuntimeError):
+    """A task of the step reported an error (status code from the runtime)."""
+
+
+class ShardedTensor:
+    """A logical array stored as one tile per owning device.
+
+    ``sharding`` is the descriptor dict produced by the compiler (dtype, global
+    sizes, mesh axes per dimension, mesh shape, device range). Only tiles of
+    devices local to this process are held."""
+
+    def __init__(self, sharding: dict, tiles: Dict[int, torch.Tensor], topology: Topology, waiter=None):
+        self.sharding = sharding
+        self._tiles = tiles
+        self.topology = topology
+        self._waiter = waiter
+
+    @property
+    def shape(self) -> Tuple[int, ...]:
+        return tuple(self.sharding["sizes"])
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return DTYPE_FROM_NAME[self.sharding["dtype"]]
+
+    @property
+    def devices(self) -> range:
+        s = self.sharding["device_start"]
+        return range(s, s + self.sharding["num_devices"])
+
+    def wait(self) -> "ShardedTensor":
+        if self._waiter is not None:
+            w, self._waiter = self._waiter, None
+            w()
+        return self
+
+    def local_tiles(self) -> Dict[int, torch.Tensor]:
+        self.wait()
+        return dict(self._tiles)
+
+    def tile(self, device: int) -> torch.Tensor:
+        self.wait()
+        return self._tiles[device]
+
+    def has_local_tile(self) -> bool:
+        return any(self.topology.is_local(d) for d in self.devices)
+
+    def full_tensor(self) -> torch.Tensor:
+        """Assembles the global value (on the first local device, or CPU)."""
+        self.wait()
+        topo = self.topology
+        sizes = self.sharding["sizes"]
+        start = self.sharding["device_start"]
+        if topo.kind != "dist":
+            first = self._tiles[start]
+            out = torch.empty(sizes, dtype=first.dtype, device=first.device)
+            for d in self.devices:
+                lo, hi = tile_box(self.sharding, d - start)
+                out[tuple(slice(a, b) for a, b in zip(lo, hi))] = self._tiles[d].to(first.device)
+            return out
+        import torch.distributed as dist
+        dev = topo.torch_device(topo.rank)
+        out = torch.empty(sizes, dtype=self.dtype, device=dev)
+        for d in self.devices:
+            lo, hi = tile_box(self.sharding, d - start)
+            shape = [b - a for a, b in zip(lo, hi)]
+            buf = self._tiles[d].contiguous() if d == topo.rank else torch.empty(shape, dtype=self.dtype, device=dev)
+            dist.broadcast(buf, src=d)
+            out[tuple(slice(a, b) for a, b in zip(lo, hi))] = buf
+        return out
+
+    def item(self):
+        return self.full_tensor().item()
+
+    def __repr__(self):
+        return f"ShardedTensor({self.sharding['key']})"
+
+
+def shard_tensor(t: torch.Tensor, sharding: dict, topology: Topology) -> ShardedTensor:
+    """Slices a global tensor into the tiles of ``sharding`` (local devices only)."""
+    tiles: Dict[int, torch.Tensor] = {}
+    start = sharding["device_start"]
+    for o in range(sharding["num_devices"]):
+        d = start + o
+        if not topology.is_local(d):
+            continue
+        lo, hi = tile_box(sharding, o)
+        piece = t[tuple(slice(a, b) for a, b in zip(lo, hi))]
+        tiles[d] = piece.to(topology.torch_device(d))
+    return ShardedTensor(sharding, tiles, topology)
+
+
+class Executable:
+    def __init__(self, cap: Captured, plan: dict, topology: Topology, *, context=None, name: str = "step",
+                 fast_ops: Optional[Dict[str, Any]] = None):
+        from .. import _mm_C
+        self.cap = cap
+        self.plan = plan
+        self.topology = topology
+        self.name = name
+        self.programs: Dict[int, TemplateProgram] = {}
+        for t in plan["templates"]:
+            local = any(topology.is_local(d) for d in self._template_devices(t))
+            if local or topology.kind != "dist":
+                self.programs[t["id"]] = build_program(cap, plan, t, fast_ops)
+        if context is None:
+            inline = len(topology.local_devices) == 1
+            context = _mm_C.ThreadedContext(topology.local_devices, inline, False)
+        self.context = context
+        self.rendezvous = Rendezvous()
+        self.dev_ctx = {d: DeviceCtx(topology, d, self.rendezvous) for d in topology.local_devices}
+        # physical buffers: stores sharing a scheduling name and layout share one id
+        self.buffer_of: Dict[int, int] = {}
+        names: Dict[str, int] = {}
+        for st in plan["stores"]:
+            root = st
+            while root["alias_of"] >= 0:
+                root = plan["stores"][root["alias_of"]]
+            key = root["name"] + "@" + root["shape"]["key"]
+            self.buffer_of[st["id"]] = names.setdefault(key, len(names))
+        self.tiles: Dict[int, Dict[int, torch.Tensor]] = {st["id"]: {} for st in plan["stores"]}
+        self._step = 0
+        self._created = False
+        self._reshard_plans: Dict[Tuple[int, int], dict] = {}
+        self.launches = 0
+        self._inline = len(topology.local_devices) == 1
+        live_executables.add(self)
+
+    @staticmethod
+    def _template_devices(t: dict) -> range:
+        return range(t["device_start"], t["device_start"] + t["num_devices"])
+
+    # ------------------------------------------------------------------ inputs
+    def input_shardings(self) -> List[Optional[dict]]:
+        out = []
+        for sid in self.plan["param_stores"]:
+            out.append(self.plan["stores"][sid]["shape"] if sid >= 0 else None)
+        return out
+
+    def output_shardings(self) -> List[dict]:
+        return [self.plan["stores"][sid]["shape"] for sid in self.plan["root_stores"]]
+
+    def shard_argument(self, argnum: int, value: Any) -> Any:
+        """Lays out argument ``argnum`` (a pytree of global tensors) as the
+        compiled step expects it."""
+        cap = self.cap
+        example = pytree.tree_unflatten(list(range(len(cap.input_is_tensor))), cap.in_spec)
+        positions = pytree.tree_leaves(example[argnum])
+        tensor_index = {}
+        k = 0
+        for i, ok in enumerate(cap.input_is_tensor):
+            if ok:
+                tensor_index[i] = k
+                k += 1
+        leaves, spec = pytree.tree_flatten(value)
+        out = []
+        for pos, leaf in zip(positions, leaves):
+            if pos in tensor_index and isinstance(leaf, torch.Tensor):
+                sid = self.plan["param_stores"][tensor_index[pos]]
+                out.append(shard_tensor(leaf, self.plan["stores"][sid]["shape"], self.topology) if sid >= 0 else leaf)
+            else:
+                out.append(leaf)
+        return pytree.tree_unflatten(out, spec)
+
+    # ------------------------------------------------------------------ run
+    def __call__(self, *args):
+        cap, plan, ctx, topo = self.cap, self.plan, self.context, self.topology
+        flat, _ = pytree.tree_flatten(tuple(args))
+        tensors = [a for a in flat if isinstance(a, (torch.Tensor, ShardedTensor))]
+        if len(tensors) != cap.num_inputs:
+            raise ValueError(f"expected {cap.num_inputs} tensor arguments, got {len(tensors)}")
+        step = self._step
+        self._step += 1
+        if not self._inline:
+            # parameter tiles are rebound below: the previous step must not be reading them any more
+            self.wait()
+        ctx.open_window()
+        ctx.start_timer(self.name)
+        ctx.mark_profile(f"start {self.name}")
+        if not self._created:
+            for st in plan["stores"]:
+                nbytes = 1
+                for s in st["shape"]["shard_size"]:
+                    nbytes *= s
+                nbytes *= DTYPE_FROM_NAME[st["shape"]["dtype"]].itemsize
+                for d in range(st["shape"]["device_start"], st["shape"]["device_start"] + st["shape"]["num_devices"]):
+                    if topo.is_local(d):
+                        ctx.create_store(self.buffer_of[st["id"]], d, nbytes, False)
+            self._created = True
+        # parameter stores
+        for i, sid in enumerate(plan["param_stores"]):
+            if sid < 0:
+                continue
+            want = plan["stores"][sid]["shape"]
+            a = tensors[i]
+            if isinstance(a, ShardedTensor):
+                if a.sharding["key"] != want["key"]:
+                    a = shard_tensor(a.full_tensor(), want, topo)
+                self.tiles[sid] = a.local_tiles()
+            else:
+                self.tiles[sid] = shard_tensor(a, want, topo).local_tiles()
+        root_tiles: Dict[int, Dict[int, torch.Tensor]] = {sid: {} for sid in plan["root_stores"]}
+        # dispatch loop
+        for k, op in enumerate(plan["ops"]):
+            kind = op["kind"]
+            if kind == "task":
+                for d in range(op["device_start"], op["device_start"] + op["num_devices"]):
+                    if topo.is_local(d):
+                        self._submit_task(k, op, d, step, root_tiles)
+            elif kind == "reshard":
+                self._submit_reshard(k, op, step, root_tiles)
+        ctx.stop_timer(self.name)
+        ctx.close_window()
+        ctx.mark_profile(f"finish {self.name}")
+        # results
+        waited = {"done": False}
+
+        def waiter():
+            if waited["done"]:
+                return
+            waited["done"] = True
+            status, msg = ctx.wait_all()
+            if int(status) != 0:
+                ctx.reset_error()
+                raise StepFailed(f"{self.name}: {status.name}: {msg}")
+
+        outs: List[Any] = []
+        it = iter(plan["root_stores"])
+        n_out = len(cap.output_values) + len(cap.output_constants)
+        for pos in range(n_out):
+            if pos in cap.output_constants:
+                outs.append(cap.output_constants[pos])
+                continue
+            sid = next(it)
+            outs.append(ShardedTensor(plan["stores"][sid]["shape"], root_tiles[sid], topo, waiter))
+        return pytree.tree_unflatten(outs, cap.out_spec)
+
+    # ------------------------------------------------------------------ tasks
+    def _submit_task(self, k: int, op: dict, d: int, step: int, root_tiles):
+        prog = self.programs[op["template"]]
+        tiles = self.tiles
+        dctx = self.dev_ctx[d]
+        buf = self.buffer_of
+        reads = [(buf[s], d) for s in op["inputs"]]
+        writes = [(buf[s], d) for s in op["outputs"]]
+        reads += [(buf[s], d) for s, m in zip(op["outputs"], op["accumulate"]) if m == 2]
+        scalars = op["scalars"]
+        in_ids, out_ids, modes = op["inputs"], op["outputs"], op["accumulate"]
+        dev_start, mesh_dims = op["device_start"], prog.mesh_dims
+
+        def body():
+            dctx.device_start = dev_start
+            dctx.mesh_dims = mesh_dims
+            dctx.key_prefix = (step, k)
+            if dctx.torch_device.type == "cuda":
+                torch.cuda.set_device(dctx.torch_device)
+            ins = [tiles[s][d] for s in in_ids]
+            outs = prog.run(dctx, scalars, ins)
+            for s, o, m in zip(out_ids, outs, modes):
+                if m == 2:
+                    tiles[s][d].add_(o)
+                else:
+                    tiles[s][d] = o.clone() if m == 1 else o
+                if s in root_tiles:
+                    root_tiles[s][d] = tiles[s][d]
+
+        self.launches += 1
+        self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step)
+
+    # ------------------------------------------------------------------ reshards
+    def _reshard_plan(self, src_sid: int, dst_sid: int) -> dict:
+        from .. import _mm_C
+        key = (src_sid, dst_sid)
+        if key not in self._reshard_plans:
+            self._reshard_plans[key] = _mm_C.plan_reshard(self.plan["stores"][src_sid]["shape"],
+                                                          self.plan["stores"][dst_sid]["shape"])
+        return self._reshard_plans[key]
+
+    def _submit_reshard(self, k: int, op: dict, step: int, root_tiles):
+        from ..parallel.reshard import run_reshard_local, run_reshard_dist
+        topo = self.topology
+        src_sid, dst_sid = op["src_store"], op["dst_store"]
+        rplan = self._reshard_plan(src_sid, dst_sid)
+        src_shape = self.plan["stores"][src_sid]["shape"]
+        dst_shape = self.plan["stores"][dst_sid]["shape"]
+        buf = self.buffer_of
+        tiles = self.tiles
+        for d in range(op["device_start"], op["device_start"] + op["num_devices"]):
+            if not topo.is_local(d):
+                continue
+            mine_dst = [c for c in rplan["chunks"] if c["dst_device"] == d]
+            mine_src = [c for c in rplan["chunks"] if c["src_device"] == d]
+            if not mine_dst and not mine_src:
+                continue
+            if topo.kind == "dist":
+                reads = [(buf[src_sid], d)] if mine_src else []
+                writes = [(buf[dst_sid], d)] if mine_dst else []
+
+                def body(d=d, mine_dst=mine_dst, mine_src=mine_src):
+                    out = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape)
+                    if out is not None:
+                        tiles[dst_sid][d] = out
+                        if dst_sid in root_tiles:
+                            root_tiles[dst_sid][d] = out
+            else:
+                if not mine_dst:
+                    continue
+                reads = sorted({(buf[src_sid], c["src_device"]) for c in mine_dst})
+                writes = [(buf[dst_sid], d)]
+
+                def body(d=d, mine_dst=mine_dst):
+                    out = run_reshard_local(topo, d, tiles[src_sid], mine_dst, dst_shape)
+                    tiles[dst_sid][d] = out
+                    if dst_sid in root_tiles:
+                        root_tiles[dst_sid][d] = out
+
+            self.launches += 1
+            self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
+
+    # ------------------------------------------------------------------ misc
+    def wait(self):
+        status, msg = self.context.wait_all()
+        if int(status) != 0:
+            self.context.reset_error()
+            raise StepFailed(f"{self.name}: {status.name}: {msg}")
+
+    def event_log(self):
+        return self.context.event_log()
+
+    def shutdown(self):
+        self.context.shutdown()
