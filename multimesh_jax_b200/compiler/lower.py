@@ -90,12 +90,23 @@ class TemplateProgram:
         self.mesh_dims = template["mesh_dims"]
         self.device_start = template["device_start"]
         self._last_use = last_use
+        self.fused_acc: Dict[int, bool] = {}
 
-    def run(self, ctx, scalars: Sequence[int], inputs: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+    def run(self, ctx, scalars: Sequence[int], inputs: Sequence[torch.Tensor],
+            acc_bufs: Optional[Sequence[Optional[torch.Tensor]]] = None) -> List[torch.Tensor]:
+        """``acc_bufs[k]`` is the current accumulator tile of output ``k`` (or None for its
+        first write); outputs listed in ``self.fused_acc`` are written / accumulated by the
+        producing kernel itself and come back as the accumulator buffer."""
         env: Dict[int, Any] = dict(zip(self.inputs, inputs))
         for idx, ins in enumerate(self.instrs):
             kind = ins.kind
-            if kind == 0:  # captured operator
+            if kind == 6:  # operator that writes straight into a gradient accumulator
+                args = _materialize(ins.args, env, ctx)
+                kwargs = _materialize(ins.kwargs, env, ctx)
+                pos, dtype = ins.extra
+                buf = acc_bufs[pos] if acc_bufs is not None else None
+                env[ins.outs[0]] = ins.fn(*args, acc=(buf, dtype), **kwargs)
+            elif kind == 0:  # captured operator
                 args = ins.args if ins.static else _materialize(ins.args, env, ctx)
                 kwargs = ins.kwargs if ins.static else _materialize(ins.kwargs, env, ctx)
                 res = ins.fn(*args, **kwargs)
@@ -133,8 +144,8 @@ def _local_shape(value: dict) -> List[int]:
     return list(sh["shard_size"]) if sh else list(value["shape"])
 
 
-def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[Dict[str, Callable]] = None
-                  ) -> TemplateProgram:
+def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[Dict[str, Callable]] = None,
+                  acc_fusable: Optional[set] = None) -> TemplateProgram:
     g = cap.graph
     instrs: List[Instr] = []
     single_device = template["num_devices"] == 1
@@ -223,6 +234,30 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             instrs.append(Instr(5, None, n["inputs"][0], None, n["outputs"], None, nid, (src, dst)))
         else:
             raise NotImplementedError(f"no lowering for compiler-generated op {op}")
+    # fuse "operator -> accumulate -> task output" into the operator's own epilogue
+    fused_acc: Dict[int, bool] = {}
+    if acc_fusable:
+        out_pos = {v: k for k, v in enumerate(template["outputs"])}
+        reads_count: Dict[int, int] = {}
+        for ins in instrs:
+            for v in _reads(ins):
+                reads_count[v] = reads_count.get(v, 0) + 1
+        by_out = {ins.outs[0]: ins for ins in instrs if ins.outs}
+        for ins in instrs:
+            if ins.kind != 1 or g.node(ins.node_id)["op"] != "mm.accumulate":
+                continue
+            if ins.outs[0] not in out_pos:
+                continue
+            prod = by_out.get(ins.args)
+            if prod is None or prod.kind != 0 or reads_count.get(ins.args, 0) != 1 or ins.args in out_pos:
+                continue
+            if g.node(prod.node_id)["op"] not in acc_fusable or prod.slots is not None:
+                continue
+            pos = out_pos[ins.outs[0]]
+            acc_dtype = DTYPE_FROM_NAME[g.value(ins.outs[0])["dtype"]]
+            prod.kind = 6
+            prod.extra = (pos, acc_dtype)
+            fused_acc[pos] = True
     # liveness inside the program
     last: Dict[int, int] = {}
     keep = set(template["outputs"])
@@ -233,7 +268,9 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
     for v, idx in last.items():
         if v not in keep:
             last_use.setdefault(idx, []).append(v)
-    return TemplateProgram(template, instrs, list(template["inputs"]), list(template["outputs"]), last_use)
+    prog = TemplateProgram(template, instrs, list(template["inputs"]), list(template["outputs"]), last_use)
+    prog.fused_acc = fused_acc
+    return prog
 
 
 def _ir_value_of(cap: Captured, node: fx.Node) -> Optional[int]:
@@ -279,6 +316,6 @@ def _fix_sizes(arg, gshape, lshape):
 
 
 def _reads(ins: Instr) -> List[int]:
-    if ins.kind == 0:
+    if ins.kind in (0, 6):
         return _tensor_ids_in_order(ins.args, ins.kwargs)
     return [ins.args]

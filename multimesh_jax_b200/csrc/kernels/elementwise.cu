@@ -427,9 +427,14 @@ __global__ void adamw_kernel(float* __restrict__ master, __nv_bfloat16* __restri
                              float* __restrict__ m, float* __restrict__ v,
                              const float* __restrict__ grad, int64_t n4, float lr, float beta1,
                              float beta2, float eps, float wd, float bc1, float bc2,
-                             float grad_scale) {
+                             float grad_scale, const int64_t* __restrict__ step_dev) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= n4) return;
+  if (step_dev) {  // step count lives on the device: no host synchronisation per update
+    const float t = static_cast<float>(*step_dev);
+    bc1 = 1.f - powf(beta1, t);
+    bc2 = 1.f - powf(beta2, t);
+  }
   float4 p = reinterpret_cast<float4*>(master)[i];
   float4 mm_ = reinterpret_cast<float4*>(m)[i];
   float4 vv = reinterpret_cast<float4*>(v)[i];
@@ -614,14 +619,14 @@ int mm_accumulate_f32_bf16(float* acc, const void* src, int64_t n, cudaStream_t 
 
 int mm_adamw(float* master, void* param, float* m, float* v, const float* grad, int64_t n, float lr,
              float beta1, float beta2, float eps, float wd, int step, float grad_scale,
-             cudaStream_t stream) {
+             const int64_t* step_dev, cudaStream_t stream) {
   if (n % 4) return -2;
   if (n == 0) return 0;
   const float bc1 = 1.f - powf(beta1, static_cast<float>(step));
   const float bc2 = 1.f - powf(beta2, static_cast<float>(step));
   adamw_kernel<<<blocks_for(n / 4, 256), 256, 0, stream>>>(master, static_cast<__nv_bfloat16*>(param),
                                                          m, v, grad, n / 4, lr, beta1, beta2, eps,
-                                                         wd, bc1, bc2, grad_scale);
+                                                         wd, bc1, bc2, grad_scale, step_dev);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -359,8 +359,9 @@ bool Coloring(CompileState& s) {
         auto vote = [&](int neighbour, int via_value) {
           const Node& m = g.node(neighbour);
           if (m.color.empty()) return;
-          // loop membership must agree: a loop node is never coloured from outside the loop
-          if ((m.loop >= 0) != (n.loop >= 0)) return;
+          // a loop node is never coloured from outside the loop (the reverse is fine: work that
+          // consumes a summed gradient runs where that gradient lives)
+          if (n.loop >= 0 && m.loop < 0) return;
           double w = 1;
           if (prio == "WEIGHT") w = static_cast<double>(EdgeWeight(g, n, via_value));
           else if (prio == "DEPTH") w = 1.0 + props.depth[neighbour];
@@ -389,7 +390,7 @@ bool Coloring(CompileState& s) {
     if (n.dead || !n.color.empty() || !votes(*it)) continue;
     std::string c;
     for (int o : n.outputs) for (int u : users[o]) if (c.empty() && !g.node(u).color.empty() &&
-                                                       (g.node(u).loop >= 0) == (n.loop >= 0)) c = g.node(u).color;
+                                                       !(n.loop >= 0 && g.node(u).loop < 0)) c = g.node(u).color;
     n.color = c.empty() ? Partition::kGlobalColor : c;
   }
   return true;

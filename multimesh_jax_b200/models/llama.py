@@ -1,0 +1,238 @@
+"""Llama-family decoder (Llama-2 MHA and Llama-3 GQA shapes) written against ``mm_ops``.
+
+The model is a pure function of a parameter pytree, so the same code runs
+eagerly on one device (reference for differential tests) and is captured by
+``torch.fx`` and partitioned into pipeline stages / tensor-parallel shards by
+the MPMD compiler. Parameter layouts are chosen so that tensor-parallel
+sharding is a plain dimension split:
+
+* ``wqkv``  [H_total, Dh, D]   packed heads: ``hq`` query heads, then ``hkv`` key heads,
+                               then ``hkv`` value heads (per tensor-parallel shard)
+* ``wo``    [D, hq*Dh]
+* ``wgu``   [2, F, D]          gate (index 0) and up (index 1) projections
+* ``wdown`` [D, F]
+
+Every layer is wrapped in ``named_scope("layers.<i>")`` so that regex task
+registrations can place layers on pipeline stages.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import lib as mm_lib
+from ..ops import kernels as K
+from ..ops import mm_ops  # noqa: F401  (registers the operators)
+from ..task import MultiMesh, Task, microbatch, named_scope, register_task, value_and_grad
+
+ops = torch.ops.mm_ops
+
+
+@dataclass
+class LlamaConfig:
+    vocab: int = 32000
+    d_model: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 32
+    d_ff: int = 11008
+    rope_theta: float = 1e4
+    eps: float = 1e-5
+    dtype: torch.dtype = torch.bfloat16
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.n_heads
+
+    @staticmethod
+    def llama2_7b() -> "LlamaConfig":
+        return LlamaConfig()
+
+    @staticmethod
+    def llama3_8b() -> "LlamaConfig":
+        return LlamaConfig(vocab=128256, n_kv_heads=8, d_ff=14336, rope_theta=5e5)
+
+    @staticmethod
+    def tiny(n_layers: int = 2, d_model: int = 256, n_heads: int = 2, n_kv_heads: int = 2, d_ff: int = 512,
+             vocab: int = 512) -> "LlamaConfig":
+        return LlamaConfig(vocab=vocab, d_model=d_model, n_layers=n_layers, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                           d_ff=d_ff)
+
+    def num_params(self) -> int:
+        per_layer = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim * self.d_model + self.d_model * self.d_model \
+            + 3 * self.d_ff * self.d_model + 2 * self.d_model
+        return self.n_layers * per_layer + 2 * self.vocab * self.d_model + self.d_model
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Training FLOPs per token (forward + backward = 3x forward), causal attention counted at half."""
+        dense = 2 * (self.num_params() - self.vocab * self.d_model)
+        attn = 2 * 2 * seq_len * self.d_model * self.n_layers / 2
+        return 3.0 * (dense + attn)
+
+
+def init_params(cfg: LlamaConfig, device="cpu", seed: int = 0) -> Dict[str, Any]:
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    dt = cfg.dtype
+    D, Dh, F = cfg.d_model, cfg.head_dim, cfg.d_ff
+    H = cfg.n_heads + 2 * cfg.n_kv_heads
+    dev = torch.device(device)
+    meta = dev.type == "meta"
+
+    def normal(*shape, std=0.02):
+        if meta:
+            return torch.empty(*shape, dtype=dt, device=dev)
+        if dev.type == "cuda":
+            return (torch.randn(*shape, device=dev, dtype=torch.float32) * std).to(dt)
+        return (torch.randn(*shape, generator=g) * std).to(dt).to(dev)
+
+    def ones(*shape):
+        return torch.ones(*shape, dtype=dt, device=dev)
+
+    layers = []
+    for _ in range(cfg.n_layers):
+        layers.append({
+            "attn_norm": ones(D),
+            "wqkv": normal(H, Dh, D),
+            "wo": normal(D, cfg.n_heads * Dh, std=0.02 / math.sqrt(2 * cfg.n_layers)),
+            "ffn_norm": ones(D),
+            "wgu": normal(2, F, D),
+            "wdown": normal(D, F, std=0.02 / math.sqrt(2 * cfg.n_layers)),
+        })
+    return {"embed": normal(cfg.vocab, D), "layers": layers, "final_norm": ones(D), "lm_head": normal(cfg.vocab, D)}
+
+
+def rope_tables(cfg: LlamaConfig, seq_len: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    return K.rope_tables(seq_len, cfg.head_dim, cfg.rope_theta, device)
+
+
+def attention_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor, cos, sin) -> torch.Tensor:
+    """h: normalised activations [B, S, D] -> attention branch output [B, S, D]."""
+    B, S, D = h.shape
+    qkv = ops.linear(h, p["wqkv"])                       # [B, S, H_total, Dh]
+    qkv = mm_lib.with_sharding_constraint(qkv, ("batch", None, "heads", None))
+    out, _, _ = ops.attention(qkv, cos, sin, cfg.n_heads // cfg.n_kv_heads)
+    return ops.linear(out.flatten(2), p["wo"])
+
+
+def mlp_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor) -> torch.Tensor:
+    gu = ops.linear(h, p["wgu"])                          # [B, S, 2, F]
+    gu = mm_lib.with_sharding_constraint(gu, ("batch", None, None, "mlp"))
+    return ops.linear(ops.swiglu(gu), p["wdown"])
+
+
+def forward_layers(cfg: LlamaConfig, layers: Sequence[Dict[str, torch.Tensor]], x: torch.Tensor, h: torch.Tensor,
+                   cos, sin, next_norms: Sequence[torch.Tensor], first_index: int = 0):
+    """Runs a run of layers. ``x`` is the residual stream, ``h`` its normalised copy for the
+    first layer; ``next_norms[i]`` is the norm weight applied after layer i (the next
+    layer's attention norm, or the final norm). Returns the new (x, h)."""
+    for i, p in enumerate(layers):
+        with named_scope(f"layers.{first_index + i}"):
+            a = attention_block(cfg, p, h, cos, sin)
+            x, h, _ = ops.add_rmsnorm(x, a, p["ffn_norm"], cfg.eps)
+            m = mlp_block(cfg, p, h)
+            x, h, _ = ops.add_rmsnorm(x, m, next_norms[i], cfg.eps)
+            x = mm_lib.with_sharding_constraint(x, ("batch", None, None))
+    return x, h
+
+
+def loss_fn(cfg: LlamaConfig, params: Dict[str, Any], tokens: torch.Tensor, labels: torch.Tensor, cos, sin,
+            loss_scale: float) -> torch.Tensor:
+    """Sum over tokens of the next-token cross-entropy, times ``loss_scale``."""
+    layers = params["layers"]
+    with named_scope("embed"):
+        x = ops.embedding(params["embed"], tokens)         # [B, S, D]
+        h, _ = ops.rmsnorm(x, layers[0]["attn_norm"], cfg.eps)
+    next_norms = [l["attn_norm"] for l in layers[1:]] + [params["final_norm"]]
+    x, h = forward_layers(cfg, layers, x, h, cos, sin, next_norms)
+    with named_scope("head"):
+        logits = ops.linear(h, params["lm_head"])          # [B, S, V]
+        loss, _ = ops.cross_entropy(logits, labels, loss_scale)
+    return loss
+
+
+# ---------------------------------------------------------------------------
+# Optimiser state and the training step
+# ---------------------------------------------------------------------------
+@dataclass
+class AdamWConfig:
+    lr: float = 3e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+
+
+def init_opt_state(params: Dict[str, Any]) -> Dict[str, Any]:
+    from torch.utils import _pytree as pytree
+    leaves, spec = pytree.tree_flatten(params)
+    master = [l.float() for l in leaves]
+    m = [torch.zeros_like(x) for x in master]
+    v = [torch.zeros_like(x) for x in master]
+    step = torch.zeros(1, dtype=torch.int64, device=leaves[0].device)
+    return {"master": pytree.tree_unflatten(master, spec), "m": pytree.tree_unflatten(m, spec),
+            "v": pytree.tree_unflatten(v, spec), "step": step}
+
+
+def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_batch: int, microbatch_size: int,
+                    schedule: Optional[str] = "1f1b", grad_dtype: torch.dtype = torch.float32) -> Callable:
+    """Builds ``step(params, opt_state, tokens, labels, cos, sin) -> (loss, params, opt_state)``.
+
+    The loss is the mean token cross-entropy over the global batch; gradients are summed
+    over microbatches in ``grad_dtype`` accumulators; AdamW keeps fp32 master weights."""
+    from torch.utils import _pytree as pytree
+    loss_scale = 1.0 / float(global_batch * seq_len)
+
+    def step(params, opt_state, tokens, labels, cos, sin):
+        def mb_loss(p, batch):
+            tok, lab = batch
+            return loss_fn(cfg, p, tok, lab, cos, sin, loss_scale)
+
+        vg = value_and_grad(mb_loss)
+        if microbatch_size < global_batch:
+            vg = microbatch(vg, dim=0, size=microbatch_size, argnum=1, schedule=schedule,
+                            accumulate_dtype=grad_dtype)
+        loss, grads = vg(params, (tokens, labels))
+        with named_scope("optimizer"):
+            new_step = opt_state["step"] + 1
+            g_leaves, spec = pytree.tree_flatten(grads)
+            p_leaves = pytree.tree_leaves(params)
+            ma, mm_, vv = (pytree.tree_leaves(opt_state[k]) for k in ("master", "m", "v"))
+            new_p, new_master, new_m, new_v = [], [], [], []
+            for p0, g, a, b, c in zip(p_leaves, g_leaves, ma, mm_, vv):
+                p2, a2, b2, c2 = ops.adamw(p0, a, b, c, g, new_step, opt.lr, opt.beta1, opt.beta2, opt.eps,
+                                           opt.weight_decay, 1.0)
+                new_p.append(p2)
+                new_master.append(a2)
+                new_m.append(b2)
+                new_v.append(c2)
+        new_params = pytree.tree_unflatten(new_p, spec)
+        new_state = {"master": pytree.tree_unflatten(new_master, spec), "m": pytree.tree_unflatten(new_m, spec),
+                     "v": pytree.tree_unflatten(new_v, spec), "step": new_step}
+        return loss, new_params, new_state
+
+    return step
+
+
+def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
+                            logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
+                                                                       ("mlp", "model"))) -> None:
+    """Places layer ``i`` on pipeline stage ``i // (n_layers / num_stages)`` (mesh axis
+    ``stage``), the embedding on the first stage and the head / loss on the last one. The
+    optimiser update of a parameter runs where its gradient lives."""
+    per_stage = cfg.n_layers // num_stages
+    la = [(a, b) for a, b in logical_axes if b in mesh.axis_names]
+
+    def layer_task(matched: str, backprop: bool) -> Task:
+        idx = int(matched.split(".")[1])
+        stage = min(idx // per_stage, num_stages - 1)
+        return Task(name=f"stage{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage}, logical_axes=la)
+
+    mesh.register_task(r"(layers\.\d+)", factory=layer_task)
+    mesh.register_task("(embed)", factory=lambda m, b: Task(name="stage0" + ("_bwd" if b else ""),
+                                                            mesh_slice={"stage": 0}, logical_axes=la))
+    last = num_stages - 1
+    mesh.register_task("(head)", factory=lambda m, b: Task(name=f"stage{last}" + ("_bwd" if b else ""),
+                                                           mesh_slice={"stage": last}, logical_axes=la))

@@ -32,7 +32,7 @@ _SIGS = {
     "mm_add_bf16": (c_int, [_P, _P, _P, c_int64, _P]),
     "mm_accumulate_f32_bf16": (c_int, [_P, _P, c_int64, _P]),
     "mm_adamw": (c_int, [_P, _P, _P, _P, _P, c_int64, c_float, c_float, c_float, c_float,
-                         c_float, c_int, c_float, _P]),
+                         c_float, c_int, c_float, _P, _P]),
     "mm_sumsq_f32": (c_int, [_P, c_int64, _P, _P]),
 }
 

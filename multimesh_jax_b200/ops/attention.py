@@ -1,0 +1,96 @@
+"""Causal self-attention forward / backward on strided [B, S, H, D] views.
+
+``q`` has ``hq`` heads, ``k`` / ``v`` have ``hkv`` heads (``hq % hkv == 0``, grouped-query
+attention); all are views into one packed projection buffer, so only the last dimension
+is contiguous. The softmax scale is ``1/sqrt(D)``.
+
+CUDA tensors use the tcgen05 flash-attention kernels of ``_mm_kernels.so`` when they are
+built in (``mm_flash_attn_fwd`` / ``mm_flash_attn_bwd``); otherwise the fused
+scaled-dot-product kernels that ship with PyTorch are called (a library path, counted as
+such in the benchmarks). CPU tensors use an fp32 restatement.
+"""
+from __future__ import annotations
+
+import math
+from typing import Tuple
+
+import torch
+
+from . import _lib
+from . import kernels as K
+
+_aten = torch.ops.aten
+
+
+def have_native_kernels() -> bool:
+    try:
+        lib = _lib.load()
+    except RuntimeError:
+        return False
+    return hasattr(lib, "mm_flash_attn_fwd") and hasattr(lib, "mm_flash_attn_bwd")
+
+
+def _ref_fwd(q, k, v):
+    B, S, Hq, D = q.shape
+    rep = Hq // k.shape[2]
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(D)
+    mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = (p @ vf).permute(0, 2, 1, 3).contiguous()
+    return o.to(q.dtype), lse, (qf, kf, vf, p)
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns (out [B,S,Hq,D] contiguous, lse [B,Hq,S] fp32)."""
+    if not q.is_cuda:
+        o, lse, _ = _ref_fwd(q, k, v)
+        return o, lse
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    rep = Hq // Hkv
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if rep > 1:
+        kt = kt.repeat_interleave(rep, dim=1)
+        vt = vt.repeat_interleave(rep, dim=1)
+    out, lse, _, _, _, _, _, _, _ = _aten._scaled_dot_product_flash_attention(
+        qt, kt, vt, 0.0, True, False, scale=1.0 / math.sqrt(D))
+    return out.transpose(1, 2).contiguous(), lse
+
+
+def attention_bwd(dout, q, k, v, out, lse, dq, dk, dv) -> None:
+    """Writes the gradients into the (strided) views ``dq``, ``dk``, ``dv``."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    rep = Hq // Hkv
+    if not q.is_cuda:
+        _, _, (qf, kf, vf, p) = _ref_fwd(q, k, v)
+        dof = dout.float().permute(0, 2, 1, 3)
+        dvf = p.transpose(-1, -2) @ dof
+        dp = dof @ vf.transpose(-1, -2)
+        delta = (dof * out.float().permute(0, 2, 1, 3)).sum(-1, keepdim=True)
+        ds = p * (dp - delta) / math.sqrt(D)
+        dqf = ds @ kf
+        dkf = ds.transpose(-1, -2) @ qf
+        dq.copy_(dqf.permute(0, 2, 1, 3).to(dq.dtype))
+        dk.copy_(dkf.view(B, Hkv, rep, S, D).sum(2).permute(0, 2, 1, 3).to(dk.dtype))
+        dv.copy_(dvf.view(B, Hkv, rep, S, D).sum(2).permute(0, 2, 1, 3).to(dv.dtype))
+        return
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if rep > 1:
+        kt = kt.repeat_interleave(rep, dim=1)
+        vt = vt.repeat_interleave(rep, dim=1)
+    ot, dot = out.transpose(1, 2), dout.transpose(1, 2)
+    zero = torch.zeros((), dtype=torch.int64, device=q.device)
+    gq, gk, gv = _aten._scaled_dot_product_flash_attention_backward(
+        dot, qt, kt, vt, ot, lse, None, None, S, S, 0.0, True, zero, zero, scale=1.0 / math.sqrt(D))
+    dq.copy_(gq.transpose(1, 2))
+    if rep > 1:
+        gk = gk.view(B, Hkv, rep, S, D).sum(2)
+        gv = gv.view(B, Hkv, rep, S, D).sum(2)
+    dk.copy_(gk.transpose(1, 2))
+    dv.copy_(gv.transpose(1, 2))

@@ -40,7 +40,7 @@ _OUT_MODE = {(bf16, False): 0, (torch.float32, False): 1, (torch.float32, True):
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
-         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = bf16,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
          accumulate: bool = False) -> torch.Tensor:
     """``C[M,N] (+)= A[M,K] @ B[N,K]^T`` with bf16 inputs and fp32 accumulation.
 
@@ -54,7 +54,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     if out is None:
         assert not accumulate
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
     else:
         assert out.shape == (M, N) and out.stride(1) == 1
     if not a.is_cuda:
@@ -88,7 +88,7 @@ def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
 
 
 def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 accumulate: bool = False, out_dtype: torch.dtype = bf16) -> torch.Tensor:
+                 accumulate: bool = False, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """dw[N, K] (+)= dy[T, N]^T @ x[T, K]."""
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
 
@@ -317,10 +317,14 @@ def accumulate_(acc: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------- AdamW
 def adamw_step_(master: torch.Tensor, param: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
                 grad: torch.Tensor, *, lr: float, beta1: float, beta2: float, eps: float,
-                weight_decay: float, step: int, grad_scale: float = 1.0) -> None:
-    """Fused AdamW on flat buffers (fp32 master/m/v/grad, bf16 working copy)."""
+                weight_decay: float, step, grad_scale: float = 1.0) -> None:
+    """Fused AdamW on flat buffers (fp32 master/m/v/grad, bf16 working copy).
+    ``step`` is an int, or a 1-element int64 tensor on the same device (read by the
+    kernel, so no host synchronisation)."""
     n = master.numel()
+    step_t = step if isinstance(step, torch.Tensor) else None
     if not master.is_cuda:
+        step = int(step)
         g = grad * grad_scale
         m.mul_(beta1).add_(g, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
@@ -331,8 +335,9 @@ def adamw_step_(master: torch.Tensor, param: torch.Tensor, m: torch.Tensor, v: t
         return
     assert n % 4 == 0
     rc = _lib.load().mm_adamw(master.data_ptr(), param.data_ptr(), m.data_ptr(), v.data_ptr(),
-                              grad.data_ptr(), n, lr, beta1, beta2, eps, weight_decay, step, grad_scale,
-                              _stream())
+                              grad.data_ptr(), n, lr, beta1, beta2, eps, weight_decay,
+                              1 if step_t is not None else int(step), grad_scale,
+                              step_t.data_ptr() if step_t is not None else None, _stream())
     _lib.check(rc, "mm_adamw")
     _count()
 

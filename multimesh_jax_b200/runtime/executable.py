@@ -18,6 +18,7 @@ from torch.utils import _pytree as pytree
 
 from ..compiler.capture import Captured, DTYPE_FROM_NAME
 from ..compiler.lower import TemplateProgram, build_program
+from ..ops import kernels as K
 from .collectives import DeviceCtx, Rendezvous, Topology, tile_box
 
 
@@ -120,8 +121,14 @@ def shard_tensor(t: torch.Tensor, sharding: dict, topology: Topology) -> Sharded
 
 class Executable:
     def __init__(self, cap: Captured, plan: dict, topology: Topology, *, context=None, name: str = "step",
-                 fast_ops: Optional[Dict[str, Any]] = None):
+                 fast_ops: Optional[Dict[str, Any]] = None, acc_fusable: Optional[set] = None):
         from .. import _mm_C
+        if fast_ops is None:
+            try:
+                from ..ops.mm_ops import ACC_FUSABLE, FAST_OPS
+                fast_ops, acc_fusable = FAST_OPS, ACC_FUSABLE
+            except Exception:  # pragma: no cover
+                fast_ops = None
         self.cap = cap
         self.plan = plan
         self.topology = topology
@@ -130,7 +137,7 @@ class Executable:
         for t in plan["templates"]:
             local = any(topology.is_local(d) for d in self._template_devices(t))
             if local or topology.kind != "dist":
-                self.programs[t["id"]] = build_program(cap, plan, t, fast_ops)
+                self.programs[t["id"]] = build_program(cap, plan, t, fast_ops, acc_fusable)
         if context is None:
             inline = len(topology.local_devices) == 1
             context = _mm_C.ThreadedContext(topology.local_devices, inline, False)
@@ -275,6 +282,8 @@ class Executable:
         scalars = op["scalars"]
         in_ids, out_ids, modes = op["inputs"], op["outputs"], op["accumulate"]
         dev_start, mesh_dims = op["device_start"], prog.mesh_dims
+        fused = prog.fused_acc
+        acc_dtypes = [DTYPE_FROM_NAME[self.plan["stores"][s]["shape"]["dtype"]] for s in out_ids]
 
         def body():
             dctx.device_start = dev_start
@@ -283,12 +292,17 @@ class Executable:
             if dctx.torch_device.type == "cuda":
                 torch.cuda.set_device(dctx.torch_device)
             ins = [tiles[s][d] for s in in_ids]
-            outs = prog.run(dctx, scalars, ins)
-            for s, o, m in zip(out_ids, outs, modes):
-                if m == 2:
-                    tiles[s][d].add_(o)
+            accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
+            outs = prog.run(dctx, scalars, ins, accs)
+            for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
+                if m and fused.get(oi):
+                    tiles[s][d] = o          # the kernel wrote / accumulated into the accumulator itself
+                elif m == 2:
+                    K.accumulate_(tiles[s][d], o)
+                elif m == 1:
+                    tiles[s][d] = o.to(acc_dtypes[oi], copy=True)
                 else:
-                    tiles[s][d] = o.clone() if m == 1 else o
+                    tiles[s][d] = o
                 if s in root_tiles:
                     root_tiles[s][d] = tiles[s][d]
 

@@ -379,21 +379,28 @@ def task(fun: Optional[Callable] = None, *, name: Optional[str] = None, mesh: Op
 
 _mm_lib = torch.library.Library("mm", "FRAGMENT")
 _mm_lib.define("microbatch_slice(Tensor x, int dim, int size, int loop) -> Tensor")
-_mm_lib.define("microbatch_out(Tensor y, int loop) -> Tensor")
+_mm_lib.define("microbatch_out(Tensor y, int loop, str dtype) -> Tensor")
 
 
 def _mb_slice_impl(x, dim, size, loop):
     return x.narrow(dim, 0, size).clone()
 
 
-def _mb_out_impl(y, loop):
-    return y.clone()
+def _acc_dtype(y, dtype: str):
+    if dtype and y.is_floating_point():
+        return getattr(torch, dtype)
+    return y.dtype
+
+
+def _mb_out_impl(y, loop, dtype):
+    return y.to(_acc_dtype(y, dtype), copy=True)
 
 
 torch.library.impl(_mm_lib, "microbatch_slice", "CompositeExplicitAutograd")(_mb_slice_impl)
 torch.library.impl(_mm_lib, "microbatch_out", "CompositeExplicitAutograd")(_mb_out_impl)
 torch.library.register_fake("mm::microbatch_slice")(lambda x, dim, size, loop: x.narrow(dim, 0, size).clone())
-torch.library.register_fake("mm::microbatch_out")(lambda y, loop: torch.empty_like(y))
+torch.library.register_fake("mm::microbatch_out")(
+    lambda y, loop, dtype: torch.empty_like(y, dtype=_acc_dtype(y, dtype)))
 
 SCHEDULES = ("gpipe", "1f1b", "wavefront", "custom", "zero-bubble-h2", "prefetch-wavefront")
 
@@ -474,8 +481,10 @@ def microbatch(fun: Callable, *, dim: int = 0, size: int, argnum: Union[int, Seq
                     lambda x: torch.ops.mm.microbatch_slice(x, dim, size, loop_id)
                     if isinstance(x, torch.Tensor) else x, args[a])
             out = fun(*new_args, **kwargs)
+            acc_name = cfg.get("accumulate_dtype", "")
             out = pytree.tree_map(
-                lambda y: torch.ops.mm.microbatch_out(y, loop_id) if isinstance(y, torch.Tensor) else y, out)
+                lambda y: torch.ops.mm.microbatch_out(y, loop_id, acc_name) if isinstance(y, torch.Tensor) else y,
+                out)
         finally:
             tr.loop = None
         return out
