@@ -1,0 +1,245 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of a Llama-2-7B-shape decoder (bf16, seq 2048,
+AdamW, random init, synthetic token ids) through the MPMD compiler and runtime.
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Weak scaling: 8 sequences of 2048 tokens per GPU and step (global batch 64 at N = 8, the
+configuration named by the baseline), microbatches of 4 sequences, 1F1B schedule.
+Parallelism: N = 1 single stage; N = 2 -> 2 pipeline stages; N = 4 -> 2 stages x TP 2 (or 4
+stages with --tp 1); N = 8 -> 4 stages x TP 2.
+
+Prints ONE JSON line (rank 0). `value` is device-timed (CUDA events around exactly K steps,
+barrier + synchronize on both sides, max over ranks); `e2e` repeats the measurement with the
+per-step host->device copy of that step's token ids from pinned memory and a device->host
+read of the loss inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_TOKENS_PER_S = None  # the reference publishes no number for this metric
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--model", default="llama2_7b", choices=["llama2_7b", "llama3_8b", "tiny"])
+    p.add_argument("--seq", type=int, default=2048)
+    p.add_argument("--per-gpu-batch", type=int, default=8)
+    p.add_argument("--microbatch", type=int, default=4)
+    p.add_argument("--layers", type=int, default=0, help="override the number of layers (debugging only)")
+    p.add_argument("--tp", type=int, default=0, help="tensor-parallel degree (0 = default for N)")
+    p.add_argument("--schedule", default="1f1b")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "reference cannot be installed offline: its build needs scikit-build, JAX/jaxlib patches, "
+                          "Bazel and network fetches of OpenXLA, zuku and Legion (pip: ModuleNotFoundError: skbuild)"}))
+        return 0
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    n = args.gpus
+    if world != n and not (world == 1 and n == 1):
+        raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import multimesh_jax_b200 as mm
+    from multimesh_jax_b200.models import llama
+    from multimesh_jax_b200.ops import kernels as K
+    if n > 1:
+        mm.init(gpus=n, distributed=True)
+    import torch.distributed as dist
+
+    cfg = {"llama2_7b": llama.LlamaConfig.llama2_7b, "llama3_8b": llama.LlamaConfig.llama3_8b,
+           "tiny": llama.LlamaConfig.tiny}[args.model]()
+    if args.layers:
+        cfg.n_layers = args.layers
+    tp = args.tp or {1: 1, 2: 1, 4: 2, 8: 2}.get(n, 1)
+    pp = n // tp
+    seq = args.seq
+    global_batch = args.per_gpu_batch * n
+    mb = min(args.microbatch * tp, global_batch)
+    opt = llama.AdamWConfig()
+    step_fn = llama.make_train_step(cfg, opt, seq_len=seq, global_batch=global_batch, microbatch_size=mb,
+                                    schedule=args.schedule)
+    mesh = mm.MultiMesh((pp, tp), ("stage", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+
+    # abstract arguments for the capture; real tensors are created shard by shard below
+    with torch.device("meta"):
+        a_params = llama.init_params(cfg, device="meta")
+        a_state = llama.init_opt_state(a_params)
+    a_tok = torch.empty(global_batch, seq, dtype=torch.int64, device="meta")
+    a_cos = torch.empty(seq, cfg.head_dim // 2, dtype=torch.float32, device="meta")
+    t0 = time.time()
+    with mesh:
+        exe = mm.compile_function(step_fn, (a_params, a_state, a_tok, a_tok, a_cos, a_cos), mesh=mesh,
+                                  donate_argnums=(0, 1), backend="dist" if n > 1 else "cuda", name="train_step")
+    compile_s = time.time() - t0
+
+    from multimesh_jax_b200.models.init_sharded import init_sharded_llama
+    params, state = init_sharded_llama(cfg, exe, dev, seed=1234)
+    cos, sin = llama.rope_tables(cfg, seq, dev)
+
+    g = torch.Generator().manual_seed(rank + 1)
+    pool = 4
+    host_tok = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
+    host_lab = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
+    dev_tok = [t.to(dev) for t in host_tok]
+    dev_lab = [t.to(dev) for t in host_lab]
+
+    def run_step(i, e2e: bool):
+        nonlocal params, state
+        if e2e:
+            tok = host_tok[i % pool].to(dev, non_blocking=True)
+            lab = host_lab[i % pool].to(dev, non_blocking=True)
+        else:
+            tok, lab = dev_tok[i % pool], dev_lab[i % pool]
+        loss, params, state = exe(params, state, tok, lab, cos, sin)
+        if e2e:
+            return float(loss.full_tensor().item())
+        return loss
+
+    def barrier():
+        if n > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(steps: int, e2e: bool):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        last = None
+        for i in range(steps):
+            last = run_step(i, e2e)
+        e.record()
+        barrier()
+        ms = s.elapsed_time(e)
+        if n > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, last
+
+    last = None
+    for i in range(args.warmup):
+        last = run_step(i, False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0, lib0 = K.launch_count, K.library_call_count
+    ms, last = timed(args.steps, False)
+    launches = K.launch_count - launches0
+    lib_calls = K.library_call_count - lib0
+    clocks = sampler.stop()
+    loss_val = float(last.full_tensor().item()) if hasattr(last, "full_tensor") else float(last)
+    ms_e2e, _ = timed(args.steps, True)
+    status = K.read_status()
+
+    tokens = global_batch * seq * args.steps
+    value = tokens / (ms / 1e3)
+    e2e_value = tokens / (ms_e2e / 1e3)
+    flops = cfg.flops_per_token(seq) * global_batch * seq
+    if rank == 0:
+        out = {
+            "metric": "train tokens/s (device-timed, max over ranks)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+            "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+            "config": {"model": f"{args.model} shape ({cfg.n_layers} layers, d_model {cfg.d_model}, "
+                                f"{cfg.n_heads}q/{cfg.n_kv_heads}kv heads, ffn {cfg.d_ff}, vocab {cfg.vocab})",
+                       "global_batch": global_batch, "seq_len": seq, "microbatch": mb,
+                       "parallelism": f"pp{pp}xtp{tp}", "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
+                       "l2": "working set (>= 13 GB of weights per step) far exceeds the 126 MB L2; no flush needed"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 2 * global_batch * seq * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "library_kernel_calls": lib_calls,
+            "tflops_per_gpu": round(flops / (ms / args.steps / 1e3) / n / 1e12, 1),
+            "loss": round(loss_val, 4), "compile_s": round(compile_s, 1), "kernel_status": status,
+            "impl": "ours",
+        }
+        print(json.dumps(out), flush=True)
+    if n > 1:
+        dist.barrier()
+    exe.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

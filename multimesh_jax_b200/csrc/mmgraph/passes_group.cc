@@ -6,6 +6,7 @@
 #include <queue>
 #include <set>
 #include <stdexcept>
+#include <tuple>
 
 #include "passes.h"
 
@@ -328,6 +329,7 @@ bool ArgumentRecompute(CompileState& s) {
   Graph& g = *s.graph;
   Partition& part = *s.partition;
   bool changed = false;
+  std::map<std::tuple<int, std::string, int>, int> shared_clones;
   for (int id : std::vector<int>(g.order)) {
     if (g.node(id).dead || g.node(id).color.empty()) continue;
     for (size_t ii = 0; ii < g.node(id).inputs.size(); ++ii) {
@@ -365,6 +367,14 @@ bool ArgumentRecompute(CompileState& s) {
       std::map<int, int> remap;  // old value -> new value
       const std::string color = g.node(id).color;
       const int loop = g.node(id).loop;
+      // consumers of one colour share a single clone of the tree
+      auto shared_key = std::make_tuple(v, color, loop);
+      auto shared_hit = shared_clones.find(shared_key);
+      if (shared_hit != shared_clones.end()) {
+        g.node(id).inputs[ii] = shared_hit->second;
+        changed = true;
+        continue;
+      }
       for (int nid : tree) {
         const int clone = CloneNode(g, nid, color, loop);
         Node& c = g.node(clone);
@@ -372,6 +382,7 @@ bool ArgumentRecompute(CompileState& s) {
         for (size_t k = 0; k < c.outputs.size(); ++k) remap[g.node(nid).outputs[k]] = c.outputs[k];
       }
       g.node(id).inputs[ii] = remap[v];
+      shared_clones[shared_key] = remap[v];
       changed = true;
     }
   }

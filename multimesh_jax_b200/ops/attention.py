@@ -57,6 +57,7 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[to
     if rep > 1:
         kt = kt.repeat_interleave(rep, dim=1)
         vt = vt.repeat_interleave(rep, dim=1)
+    K.count_library_call()
     out, lse, _, _, _, _, _, _, _ = _aten._scaled_dot_product_flash_attention(
         qt, kt, vt, 0.0, True, False, scale=1.0 / math.sqrt(D))
     return out.transpose(1, 2).contiguous(), lse
@@ -85,6 +86,7 @@ def attention_bwd(dout, q, k, v, out, lse, dq, dk, dv) -> None:
         kt = kt.repeat_interleave(rep, dim=1)
         vt = vt.repeat_interleave(rep, dim=1)
     ot, dot = out.transpose(1, 2), dout.transpose(1, 2)
+    K.count_library_call()
     zero = torch.zeros((), dtype=torch.int64, device=q.device)
     gq, gk, gv = _aten._scaled_dot_product_flash_attention_backward(
         dot, qt, kt, vt, ot, lse, None, None, S, S, 0.0, True, zero, zero, scale=1.0 / math.sqrt(D))

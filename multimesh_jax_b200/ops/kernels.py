@@ -17,8 +17,15 @@ from . import _lib
 
 bf16 = torch.bfloat16
 
-# Number of kernel launches issued through this module (for benchmarks).
+# Number of kernel launches issued through this module (for benchmarks), and the number of
+# calls that went to a vendor-library kernel instead of one of ours.
 launch_count = 0
+library_call_count = 0
+
+
+def count_library_call(n: int = 1) -> None:
+    global library_call_count
+    library_call_count += n
 
 
 def _stream() -> int:

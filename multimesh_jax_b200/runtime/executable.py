@@ -89,6 +89,9 @@ class ShardedTensor:
             return out
         import torch.distributed as dist
         dev = topo.torch_device(topo.rank)
+        replicated = all(len(a) == 0 for a in self.sharding["dim_axes"])
+        if replicated and self.sharding["num_devices"] == topo.num_devices:
+            return self._tiles[topo.rank]      # every rank already holds the whole value
         out = torch.empty(sizes, dtype=self.dtype, device=dev)
         for d in self.devices:
             lo, hi = tile_box(self.sharding, d - start)
@@ -153,7 +156,11 @@ class Executable:
                 root = plan["stores"][root["alias_of"]]
             key = root["name"] + "@" + root["shape"]["key"]
             self.buffer_of[st["id"]] = names.setdefault(key, len(names))
-        self.tiles: Dict[int, Dict[int, torch.Tensor]] = {st["id"]: {} for st in plan["stores"]}
+        # stores that share a physical buffer share one tile table: writing a store drops the
+        # tensor of the store that used the buffer before (the compiler's liveness plan)
+        self._buffer_tiles: Dict[int, Dict[int, torch.Tensor]] = {}
+        self.tiles: Dict[int, Dict[int, torch.Tensor]] = {
+            st["id"]: self._buffer_tiles.setdefault(self.buffer_of[st["id"]], {}) for st in plan["stores"]}
         self._step = 0
         self._created = False
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
@@ -231,9 +238,11 @@ class Executable:
             if isinstance(a, ShardedTensor):
                 if a.sharding["key"] != want["key"]:
                     a = shard_tensor(a.full_tensor(), want, topo)
-                self.tiles[sid] = a.local_tiles()
+                new_tiles = a.local_tiles()
             else:
-                self.tiles[sid] = shard_tensor(a, want, topo).local_tiles()
+                new_tiles = shard_tensor(a, want, topo).local_tiles()
+            self.tiles[sid].clear()
+            self.tiles[sid].update(new_tiles)
         root_tiles: Dict[int, Dict[int, torch.Tensor]] = {sid: {} for sid in plan["root_stores"]}
         # dispatch loop
         for k, op in enumerate(plan["ops"]):
