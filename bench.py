@@ -156,14 +156,18 @@ def main():
     cos, sin = llama.rope_tables(cfg, seq, dev)
 
     g = torch.Generator().manual_seed(rank + 1)
-    pool = 4
+    pool = min(24, args.warmup + 2 * args.steps)   # a fresh batch every step
     host_tok = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
     host_lab = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
     dev_tok = [t.to(dev) for t in host_tok]
     dev_lab = [t.to(dev) for t in host_lab]
 
-    def run_step(i, e2e: bool):
+    counter = [0]
+
+    def run_step(_i, e2e: bool):
         nonlocal params, state
+        i = counter[0]
+        counter[0] += 1
         if e2e:
             tok = host_tok[i % pool].to(dev, non_blocking=True)
             lab = host_lab[i % pool].to(dev, non_blocking=True)

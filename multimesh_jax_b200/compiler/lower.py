@@ -98,6 +98,8 @@ class TemplateProgram:
         first write); outputs listed in ``self.fused_acc`` are written / accumulated by the
         producing kernel itself and come back as the accumulator buffer."""
         env: Dict[int, Any] = dict(zip(self.inputs, inputs))
+        if isinstance(inputs, list):
+            inputs.clear()  # the environment is now the only owner of handed-over inputs
         for idx, ins in enumerate(self.instrs):
             kind = ins.kind
             if kind == 6:  # operator that writes straight into a gradient accumulator

@@ -1,0 +1,218 @@
+// Peer-memory plumbing and the cross-submesh reshard kernel.
+//
+// One process drives one GPU. Each process allocates a "symmetric arena" with
+// cudaMalloc, exports it with a CUDA IPC handle and maps the arenas of the
+// other processes of the node, so every kernel can address any peer's HBM
+// directly over NVLink (plain ld/st, no TMA multicast anywhere).
+//
+// The reshard kernel is a *pull*: the destination GPU reads the rectangular
+// pieces it needs straight out of the source GPUs' tiles and writes its own
+// tile, so stores stay local, nothing is staged and no all-to-all runs. The
+// host supplies the pieces (boxes from the reshard planner). Readiness of a
+// source tile and permission to overwrite it again are exchanged through
+// epoch counters in the arenas' flag areas, with bounded waits that record an
+// error in the status word instead of spinning forever.
+#include "host_common.h"
+#include "ptx.cuh"
+
+namespace mm {
+
+constexpr int RS_MAX_DIMS = 4;
+constexpr int RS_MAX_CHUNKS = 64;
+constexpr int RS_MAX_WAITS = 16;
+
+struct ReshardChunkDesc {
+  const uint8_t* src;            // address of the chunk's first byte in the source tile (peer or local)
+  uint8_t* dst;                  // address of the chunk's first byte in the destination tile (local)
+  int64_t extent[RS_MAX_DIMS];   // extent[RS_MAX_DIMS-1] is in 16-byte vectors, the others in rows
+  int64_t src_stride[RS_MAX_DIMS];  // byte strides (innermost unused: contiguous)
+  int64_t dst_stride[RS_MAX_DIMS];
+  int64_t vec_begin;             // first global vector index of this chunk
+};
+
+struct ReshardArgs {
+  ReshardChunkDesc chunk[RS_MAX_CHUNKS];
+  int num_chunks;
+  int64_t total_vecs;
+  // flags: wait until *wait_flag[i] >= wait_value before reading; afterwards the last CTA
+  // stores done_value to every done_flag[i] (peer addresses)
+  const int* wait_flag[RS_MAX_WAITS];
+  int num_waits;
+  int wait_value;
+  int* done_flag[RS_MAX_WAITS];
+  int num_done;
+  int done_value;
+  unsigned int* cta_counter;     // local scratch word, zero on entry, reset on exit
+};
+
+__global__ void __launch_bounds__(256)
+    reshard_pull_kernel(const __grid_constant__ ReshardArgs args, int* __restrict__ err) {
+  __shared__ int ok_shared;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int i = 0; i < args.num_waits && ok; ++i) ok = wait_flag_ge(args.wait_flag[i], args.wait_value, err) ? 1 : 0;
+    ok_shared = ok;
+  }
+  __syncthreads();
+  if (ok_shared) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    constexpr int UNROLL = 4;
+    for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; base < args.total_vecs;
+         base += stride * UNROLL) {
+      uint4 v[UNROLL];
+      uint4* dptr[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const int64_t idx = base + u * stride;
+        dptr[u] = nullptr;
+        if (idx >= args.total_vecs) continue;
+        int c = 0;
+        while (c + 1 < args.num_chunks && args.chunk[c + 1].vec_begin <= idx) ++c;
+        const ReshardChunkDesc& ch = args.chunk[c];
+        int64_t rem = idx - ch.vec_begin;
+        const int64_t inner = rem % ch.extent[RS_MAX_DIMS - 1];
+        rem /= ch.extent[RS_MAX_DIMS - 1];
+        int64_t so = inner * 16, dof = inner * 16;
+#pragma unroll
+        for (int d = RS_MAX_DIMS - 2; d >= 0; --d) {
+          const int64_t i = rem % ch.extent[d];
+          rem /= ch.extent[d];
+          so += i * ch.src_stride[d];
+          dof += i * ch.dst_stride[d];
+        }
+        v[u] = *reinterpret_cast<const uint4*>(ch.src + so);
+        dptr[u] = reinterpret_cast<uint4*>(ch.dst + dof);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (dptr[u]) *dptr[u] = v[u];
+    }
+  }
+  // the last CTA to finish tells the sources that their tiles have been consumed
+  __syncthreads();
+  if (threadIdx.x == 0 && args.cta_counter) {
+    __threadfence_system();
+    const unsigned int prev = atomicAdd(args.cta_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      if (ok_shared)
+        for (int i = 0; i < args.num_done; ++i) st_release_sys(args.done_flag[i], args.done_value);
+      *args.cta_counter = 0;
+    }
+  }
+}
+
+// Sets a flag in (peer or local) memory after all prior work of the stream.
+__global__ void set_flag_kernel(int* flag, int value) {
+  __threadfence_system();
+  st_release_sys(flag, value);
+}
+// Waits (bounded) for a flag.
+__global__ void wait_flag_kernel(const int* flag, int value, int* err) {
+  wait_flag_ge(flag, value, err);
+}
+
+}  // namespace mm
+
+extern "C" {
+using namespace mm;
+
+int mm_peer_alloc(void** ptr, size_t bytes) {
+  MM_CUDA_TRY(cudaMalloc(ptr, bytes));
+  MM_CUDA_TRY(cudaMemset(*ptr, 0, bytes));
+  return 0;
+}
+int mm_peer_free(void* ptr) {
+  MM_CUDA_TRY(cudaFree(ptr));
+  return 0;
+}
+// handle_out must hold 64 bytes
+int mm_ipc_get_handle(void* ptr, void* handle_out) {
+  cudaIpcMemHandle_t h;
+  MM_CUDA_TRY(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle_out, &h, sizeof(h));
+  return 0;
+}
+int mm_ipc_open_handle(const void* handle_in, void** ptr_out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_in, sizeof(h));
+  MM_CUDA_TRY(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+int mm_ipc_close(void* ptr) {
+  MM_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+// Single-process multi-GPU: enable direct access from the current device to `peer`.
+int mm_enable_peer_access(int peer) {
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return 0; }
+  MM_CUDA_TRY(e);
+  return 0;
+}
+
+// chunks: num_chunks records of (src ptr, dst ptr, extent[4], src_stride[4], dst_stride[4]) as int64,
+// extents in elements of `elem_size` bytes with the innermost dimension contiguous on both sides.
+int mm_reshard_pull(const int64_t* chunks, int num_chunks, int elem_size, const int64_t* wait_flags,
+                    int num_waits, int wait_value, const int64_t* done_flags, int num_done, int done_value,
+                    void* cta_counter, int max_ctas, cudaStream_t stream) {
+  if (num_chunks <= 0) return 0;
+  if (num_chunks > RS_MAX_CHUNKS || num_waits > RS_MAX_WAITS || num_done > RS_MAX_WAITS) return -2;
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  ReshardArgs args;
+  memset(&args, 0, sizeof(args));
+  int64_t total = 0;
+  for (int c = 0; c < num_chunks; ++c) {
+    const int64_t* r = chunks + c * 14;
+    ReshardChunkDesc& d = args.chunk[c];
+    d.src = reinterpret_cast<const uint8_t*>(r[0]);
+    d.dst = reinterpret_cast<uint8_t*>(r[1]);
+    const int64_t inner_bytes = r[2 + 3] * elem_size;
+    if (inner_bytes % 16 || (r[0] & 15) || (r[1] & 15)) {
+      fprintf(stderr, "[mm_kernels] reshard: chunk %d is not 16-byte aligned (inner %lld bytes)\n", c,
+              (long long)inner_bytes);
+      return -2;
+    }
+    int64_t vol = 1;
+    for (int k = 0; k < RS_MAX_DIMS; ++k) {
+      d.extent[k] = k == RS_MAX_DIMS - 1 ? inner_bytes / 16 : r[2 + k];
+      d.src_stride[k] = r[6 + k] * elem_size;
+      d.dst_stride[k] = r[10 + k] * elem_size;
+      if (k < RS_MAX_DIMS - 1 && ((d.src_stride[k] & 15) || (d.dst_stride[k] & 15)) && d.extent[k] > 1) return -2;
+      vol *= d.extent[k];
+    }
+    d.vec_begin = total;
+    total += vol;
+  }
+  args.num_chunks = num_chunks;
+  args.total_vecs = total;
+  for (int i = 0; i < num_waits; ++i) args.wait_flag[i] = reinterpret_cast<const int*>(wait_flags[i]);
+  args.num_waits = num_waits;
+  args.wait_value = wait_value;
+  for (int i = 0; i < num_done; ++i) args.done_flag[i] = reinterpret_cast<int*>(done_flags[i]);
+  args.num_done = num_done;
+  args.done_value = done_value;
+  args.cta_counter = reinterpret_cast<unsigned int*>(cta_counter);
+  int64_t want = (total + 256 * 4 - 1) / (256 * 4);
+  int cap = max_ctas > 0 ? max_ctas : ds->sm_count * 8;
+  int grid = static_cast<int>(want < cap ? want : cap);
+  if (grid < 1) grid = 1;
+  reshard_pull_kernel<<<grid, 256, 0, stream>>>(args, ds->status);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+int mm_set_flag(void* flag, int value, cudaStream_t stream) {
+  set_flag_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<int*>(flag), value);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+int mm_wait_flag(const void* flag, int value, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  wait_flag_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<const int*>(flag), value, ds->status);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

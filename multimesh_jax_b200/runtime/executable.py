@@ -166,6 +166,22 @@ class Executable:
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
+        # temporaries whose last reader is task op k (and that no reshard reads later)
+        last_read: Dict[int, int] = {}
+        for k, op in enumerate(plan["ops"]):
+            if op["kind"] == "task":
+                for sid in op["inputs"]:
+                    last_read[sid] = k
+                for sid, m in zip(op["outputs"], op["accumulate"]):
+                    if m:
+                        last_read[sid] = -1          # accumulators are read-modify-written: never hand over
+            elif op["kind"] == "reshard":
+                last_read[op["src_store"]] = -1
+        self._dying_inputs: Dict[int, set] = {}
+        for sid, k in last_read.items():
+            st = plan["stores"][sid]
+            if k >= 0 and st["kind"] == "TEMP" and st["alias_of"] < 0:
+                self._dying_inputs.setdefault(k, set()).add(sid)
         live_executables.add(self)
 
     @staticmethod
@@ -292,6 +308,7 @@ class Executable:
         in_ids, out_ids, modes = op["inputs"], op["outputs"], op["accumulate"]
         dev_start, mesh_dims = op["device_start"], prog.mesh_dims
         fused = prog.fused_acc
+        dying = self._dying_inputs.get(k, ())
         acc_dtypes = [DTYPE_FROM_NAME[self.plan["stores"][s]["shape"]["dtype"]] for s in out_ids]
 
         def body():
@@ -300,7 +317,9 @@ class Executable:
             dctx.key_prefix = (step, k)
             if dctx.torch_device.type == "cuda":
                 torch.cuda.set_device(dctx.torch_device)
-            ins = [tiles[s][d] for s in in_ids]
+            # inputs read for the last time here are handed over: the program frees each one
+            # right after its last use instead of keeping it alive for the whole task
+            ins = [tiles[s].pop(d) if s in dying else tiles[s][d] for s in in_ids]
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
             outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):

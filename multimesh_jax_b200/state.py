@@ -48,8 +48,10 @@ class ScopeEntry:
     explicit_task: Optional[Dict[str, Any]] = None  # payload of an explicit task()
 
 
-class TraceState(threading.local):
-    """State that exists only while a step function is being captured."""
+class TraceState:
+    """State that exists only while a step function is being captured. It is process-wide
+    on purpose: the autograd engine runs the backward pass of CUDA tensors on its own
+    worker threads, and the nodes created there must see the same tables."""
 
     def __init__(self):
         self.active = False
