@@ -641,3 +641,77 @@ int mm_sumsq_f32(const float* x, int64_t n, float* out, cudaStream_t stream) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------ allocation-free variant
+// See no_alloc.h. The scratch for the weight-gradient partial sums lives in the library
+// image; host code must not pass the symbol itself to a kernel (on the host it is only a
+// stand-in), so the device address is looked up once per device and cached.
+#include "no_alloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_scratch[MM_NOALLOC_MAX_PARTS * MM_NOALLOC_MAX_D];
+
+namespace {
+float* g_noalloc_ptr[mm::kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+// Device address of the scratch array on the current device (looked up on first use).
+float* noalloc_scratch_for_current_device(int* rc) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= mm::kMaxDevices) {
+    fprintf(stderr, "[mm_kernels] rmsnorm_bwd_noalloc: cannot identify the current device\n");
+    *rc = -1;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch);
+    if (e != cudaSuccess || !p) {
+      fprintf(stderr, "[mm_kernels] rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n",
+              cudaGetErrorString(e));
+      *rc = static_cast<int>(e ? e : cudaErrorUnknown);
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = p;
+  }
+  *rc = 0;
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+extern "C" int mm_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* dy, const float* rstd,
+                                      void* dx, float* dw_out, int64_t rows, int D, int accumulate_dw,
+                                      int add_to_dx, cudaStream_t stream) {
+  using namespace mm;
+  if (D <= 0 || D % 8 != 0 || D > MM_NOALLOC_MAX_D) {
+    fprintf(stderr,
+            "[mm_kernels] rmsnorm_bwd_noalloc: hidden size %d is not supported (multiple of 8, at most %d); "
+            "use mm_rmsnorm_bwd with a caller-provided scratch buffer\n",
+            D, MM_NOALLOC_MAX_D);
+    return -2;
+  }
+  if (rows < 0) return -2;
+  if (rows == 0) return 0;
+  int rc = 0;
+  float* scratch = noalloc_scratch_for_current_device(&rc);
+  if (!scratch) return rc;
+  const int parts = static_cast<int>(rows < MM_NOALLOC_MAX_PARTS ? rows : MM_NOALLOC_MAX_PARTS);
+#define MM_RN_BWD_NA(TH, VPT)                                                                 \
+  rmsnorm_bwd_kernel<TH, VPT><<<parts, TH, 0, stream>>>(                                      \
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),             \
+      static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<__nv_bfloat16*>(dx), scratch,  \
+      static_cast<int>(rows), D, add_to_dx)
+  if (D <= 1024) MM_RN_BWD_NA(128, 1);
+  else if (D <= 2048) MM_RN_BWD_NA(128, 2);
+  else if (D <= 4096) MM_RN_BWD_NA(128, 4);
+  else MM_RN_BWD_NA(256, 4);
+#undef MM_RN_BWD_NA
+  MM_CUDA_TRY(cudaGetLastError());
+  // every block wrote its full row of partials above, so the reduction reads only fresh data
+  colsum_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(scratch, dw_out, parts, D, accumulate_dw);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
