@@ -132,7 +132,7 @@ def main():
     pp = n // tp
     seq = args.seq
     global_batch = args.per_gpu_batch * n
-    mb = min(args.microbatch * tp, global_batch)
+    mb = min(args.microbatch, global_batch)
     opt = llama.AdamWConfig()
     step_fn = llama.make_train_step(cfg, opt, seq_len=seq, global_batch=global_batch, microbatch_size=mb,
                                     schedule=args.schedule)

@@ -87,6 +87,7 @@ def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optiona
                 if pos in tensor_rank:
                     donated.append(tensor_rank[pos])
         cap.graph.set_donated_inputs(donated)
+        cap.donated_inputs = donated
     nmb = cap.loop_configs[0]["num_microbatches"] if cap.loop_configs else 0
     part = make_partition(num_devices, mesh, nmb)
     cfg = _partition_config(**(config_overrides or {}))

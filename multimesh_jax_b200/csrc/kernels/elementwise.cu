@@ -193,9 +193,12 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, float*
 // `stride_t` elements (lets q and k be slices of one fused QKV buffer).
 // cos/sin tables are fp32 [S, Dh/2]; position of token t is t % S.
 // `sign` = +1 forward, -1 backward (inverse rotation).
+// Heads may be packed in groups of `group_size` of which only the first `rot_per_group`
+// are rotated (query heads and the key head of a grouped-query group; the value head is
+// skipped): logical head h maps to (h / rot_per_group) * group_size + h % rot_per_group.
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cs,
                             const float* __restrict__ sn, int64_t T, int S, int H, int Dh,
-                            int64_t stride_t, float sign) {
+                            int64_t stride_t, float sign, int rot_per_group, int group_size) {
   const int half = Dh / 2;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int per_tok = H * (half / 2);  // each thread handles 2 adjacent pairs (bf162)
@@ -203,8 +206,9 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restr
   if (idx >= total) return;
   const int64_t t = idx / per_tok;
   const int rem = static_cast<int>(idx - t * per_tok);
-  const int h = rem / (half / 2);
+  int h = rem / (half / 2);
   const int i = (rem - h * (half / 2)) * 2;
+  h = (h / rot_per_group) * group_size + h % rot_per_group;
   const int pos = static_cast<int>(t % S);
   __nv_bfloat16* base = qk + t * stride_t + static_cast<int64_t>(h) * Dh;
   __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(base + i);
@@ -534,13 +538,15 @@ int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rs
 }
 
 int mm_rope(void* qk, const float* cos_t, const float* sin_t, int64_t T, int S, int H, int Dh,
-            int64_t stride_t, int backward, cudaStream_t stream) {
+            int64_t stride_t, int backward, int rot_per_group, int group_size, cudaStream_t stream) {
   if (Dh % 4) return -2;
+  if (rot_per_group <= 0 || group_size <= 0) { rot_per_group = 1; group_size = 1; }
   const int64_t total = T * H * (Dh / 4);
   if (total == 0) return 0;
   rope_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(qk), cos_t,
                                                          sin_t, T, S, H, Dh, stride_t,
-                                                         backward ? -1.f : 1.f);
+                                                         backward ? -1.f : 1.f, rot_per_group,
+                                                         group_size);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

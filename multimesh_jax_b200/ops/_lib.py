@@ -22,7 +22,7 @@ _SIGS = {
     "mm_rmsnorm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, _P]),
     "mm_rmsnorm_bwd_parts": (c_int, [c_int64]),
     "mm_rmsnorm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
-    "mm_rope": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int64, c_int, _P]),
+    "mm_rope": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_int, _P]),
     "mm_swiglu_fwd": (c_int, [_P, _P, c_int64, c_int, _P]),
     "mm_swiglu_bwd": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
     "mm_cross_entropy": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int64, c_int, c_float,

@@ -30,7 +30,14 @@ def have_native_kernels() -> bool:
     return hasattr(lib, "mm_flash_attn_fwd") and hasattr(lib, "mm_flash_attn_bwd")
 
 
+def _merge_q(q):
+    """[B,S,hkv,rep,D] -> [B,S,hq,D] (a view for rep == 1, otherwise a copy)."""
+    B, S, Hkv, rep, D = q.shape
+    return q.squeeze(3) if rep == 1 else q.reshape(B, S, Hkv * rep, D)
+
+
 def _ref_fwd(q, k, v):
+    q = _merge_q(q)
     B, S, Hq, D = q.shape
     rep = Hq // k.shape[2]
     qf = q.float().permute(0, 2, 1, 3)
@@ -46,10 +53,12 @@ def _ref_fwd(q, k, v):
 
 
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns (out [B,S,Hq,D] contiguous, lse [B,Hq,S] fp32)."""
+    """q [B,S,hkv,rep,D], k/v [B,S,hkv,D] (strided views). Returns (out [B,S,hq,D]
+    contiguous with hq = hkv*rep in group-major order, lse [B,hq,S] fp32)."""
     if not q.is_cuda:
         o, lse, _ = _ref_fwd(q, k, v)
         return o, lse
+    q = _merge_q(q)
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     rep = Hq // Hkv
@@ -64,10 +73,10 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> Tuple[to
 
 
 def attention_bwd(dout, q, k, v, out, lse, dq, dk, dv) -> None:
-    """Writes the gradients into the (strided) views ``dq``, ``dk``, ``dv``."""
-    B, S, Hq, D = q.shape
-    Hkv = k.shape[2]
-    rep = Hq // Hkv
+    """Writes the gradients into the (strided) views ``dq`` [B,S,hkv,rep,D], ``dk``, ``dv``."""
+    B, S, Hkv, rep, D = q.shape
+    Hq = Hkv * rep
+    dq5 = dq
     if not q.is_cuda:
         _, _, (qf, kf, vf, p) = _ref_fwd(q, k, v)
         dof = dout.float().permute(0, 2, 1, 3)
@@ -77,11 +86,11 @@ def attention_bwd(dout, q, k, v, out, lse, dq, dk, dv) -> None:
         ds = p * (dp - delta) / math.sqrt(D)
         dqf = ds @ kf
         dkf = ds.transpose(-1, -2) @ qf
-        dq.copy_(dqf.permute(0, 2, 1, 3).to(dq.dtype))
+        dq5.copy_(dqf.permute(0, 2, 1, 3).reshape(B, S, Hkv, rep, D).to(dq.dtype))
         dk.copy_(dkf.view(B, Hkv, rep, S, D).sum(2).permute(0, 2, 1, 3).to(dk.dtype))
         dv.copy_(dvf.view(B, Hkv, rep, S, D).sum(2).permute(0, 2, 1, 3).to(dv.dtype))
         return
-    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    qt, kt, vt = _merge_q(q).transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     if rep > 1:
         kt = kt.repeat_interleave(rep, dim=1)
         vt = vt.repeat_interleave(rep, dim=1)
@@ -90,7 +99,7 @@ def attention_bwd(dout, q, k, v, out, lse, dq, dk, dv) -> None:
     zero = torch.zeros((), dtype=torch.int64, device=q.device)
     gq, gk, gv = _aten._scaled_dot_product_flash_attention_backward(
         dot, qt, kt, vt, ot, lse, None, None, S, S, 0.0, True, zero, zero, scale=1.0 / math.sqrt(D))
-    dq.copy_(gq.transpose(1, 2))
+    dq5.copy_(gq.transpose(1, 2).reshape(B, S, Hkv, rep, D))
     if rep > 1:
         gk = gk.view(B, Hkv, rep, S, D).sum(2)
         gv = gv.view(B, Hkv, rep, S, D).sum(2)

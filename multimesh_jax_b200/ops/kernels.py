@@ -179,23 +179,30 @@ def rope_tables(seq_len: int, head_dim: int, theta: float, device) -> Tuple[torc
     return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
 
 
-def rope_(qk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, backward: bool = False) -> torch.Tensor:
-    """In-place rotate-half RoPE on ``qk`` of shape [T, H, Dh] (token stride may
-    exceed H*Dh, e.g. a slice of a fused QKV buffer). Position = t % S."""
+def rope_(qk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, backward: bool = False,
+          rot_per_group: int = 1, group_size: int = 1) -> torch.Tensor:
+    """In-place rotate-half RoPE on ``qk`` of shape [T, H, Dh] (token stride may exceed
+    H*Dh, e.g. a slice of a fused QKV buffer). Position = t % S. With ``group_size`` > 1
+    the H heads are packed in groups and only the first ``rot_per_group`` heads of every
+    group are rotated (H counts all heads, rotated or not)."""
     T, H, Dh = qk.shape
     S = cos.shape[0]
     assert qk.stride(2) == 1 and qk.stride(1) == Dh
+    assert H % group_size == 0
+    n_rot = H // group_size * rot_per_group
     if not qk.is_cuda:
         pos = torch.arange(T) % S
         c = cos[pos].unsqueeze(1)
         s = sin[pos].unsqueeze(1) * (-1.0 if backward else 1.0)
-        a, b = qk[..., : Dh // 2].float(), qk[..., Dh // 2:].float()
+        view = qk.view(T, H // group_size, group_size, Dh)[:, :, :rot_per_group]
+        a, b = view[..., : Dh // 2].float(), view[..., Dh // 2:].float()
+        c, s = c.unsqueeze(1), s.unsqueeze(1)
         lo, hi = a * c - b * s, b * c + a * s
-        qk[..., : Dh // 2] = lo.to(qk.dtype)
-        qk[..., Dh // 2:] = hi.to(qk.dtype)
+        view[..., : Dh // 2] = lo.to(qk.dtype)
+        view[..., Dh // 2:] = hi.to(qk.dtype)
         return qk
-    rc = _lib.load().mm_rope(qk.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, S, H, Dh, qk.stride(0),
-                             int(backward), _stream())
+    rc = _lib.load().mm_rope(qk.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, S, n_rot, Dh, qk.stride(0),
+                             int(backward), rot_per_group, group_size, _stream())
     _lib.check(rc, "mm_rope")
     _count()
     return qk

@@ -215,22 +215,26 @@ _define("swiglu_bwd(Tensor gu, Tensor dh) -> Tensor", swiglu_bwd_impl, lambda gu
 
 # --------------------------------------------------------------------- attention
 def _split_qkv(qkv, rep: int):
-    hkv = qkv.shape[2] // (rep + 2)
-    hq = rep * hkv
-    return qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:], hq, hkv
+    """Views of a packed projection [B, S, hkv*(rep+2), D] whose heads are grouped per
+    key/value head: ``rep`` query heads, then the key head, then the value head. A split of
+    the packed dimension into equal contiguous parts therefore keeps whole groups together,
+    which is what makes the layout tensor-parallel friendly. Returns q [B,S,hkv,rep,D] and
+    k, v [B,S,hkv,D] (all strided views)."""
+    B, S, H, D = qkv.shape
+    g = qkv.view(B, S, H // (rep + 2), rep + 2, D)
+    return g[:, :, :, :rep], g[:, :, :, rep], g[:, :, :, rep + 1]
 
 
 def attention_impl(qkv, cos, sin, rep: int, inplace: bool = False):
-    """Causal self-attention over a packed [B, S, hq + 2*hkv, D] projection (hq = rep*hkv)
+    """Causal self-attention over a packed, group-major [B, S, hkv*(rep+2), D] projection
     with rotary embedding applied to the query and key heads first. Returns (out
-    [B,S,hq,D], lse [B,hq,S], the rotated qkv saved for the backward pass). The head
-    counts are derived from the tensor, so a head-sharded (tensor-parallel) slice works
-    unchanged."""
+    [B,S,hq,D], lse [B,hq,S], the rotated qkv saved for the backward pass). Head counts are
+    derived from the tensor, so a head-sharded (tensor-parallel) slice works unchanged."""
     from .attention import attention_fwd
     B, S, H, D = qkv.shape
     qkv_r = qkv if inplace else qkv.clone()
-    q, k, v, hq, hkv = _split_qkv(qkv_r, rep)
-    K.rope_(qkv_r.view(B * S, H, D)[:, :hq + hkv], cos, sin)
+    K.rope_(qkv_r.view(B * S, H, D), cos, sin, rot_per_group=rep + 1, group_size=rep + 2)
+    q, k, v = _split_qkv(qkv_r, rep)
     out, lse = attention_fwd(q, k, v)
     return out, lse, qkv_r
 
@@ -238,11 +242,11 @@ def attention_impl(qkv, cos, sin, rep: int, inplace: bool = False):
 def attention_bwd_impl(dout, qkv_r, out, lse, cos, sin, rep: int):
     from .attention import attention_bwd
     B, S, H, D = qkv_r.shape
-    q, k, v, hq, hkv = _split_qkv(qkv_r, rep)
+    q, k, v = _split_qkv(qkv_r, rep)
     dqkv = torch.empty_like(qkv_r)
-    dq, dk, dv, _, _ = _split_qkv(dqkv, rep)
+    dq, dk, dv = _split_qkv(dqkv, rep)
     attention_bwd(dout, q, k, v, out, lse, dq, dk, dv)
-    K.rope_(dqkv.view(B * S, H, D)[:, :hq + hkv], cos, sin, backward=True)
+    K.rope_(dqkv.view(B * S, H, D), cos, sin, backward=True, rot_per_group=rep + 1, group_size=rep + 2)
     return dqkv
 
 

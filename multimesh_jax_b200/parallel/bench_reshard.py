@@ -124,10 +124,11 @@ def main():
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                     results[name] = float(t.item())
                 ok = True
-                if args.check and is_dst and mine:
-                    # compare the pulled tile with the NCCL result
+                if args.check:
+                    # compare the pulled tile with the NCCL result (every rank takes part in the exchange)
                     ref = run_nccl()
-                    ok = bool(torch.equal(ref, dst_t.local))
+                    if is_dst and mine:
+                        ok = bool(torch.equal(ref, dst_t.local))
                 okt = torch.tensor([1 if ok else 0], device=dev)
                 dist.all_reduce(okt, op=dist.ReduceOp.MIN)
                 # roofline: busiest link direction

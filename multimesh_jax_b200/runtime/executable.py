@@ -108,17 +108,25 @@ class ShardedTensor:
         return f"ShardedTensor({self.sharding['key']})"
 
 
-def shard_tensor(t: torch.Tensor, sharding: dict, topology: Topology) -> ShardedTensor:
-    """Slices a global tensor into the tiles of ``sharding`` (local devices only)."""
+def shard_tensor(t: torch.Tensor, sharding: dict, topology: Topology, private: bool = False) -> ShardedTensor:
+    """Slices a global tensor into the tiles of ``sharding`` (local devices only). Tiles are
+    contiguous; with ``private`` they never share storage with ``t`` (needed for arguments
+    that were not donated, because compiled tasks may update dead inputs in place)."""
     tiles: Dict[int, torch.Tensor] = {}
     start = sharding["device_start"]
+    seen_shared = False
     for o in range(sharding["num_devices"]):
         d = start + o
         if not topology.is_local(d):
             continue
         lo, hi = tile_box(sharding, o)
         piece = t[tuple(slice(a, b) for a, b in zip(lo, hi))]
-        tiles[d] = piece.to(topology.torch_device(d))
+        tile = piece.to(topology.torch_device(d)).contiguous()
+        shares = tile.untyped_storage().data_ptr() == t.untyped_storage().data_ptr()
+        if shares and (private or seen_shared):
+            tile = tile.clone()   # virtual devices of one process must not share a buffer either
+        seen_shared = seen_shared or shares
+        tiles[d] = tile
     return ShardedTensor(sharding, tiles, topology)
 
 
@@ -166,6 +174,7 @@ class Executable:
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
+        self.donated = set(getattr(cap, "donated_inputs", ()))
         # temporaries whose last reader is task op k (and that no reshard reads later)
         last_read: Dict[int, int] = {}
         for k, op in enumerate(plan["ops"]):
@@ -256,7 +265,7 @@ class Executable:
                     a = shard_tensor(a.full_tensor(), want, topo)
                 new_tiles = a.local_tiles()
             else:
-                new_tiles = shard_tensor(a, want, topo).local_tiles()
+                new_tiles = shard_tensor(a, want, topo, private=i not in self.donated).local_tiles()
             self.tiles[sid].clear()
             self.tiles[sid].update(new_tiles)
         root_tiles: Dict[int, Dict[int, torch.Tensor]] = {sid: {} for sid in plan["root_stores"]}
