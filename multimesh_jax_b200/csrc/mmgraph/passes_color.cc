@@ -451,6 +451,35 @@ bool LogicalShardingPropagation(CompileState& s) {
           if (in.has_axes && !out.has_axes) { SetAxes(out, in.axes, in.axes_logical); progress = true; }
           if (out.has_axes && !in.has_axes) { SetAxes(in, out.axes, out.axes_logical); progress = true; }
         }
+      } else if (n.attrs.count("shard_rule")) {
+        // Operators that describe their index structure: a result dimension inherits the
+        // names of the operand dimensions that carry the same index (right operand first,
+        // as in the dot rule below); a name is never used twice in one tensor.
+        const Json rule = Json::parse(n.attrs.at("shard_rule"));
+        const int nin = static_cast<int>(n.inputs.size());
+        for (size_t o = 0; o < n.outputs.size(); ++o) {
+          Value& ov = g.value(n.outputs[o]);
+          if (ov.has_axes) continue;
+          std::vector<std::vector<std::string>> axes(ov.shape.size());
+          std::set<std::string> used;
+          bool any = false, logical = true;
+          for (auto& c : rule.at("classes").arr) {
+            int out_dim = -1;
+            for (auto& m : c.at("members").arr)
+              if (m.arr[0].as_int() == nin + static_cast<int>(o)) out_dim = static_cast<int>(m.arr[1].as_int());
+            if (out_dim < 0 || out_dim >= static_cast<int>(axes.size())) continue;
+            for (int pass = nin - 1; pass >= 0; --pass)
+              for (auto& m : c.at("members").arr) {
+                if (m.arr[0].as_int() != pass) continue;
+                const Value& iv = g.value(n.inputs[pass]);
+                const int d = static_cast<int>(m.arr[1].as_int());
+                if (!iv.has_axes || d >= static_cast<int>(iv.axes.size())) continue;
+                for (auto& a : iv.axes[d]) if (used.insert(a).second) { axes[out_dim].push_back(a); any = true; }
+                logical = iv.axes_logical;
+              }
+          }
+          if (any) { SetAxes(ov, axes, logical); progress = true; }
+        }
       } else if (IsDot(n) && n.inputs.size() >= 2 && !out.has_axes) {
         // Dot rule: result names come from the right operand's free dims first, then the
         // left operand's; a name is never used twice
