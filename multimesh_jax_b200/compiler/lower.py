@@ -133,6 +133,11 @@ class TemplateProgram:
             elif kind == 5:  # local reshard
                 src, dst = ins.extra
                 env[ins.outs[0]] = ctx.spmd_reshard(env[ins.args], src, dst, ins.node_id)
+            elif kind == 7:  # linear whose partial result is all-reduced: one fused kernel
+                axes, scale, is_dgrad = ins.extra
+                x, w = _materialize(ins.args, env, ctx)
+                y = ctx.linear_all_reduce(x, w, axes, is_dgrad, ins.node_id)
+                env[ins.outs[0]] = y if scale == 1.0 else y * scale
             # free values whose last use was this instruction (keeps peak memory low)
             dead = self._last_use.get(idx)
             if dead:
@@ -236,6 +241,32 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             instrs.append(Instr(5, None, n["inputs"][0], None, n["outputs"], None, nid, (src, dst)))
         else:
             raise NotImplementedError(f"no lowering for compiler-generated op {op}")
+    # fuse "linear -> all-reduce of its partial result" into one GEMM+collective kernel
+    if not single_device:
+        readers: Dict[int, List[Instr]] = {}
+        for ins in instrs:
+            for v in _reads(ins):
+                readers.setdefault(v, []).append(ins)
+        outputs_set = set(template["outputs"])
+        removed = set()
+        for ins in instrs:
+            if ins.kind != 0 or ins.slots is not None or not ins.outs:
+                continue
+            opname = g.node(ins.node_id)["op"]
+            if opname not in ("mm_ops.linear.default", "mm_ops.linear_dgrad.default"):
+                continue
+            v = ins.outs[0]
+            rd = readers.get(v, [])
+            if len(rd) != 1 or rd[0].kind != 4 or v in outputs_set:
+                continue
+            ar = rd[0]
+            axes, scale = ar.extra
+            ins.kind = 7
+            ins.extra = (axes, scale, opname == "mm_ops.linear_dgrad.default")
+            ins.outs = ar.outs
+            removed.add(id(ar))
+        if removed:
+            instrs = [i for i in instrs if id(i) not in removed]
     # fuse "operator -> accumulate -> task output" into the operator's own epilogue
     fused_acc: Dict[int, bool] = {}
     if acc_fusable:
@@ -318,6 +349,6 @@ def _fix_sizes(arg, gshape, lshape):
 
 
 def _reads(ins: Instr) -> List[int]:
-    if ins.kind in (0, 6):
+    if ins.kind in (0, 6, 7):
         return _tensor_ids_in_order(ins.args, ins.kwargs)
     return [ins.args]

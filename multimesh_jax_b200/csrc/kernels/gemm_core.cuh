@@ -122,11 +122,22 @@ struct PlainHook {
   __device__ __forceinline__ bool before_tile_loads(int, int, int*) const { return true; }
   // Row of A (in the tensor map's coordinates) where tile row-block m_blk starts.
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
-  __device__ __forceinline__ void store(int row, int col0, int N, const uint32_t (&r)[32]) const {
-    gemm_store_chunk<OUT>(C, ldc, row, col0, N, r, vec_ok);
+  // Drains one 128x256 accumulator: warp `q` owns TMEM lanes [32q, 32q+32), i.e. rows
+  // m_blk*128 + 32q + lane. `t_base` already points at that lane quarter.
+  __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
+                                           int* err) const {
+    (void)err;
+    const int row = m_blk * GEMM_BM + q * 32 + lane;
+#pragma unroll 1
+    for (int c = 0; c < GEMM_BN / 32; ++c) {
+      const int col0 = n_blk * GEMM_BN + c * 32;
+      if (col0 >= N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(t_base + c * 32, r);
+      tmem_ld_wait();
+      if (row < M) gemm_store_chunk<OUT>(C, ldc, row, col0, N, r, vec_ok);
+    }
   }
-  // Called by one lane per epilogue warp after the warp's rows of a tile are stored.
-  __device__ __forceinline__ void after_tile_store(int, int, int) const {}
 };
 
 template <bool A_MN, bool B_MN, class Hook>
@@ -257,23 +268,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       gemm_tile_coords(tile, num_m, num_n, m_blk, n_blk);
       if (!mbar_wait(&tfull[acc], acc_phase, err, MM_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
-      const int row = m_blk * GEMM_BM + q * 32 + lane;
       const uint32_t t_base = tmem_base + acc * GEMM_BN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < GEMM_BN / 32; ++c) {
-        const int col0 = n_blk * GEMM_BN + c * 32;
-        if (col0 >= N) break;
-        uint32_t r[32];
-        tmem_ld_32x32(t_base + c * 32, r);
-        tmem_ld_wait();
-        if (row < M) hook.store(row, col0, N, r);
-      }
+      hook.epilogue(t_base, m_blk, n_blk, q, lane, M, N, err);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) {
-        hook.after_tile_store(m_blk, n_blk, q);
-        mbar_arrive(&tempty[acc]);
-      }
+      if (lane == 0) mbar_arrive(&tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }

@@ -95,6 +95,21 @@ class Rendezvous:
             return out
 
 
+class FusedTP:
+    """Lazily created fused GEMM+all-reduce operators, one per tensor-parallel rank group,
+    all carved out of one symmetric arena that is created collectively up front."""
+
+    def __init__(self, arena):
+        self.arena = arena
+        self._ops: Dict[Tuple[int, ...], object] = {}
+
+    def get(self, ranks: Tuple[int, ...]):
+        from ..parallel.tp import FusedLinearAllReduce
+        if ranks not in self._ops:
+            self._ops[ranks] = FusedLinearAllReduce(self.arena, ranks)
+        return self._ops[ranks]
+
+
 def mesh_group(ordinal: int, mesh_dims: Sequence[int], axes: Sequence[int]) -> List[int]:
     """Ordinals (within the task's device list) that differ from ``ordinal``
     only in the coordinates of ``axes``; row-major mesh."""
@@ -126,6 +141,7 @@ class DeviceCtx:
         self.device = device
         self.torch_device = topology.torch_device(device)
         self.rendezvous = rendezvous
+        self.fused_tp = None  # FusedTP registry (one-process-per-GPU CUDA jobs only)
         # set per task launch
         self.device_start = 0
         self.mesh_dims: Sequence[int] = (1,)
@@ -160,6 +176,36 @@ class DeviceCtx:
         for p in parts[1:]:
             acc = acc + (p.float() if acc.dtype != p.dtype else p)
         return acc.to(x.dtype)
+
+    def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, axes: Sequence[int], is_dgrad: bool, key
+                          ) -> torch.Tensor:
+        """``all_reduce(linear(x, w))`` (or of the input gradient ``dy @ w``) over the mesh
+        axes ``axes``. One-process-per-GPU jobs run the fused tcgen05 GEMM + NVLink
+        all-reduce kernel; everything else computes the partial result and reduces it."""
+        from ..ops import mm_ops
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        fused = self.fused_tp
+        if fused is not None and len(group) > 1 and x.is_cuda and x.dtype == torch.bfloat16:
+            ranks = tuple(self.device_start + o for o in group)
+            op = fused.get(ranks)
+            if is_dgrad:
+                n_lead = w.dim() - 1
+                w2 = w.reshape(-1, w.shape[-1])
+                a2 = x.reshape(-1, w2.shape[0])
+                M, N, Kd = a2.shape[0], w2.shape[1], w2.shape[0]
+                if op.supported(M, N, Kd, x.dtype):
+                    y = op(a2, w2, b_mn=True)
+                    return y.view(*x.shape[:x.dim() - n_lead], N)
+            else:
+                w2 = w.reshape(-1, w.shape[-1])
+                a2 = x.reshape(-1, x.shape[-1])
+                M, N, Kd = a2.shape[0], w2.shape[0], a2.shape[1]
+                if op.supported(M, N, Kd, x.dtype):
+                    y = op(a2, w2)
+                    return y.view(*x.shape[:-1], *w.shape[:-1])
+        y = mm_ops.linear_dgrad_impl(x, w) if is_dgrad else mm_ops.linear_impl(x, w)
+        return self.all_reduce(y, axes, key)
 
     def spmd_reshard(self, x: torch.Tensor, src: dict, dst: dict, key) -> torch.Tensor:
         """Local tile of layout ``dst`` from tiles in layout ``src`` (same

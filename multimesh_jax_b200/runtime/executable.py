@@ -155,6 +155,7 @@ class Executable:
         self.context = context
         self.rendezvous = Rendezvous()
         self.dev_ctx = {d: DeviceCtx(topology, d, self.rendezvous) for d in topology.local_devices}
+        self._setup_fused_tp()
         # physical buffers: stores sharing a scheduling name and layout share one id
         self.buffer_of: Dict[int, int] = {}
         names: Dict[str, int] = {}
@@ -192,6 +193,29 @@ class Executable:
             if k >= 0 and st["kind"] == "TEMP" and st["alias_of"] < 0:
                 self._dying_inputs.setdefault(k, set()).add(sid)
         live_executables.add(self)
+
+    def _setup_fused_tp(self) -> None:
+        """One-process-per-GPU CUDA jobs whose plan contains all-reduces of partial GEMM
+        results get a peer-mapped arena for the fused GEMM+all-reduce kernel. The arena is
+        created here, collectively, so that no rank meets the handle exchange in the middle
+        of a step. Disabled with MM_FUSED_TP=0 (then NCCL reduces the partial results)."""
+        import os
+        topo = self.topology
+        if topo.kind != "dist" or topo.torch_device(topo.rank).type != "cuda":
+            return
+        if os.environ.get("MM_FUSED_TP", "1") == "0":
+            return
+        g = self.cap.graph
+        wanted = any(g.node(n)["op"] == "mm.all_reduce" for t in self.plan["templates"] for n in t["nodes"])
+        if not wanted:
+            return
+        from ..parallel import symm
+        from .collectives import FusedTP
+        mb = int(os.environ.get("MM_SYMM_ARENA_MB", "1024"))
+        arena = symm.SymmetricArena(mb << 20, topo.torch_device(topo.rank))
+        self._fused_tp = FusedTP(arena)
+        for ctx in self.dev_ctx.values():
+            ctx.fused_tp = self._fused_tp
 
     @staticmethod
     def _template_devices(t: dict) -> range:

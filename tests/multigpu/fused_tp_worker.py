@@ -1,0 +1,51 @@
+"""Worker of the multi-GPU fused tensor-parallel test (one process per GPU, launched by torchrun)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl")
+    from multimesh_jax_b200.ops import kernels as K
+    from multimesh_jax_b200.parallel import symm
+    from multimesh_jax_b200.parallel.tp import FusedLinearAllReduce
+
+    arena = symm.SymmetricArena(512 << 20, dev)
+    op = FusedLinearAllReduce(arena, list(range(world)))
+    ok = True
+    for it, (M, N, Kd, b_mn) in enumerate([(1024, 4096, 1024, False), (1024, 4096, 1024, False), (8192, 4096, 2048, False),
+                                           (1024, 4096, 1024, True), (384, 512, 320, False), (8192, 4096, 2048, True),
+                                           (8192, 4096, 2048, False)]):
+        torch.manual_seed(100 * it + rank)
+        a = torch.randn(M, Kd, device=dev).bfloat16()
+        b = (torch.randn(Kd, N, device=dev) if b_mn else torch.randn(N, Kd, device=dev)).bfloat16()
+        out = op(a, b, b_mn=b_mn)
+        ref = a.float() @ (b.float() if b_mn else b.float().t())
+        dist.all_reduce(ref)
+        torch.cuda.synchronize()
+        err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+        if err > 2e-2:
+            ok = False
+            print(f"rank {rank}: case {it} relative error {err}", flush=True)
+    status = K.read_status()
+    if status != 0:
+        ok = False
+        print(f"rank {rank}: kernel status {status}", flush=True)
+    t = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print("FUSED_TP_OK" if t.item() == 1 else "FUSED_TP_FAILED", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
