@@ -236,6 +236,7 @@ def main():
             "gpu_launches": launches, "library_kernel_calls": lib_calls,
             "tflops_per_gpu": round(flops / (ms / args.steps / 1e3) / n / 1e12, 1),
             "loss": round(loss_val, 4), "compile_s": round(compile_s, 1), "kernel_status": status,
+            "fused_gemm_allreduce_calls": sum(o.calls for o in getattr(getattr(exe, "_fused_tp", None), "_ops", {}).values()),
             "impl": "ours",
         }
         print(json.dumps(out), flush=True)

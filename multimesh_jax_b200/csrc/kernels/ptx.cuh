@@ -73,6 +73,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
   for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 128) __nanosleep(64);
+    // once any wait of the kernel has expired, the others give up at once
+    if ((i & 1023) == 1023 && err && *reinterpret_cast<volatile int*>(err) != 0) return false;
   }
   if (err) atomicCAS(err, 0, code);
   return false;
@@ -217,6 +219,7 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* err)
   for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
     if (ld_acquire_sys(p) >= target) return true;
     if (i > 32) __nanosleep(100);
+    if ((i & 1023) == 1023 && err && *reinterpret_cast<volatile int*>(err) != 0) return false;
   }
   if (err) atomicCAS(err, 0, MM_ERR_WAIT_PEER);
   return false;

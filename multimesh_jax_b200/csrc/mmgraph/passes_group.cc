@@ -521,17 +521,19 @@ bool SplitCriticalPath(CompileState& s) {
 bool UnusedParamOutputRemover(CompileState& s) {
   Graph& g = *s.graph;
   const int removed = g.DeadCodeElimination();
-  if (removed) {
-    for (auto& grp : s.groups) {
-      std::vector<int> keep;
-      for (int id : grp.nodes) if (!g.node(id).dead) keep.push_back(id);
-      grp.nodes = keep;
-    }
-    std::vector<TaskGroup> keep_groups;
-    for (auto& grp : s.groups) if (!grp.nodes.empty()) keep_groups.push_back(grp);
-    s.groups = keep_groups;
+  // drop dead nodes (from this or earlier passes) from the task groups, and empty groups
+  bool pruned = false;
+  for (auto& grp : s.groups) {
+    std::vector<int> keep;
+    for (int id : grp.nodes) if (!g.node(id).dead) keep.push_back(id);
+    pruned = pruned || keep.size() != grp.nodes.size();
+    grp.nodes = keep;
   }
-  return removed > 0;
+  std::vector<TaskGroup> keep_groups;
+  for (auto& grp : s.groups) if (!grp.nodes.empty()) keep_groups.push_back(grp);
+  pruned = pruned || keep_groups.size() != s.groups.size();
+  s.groups = keep_groups;
+  return removed > 0 || pruned;
 }
 
 }  // namespace mmg

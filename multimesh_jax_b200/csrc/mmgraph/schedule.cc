@@ -53,7 +53,8 @@ ScheduleResult ScheduleWavefront(const LoopConfig& cfg, const std::vector<std::v
   std::vector<SchedTask> row;
   for (int s : stages) row.push_back(tasks[0][s]);
   const int minibatch_size = NumGroups(row);
-  const int delay = cfg.num_stages > 0 ? cfg.num_stages : std::max(1, (pipeline_tasks + 1) / 2);
+  // a minibatch needs at least one tick per member, whatever the caller asked for
+  const int delay = std::max(minibatch_size, cfg.num_stages > 0 ? cfg.num_stages : std::max(1, (pipeline_tasks + 1) / 2));
   const int num_minibatches = (num_iters + minibatch_size - 1) / minibatch_size;
   const int last_wf = pipeline_tasks + num_minibatches * delay;
   for (int wf = 0; wf < last_wf; ++wf) {
