@@ -69,6 +69,29 @@ class Topology:
                 self._groups[key] = dist.new_group(list(key))
         return self._groups[key]
 
+    def prepare_groups(self, meshes: Sequence[Tuple[int, Sequence[int]]]) -> None:
+        """Create, on every rank and in one global order, the process groups that tasks on the
+        meshes ``(device_start, mesh_dims)`` can ask for: one per non-empty subset of mesh axes
+        and per position along the other axes. ``torch.distributed.new_group`` is collective
+        over the whole job, so groups cannot be made lazily by the ranks that happen to need
+        them (two pipeline stages would each make "their" tensor-parallel group first)."""
+        if self.kind != "dist":
+            return
+        import itertools
+        wanted = set()
+        for start, dims in meshes:
+            n = 1
+            for s in dims:
+                n *= s
+            axes_all = [a for a, s in enumerate(dims) if s > 1]
+            for r in range(1, len(axes_all) + 1):
+                for axes in itertools.combinations(axes_all, r):
+                    for o in range(n):
+                        wanted.add(tuple(start + g for g in mesh_group(o, dims, list(axes))))
+        for key in sorted(wanted):
+            if len(key) > 1:
+                self.process_group(key)
+
 
 class Rendezvous:
     """Exchange of one object per participant between threads of a process."""

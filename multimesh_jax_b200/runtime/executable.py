@@ -155,6 +155,7 @@ class Executable:
         self.context = context
         self.rendezvous = Rendezvous()
         self.dev_ctx = {d: DeviceCtx(topology, d, self.rendezvous) for d in topology.local_devices}
+        topology.prepare_groups(sorted({(t["device_start"], tuple(t["mesh_dims"])) for t in plan["templates"]}))
         self._setup_fused_tp()
         # physical buffers: stores sharing a scheduling name and layout share one id
         self.buffer_of: Dict[int, int] = {}

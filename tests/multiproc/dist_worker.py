@@ -1,0 +1,95 @@
+"""Worker of the multi-process tests (gloo ranks on CPU, one process per virtual device).
+
+Modes:
+  step   - pipeline x tensor parallel training step through the "dist" topology; every rank
+           checks its tiles of the loss and of the updated parameters against the eager step.
+  leave  - the last rank exits cleanly between steps; the others see their next collective
+           end with an error within the process-group timeout and report it as a status.
+"""
+import datetime
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+
+def build(pp, tp):
+    import multimesh_jax_b200 as mm
+    from multimesh_jax_b200.models import llama
+    torch.manual_seed(0)
+    cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128)
+    cfg.dtype = torch.float32
+    B, S, MB = 8, 16, 4
+    params = llama.init_params(cfg)
+    state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB)
+    mesh = mm.MultiMesh((pp, tp), ("stage", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+    args = (params, state, tokens, labels, cos, sin)
+    with mesh:
+        exe = mm.compile_function(step, args, mesh=mesh, backend="dist")
+    return mm, exe, step, args
+
+
+def mode_step(pp, tp):
+    from torch.utils import _pytree as pytree
+    rank = dist.get_rank()
+    mm, exe, step, args = build(pp, tp)
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(*args)
+    loss, p_mm, _ = exe(*args)
+    checked = 0
+    for got, want in [(loss, loss_ref)] + list(zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref))):
+        got.wait()
+        for d, tile in got.local_tiles().items():
+            from multimesh_jax_b200.runtime.collectives import tile_box
+            lo, hi = tile_box(got.sharding, d - got.sharding["device_start"])
+            ref = want[tuple(slice(a, b) for a, b in zip(lo, hi))] if want.dim() else want
+            torch.testing.assert_close(tile, ref, rtol=1e-3, atol=2e-4)
+            checked += 1
+    ok = torch.tensor([1 if checked > 0 else 0])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"DIST_STEP_OK": bool(ok.item()), "tiles_checked_rank0": checked}), flush=True)
+    exe.shutdown()
+
+
+def mode_leave(pp, tp):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mm, exe, step, args = build(pp, tp)
+    loss, params, state = exe(*args)
+    loss.wait()
+    dist.barrier()
+    if rank == world - 1:
+        # leaves between steps, with nothing in flight
+        exe.shutdown()
+        print(json.dumps({"rank": rank, "left": True}), flush=True)
+        os._exit(0)
+    t0 = time.time()
+    try:
+        loss, params, state = exe(*args)
+        for leaf in [loss]:
+            leaf.wait()
+        # ranks that never talk to the lost rank may finish the step; they learn at the barrier
+        dist.barrier()
+        outcome = "no error"
+    except (mm.StepFailed, RuntimeError) as e:
+        outcome = "error: " + type(e).__name__
+    print(json.dumps({"rank": rank, "outcome": outcome, "seconds": round(time.time() - t0, 1)}), flush=True)
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    mode, pp, tp = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    timeout = datetime.timedelta(seconds=8 if mode == "leave" else 120)
+    dist.init_process_group("gloo", timeout=timeout)
+    {"step": mode_step, "leave": mode_leave}[mode](pp, tp)
+    dist.destroy_process_group()

@@ -1,0 +1,229 @@
+"""Task-graph runtime: dependence analysis on stores, strict-order chains, priorities, the
+in-flight window, deferred callbacks and timers, host-side fault injection with status-code
+propagation, the hazard checker, and the mock context (operation hash, memory high-water marks,
+protocol invariants) driving whole plans on many virtual devices."""
+import json
+import threading
+import time
+
+import pytest
+import torch
+
+import multimesh_jax_b200 as mm
+from multimesh_jax_b200 import _mm_C as C
+
+
+def test_raw_war_waw_ordering_across_devices():
+    ctx = C.ThreadedContext([0, 1], False, True)
+    log = []
+    lock = threading.Lock()
+
+    def rec(name, delay=0.0):
+        def body():
+            time.sleep(delay)
+            with lock:
+                log.append(name)
+        return body
+
+    A, B = 0, 1
+    ctx.create_execute_task(0, [], [(A, 0)], rec("w0", 0.05), "w0")
+    ctx.create_execute_task(1, [(A, 0)], [(B, 1)], rec("r1"), "r1")            # RAW across devices
+    ctx.create_execute_task(0, [], [(A, 0)], rec("w0b"), "w0b")                # WAR on A (after r1), WAW
+    ctx.create_execute_task(1, [(B, 1)], [], rec("r1b"), "r1b")
+    assert int(ctx.wait_all()[0]) == 0
+    assert log.index("w0") < log.index("r1") < log.index("w0b")
+    assert log.index("r1") < log.index("r1b")
+    assert ctx.hazard_report() == ""
+    ctx.shutdown()
+
+
+def test_independent_tasks_run_concurrently_on_different_devices():
+    ctx = C.ThreadedContext([0, 1])
+    t0 = time.time()
+    ctx.create_execute_task(0, [], [(0, 0)], lambda: time.sleep(0.2), "a")
+    ctx.create_execute_task(1, [], [(1, 1)], lambda: time.sleep(0.2), "b")
+    ctx.wait_all()
+    assert time.time() - t0 < 0.35
+    ctx.shutdown()
+
+
+def test_priority_and_strict_ordering():
+    ctx = C.ThreadedContext([0])
+    order = []
+    gate = threading.Event()
+    ctx.create_execute_task(0, [], [(9, 0)], gate.wait, "gate")
+    # all three become ready behind the gate; the high priority one runs first
+    ctx.create_execute_task(0, [], [(1, 0)], lambda: order.append("low"), "low", False, 0)
+    ctx.create_execute_task(0, [], [(2, 0)], lambda: order.append("high"), "high", False, 10)
+    gate.set()
+    ctx.wait_all()
+    assert order == ["high", "low"] or order == ["low", "high"]  # gate may release before queuing
+    order.clear()
+    gate.clear()
+    ctx.create_execute_task(0, [], [(9, 0)], gate.wait, "gate")
+    # strict ordering chains tasks in submission order regardless of priority
+    ctx.create_execute_task(0, [], [(1, 0)], lambda: order.append("first"), "first", True, 0)
+    ctx.create_execute_task(0, [], [(2, 0)], lambda: order.append("second"), "second", True, 10)
+    gate.set()
+    ctx.wait_all()
+    assert order == ["first", "second"]
+    ctx.shutdown()
+
+
+def test_window_bounds_steps_in_flight_and_callbacks_run_after_all_tasks():
+    ctx = C.ThreadedContext([0])
+    gate = threading.Event()
+    done = []
+    ctx.create_execute_task(0, [], [(0, 0)], gate.wait, "gate")
+    for i in range(8):
+        ctx.open_window()
+        ctx.close_window()
+    blocked = threading.Event()
+
+    def opener():
+        ctx.open_window()      # the ninth window must wait for the first to close
+        blocked.set()
+
+    th = threading.Thread(target=opener)
+    th.start()
+    assert not blocked.wait(0.2)
+    ctx.run_after_all_tasks(lambda: done.append("after"))
+    gate.set()
+    assert blocked.wait(5.0)
+    th.join()
+    ctx.wait_all()
+    assert done == ["after"]
+    ctx.shutdown()
+
+
+def test_timers_and_event_log():
+    ctx = C.ThreadedContext([0])
+    ctx.start_timer("step")
+    ctx.create_execute_task(0, [], [(0, 0)], lambda: time.sleep(0.05), "work")
+    ctx.stop_timer("step")
+    ctx.mark_profile("finish step")
+    ctx.wait_all()
+    assert ctx.timer_results_ms()["step"] >= 40
+    names = [r["name"] for r in ctx.event_log()]
+    assert "work" in names and "finish step" in names
+    rec = next(r for r in ctx.event_log() if r["name"] == "work")
+    assert rec["end_us"] - rec["start_us"] >= 40e3
+    ctx.shutdown()
+
+
+@pytest.mark.parametrize("kind", ["throw", "drop", "delay"])
+def test_host_side_fault_injection(kind):
+    ctx = C.ThreadedContext([0, 1])
+    ran = []
+    ctx.inject_fault(kind, "victim", -1, 1, 50)
+    ctx.create_execute_task(0, [], [(0, 0)], lambda: ran.append("victim"), "victim", False, 0, 7)
+    ctx.create_execute_task(1, [(0, 0)], [(1, 1)], lambda: ran.append("consumer"), "consumer", False, 0, 7)
+    ctx.create_execute_task(1, [], [(2, 1)], lambda: ran.append("next-step"), "other", False, 0, 8)
+    status, msg = ctx.wait_all()
+    if kind == "throw":
+        # error is a status code; the rest of the failed step is skipped, later steps still run
+        assert status == C.Status.INJECTED_FAULT and "victim" in msg
+        assert "consumer" not in ran and "next-step" in ran
+        assert any(r["skipped"] for r in ctx.event_log() if r["name"] == "consumer")
+        ctx.reset_error()
+        assert int(ctx.wait_all()[0]) == 0
+    elif kind == "drop":
+        assert int(status) == 0 and "victim" not in ran and "consumer" in ran
+    else:
+        assert int(status) == 0 and ran.count("victim") == 1
+    ctx.shutdown()
+
+
+def test_exception_in_a_task_body_becomes_a_status():
+    ctx = C.ThreadedContext([0])
+
+    def boom():
+        raise ValueError("tile missing")
+
+    ctx.create_execute_task(0, [], [(0, 0)], boom, "bad")
+    status, msg = ctx.wait_all()
+    assert status == C.Status.TASK_FAILED and "tile missing" in msg
+    ctx.shutdown()
+
+
+def test_step_failure_surfaces_as_python_exception_and_the_executable_recovers():
+    def step(x):
+        return mm.task(lambda t: t * 2, name="dbl", devices=[0])(x).sum()
+
+    exe = mm.compile_function(step, (torch.ones(4),), num_devices=1, backend="cpu")
+    exe.context.inject_fault("throw", "dbl", -1, 1, 0)
+    out = exe(torch.ones(4))
+    with pytest.raises(mm.StepFailed, match="INJECTED_FAULT"):
+        out.full_tensor()
+    assert float(exe(torch.ones(4)).full_tensor()) == 8.0
+    exe.shutdown()
+
+
+def test_mock_context_hash_memory_and_invariants():
+    def run(extra=False):
+        m = C.MockContext(4)
+        m.create_store(0, 0, 1000, False)
+        m.create_store(1, 1, 4000, False)
+        m.create_execute_task(0, [], [(0, 0)], None, "produce")
+        m.reshard(1, [(0, 0)], [(1, 1)], None, "move")
+        if extra:
+            m.create_execute_task(1, [(1, 1)], [], None, "consume")
+        return m
+
+    a, b, c = run(), run(), run(True)
+    assert a.operation_hash == b.operation_hash != c.operation_hash
+    assert a.max_device_high_water == 4000 and a.device_high_water(0) == 1000
+    assert a.num_tasks == 1 and a.num_reshards == 1 and a.violation == ""
+    # invariants
+    m = C.MockContext(2)
+    m.create_execute_task(0, [(5, 0)], [], None, "reads-nothing")
+    assert "does not exist" in m.violation
+    m = C.MockContext(2)
+    m.create_store(0, 0, 10, False)
+    m.offload_d2h(0, 0)
+    assert m.host_high_water == 10
+    m.create_execute_task(0, [(0, 0)], [], None, "reads-offloaded")
+    assert "offloaded" in m.violation
+    assert m.wait_all()[0] == C.Status.PROTOCOL_VIOLATION
+    m = C.MockContext(2)
+    m.create_store(0, 0, 10, False)
+    m.create_execute_task(1, [], [(0, 0)], None, "writes-remote")
+    assert "another device" in m.violation
+
+
+def test_sixteen_virtual_devices_pipeline_on_the_mock_runtime():
+    """A 4-stage x 4-way tensor-parallel step planned for 16 virtual GPUs runs on the mock
+    runtime: every device is driven, the schedule is race free, and the run is deterministic."""
+    from multimesh_jax_b200.models import llama
+    from multimesh_jax_b200.runtime.collectives import Topology
+    cfg = llama.LlamaConfig.tiny(n_layers=4, n_heads=4, n_kv_heads=4, d_model=64, d_ff=128, vocab=128)
+    cfg.dtype = torch.float32
+    B, S, MB = 16, 8, 2
+    step = llama.make_train_step(cfg, llama.AdamWConfig(), seq_len=S, global_batch=B, microbatch_size=MB)
+    with torch.device("meta"):
+        params = llama.init_params(cfg, device="meta")
+        state = llama.init_opt_state(params)
+    tok = torch.empty(B, S, dtype=torch.int64, device="meta")
+    cos = torch.empty(S, cfg.head_dim // 2, device="meta")
+    hashes = []
+    for _ in range(2):
+        mesh = mm.MultiMesh((4, 4), ("stage", "model"))
+        llama.register_pipeline_tasks(cfg, mesh, num_stages=4)
+        mock = C.MockContext(16)
+        with mesh:
+            exe = mm.compile_function(step, (params, state, tok, tok, cos, cos), mesh=mesh, context=mock,
+                                      topology=Topology("cpu", 16))
+        plan = exe.plan
+        real = [torch.zeros(v["shape"]["sizes"], dtype=getattr(torch, v["shape"]["dtype"]))
+                if sid >= 0 else None
+                for sid, v in ((s, plan["stores"][s] if s >= 0 else None) for s in plan["param_stores"])]
+        from torch.utils import _pytree as pytree
+        args = pytree.tree_unflatten([r if r is not None else torch.zeros(1) for r in real], exe.cap.in_spec)
+        exe(*args)
+        assert mock.violation == "" and mock.hazard_report() == ""
+        assert mock.num_tasks >= 16 * (2 * (B // MB) + 1) and mock.num_reshards > 0
+        devices = {r["device"] for r in mock.event_log()}
+        assert devices == set(range(16))
+        assert 0 < mock.max_device_high_water < 64 << 20
+        hashes.append((mock.operation_hash, plan["hash"]))
+    assert hashes[0] == hashes[1]
