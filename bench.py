@@ -46,6 +46,8 @@ def parse_args():
     p.add_argument("--layers", type=int, default=0, help="override the number of layers (debugging only)")
     p.add_argument("--tp", type=int, default=0, help="tensor-parallel degree (0 = default for N)")
     p.add_argument("--schedule", default="1f1b")
+    p.add_argument("--trace", default="", help="after the timed runs, profile one more step per rank and write "
+                                               "its time breakdown to this directory (not a benchmark value)")
     return p.parse_args()
 
 
@@ -213,6 +215,18 @@ def main():
     loss_val = float(last.full_tensor().item()) if hasattr(last, "full_tensor") else float(last)
     ms_e2e, _ = timed(args.steps, True)
     status = K.read_status()
+    if args.trace:
+        from multimesh_jax_b200.utils import timeline
+        os.makedirs(args.trace, exist_ok=True)
+        res = {}
+        barrier()
+        with timeline.profile(res, device=local_rank):
+            t_last = run_step(0, False)
+            t_last.wait() if hasattr(t_last, "wait") else None
+            torch.cuda.synchronize()
+        with open(os.path.join(args.trace, f"breakdown_n{n}_rank{rank}.txt"), "w") as f:
+            f.write(res["breakdown"].format() + "\n" + json.dumps(res["breakdown"].to_dict()) + "\n")
+        barrier()
 
     tokens = global_batch * seq * args.steps
     value = tokens / (ms / 1e3)

@@ -522,6 +522,16 @@ bool ShardingPropagation(CompileState& s, PropagationMode mode) {
   const bool forward = mode != PropagationMode::kBackwardInputOutput;
   for (int round = 0; round < 4; ++round) {
     bool changed = false;
+    // Layout that some task already chose for an argument of the step (a parameter, its
+    // optimizer state): other tasks on the same mesh read the argument in that layout too
+    // instead of each settling on its own (a replicated reader of a sharded weight would
+    // pay a gather of the weight and redundant math every step).
+    std::map<int, ShardedShape> argument_layout;
+    for (auto& kv : TablesOf(s).input_sharding) {
+      const int value = kv.first.second;
+      if (g.value(value).producer >= 0 || kv.second.IsReplicated()) continue;
+      argument_layout.emplace(value, kv.second);
+    }
     auto do_group = [&](TaskGroup& grp) {
       const TaskMeshInfo mesh = MeshOf(part, grp.color);
       if (mesh.devices.n == 1) return;
@@ -531,7 +541,15 @@ bool ShardingPropagation(CompileState& s, PropagationMode mode) {
           for (int in : g.node(id).inputs) {
             const Value& v = g.value(in);
             const int p = v.producer;
-            if (p < 0 || g.node(p).task == grp.id || !v.has_sharding) continue;
+            if (p < 0) {
+              auto al = argument_layout.find(in);
+              if (al == argument_layout.end() || InputShardingOf(s, grp.id, in)) continue;
+              if (al->second.mesh_dims != mesh.dims || !(al->second.devices == mesh.devices)) continue;
+              TablesOf(s).input_sharding[{grp.id, in}] = al->second;
+              changed = true;
+              continue;
+            }
+            if (g.node(p).task == grp.id || !v.has_sharding) continue;
             if (InputShardingOf(s, grp.id, in)) continue;
             ShardedShape adopted = AdoptSharding(v.sharding, v, mesh);
             if (adopted.IsReplicated() && !full) continue;

@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 from torch.utils import _pytree as pytree
 
+from .. import state
 from ..compiler.capture import Captured, DTYPE_FROM_NAME
 from ..compiler.lower import TemplateProgram, build_program
 from ..ops import kernels as K
@@ -345,7 +346,15 @@ class Executable:
         dying = self._dying_inputs.get(k, ())
         acc_dtypes = [DTYPE_FROM_NAME[self.plan["stores"][s]["shape"]["dtype"]] for s in out_ids]
 
+        name = op["name"]
+
         def body():
+            if state.knobs["task_ranges"]:
+                with torch.profiler.record_function("mm.task:" + name):
+                    return run()
+            return run()
+
+        def run():
             dctx.device_start = dev_start
             dctx.mesh_dims = mesh_dims
             dctx.key_prefix = (step, k)
@@ -418,6 +427,10 @@ class Executable:
                     if dst_sid in root_tiles:
                         root_tiles[dst_sid][d] = out
 
+            if state.knobs["task_ranges"]:
+                def body(inner=body, label=f"mm.reshard:S{src_sid}->S{dst_sid}"):
+                    with torch.profiler.record_function(label):
+                        inner()
             self.launches += 1
             self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
 

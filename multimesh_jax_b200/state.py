@@ -8,6 +8,7 @@ environment variables read by the C++ passes.
 from __future__ import annotations
 
 import contextlib
+import os
 import threading
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
@@ -84,6 +85,9 @@ trace = TraceState()
 knobs = {
     "replicated_parameter_num_elements_cutoff": 0,
     "recompute_from_arguments_if_cost_less_than": 1 << 20,
+    # open a named profiler / NVTX range around every task launch (MM_TASK_RANGES=1, or set by
+    # utils.timeline.profile); off by default because it costs a few microseconds per task
+    "task_ranges": os.environ.get("MM_TASK_RANGES", "0") == "1",
 }
 
 
