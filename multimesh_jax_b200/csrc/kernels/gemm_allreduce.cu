@@ -3,112 +3,182 @@
 //
 // Every rank computes a partial C = A_shard * B_shard^T with the tcgen05 main loop. The
 // epilogue of each 128x256 tile
-//   1. converts the accumulator to bf16 and *pushes* it into the receive buffer of every
-//      peer with plain peer stores (posted writes over NVLink), then raises that tile's
-//      flag in the peer's memory (release, system scope);
-//   2. waits - bounded - for the same tile's flags from its peers, re-reads its own
-//      accumulator from TMEM, adds the received partials from local memory and writes the
-//      reduced tile.
-// Ranks walk the tiles in the same order, so a peer's tile usually arrives while this
-// rank's MMA warp is already working on the next tile (the second TMEM accumulator): the
-// transfer overlaps the math tile by tile and no separate collective runs. Receive
-// buffers are double-buffered by call parity; flags carry the call's epoch and are never
-// reset. No TMA load touches peer memory and no multicast is used.
+//   1. drains the accumulator from TMEM, converts it to bf16 and transposes it through a
+//      swizzled shared-memory staging area so that every store instruction of a warp covers
+//      whole 256-byte row segments; the tile is written to the local output and *pushed*
+//      into the receive buffer of every peer with plain peer stores (posted writes over
+//      NVLink); the accumulator is released to the MMA warp right after the drain;
+//   2. raises, per epilogue warp, the flag of its 32 rows of that tile in every peer's memory
+//      (release, system scope);
+//   3. reduces the tile this CTA pushed one iteration earlier: waits - bounded - for the
+//      peers' flags of that tile and adds their partials (read from local memory) to the
+//      local output. Deferring the reduction by one tile hides the NVLink latency and small
+//      skew between ranks behind the next tile's math; the last tile is reduced after the
+//      loop.
+// Ranks walk the tiles in the same order. Receive buffers are double-buffered by call
+// parity; flags carry the call's epoch and are never reset. No TMA load touches peer
+// memory and no multicast is used.
 #include "gemm_core.cuh"
 #include "host_common.h"
 
 namespace mm {
 
 constexpr int AR_MAX_PEERS = 7;
+constexpr int AR_HALF_COLS = 128;                    // columns staged at a time
+constexpr int AR_ROW_BYTES = AR_HALF_COLS * 2;       // 256 B of bf16 per staged row
+constexpr int AR_WARP_STAGE = 32 * AR_ROW_BYTES;     // 8 KiB per epilogue warp
 
 struct AllReduceHook {
   __nv_bfloat16* out;                      // reduced result (local), row stride ldo
   int64_t ldo;
   const __nv_bfloat16* recv_local[AR_MAX_PEERS];  // where peer p's partial lands in local memory [M][N]
   __nv_bfloat16* recv_peer[AR_MAX_PEERS];         // this rank's slot in peer p's memory [M][N]
-  const int* flag_local[AR_MAX_PEERS];            // flags raised by peer p, one per tile
+  const int* flag_local[AR_MAX_PEERS];            // flags raised by peer p: four per tile (one per 32-row quarter)
   int* flag_peer[AR_MAX_PEERS];                   // this rank's flags in peer p's memory
   int npeers;
   int epoch;
   int num_n;
 
+  static constexpr int kStageBytes = 4 * AR_WARP_STAGE;  // 32 KiB
+  struct State {
+    int prev_m = -1, prev_n = -1;
+  };
+
   __device__ __forceinline__ bool before_tile_loads(int, int, int*) const { return true; }
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
 
-  __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
-                                           int* err) const {
-    const int row = m_blk * GEMM_BM + q * 32 + lane;
+  // out[tile] += sum of the peers' partials of that tile (rows of warp q).
+  __device__ __forceinline__ void reduce_tile(int m_blk, int n_blk, int q, int lane, int M, int N, int* err) const {
     const int tile = m_blk * num_n + n_blk;
-    // pass 1: push the bf16 partial to every peer
-#pragma unroll 1
-    for (int c = 0; c < GEMM_BN / 32; ++c) {
-      const int col0 = n_blk * GEMM_BN + c * 32;
-      if (col0 >= N) break;
-      uint32_t r[32];
-      tmem_ld_32x32(t_base + c * 32, r);
-      tmem_ld_wait();
-      if (row < M) {
-        uint4 v[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          v[i].x = pack_bf16(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
-          v[i].y = pack_bf16(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
-          v[i].z = pack_bf16(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
-          v[i].w = pack_bf16(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
-        }
-        for (int p = 0; p < npeers; ++p) {
-          uint4* dst = reinterpret_cast<uint4*>(recv_peer[p] + static_cast<int64_t>(row) * N + col0);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) dst[i] = v[i];
-        }
-      }
-    }
-    __threadfence_system();
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-    if (q == 0 && lane == 0)
-      for (int p = 0; p < npeers; ++p) st_release_sys(flag_peer[p] + tile, epoch);
-    // pass 2: wait for the peers' partials of this tile, add, write the reduced tile
     int ok = 1;
     if (lane == 0)
-      for (int p = 0; p < npeers && ok; ++p) ok = wait_flag_ge(flag_local[p] + tile, epoch, err) ? 1 : 0;
+      for (int p = 0; p < npeers && ok; ++p) ok = wait_flag_ge(flag_local[p] + tile * 4 + q, epoch, err) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return;
+    const int col = n_blk * GEMM_BN + lane * 8;   // one 512-byte tile row per warp instruction
+    if (col >= N) return;
+    const int row0 = m_blk * GEMM_BM + q * 32;
+    // 8 rows at a time with all loads issued before the first use: the loop is bound by
+    // memory latency, so the loads in flight per thread set its speed
+    constexpr int R = 8;
 #pragma unroll 1
-    for (int c = 0; c < GEMM_BN / 32; ++c) {
-      const int col0 = n_blk * GEMM_BN + c * 32;
-      if (col0 >= N) break;
-      uint32_t r[32];
-      tmem_ld_32x32(t_base + c * 32, r);
-      tmem_ld_wait();
-      if (row >= M || !ok) continue;
-      float f[32];
+    for (int rb = 0; rb < 32; rb += R) {
+      if (row0 + rb >= M) break;
+      float acc[R][8];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(r[j]);
+      for (int r = 0; r < R; ++r) {
+        const int row = min(row0 + rb + r, M - 1);
+        const uint4 own = __ldcg(reinterpret_cast<const uint4*>(out + static_cast<int64_t>(row) * ldo + col));
+        const float2 a = unpack_bf16(own.x), b = unpack_bf16(own.y), c = unpack_bf16(own.z), d = unpack_bf16(own.w);
+        acc[r][0] = a.x; acc[r][1] = a.y; acc[r][2] = b.x; acc[r][3] = b.y;
+        acc[r][4] = c.x; acc[r][5] = c.y; acc[r][6] = d.x; acc[r][7] = d.y;
+      }
       for (int p = 0; p < npeers; ++p) {
-        const uint4* src = reinterpret_cast<const uint4*>(recv_local[p] + static_cast<int64_t>(row) * N + col0);
+        uint4 u[R];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 u = __ldcg(src + i);  // bypass L1: the line was written by a peer
-          float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), cc = unpack_bf16(u.z), d = unpack_bf16(u.w);
-          f[i * 8 + 0] += a.x; f[i * 8 + 1] += a.y; f[i * 8 + 2] += b.x; f[i * 8 + 3] += b.y;
-          f[i * 8 + 4] += cc.x; f[i * 8 + 5] += cc.y; f[i * 8 + 6] += d.x; f[i * 8 + 7] += d.y;
+        for (int r = 0; r < R; ++r) {
+          const int row = min(row0 + rb + r, M - 1);
+          // bypass L1: the line was written by a peer
+          u[r] = __ldcg(reinterpret_cast<const uint4*>(recv_local[p] + static_cast<int64_t>(row) * N + col));
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float2 ua = unpack_bf16(u[r].x), ub = unpack_bf16(u[r].y), uc = unpack_bf16(u[r].z),
+                       ud = unpack_bf16(u[r].w);
+          acc[r][0] += ua.x; acc[r][1] += ua.y; acc[r][2] += ub.x; acc[r][3] += ub.y;
+          acc[r][4] += uc.x; acc[r][5] += uc.y; acc[r][6] += ud.x; acc[r][7] += ud.y;
         }
       }
-      uint4* o4 = reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * ldo + col0);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 o;
-        o.x = pack_bf16(f[i * 8 + 0], f[i * 8 + 1]);
-        o.y = pack_bf16(f[i * 8 + 2], f[i * 8 + 3]);
-        o.z = pack_bf16(f[i * 8 + 4], f[i * 8 + 5]);
-        o.w = pack_bf16(f[i * 8 + 6], f[i * 8 + 7]);
-        o4[i] = o;
+      for (int r = 0; r < R; ++r) {
+        const int row = row0 + rb + r;
+        if (row < M) {
+          uint4 o;
+          o.x = pack_bf16(acc[r][0], acc[r][1]);
+          o.y = pack_bf16(acc[r][2], acc[r][3]);
+          o.z = pack_bf16(acc[r][4], acc[r][5]);
+          o.w = pack_bf16(acc[r][6], acc[r][7]);
+          *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * ldo + col) = o;
+        }
       }
     }
+  }
+
+  __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
+                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+    uint8_t* ws = stage + q * AR_WARP_STAGE;          // this warp's 32 rows x 256 B
+    const int row0 = m_blk * GEMM_BM + q * 32;
+    const int tile = m_blk * num_n + n_blk;
+#pragma unroll 1
+    for (int h = 0; h < GEMM_BN / AR_HALF_COLS; ++h) {
+      const int hcol0 = n_blk * GEMM_BN + h * AR_HALF_COLS;
+      if (hcol0 < N) {
+        // TMEM -> registers -> swizzled staging: lane = row, 16-byte unit j goes to j ^ (row & 7)
+#pragma unroll 1
+        for (int c = 0; c < AR_HALF_COLS / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_base + h * AR_HALF_COLS + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[i * 8 + 0]), __uint_as_float(r[i * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(r[i * 8 + 2]), __uint_as_float(r[i * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(r[i * 8 + 4]), __uint_as_float(r[i * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(r[i * 8 + 6]), __uint_as_float(r[i * 8 + 7]));
+            const int j = (c * 4 + i) ^ (lane & 7);
+            *reinterpret_cast<uint4*>(ws + lane * AR_ROW_BYTES + j * 16) = v;
+          }
+        }
+      }
+      if (h == GEMM_BN / AR_HALF_COLS - 1) {
+        // accumulator fully drained: hand it back to the MMA warp before touching NVLink
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty);
+      } else {
+        __syncwarp();
+      }
+      if (hcol0 < N) {
+        // staging -> local output and peers: half a warp covers one 256-byte row segment
+        const int unit = lane & 15;
+        const int col = hcol0 + unit * 8;
+        if (col < N) {
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int rr = it * 2 + (lane >> 4);
+            const int row = row0 + rr;
+            if (row >= M) break;
+            const uint4 v = *reinterpret_cast<const uint4*>(ws + rr * AR_ROW_BYTES + ((unit ^ (rr & 7)) * 16));
+            *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * ldo + col) = v;
+            for (int p = 0; p < npeers; ++p)
+              *reinterpret_cast<uint4*>(recv_peer[p] + static_cast<int64_t>(row) * N + col) = v;
+          }
+        }
+      }
+      __syncwarp();   // staging is reused by the next half
+    }
+    // each warp publishes its own 32 rows: no barrier between the epilogue warps
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0)
+      for (int p = 0; p < npeers; ++p) st_release_sys(flag_peer[p] + tile * 4 + q, epoch);
+    // deferred reduction of the tile pushed one iteration ago
+    if (st.prev_m >= 0) reduce_tile(st.prev_m, st.prev_n, q, lane, M, N, err);
+    st.prev_m = m_blk;
+    st.prev_n = n_blk;
+  }
+
+  __device__ __forceinline__ void finish(State& st, uint8_t*, int q, int lane, int M, int N, int* err) const {
+    if (st.prev_m >= 0) reduce_tile(st.prev_m, st.prev_n, q, lane, M, N, err);
   }
 };
 
 int make_gemm_tmaps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, int a_mn, int64_t lda, const void* B,
                     int b_mn, int64_t ldb, int M, int N, int K);
+
+constexpr int AR_SMEM_BYTES = GEMM_SMEM_BYTES + AllReduceHook::kStageBytes;
+static_assert(AR_SMEM_BYTES <= 232448, "shared memory of the fused GEMM + all-reduce kernel exceeds the CTA limit");
 
 template <bool A_MN, bool B_MN>
 static int launch_ar(const CUtensorMap& tmA, const CUtensorMap& tmB, const AllReduceHook& hook, int M, int N, int K,
@@ -120,13 +190,13 @@ static int launch_ar(const CUtensorMap& tmA, const CUtensorMap& tmB, const AllRe
   int dev = 0;
   cudaGetDevice(&dev);
   if (!configured[dev]) {
-    MM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
+    MM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, AR_SMEM_BYTES));
     configured[dev] = true;
   }
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + GEMM_BN - 1) / GEMM_BN);
   const int grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;
   GemmShape shape{M, N, K};
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, shape, hook, ds->status);
+  kern<<<grid, GEMM_THREADS, AR_SMEM_BYTES, stream>>>(tmA, tmB, shape, hook, ds->status);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }
@@ -137,8 +207,9 @@ extern "C" {
 
 // out[M,N] = sum over ranks of (A[M,K] * B[N,K]^T) with this rank's K-shard; operand layout
 // flags as in mm_gemm_bf16. recv_local / flag_local: npeers local addresses (one slot per
-// peer); recv_peer / flag_peer: this rank's slot inside each peer's memory. N must be a
-// multiple of 32 and out / receive rows 16-byte aligned.
+// peer); recv_peer / flag_peer: this rank's slot inside each peer's memory (a flag slot
+// holds 4 ints per 128x256 tile). N must be a multiple of 32 and out / receive rows 16-byte
+// aligned.
 int mm_gemm_allreduce_bf16(const void* A, int a_mn, int64_t lda, const void* B, int b_mn, int64_t ldb, void* out,
                            int64_t ldo, int M, int N, int K, const int64_t* recv_local, const int64_t* recv_peer,
                            const int64_t* flag_local, const int64_t* flag_peer, int npeers, int epoch,

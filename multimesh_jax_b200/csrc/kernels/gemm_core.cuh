@@ -30,6 +30,7 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_GROUP_M = 16;
 constexpr int GEMM_SMEM_BYTES =
     GEMM_STAGES * (GEMM_A_STAGE + GEMM_B_STAGE) + 256 /*barriers*/ + 1024 /*alignment slack*/;
+// a hook that stages epilogue tiles in shared memory adds Hook::kStageBytes to this
 
 enum GemmOut : int {
   OUT_BF16 = 0,      // C(bf16)  = acc
@@ -124,9 +125,12 @@ struct PlainHook {
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
   // Drains one 128x256 accumulator: warp `q` owns TMEM lanes [32q, 32q+32), i.e. rows
   // m_blk*128 + 32q + lane. `t_base` already points at that lane quarter.
+  static constexpr int kStageBytes = 0;  // no shared-memory staging in the epilogue
+  struct State {};
+  __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
-                                           int* err) const {
-    (void)err;
+                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+    (void)err; (void)stage; (void)st;
     const int row = m_blk * GEMM_BM + q * 32 + lane;
 #pragma unroll 1
     for (int c = 0; c < GEMM_BN / 32; ++c) {
@@ -137,6 +141,9 @@ struct PlainHook {
       tmem_ld_wait();
       if (row < M) gemm_store_chunk<OUT>(C, ldc, row, col0, N, r, vec_ok);
     }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tempty);
   }
 };
 
@@ -155,6 +162,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   uint64_t* tfull = bars + 2 * GEMM_STAGES; // [2]
   uint64_t* tempty = tfull + 2;             // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint8_t* epi_stage = smem + GEMM_STAGES * (GEMM_A_STAGE + GEMM_B_STAGE) + 256;  // Hook::kStageBytes
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -263,19 +271,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    typename Hook::State hstate{};
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       gemm_tile_coords(tile, num_m, num_n, m_blk, n_blk);
       if (!mbar_wait(&tfull[acc], acc_phase, err, MM_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t t_base = tmem_base + acc * GEMM_BN + (static_cast<uint32_t>(q * 32) << 16);
-      hook.epilogue(t_base, m_blk, n_blk, q, lane, M, N, err);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      // the hook arrives on tempty[acc] itself as soon as it has drained the accumulator
+      hook.epilogue(t_base, m_blk, n_blk, q, lane, M, N, err, epi_stage, hstate, &tempty[acc]);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    hook.finish(hstate, epi_stage, q, lane, M, N, err);
   }
 
   tc_fence_before();

@@ -103,7 +103,7 @@ def main():
                         symm.reshard_pull(records, 2, arena)
 
                 def run_nccl():
-                    out = run_reshard_dist(topo, rank, src_t.local if is_src else None, mine_src, mine, dst)
+                    out, _ = run_reshard_dist(topo, rank, src_t.local if is_src else None, mine_src, mine, dst)
                     return out
 
                 results = {}

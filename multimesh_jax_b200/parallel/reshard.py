@@ -41,10 +41,39 @@ def run_reshard_local(topo, device: int, src_tiles: Dict[int, torch.Tensor], chu
     return out
 
 
+class CommStream:
+    """Side stream for point-to-point messages of one process (one GPU).
+
+    Messages are issued on this stream, behind everything the compute stream has queued so
+    far, so a receive that is posted early does not hold back later compute kernels and a send
+    does not wait in front of them. ``run_reshard_dist`` returns an event; the first task that
+    reads the received tile makes the compute stream wait for it. Tensors of messages in
+    flight are kept referenced here until their event has fired, so the caching allocator
+    cannot hand their memory to another stream's kernels."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.stream = torch.cuda.Stream(device=device)
+        self.pending: List[tuple] = []
+
+    def reap(self) -> None:
+        self.pending = [(ev, keep) for ev, keep in self.pending if not ev.query()]
+
+    def drain(self) -> None:
+        """Makes the compute stream wait for every message still in flight."""
+        cur = torch.cuda.current_stream(self.device)
+        for ev, _ in self.pending:
+            cur.wait_event(ev)
+        self.reap()
+
+
 def run_reshard_dist(topo, device: int, src_tile: Optional[torch.Tensor], send_chunks: List[dict],
-                     recv_chunks: List[dict], dst_shape: dict) -> Optional[torch.Tensor]:
+                     recv_chunks: List[dict], dst_shape: dict, comm: Optional[CommStream] = None):
     """Point-to-point realisation: every chunk whose source and destination
-    differ is one message; all ranks issue their sends and receives as one batch."""
+    differ is one message; all ranks issue their sends and receives as one batch.
+    Returns ``(tile or None, event or None)``: with a :class:`CommStream` the messages run
+    on the side stream and the event marks their completion; without one the call returns
+    after making the current stream wait for them."""
     import torch.distributed as dist
     dev = topo.torch_device(device)
     out = None
@@ -52,10 +81,12 @@ def run_reshard_dist(topo, device: int, src_tile: Optional[torch.Tensor], send_c
         out = torch.empty(dst_shape["shard_size"], dtype=DTYPE_FROM_NAME[dst_shape["dtype"]], device=dev)
     ops = []
     staged = []
+    keep: List[torch.Tensor] = []
     for c in send_chunks:
         if c["dst_device"] == device:
             continue
         piece = src_tile[_slices(c["src_offset"], c["lo"], c["hi"])].contiguous()
+        keep.append(piece)
         ops.append(dist.P2POp(dist.isend, piece, c["dst_device"]))
     for c in recv_chunks:
         view = out[_slices(c["dst_offset"], c["lo"], c["hi"])]
@@ -67,10 +98,26 @@ def run_reshard_dist(topo, device: int, src_tile: Optional[torch.Tensor], send_c
         else:
             tmp = torch.empty(view.shape, dtype=out.dtype, device=dev)
             staged.append((view, tmp))
+            keep.append(tmp)
             ops.append(dist.P2POp(dist.irecv, tmp, c["src_device"]))
-    if ops:
+    if not ops:
+        return out, None
+    if comm is None:
         for w in dist.batch_isend_irecv(ops):
             w.wait()
-    for view, tmp in staged:
-        view.copy_(tmp)
-    return out
+        for view, tmp in staged:
+            view.copy_(tmp)
+        return out, None
+    comm.reap()
+    comm.stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(comm.stream):
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+        for view, tmp in staged:
+            view.copy_(tmp)
+        ev = torch.cuda.Event()
+        ev.record(comm.stream)
+    if out is not None:
+        keep.append(out)
+    comm.pending.append((ev, keep))
+    return out, ev

@@ -28,7 +28,7 @@ BM, BN = 128, 256
 
 class _BufferSet:
     def __init__(self, arena: symm.SymmetricArena, M: int, N: int, npeers: int):
-        self.tiles = ((M + BM - 1) // BM) * ((N + BN - 1) // BN)
+        self.tiles = 4 * ((M + BM - 1) // BM) * ((N + BN - 1) // BN)   # one flag per 32-row quarter of a tile
         self.recv = [arena.alloc((npeers, M, N), torch.bfloat16) for _ in range(2)]
         self.flags = [arena.alloc((npeers, self.tiles), torch.int32) for _ in range(2)]
         self.epoch = 0

@@ -174,6 +174,10 @@ class Executable:
             st["id"]: self._buffer_tiles.setdefault(self.buffer_of[st["id"]], {}) for st in plan["stores"]}
         self._step = 0
         self._created = False
+        # one-process-per-GPU jobs: side stream for stage-boundary messages, and the events
+        # that mark the arrival of a received tile, keyed by (buffer, device)
+        self._comm: Dict[int, Any] = {}
+        self._arrival: Dict[Tuple[int, int], Any] = {}
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
@@ -218,6 +222,18 @@ class Executable:
         self._fused_tp = FusedTP(arena)
         for ctx in self.dev_ctx.values():
             ctx.fused_tp = self._fused_tp
+
+    def _comm_stream(self, d: int):
+        """Side stream of device ``d`` for point-to-point messages (``None`` unless this is a
+        one-process-per-GPU CUDA job; MM_COMM_STREAM=0 keeps messages on the compute stream)."""
+        import os
+        topo = self.topology
+        if topo.kind != "dist" or topo.torch_device(d).type != "cuda" or os.environ.get("MM_COMM_STREAM", "1") == "0":
+            return None
+        if d not in self._comm:
+            from ..parallel.reshard import CommStream
+            self._comm[d] = CommStream(topo.torch_device(d))
+        return self._comm[d]
 
     @staticmethod
     def _template_devices(t: dict) -> range:
@@ -304,6 +320,13 @@ class Executable:
                         self._submit_task(k, op, d, step, root_tiles)
             elif kind == "reshard":
                 self._submit_reshard(k, op, step, root_tiles)
+        if self._comm:
+            # bodies ran inline: every message of the step is queued; results handed to the
+            # caller must be ordered behind them on the compute stream
+            for d, comm in self._comm.items():
+                with torch.cuda.device(comm.device):
+                    comm.drain()
+            self._arrival.clear()
         ctx.stop_timer(self.name)
         ctx.close_window()
         ctx.mark_profile(f"finish {self.name}")
@@ -345,6 +368,8 @@ class Executable:
         fused = prog.fused_acc
         dying = self._dying_inputs.get(k, ())
         acc_dtypes = [DTYPE_FROM_NAME[self.plan["stores"][s]["shape"]["dtype"]] for s in out_ids]
+        arrival = self._arrival
+        in_keys = [(buf[s], d) for s in in_ids] + [(buf[s], d) for s, m in zip(out_ids, modes) if m == 2]
 
         name = op["name"]
 
@@ -360,6 +385,12 @@ class Executable:
             dctx.key_prefix = (step, k)
             if dctx.torch_device.type == "cuda":
                 torch.cuda.set_device(dctx.torch_device)
+            if arrival:
+                # tiles that a message on the side stream delivers: wait for them on the stream
+                for key in in_keys:
+                    ev = arrival.pop(key, None)
+                    if ev is not None:
+                        torch.cuda.current_stream().wait_event(ev)
             # inputs read for the last time here are handed over: the program frees each one
             # right after its last use instead of keeping it alive for the whole task
             ins = [tiles[s].pop(d) if s in dying else tiles[s][d] for s in in_ids]
@@ -410,7 +441,13 @@ class Executable:
                 writes = [(buf[dst_sid], d)] if mine_dst else []
 
                 def body(d=d, mine_dst=mine_dst, mine_src=mine_src):
-                    out = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape)
+                    prev = self._arrival.get((self.buffer_of[src_sid], d))
+                    if prev is not None:     # the source itself arrived by message
+                        torch.cuda.current_stream().wait_event(prev)
+                    out, ev = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape,
+                                               self._comm_stream(d))
+                    if ev is not None and out is not None:
+                        self._arrival[(self.buffer_of[dst_sid], d)] = ev
                     if out is not None:
                         tiles[dst_sid][d] = out
                         if dst_sid in root_tiles:
