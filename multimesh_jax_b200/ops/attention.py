@@ -4,14 +4,18 @@
 attention); all are views into one packed projection buffer, so only the last dimension
 is contiguous. The softmax scale is ``1/sqrt(D)``.
 
-CUDA tensors use the tcgen05 flash-attention kernels of ``_mm_kernels.so`` when they are
-built in (``mm_flash_attn_fwd`` / ``mm_flash_attn_bwd``); otherwise the fused
-scaled-dot-product kernels that ship with PyTorch are called (a library path, counted as
-such in the benchmarks). CPU tensors use an fp32 restatement.
+The packed entry points (``attention_fwd_packed`` / ``attention_bwd_packed``) run the
+tcgen05 flash-attention kernels of ``_mm_kernels.so`` (``mm_flash_attn_fwd`` /
+``mm_flash_attn_bwd``) for bf16 CUDA tensors with head dimension 128 and a sequence length
+that is a multiple of 128. Other CUDA shapes fall back to the fused scaled-dot-product
+kernels that ship with PyTorch (a library path, counted as such in the benchmarks). CPU
+tensors use an fp32 restatement.
 """
 from __future__ import annotations
 
+import ctypes
 import math
+import os
 from typing import Tuple
 
 import torch
@@ -28,6 +32,68 @@ def have_native_kernels() -> bool:
     except RuntimeError:
         return False
     return hasattr(lib, "mm_flash_attn_fwd") and hasattr(lib, "mm_flash_attn_bwd")
+
+
+_lib.register("mm_flash_attn_supported", ctypes.c_int, [ctypes.c_int, ctypes.c_int])
+_lib.register("mm_flash_attn_fwd", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                                  ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p])
+_lib.register("mm_flash_attn_bwd", ctypes.c_int, [ctypes.c_void_p] * 7 + [ctypes.c_int] * 5 + [ctypes.c_void_p])
+
+
+def native_supported(qkv: torch.Tensor) -> bool:
+    """True when the packed projection can go through the tcgen05 attention kernels: CUDA,
+    bf16, contiguous, head dimension 128, sequence length a multiple of 128."""
+    if not (qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.dim() == 4):
+        return False
+    if os.environ.get("MM_NATIVE_ATTENTION", "1") == "0":
+        return False
+    return bool(_lib.load().mm_flash_attn_supported(qkv.shape[1], qkv.shape[3]))
+
+
+def _split_packed(qkv, rep: int):
+    B, S, H, D = qkv.shape
+    g = qkv.view(B, S, H // (rep + 2), rep + 2, D)
+    return g[:, :, :, :rep], g[:, :, :, rep], g[:, :, :, rep + 1]
+
+
+def attention_fwd_packed(qkv: torch.Tensor, rep: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Causal attention over a packed group-major projection [B,S,hkv*(rep+2),D] (rotary
+    embedding already applied). Returns (out [B,S,hq,D], lse [B,hq,S] fp32)."""
+    if not native_supported(qkv):
+        return attention_fwd(*_split_packed(qkv, rep))
+    B, S, H, D = qkv.shape
+    hkv = H // (rep + 2)
+    out = torch.empty((B, S, hkv * rep, D), dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty((B, hkv * rep, S), dtype=torch.float32, device=qkv.device)
+    rc = _lib.load().mm_flash_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, S, hkv, rep, D,
+                                       torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "mm_flash_attn_fwd")
+    K._count()
+    return out, lse
+
+
+def attention_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                         rep: int) -> torch.Tensor:
+    """Gradient of :func:`attention_fwd_packed` with respect to the packed projection."""
+    dqkv = torch.empty_like(qkv)
+    if not (native_supported(qkv) and dout.dtype == torch.bfloat16):
+        q, k, v = _split_packed(qkv, rep)
+        dq, dk, dv = _split_packed(dqkv, rep)
+        attention_bwd(dout, q, k, v, out, lse, dq, dk, dv)
+        return dqkv
+    B, S, H, D = qkv.shape
+    hkv = H // (rep + 2)
+    hq = hkv * rep
+    dout = dout.contiguous()
+    out = out.contiguous()
+    dq_acc = torch.empty((B, S, hq, D), dtype=torch.float32, device=qkv.device)
+    delta = torch.empty((B, hq, S), dtype=torch.float32, device=qkv.device)
+    rc = _lib.load().mm_flash_attn_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), dqkv.data_ptr(),
+                                       dq_acc.data_ptr(), delta.data_ptr(), B, S, hkv, rep, D,
+                                       torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc, "mm_flash_attn_bwd")
+    K._count(4)
+    return dqkv
 
 
 def _merge_q(q):

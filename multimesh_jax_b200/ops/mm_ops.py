@@ -230,22 +230,18 @@ def attention_impl(qkv, cos, sin, rep: int, inplace: bool = False):
     with rotary embedding applied to the query and key heads first. Returns (out
     [B,S,hq,D], lse [B,hq,S], the rotated qkv saved for the backward pass). Head counts are
     derived from the tensor, so a head-sharded (tensor-parallel) slice works unchanged."""
-    from .attention import attention_fwd
+    from .attention import attention_fwd_packed
     B, S, H, D = qkv.shape
     qkv_r = qkv if inplace else qkv.clone()
     K.rope_(qkv_r.view(B * S, H, D), cos, sin, rot_per_group=rep + 1, group_size=rep + 2)
-    q, k, v = _split_qkv(qkv_r, rep)
-    out, lse = attention_fwd(q, k, v)
+    out, lse = attention_fwd_packed(qkv_r, rep)
     return out, lse, qkv_r
 
 
 def attention_bwd_impl(dout, qkv_r, out, lse, cos, sin, rep: int):
-    from .attention import attention_bwd
+    from .attention import attention_bwd_packed
     B, S, H, D = qkv_r.shape
-    q, k, v = _split_qkv(qkv_r, rep)
-    dqkv = torch.empty_like(qkv_r)
-    dq, dk, dv = _split_qkv(dqkv, rep)
-    attention_bwd(dout, q, k, v, out, lse, dq, dk, dv)
+    dqkv = attention_bwd_packed(dout, qkv_r, out, lse, rep)
     K.rope_(dqkv.view(B * S, H, D), cos, sin, backward=True, rot_per_group=rep + 1, group_size=rep + 2)
     return dqkv
 
