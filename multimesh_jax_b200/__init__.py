@@ -23,7 +23,7 @@ _mm_C = _load_native()
 
 from . import state  # noqa: E402
 from .lib import (autoshard, context, enable_fast_path, enable_recomputation, ignore_transforms, mjit,  # noqa: E402
-                  recompute_from_arguments_if_cost_less_than, replicate_parameters_smaller_than_num_elements,
+                  recompute_from_arguments_if_cost_less_than, relayout, replicate_parameters_smaller_than_num_elements,
                   should_ignore_transforms, tasks, with_sharding_constraint)
 from .no_op import mark_gradient, mark_loss, no_op  # noqa: E402
 from .task import (Context, MultiMesh, Task, TaskMesh, clear_tasks, microbatch, module_scopes, named_scope,  # noqa: E402
@@ -35,7 +35,7 @@ from .init import init, init_test, shutdown  # noqa: E402
 __all__ = [
     "task", "microbatch", "parallelize", "register_task", "slice_global_mesh", "Task", "TaskMesh", "Context",
     "MultiMesh", "autoshard", "context", "enable_fast_path", "enable_recomputation", "ignore_transforms",
-    "with_sharding_constraint", "tasks", "mjit", "shutdown", "replicate_parameters_smaller_than_num_elements",
+    "with_sharding_constraint", "relayout", "tasks", "mjit", "shutdown", "replicate_parameters_smaller_than_num_elements",
     "recompute_from_arguments_if_cost_less_than", "clear_tasks", "no_op", "mark_gradient", "mark_loss",
     "value_and_grad", "named_scope", "module_scopes", "compile_function", "Executable", "ShardedTensor",
     "StepFailed", "init", "init_test",

@@ -155,6 +155,7 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                   acc_fusable: Optional[set] = None) -> TemplateProgram:
     g = cap.graph
     instrs: List[Instr] = []
+    fast_variants: List[Tuple[Instr, Callable, str]] = []   # (instruction, plain operator, op name)
     single_device = template["num_devices"] == 1
     fx_by_name = getattr(cap, "_fx_by_name", None)
     if fx_by_name is None:
@@ -205,6 +206,9 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             fn = fxn.target
             if fast_ops and op in fast_ops:
                 fn = fast_ops[op]
+                fast_pending = (fxn.target, op)
+            else:
+                fast_pending = None
             val = fxn.meta.get("val")
             single = isinstance(val, torch.Tensor)
             slots = None
@@ -217,9 +221,11 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                     else:
                         slots.append(None)
             instrs.append(Instr(0, fn, args, kwargs, n["outputs"], None if single else slots, nid))
+            if fast_pending is not None:
+                fast_variants.append((instrs[-1],) + fast_pending)
             continue
         attrs = n["attrs"]
-        if op in ("mm.accumulate",) or op.startswith("mm.marker"):
+        if op in ("mm.accumulate", "mm.relayout") or op.startswith("mm.marker"):
             instrs.append(Instr(1, None, n["inputs"][0], None, n["outputs"], None, nid))
         elif op == "mm.copy":
             instrs.append(Instr(2, None, n["inputs"][0], None, n["outputs"], None, nid))
@@ -297,6 +303,21 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
     for idx, ins in enumerate(instrs):
         for v in _reads(ins):
             last[v] = idx
+    # A fast variant that overwrites one of its operands is only valid when nothing reads that
+    # operand afterwards (passes may have moved a reader behind it): otherwise run the plain one.
+    if fast_variants:
+        from ..ops.mm_ops import INPLACE_OPERANDS
+        index_of = {id(ins): idx for idx, ins in enumerate(instrs)}
+        for ins_obj, plain, opname in fast_variants:
+            idx = index_of.get(id(ins_obj))
+            clobbered = INPLACE_OPERANDS.get(opname)
+            if idx is None or not clobbered:
+                continue
+            ids = _tensor_ids_in_order(ins_obj.args, ins_obj.kwargs)
+            for pos in clobbered:
+                if pos < len(ids) and (last.get(ids[pos], -1) > idx or ids[pos] in keep):
+                    ins_obj.fn = plain
+                    break
     last_use: Dict[int, List[int]] = {}
     for v, idx in last.items():
         if v not in keep:

@@ -424,6 +424,18 @@ bool LogicalShardingPropagation(CompileState& s) {
       const bool logical = !p.has("logical") || p.at("logical").as_bool();
       SetAxes(g.value(n.inputs[0]), axes, logical);
     }
+    if (kind == "Relayout") {
+      // a layout change point: the node stays (as an identity whose result has the given
+      // layout while its operand keeps its own), so the lowering gathers or slices here
+      const Json p = Json::parse(payload);
+      std::vector<std::vector<std::string>> axes;
+      for (auto& d : p.at("axes").arr) axes.push_back(d.as_string_vector());
+      const bool logical = !p.has("logical") || p.at("logical").as_bool();
+      SetAxes(g.value(n.outputs[0]), axes, logical);
+      n.op = "mm.relayout";
+      changed = true;
+      continue;
+    }
     // every marker is an identity: forward its operand and delete it
     g.ReplaceAllUses(n.outputs[0], n.inputs[0]);
     n.dead = true;

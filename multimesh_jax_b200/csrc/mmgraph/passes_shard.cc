@@ -385,6 +385,10 @@ const ShardedShape* InputShardingOf(const CompileState& s, int group, int value)
   return it == t.input_sharding.end() ? nullptr : &it->second;
 }
 
+void SetInputSharding(const CompileState& s, int group, int value, const ShardedShape& sh) {
+  TablesOf(s).input_sharding[{group, value}] = sh;
+}
+
 namespace {
 
 const ShardedShape* Available(CompileState& s, const TaskGroup& grp, int value) {
@@ -595,9 +599,36 @@ bool SpmdLowering(CompileState& s) {
     const TaskMeshInfo mesh = MeshOf(part, grp.color);
     if (mesh.devices.n == 1) continue;
     std::vector<int> new_nodes;
+    std::set<int> settled;  // external inputs whose layout some node of this task already relies on
     for (int id : std::vector<int>(grp.nodes)) {
       Node& n0 = g.node(id);
       const int nin = static_cast<int>(n0.inputs.size());
+      if (n0.op == "mm.relayout") {
+        // identity between two layouts: the result keeps the layout it was given (replicated
+        // if none), the operand is converted to it right here
+        const int in = n0.inputs[0], out = n0.outputs[0];
+        ShardedShape target = g.value(out).has_sharding ? g.value(out).sharding : ReplicatedOn(g.value(out), mesh);
+        g.value(out).sharding = target;
+        g.value(out).has_sharding = true;
+        const ShardedShape* have = Available(s, grp, in);
+        settled.insert(in);
+        if (!have) { SetAvailable(s, grp, in, target); continue; }
+        if (have->mesh_dims == target.mesh_dims && have->dim_axes == target.dim_axes) continue;
+        const ShardedShape from = *have;
+        const int rid = g.AddNode("mm.spmd_reshard", {in}, {g.value(in).shape}, {g.value(in).dtype},
+                                  {{"from", from.ToJson().dump()}, {"to", target.ToJson().dump()}});
+        Node& rn = g.node(rid);
+        rn.color = grp.color;
+        rn.task = grp.id;
+        rn.loop = g.node(id).loop;
+        rn.backprop = g.node(id).backprop;
+        g.value(rn.outputs[0]).sharding = target;
+        g.value(rn.outputs[0]).has_sharding = true;
+        g.node(id).inputs[0] = rn.outputs[0];
+        new_nodes.push_back(rid);
+        changed = true;
+        continue;
+      }
       Rule rule = RuleFor(g, n0);
       auto slot_value = [&](int slot) { return slot < nin ? g.node(id).inputs[slot] : g.node(id).outputs[slot - nin]; };
       // class axes: from outputs first (they are final), else from the most-sharded input
@@ -635,14 +666,15 @@ bool SpmdLowering(CompileState& s) {
             for (auto& m : rule.classes[c].members)
               if (m.first == slot && m.second < want.rank()) want.dim_axes[m.second] = class_axes[c];
         const ShardedShape* have = Available(s, grp, v);
-        if (!have) { SetAvailable(s, grp, v, want); continue; }
-        if (have->mesh_dims == want.mesh_dims && have->dim_axes == want.dim_axes) continue;
+        if (!have) { SetAvailable(s, grp, v, want); settled.insert(v); continue; }
+        if (have->mesh_dims == want.mesh_dims && have->dim_axes == want.dim_axes) { settled.insert(v); continue; }
         const int prod = g.value(v).producer;
         if (prod < 0 || g.node(prod).task != grp.id) {
           // external input: ask for it in the wanted layout unless another node of this task
           // already fixed a different one; then convert locally
           bool conflicting = TablesOf(s).fixed_values.count(v) > 0;
-          if (!conflicting) { TablesOf(s).input_sharding[{grp.id, v}] = want; continue; }
+          conflicting = conflicting || settled.count(v) > 0;
+          if (!conflicting) { TablesOf(s).input_sharding[{grp.id, v}] = want; settled.insert(v); continue; }
         }
         const int rid = g.AddNode("mm.spmd_reshard", {v}, {g.value(v).shape}, {g.value(v).dtype},
                                   {{"from", have->ToJson().dump()}, {"to", want.ToJson().dump()}});
@@ -757,6 +789,13 @@ bool HoistShardMapReduce(CompileState& s) {
       for (int& in : m.inputs) if (in == acc_out) in = reduced;
     }
     for (int& out : g.outputs) if (out == acc_out) out = reduced;
+    // tasks that asked for the accumulated value in some layout now read the reduced one
+    {
+      auto& table = TablesOf(s).input_sharding;
+      std::vector<std::pair<int, ShardedShape>> moved;
+      for (auto& kv : table) if (kv.first.second == acc_out) moved.emplace_back(kv.first.first, kv.second);
+      for (auto& mv : moved) table[{mv.first, reduced}] = mv.second;
+    }
     g.node(id).dead = true;
     changed = true;
   }

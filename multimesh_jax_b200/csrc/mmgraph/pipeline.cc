@@ -9,6 +9,7 @@
 namespace mmg {
 
 void ReleaseShardingTables(const CompileState& s);
+void SetInputSharding(const CompileState& s, int group, int value, const ShardedShape& sh);
 
 namespace {
 
@@ -101,6 +102,8 @@ Plan MpmdPartition(Graph& g, Partition& part, const PartitionConfig& cfg, std::v
         grp.nodes = {n.id};
         n.task = grp.id;
         n.color = grp.color;
+        // the reduction reads the accumulator in the layout the loop tasks left it in
+        if (g.value(n.inputs[0]).has_sharding) SetInputSharding(s, grp.id, n.inputs[0], g.value(n.inputs[0]).sharding);
         // place right after the last loop group
         size_t pos = s.groups.size();
         for (size_t i = 0; i < s.groups.size(); ++i) if (s.groups[i].region == 2) { pos = i; break; }

@@ -91,6 +91,27 @@ def with_sharding_constraint(x: Any, spec: Sequence[AxisSpec]):
     return pytree.tree_map(one, x)
 
 
+def relayout(x: Any, spec: Sequence[AxisSpec]):
+    """A layout change point: the result equals ``x`` but is laid out as ``spec`` says (same
+    conventions as :func:`with_sharding_constraint`; all ``None`` = replicated), while ``x``
+    itself keeps the layout it has. Where the two differ the compiled task gathers or slices
+    at this point. Typical use: parameters stored sharded over the data-parallel ranks
+    (``with_sharding_constraint(w, (..., "fsdp"))``) and gathered once per step before the
+    microbatch loop (``relayout(w, (..., None))``)."""
+    if should_ignore_transforms():
+        return x
+    from torch.utils import _pytree as pytree
+    import json as _json
+
+    def one(t):
+        if not isinstance(t, torch.Tensor):
+            return t
+        payload = {"axes": _canonical_axes(spec, t.dim()), "logical": bool(state.flags.autoshard)}
+        return torch.ops.mm.marker(t, "Relayout", _json.dumps(payload))
+
+    return pytree.tree_map(one, x)
+
+
 @contextlib.contextmanager
 def tasks(configurable: Any):
     """Registers every ``(matcher, Task | factory)`` pair produced by

@@ -176,8 +176,43 @@ def init_opt_state(params: Dict[str, Any]) -> Dict[str, Any]:
             "v": pytree.tree_unflatten(v, spec), "step": step}
 
 
+def annotate_fsdp(params: Dict[str, Any]) -> Dict[str, Any]:
+    """Gives every weight matrix the logical axis ``fsdp`` on a dimension that tensor
+    parallelism leaves alone (and keeps ``heads`` / ``mlp`` on the dimension it shards). Mapped
+    to the data axis of the mesh (``("fsdp", "data")`` after ``("batch", "data")``) this stores
+    parameters, gradients' final form and optimizer state sharded over the data-parallel
+    ranks: weights are gathered for use and gradients reduced back to the owner's shard."""
+    wsc = mm_lib.with_sharding_constraint
+    layers = []
+    for p in params["layers"]:
+        layers.append({**p,
+                       "wqkv": wsc(p["wqkv"], ("heads", None, "fsdp")),
+                       "wo": wsc(p["wo"], ("fsdp", "heads")),
+                       "wgu": wsc(p["wgu"], (None, "mlp", "fsdp")),
+                       "wdown": wsc(p["wdown"], ("fsdp", "mlp"))})
+    return {**params, "embed": wsc(params["embed"], ("fsdp", None)), "lm_head": wsc(params["lm_head"], ("fsdp", None)),
+            "layers": layers}
+
+
+def gather_fsdp(params: Dict[str, Any]) -> Dict[str, Any]:
+    """The layout the layers compute with: the ``fsdp`` axis gathered, tensor-parallel axes kept.
+    Called once per step, outside the microbatch loop, so the all-gather of the weights and
+    the reduction of their gradients each happen once per step."""
+    rl = mm_lib.relayout
+    layers = []
+    for p in params["layers"]:
+        layers.append({**p,
+                       "wqkv": rl(p["wqkv"], ("heads", None, None)),
+                       "wo": rl(p["wo"], (None, "heads")),
+                       "wgu": rl(p["wgu"], (None, "mlp", None)),
+                       "wdown": rl(p["wdown"], (None, "mlp"))})
+    return {**params, "embed": rl(params["embed"], (None, None)), "lm_head": rl(params["lm_head"], (None, None)),
+            "layers": layers}
+
+
 def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_batch: int, microbatch_size: int,
-                    schedule: Optional[str] = "1f1b", grad_dtype: torch.dtype = torch.float32) -> Callable:
+                    schedule: Optional[str] = "1f1b", grad_dtype: torch.dtype = torch.float32,
+                    fsdp: bool = False) -> Callable:
     """Builds ``step(params, opt_state, tokens, labels, cos, sin) -> (loss, params, opt_state)``.
 
     The loss is the mean token cross-entropy over the global batch; gradients are summed
@@ -186,6 +221,11 @@ def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_
     loss_scale = 1.0 / float(global_batch * seq_len)
 
     def step(params, opt_state, tokens, labels, cos, sin):
+        used = params
+        if fsdp:
+            params = annotate_fsdp(params)
+            used = gather_fsdp(params)
+
         def mb_loss(p, batch):
             tok, lab = batch
             return loss_fn(cfg, p, tok, lab, cos, sin, loss_scale)
@@ -194,7 +234,7 @@ def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_
         if microbatch_size < global_batch:
             vg = microbatch(vg, dim=0, size=microbatch_size, argnum=1, schedule=schedule,
                             accumulate_dtype=grad_dtype)
-        loss, grads = vg(params, (tokens, labels))
+        loss, grads = vg(used, (tokens, labels))
         with named_scope("optimizer"):
             new_step = opt_state["step"] + 1
             g_leaves, spec = pytree.tree_flatten(grads)
@@ -218,7 +258,7 @@ def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_
 
 def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                             logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
-                                                                       ("mlp", "model"))) -> None:
+                                                                       ("mlp", "model"), ("fsdp", "data"))) -> None:
     """Places layer ``i`` on pipeline stage ``i // (n_layers / num_stages)`` (mesh axis
     ``stage``), the embedding on the first stage and the head / loss on the last one. The
     optimiser update of a parameter runs where its gradient lives."""

@@ -511,5 +511,11 @@ FAST_OPS: Dict[str, object] = {
     "mm_ops.embedding_bwd.default": embedding_bwd_fast,
     "mm_ops.adamw.default": _adamw_fast,
 }
+# tensor operands (by position among the tensor arguments) that the fast variant overwrites
+INPLACE_OPERANDS: Dict[str, tuple] = {
+    "mm_ops.add_rmsnorm_bwd.default": (2,),
+    "mm_ops.attention.default": (0,),
+    "mm_ops.cross_entropy.default": (0,),
+}
 # operators whose fast variant can write into a gradient accumulator (acc=(buffer|None, dtype))
 ACC_FUSABLE = {"mm_ops.linear_wgrad.default", "mm_ops.embedding_bwd.default"}

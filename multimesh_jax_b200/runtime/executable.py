@@ -368,6 +368,8 @@ class Executable:
         fused = prog.fused_acc
         dying = self._dying_inputs.get(k, ())
         acc_dtypes = [DTYPE_FROM_NAME[self.plan["stores"][s]["shape"]["dtype"]] for s in out_ids]
+        stores = self.plan["stores"]
+        in_shapes = [tuple(stores[s]["shape"]["shard_size"]) for s in in_ids]
         arrival = self._arrival
         in_keys = [(buf[s], d) for s in in_ids] + [(buf[s], d) for s, m in zip(out_ids, modes) if m == 2]
 
@@ -394,6 +396,10 @@ class Executable:
             # inputs read for the last time here are handed over: the program frees each one
             # right after its last use instead of keeping it alive for the whole task
             ins = [tiles[s].pop(d) if s in dying else tiles[s][d] for s in in_ids]
+            for s, t_in, want in zip(in_ids, ins, in_shapes):
+                if tuple(t_in.shape) != want:
+                    raise RuntimeError(f"task {name}: store {s} ({stores[s]['shape']['key']}) holds a tile of shape "
+                                       f"{tuple(t_in.shape)} on device {d}, expected {want}")
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
             outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
