@@ -45,6 +45,9 @@ def parse_args():
     p.add_argument("--microbatch", type=int, default=4)
     p.add_argument("--layers", type=int, default=0, help="override the number of layers (debugging only)")
     p.add_argument("--tp", type=int, default=0, help="tensor-parallel degree (0 = default for N)")
+    p.add_argument("--dp", type=int, default=0, help="data-parallel degree (0 = default for N)")
+    p.add_argument("--pp", type=int, default=0, help="pipeline stages (0 = N / (tp * dp))")
+    p.add_argument("--fsdp", action="store_true", help="store parameters and optimizer state sharded over the data axis")
     p.add_argument("--schedule", default="1f1b")
     p.add_argument("--trace", default="", help="after the timed runs, profile one more step per rank and write "
                                                "its time breakdown to this directory (not a benchmark value)")
@@ -130,15 +133,20 @@ def main():
            "tiny": llama.LlamaConfig.tiny}[args.model]()
     if args.layers:
         cfg.n_layers = args.layers
-    tp = args.tp or {1: 1, 2: 1, 4: 2, 8: 2}.get(n, 1)
-    pp = n // tp
+    # default layouts: tensor parallel pairs first, then data parallel (no pipeline bubble), and
+    # the named 4-stage pipeline x TP2 configuration on 8 GPUs
+    tp = args.tp or {1: 1, 2: 2, 4: 2, 8: 2}.get(n, 1)
+    dp = args.dp or {4: 2}.get(n, 1)
+    pp = args.pp or n // (tp * dp)
+    if pp * dp * tp != n:
+        raise SystemExit(f"pp{pp} x dp{dp} x tp{tp} != {n} GPUs")
     seq = args.seq
     global_batch = args.per_gpu_batch * n
     mb = min(args.microbatch, global_batch)
     opt = llama.AdamWConfig()
     step_fn = llama.make_train_step(cfg, opt, seq_len=seq, global_batch=global_batch, microbatch_size=mb,
-                                    schedule=args.schedule)
-    mesh = mm.MultiMesh((pp, tp), ("stage", "model"))
+                                    schedule=args.schedule, fsdp=args.fsdp)
+    mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
     llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
 
     # abstract arguments for the capture; real tensors are created shard by shard below
@@ -157,7 +165,7 @@ def main():
     params, state = init_sharded_llama(cfg, exe, dev, seed=1234)
     cos, sin = llama.rope_tables(cfg, seq, dev)
 
-    g = torch.Generator().manual_seed(rank + 1)
+    g = torch.Generator().manual_seed(1)   # every rank draws the same global batch and keeps its own slice
     pool = min(24, args.warmup + 2 * args.steps)   # a fresh batch every step
     host_tok = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
     host_lab = [torch.randint(0, cfg.vocab, (global_batch, seq), generator=g).pin_memory() for _ in range(pool)]
@@ -242,7 +250,7 @@ def main():
             "config": {"model": f"{args.model} shape ({cfg.n_layers} layers, d_model {cfg.d_model}, "
                                 f"{cfg.n_heads}q/{cfg.n_kv_heads}kv heads, ffn {cfg.d_ff}, vocab {cfg.vocab})",
                        "global_batch": global_batch, "seq_len": seq, "microbatch": mb,
-                       "parallelism": f"pp{pp}xtp{tp}", "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
+                       "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
                        "l2": "working set (>= 13 GB of weights per step) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",

@@ -29,6 +29,8 @@ struct IndexClass {
   std::vector<std::pair<int, int>> members;  // (slot, dim); slot < #inputs: input, else output
   bool no_shard = false;                     // must stay unsharded (softmax dim, conv window ...)
   std::set<int> reduced_outputs;             // outputs (by index) in which this index is summed away
+  bool shares_axes = false;                  // may use a mesh axis that another class of the node uses
+                                             // (experts and tokens of an expert-parallel layer)
 };
 
 struct Rule {
@@ -269,6 +271,7 @@ bool RuleFromAttr(const Node& n, Rule* out) {
     for (auto& m : c.at("members").arr)
       ic.members.emplace_back(static_cast<int>(m.arr[0].as_int()), static_cast<int>(m.arr[1].as_int()));
     if (c.has("no_shard")) ic.no_shard = c.at("no_shard").as_bool();
+    if (c.has("shares_axes")) ic.shares_axes = c.at("shares_axes").as_bool();
     if (c.has("reduced_outputs"))
       for (auto v : c.at("reduced_outputs").as_int_vector()) ic.reduced_outputs.insert(static_cast<int>(v));
     r.classes.push_back(ic);
@@ -448,12 +451,13 @@ bool EvalNode(CompileState& s, const TaskGroup& grp, const TaskMeshInfo& mesh, N
       if (m.second >= static_cast<int>(v.shape.size()) || v.shape[m.second] % best) { class_axes[c].clear(); break; }
     }
   }
-  // a mesh axis may serve only one class of a node
+  // a mesh axis may serve only one class of a node (unless the class says otherwise)
   std::set<int> used;
-  for (auto& ax : class_axes) {
+  for (size_t c = 0; c < class_axes.size(); ++c) {
+    if (rule.classes[c].shares_axes) continue;
     std::vector<int> keep;
-    for (int a : ax) if (used.insert(a).second) keep.push_back(a);
-    ax = keep;
+    for (int a : class_axes[c]) if (used.insert(a).second) keep.push_back(a);
+    class_axes[c] = keep;
   }
   // write to members without sharding
   const int nslots = nin + static_cast<int>(n.outputs.size());
@@ -649,12 +653,13 @@ bool SpmdLowering(CompileState& s) {
               if (p > best_p) { best_p = p; best = sh->dim_axes[m.second]; }
             }
             bool ok = !best.empty();
-            for (int a : best) ok = ok && !used.count(a);
+            const bool shares = rule.classes[c].shares_axes;
+            for (int a : best) ok = ok && (shares || !used.count(a));
             for (auto& m : rule.classes[c].members) {
               const Value& v = g.value(slot_value(m.first));
               if (m.second >= static_cast<int>(v.shape.size()) || v.shape[m.second] % best_p) ok = false;
             }
-            if (ok) { class_axes[c] = best; for (int a : best) used.insert(a); }
+            if (ok) { class_axes[c] = best; if (!shares) for (int a : best) used.insert(a); }
           }
       }
       // required sharding of every input

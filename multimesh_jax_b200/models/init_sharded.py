@@ -13,6 +13,7 @@ import torch
 from torch.utils import _pytree as pytree
 
 from ..compiler.capture import DTYPE_FROM_NAME
+from ..runtime.collectives import tile_box
 from ..runtime.executable import Executable, ShardedTensor
 from . import llama
 
@@ -27,7 +28,10 @@ def _tile_like(sharding: dict, topo, fill, generator_seed: int) -> Dict[int, tor
         dev = topo.torch_device(d)
         shape = sharding["shard_size"]
         dtype = DTYPE_FROM_NAME[sharding["dtype"]]
-        tiles[d] = fill(shape, dtype, dev, generator_seed + 7919 * o)
+        # seeded by the tile's position in the array, so replicas of a tile start out identical
+        lo, _ = tile_box(sharding, o)
+        where = sum((int(x) + 1) * pr for x, pr in zip(lo, (7919, 104723, 1299709, 15485863, 32452843)))
+        tiles[d] = fill(shape, dtype, dev, generator_seed + where)
     return tiles
 
 
