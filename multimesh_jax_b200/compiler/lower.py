@@ -133,6 +133,16 @@ class TemplateProgram:
             elif kind == 5:  # local reshard
                 src, dst = ins.extra
                 env[ins.outs[0]] = ctx.spmd_reshard(env[ins.args], src, dst, ins.node_id)
+            elif kind == 8:  # operator whose per-device form exchanges data with other devices of the task
+                fn, axes = ins.extra
+                args = _materialize(ins.args, env, ctx)
+                res = fn(ctx, axes, ins.node_id, *args)
+                if ins.slots is None:
+                    env[ins.outs[0]] = res
+                else:
+                    for pos, slot in enumerate(ins.slots):
+                        if slot is not None:
+                            env[ins.outs[slot]] = res[pos]
             elif kind == 7:  # linear whose partial result is all-reduced: one fused kernel
                 axes, scale, is_dgrad = ins.extra
                 x, w = _materialize(ins.args, env, ctx)
@@ -221,6 +231,13 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                     else:
                         slots.append(None)
             instrs.append(Instr(0, fn, args, kwargs, n["outputs"], None if single else slots, nid))
+            shared = n["attrs"].get("shared_axes")
+            if shared is not None and not single_device and json.loads(shared):
+                from ..ops.moe import CTX_OPS
+                if op in CTX_OPS:
+                    instrs[-1].kind = 8
+                    instrs[-1].extra = (CTX_OPS[op][0], json.loads(shared))
+                    instrs[-1].static = False
             if fast_pending is not None:
                 fast_variants.append((instrs[-1],) + fast_pending)
             continue

@@ -65,7 +65,7 @@ bool IsConvert(const Node& n) { const std::string b = BaseOp(n.op); return b == 
 bool IsCollective(const Node& n) {
   return n.op == "mm.all_reduce" || n.op == "mm.all_gather" || n.op == "mm.reduce_scatter" ||
          n.op == "mm.all_to_all" || n.op == "mm.spmd_reshard" || StartsWith(n.op, "mm_ops.moe_dispatch") ||
-         StartsWith(n.op, "mm_ops.moe_combine");
+         StartsWith(n.op, "mm_ops.moe_combine") || StartsWith(n.op, "mm_ops.moe_ffn");
 }
 bool IsExpensive(const Node& n) {
   if (IsDot(n)) return true;

@@ -662,6 +662,14 @@ bool SpmdLowering(CompileState& s) {
             if (ok) { class_axes[c] = best; if (!shares) for (int a : best) used.insert(a); }
           }
       }
+      // operators whose per-device form exchanges data over a shared axis learn which axes
+      if (rule.known)
+        for (size_t c = 0; c < rule.classes.size(); ++c)
+          if (rule.classes[c].shares_axes) {
+            Json axes = Json::array();
+            for (int a : class_axes[c]) axes.push(Json::number(a));
+            g.node(id).attrs["shared_axes"] = axes.dump();
+          }
       // required sharding of every input
       for (int slot = 0; slot < nin; ++slot) {
         const int v = g.node(id).inputs[slot];

@@ -26,6 +26,7 @@ import torch
 from .. import lib as mm_lib
 from ..ops import kernels as K
 from ..ops import mm_ops  # noqa: F401  (registers the operators)
+from ..ops import moe as _moe  # noqa: F401  (registers the mixture-of-experts operators)
 from ..task import MultiMesh, Task, microbatch, named_scope, register_task, value_and_grad
 
 ops = torch.ops.mm_ops
@@ -42,6 +43,8 @@ class LlamaConfig:
     rope_theta: float = 1e4
     eps: float = 1e-5
     dtype: torch.dtype = torch.bfloat16
+    n_experts: int = 0      # > 0: every feed-forward block is a sparse mixture of SwiGLU experts
+    top_k: int = 2          # experts per token (softmax over the chosen router logits)
 
     @property
     def head_dim(self) -> int:
@@ -56,19 +59,33 @@ class LlamaConfig:
         return LlamaConfig(vocab=128256, n_kv_heads=8, d_ff=14336, rope_theta=5e5)
 
     @staticmethod
+    def mixtral_8x7b() -> "LlamaConfig":
+        return LlamaConfig(vocab=32000, n_kv_heads=8, d_ff=14336, rope_theta=1e6, n_experts=8, top_k=2)
+
+    @staticmethod
     def tiny(n_layers: int = 2, d_model: int = 256, n_heads: int = 2, n_kv_heads: int = 2, d_ff: int = 512,
-             vocab: int = 512) -> "LlamaConfig":
+             vocab: int = 512, n_experts: int = 0, top_k: int = 2) -> "LlamaConfig":
         return LlamaConfig(vocab=vocab, d_model=d_model, n_layers=n_layers, n_heads=n_heads, n_kv_heads=n_kv_heads,
-                           d_ff=d_ff)
+                           d_ff=d_ff, n_experts=n_experts, top_k=top_k)
 
     def num_params(self) -> int:
+        ffn = 3 * self.d_ff * self.d_model
+        if self.n_experts:
+            ffn = self.n_experts * ffn + self.n_experts * self.d_model
         per_layer = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim * self.d_model + self.d_model * self.d_model \
-            + 3 * self.d_ff * self.d_model + 2 * self.d_model
+            + ffn + 2 * self.d_model
         return self.n_layers * per_layer + 2 * self.vocab * self.d_model + self.d_model
+
+    def active_params(self) -> int:
+        """Parameters a token actually multiplies with (``top_k`` of the experts)."""
+        if not self.n_experts:
+            return self.num_params()
+        idle = (self.n_experts - self.top_k) * 3 * self.d_ff * self.d_model
+        return self.num_params() - self.n_layers * idle
 
     def flops_per_token(self, seq_len: int) -> float:
         """Training FLOPs per token (forward + backward = 3x forward), causal attention counted at half."""
-        dense = 2 * (self.num_params() - self.vocab * self.d_model)
+        dense = 2 * (self.active_params() - self.vocab * self.d_model)
         attn = 2 * 2 * seq_len * self.d_model * self.n_layers / 2
         return 3.0 * (dense + attn)
 
@@ -98,8 +115,11 @@ def init_params(cfg: LlamaConfig, device="cpu", seed: int = 0) -> Dict[str, Any]
             "wqkv": normal(H, Dh, D),
             "wo": normal(D, cfg.n_heads * Dh, std=0.02 / math.sqrt(2 * cfg.n_layers)),
             "ffn_norm": ones(D),
-            "wgu": normal(2, F, D),
-            "wdown": normal(D, F, std=0.02 / math.sqrt(2 * cfg.n_layers)),
+            **({"wgu": normal(2, F, D),
+                "wdown": normal(D, F, std=0.02 / math.sqrt(2 * cfg.n_layers))} if not cfg.n_experts else
+               {"router": normal(cfg.n_experts, D),
+                "wgu": normal(cfg.n_experts, 2, F, D),
+                "wdown": normal(cfg.n_experts, D, F, std=0.02 / math.sqrt(2 * cfg.n_layers))}),
         })
     return {"embed": normal(cfg.vocab, D), "layers": layers, "final_norm": ones(D), "lm_head": normal(cfg.vocab, D)}
 
@@ -118,6 +138,12 @@ def attention_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tenso
 
 
 def mlp_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor) -> torch.Tensor:
+    if cfg.n_experts:
+        # experts live on the devices of the `expert` logical axis; tokens stay where they are and
+        # travel to their experts and back inside the operator
+        wgu = mm_lib.with_sharding_constraint(p["wgu"], ("expert", None, None, None))
+        wdown = mm_lib.with_sharding_constraint(p["wdown"], ("expert", None, None))
+        return ops.moe_ffn(h, p["router"], wgu, wdown, cfg.top_k)
     gu = ops.linear(h, p["wgu"])                          # [B, S, 2, F]
     gu = mm_lib.with_sharding_constraint(gu, ("batch", None, None, "mlp"))
     return ops.linear(ops.swiglu(gu), p["wdown"])
@@ -258,7 +284,8 @@ def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_
 
 def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                             logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
-                                                                       ("mlp", "model"), ("fsdp", "data"))) -> None:
+                                                                       ("mlp", "model"), ("fsdp", "data"),
+                                                                       ("expert", "data"))) -> None:
     """Places layer ``i`` on pipeline stage ``i // (n_layers / num_stages)`` (mesh axis
     ``stage``), the embedding on the first stage and the head / loss on the last one. The
     optimiser update of a parameter runs where its gradient lives."""

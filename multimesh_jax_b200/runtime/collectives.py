@@ -183,6 +183,37 @@ class DeviceCtx:
         parts = self.rendezvous.exchange((self.key_prefix, key, tuple(group_ordinals)), group_ordinals, me, tensor)
         return [p.to(self.torch_device) if p.device != self.torch_device else p for p in parts]
 
+    def group_of(self, axes: Sequence[int]) -> Tuple[List[int], int]:
+        """Ordinals of the devices that differ from this one along ``axes`` only, and this
+        device's position among them."""
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        return group, group.index(me)
+
+    def all_to_all(self, key, group: List[int], rows: torch.Tensor, counts: List[int]
+                   ) -> Tuple[torch.Tensor, List[int]]:
+        """``rows`` holds, back to back, ``counts[r]`` rows for every member ``r`` of ``group``.
+        Returns the rows this device receives (ordered by sender) and how many each sender sent."""
+        me = self.device - self.device_start
+        topo = self.topology
+        if topo.kind == "dist":
+            import torch.distributed as dist
+            pg = topo.process_group([self.device_start + o for o in group])
+            cnt = torch.tensor(counts, dtype=torch.int64, device=rows.device)
+            got = torch.empty_like(cnt)
+            dist.all_to_all_single(got, cnt, group=pg)
+            recv_counts = [int(c) for c in got.tolist()]
+            out = rows.new_empty((sum(recv_counts),) + tuple(rows.shape[1:]))
+            dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=recv_counts, input_split_sizes=list(counts),
+                                   group=pg)
+            return out, recv_counts
+        pieces = list(torch.split(rows, list(counts)))
+        everyone = self.rendezvous.exchange((self.key_prefix, "a2a", key, tuple(group)), group, me, pieces)
+        my = group.index(me)
+        mine = [everyone[s][my] for s in range(len(group))]
+        mine = [p.to(self.torch_device) if p.device != self.torch_device else p for p in mine]
+        return torch.cat(mine, dim=0), [int(p.shape[0]) for p in mine]
+
     def all_reduce(self, x: torch.Tensor, axes: Sequence[int], key) -> torch.Tensor:
         me = self.device - self.device_start
         group = mesh_group(me, self.mesh_dims, list(axes))

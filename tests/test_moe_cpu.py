@@ -1,0 +1,83 @@
+"""Mixture-of-experts layer: the operator pair against autograd through a dense restatement,
+and the compiled Mixtral-shaped step with expert parallelism (experts and tokens share the
+`data` mesh axis; dispatch and combine run inside the task) against the eager step."""
+import pytest
+import torch
+from torch.utils import _pytree as pytree
+
+import multimesh_jax_b200 as mm
+from multimesh_jax_b200.models import llama
+from multimesh_jax_b200.ops import moe
+
+
+def _dense_moe(x, wr, wgu, wdown, top_k):
+    T, D = x.shape
+    logits = x @ wr.t()
+    topv, topi = logits.topk(top_k, dim=-1)
+    gates = torch.softmax(topv, dim=-1)
+    y = torch.zeros_like(x)
+    for e in range(wgu.shape[0]):
+        gu = torch.einsum("td,gfd->tgf", x, wgu[e])
+        out = (torch.nn.functional.silu(gu[:, 0]) * gu[:, 1]) @ wdown[e].t()
+        w = (gates * (topi == e)).sum(-1, keepdim=True)      # zero for tokens that did not pick e
+        y = y + w * out
+    return y
+
+
+def test_moe_operator_matches_dense_autograd():
+    torch.manual_seed(0)
+    T, D, F, E, k = 24, 16, 20, 4, 2
+    x = torch.randn(T, D, requires_grad=True)
+    wr = torch.randn(E, D, requires_grad=True)
+    wgu = (torch.randn(E, 2, F, D) * 0.3).requires_grad_(True)
+    wdown = (torch.randn(E, D, F) * 0.3).requires_grad_(True)
+    dy = torch.randn(T, D)
+    y = moe.moe_ffn(x, wr, wgu, wdown, k)
+    grads = torch.autograd.grad(y, (x, wr, wgu, wdown), dy)
+    y_ref = _dense_moe(x, wr, wgu, wdown, k)
+    grads_ref = torch.autograd.grad(y_ref, (x, wr, wgu, wdown), dy)
+    torch.testing.assert_close(y, y_ref, rtol=1e-4, atol=1e-5)
+    for g, r in zip(grads, grads_ref):
+        torch.testing.assert_close(g, r, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("axes", [(1, 2, 1), (1, 4, 1), (2, 2, 2)])
+def test_expert_parallel_step_matches_eager(axes):
+    pp = axes[0]
+    cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128,
+                                 n_experts=4, top_k=2)
+    cfg.dtype = torch.float32
+    B, S, MB = 8, 16, 4
+    torch.manual_seed(0)
+    params = llama.init_params(cfg)
+    opt_state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB)
+    mesh = mm.MultiMesh(axes, ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+    with mesh:
+        exe = mm.compile_function(step, (params, opt_state, tokens, labels, cos, sin), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(params, opt_state, tokens, labels, cos, sin)
+    loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)
+    # experts are spread over the data axis of every stage; the router is not
+    data_axis = list(mesh.slice(stage=0).axis_names).index("data")
+    assert p_mm["layers"][0]["wgu"].sharding["dim_axes"][0] == [data_axis]
+    assert p_mm["layers"][0]["wdown"].sharding["dim_axes"][0] == [data_axis]
+    assert p_mm["layers"][0]["router"].sharding["dim_axes"] == [[], []]
+    g = exe.cap.graph
+    shared = [g.node(n)["attrs"].get("shared_axes") for t in exe.plan["templates"] for n in t["nodes"]
+              if g.node(n)["op"].startswith("mm_ops.moe_ffn")]
+    assert shared and all(s == f"[{data_axis}]" for s in shared)
+    exe.shutdown()
+
+
+def test_mixtral_shape_parameter_count():
+    cfg = llama.LlamaConfig.mixtral_8x7b()
+    assert abs(cfg.num_params() / 1e9 - 46.7) < 0.5       # 8x7B has about 46.7 B parameters
+    assert abs(cfg.active_params() / 1e9 - 12.9) < 0.5     # about 12.9 B of them touch each token
