@@ -324,7 +324,8 @@ ShardedShape FromAxes(const Value& v, const TaskMeshInfo& m) {
   for (size_t d = 0; d < v.axes.size(); ++d)
     for (auto& name : v.axes[d])
       for (size_t a = 0; a < m.names.size(); ++a)
-        if (m.names[a] == name && !used[a] && v.shape[d] % (static_cast<int64_t>(s.Shards(static_cast<int>(d))) * m.dims[a]) == 0) {
+        if (m.names[a] == name && !used[a] && m.dims[a] > 1 &&
+            v.shape[d] % (static_cast<int64_t>(s.Shards(static_cast<int>(d))) * m.dims[a]) == 0) {
           s.dim_axes[d].push_back(static_cast<int>(a));
           used[a] = true;
         }

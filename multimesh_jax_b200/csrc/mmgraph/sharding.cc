@@ -277,7 +277,9 @@ ShardedShape LogicalToPhysical(DType dtype, const std::vector<int64_t>& sizes,
   for (auto& la : logical_axes) {
     int axis = -1;
     for (size_t i = 0; i < mesh_axis_names.size(); ++i) if (mesh_axis_names[i] == la.second) axis = static_cast<int>(i);
-    if (axis < 0 || used[axis]) continue;
+    // an axis with a single device shards nothing: listing it would only make equal layouts
+    // look different
+    if (axis < 0 || used[axis] || mesh_dims[axis] == 1) continue;
     for (size_t d = 0; d < sizes.size() && d < axes.size(); ++d) {
       if (std::find(axes[d].begin(), axes[d].end(), la.first) == axes[d].end()) continue;
       const int64_t shards = static_cast<int64_t>(s.Shards(static_cast<int>(d))) * mesh_dims[axis];

@@ -1,0 +1,103 @@
+"""One kernel, one small case, three launches - the program to put under a profiler.
+
+    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
+
+Inputs are larger than the 126 MB L2 where the kernel is memory bound and a few hundred MB at
+most, so a full-metric capture of one launch finishes in seconds. Each case prints its
+CUDA-event time (after one warm-up launch) and the algorithmic FLOPs / bytes, so that the
+numbers in a profile can be checked against an unprofiled run of the same command.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from . import attention
+from . import kernels as K
+
+
+def _time(fn, launches=2):
+    fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(launches):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / launches
+
+
+def main(argv=None) -> int:
+    case = (argv or sys.argv[1:] or ["gemm"])[0]
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    out = {"case": case}
+    if case in ("gemm", "gemm_dgrad", "gemm_wgrad"):
+        M, N, Kd = 8192, 4096, 4096
+        if case == "gemm":          # y = x w^T
+            a = torch.randn(M, Kd, device=dev).bfloat16()
+            b = torch.randn(N, Kd, device=dev).bfloat16()
+            fn = lambda: K.linear_fwd(a, b)
+        elif case == "gemm_dgrad":  # dx = dy w
+            a = torch.randn(M, N, device=dev).bfloat16()
+            b = torch.randn(N, Kd, device=dev).bfloat16()
+            fn = lambda: K.linear_dgrad(a, b)
+        else:                       # dw += dy^T x, fp32 accumulator
+            a = torch.randn(M, N, device=dev).bfloat16()
+            b = torch.randn(M, Kd, device=dev).bfloat16()
+            acc = torch.zeros(N, Kd, device=dev, dtype=torch.float32)
+            fn = lambda: K.linear_wgrad(a, b, out=acc, accumulate=True)
+        ms = _time(fn)
+        out.update(shape=[M, N, Kd], ms=ms, tflops=2.0 * M * N * Kd / ms / 1e9)
+    elif case in ("flash_fwd", "flash_bwd"):
+        B, S, H, D = 2, 2048, 16, 128
+        qkv = (torch.randn(B, S, 3 * H, D, device=dev) * 0.5).bfloat16()
+        o, lse = attention.attention_fwd_packed(qkv, 1)
+        if case == "flash_fwd":
+            ms = _time(lambda: attention.attention_fwd_packed(qkv, 1))
+            flops = 4.0 * B * H * S * S * D / 2
+        else:
+            do = torch.randn_like(o)
+            ms = _time(lambda: attention.attention_bwd_packed(do, qkv, o, lse, 1))
+            flops = 10.0 * B * H * S * S * D / 2
+        out.update(shape=[B, S, H, D], ms=ms, tflops=flops / ms / 1e9)
+    elif case == "rmsnorm_bwd":
+        T, D = 32768, 4096
+        x = torch.randn(T, D, device=dev).bfloat16()
+        w = torch.ones(D, device=dev).bfloat16()
+        dy = torch.randn(T, D, device=dev).bfloat16()
+        _, rstd = K.rmsnorm_fwd(x, w, 1e-5)
+        ms = _time(lambda: K.rmsnorm_bwd(x, w, dy, rstd))
+        out.update(shape=[T, D], ms=ms, gbs=3.0 * T * D * 2 / ms / 1e6)
+    elif case == "swiglu":
+        T, F = 16384, 11008
+        gu = torch.randn(T, 2 * F, device=dev).bfloat16()
+        ms = _time(lambda: K.swiglu_fwd(gu))
+        out.update(shape=[T, F], ms=ms, gbs=3.0 * T * F * 2 / ms / 1e6)
+    elif case == "adamw":
+        n = 64 << 20
+        master = torch.randn(n, device=dev)
+        p = master.bfloat16()
+        m, v, g = torch.zeros_like(master), torch.zeros_like(master), torch.randn(n, device=dev)
+        step = torch.ones(1, dtype=torch.int64, device=dev)
+        ms = _time(lambda: K.adamw_step_(master, p, m, v, g, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                                         step=step))
+        out.update(shape=[n], ms=ms, gbs=n * (4 * 4 + 3 * 4 + 2) / ms / 1e6)
+    elif case == "cross_entropy":
+        T, V = 8192, 32000
+        logits = torch.randn(T, V, device=dev).bfloat16()
+        tgt = torch.randint(0, V, (T,), device=dev)
+        ms = _time(lambda: K.cross_entropy_fwd_bwd(logits.clone(), tgt, 1.0 / T))
+        out.update(shape=[T, V], ms=ms)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    out["kernel_status"] = K.read_status()
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
