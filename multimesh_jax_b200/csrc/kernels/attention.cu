@@ -17,8 +17,9 @@
 //        dQ^T = K^T dS^T is read back each step and added to an fp32 dQ buffer with
 //        coalesced atomics (red.global.add.f32).
 //
-// Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
-// warps 2..5 = softmax / epilogue (TMEM lane quarter = warp % 4). All waits are bounded.
+// Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, the
+// others = softmax / epilogue (TMEM lane quarter = warp % 4; four warps forward, eight - two per
+// quarter, splitting the columns - backward). All waits are bounded.
 #include <math.h>
 
 #include "host_common.h"
@@ -303,7 +304,8 @@ struct FaBwdParams {
   float scale, scale_log2;
 };
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+constexpr int FB_THREADS = 320;   // TMA warp, MMA warp, eight compute warps
+__global__ void __launch_bounds__(FB_THREADS, 1)
     flash_bwd_kernel(const __grid_constant__ CUtensorMap tmKV, const __grid_constant__ CUtensorMap tmQ,
                      const __grid_constant__ CUtensorMap tmDO, FaBwdParams p, int* __restrict__ err) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -345,13 +347,13 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&st_full[i], 1);
-      mbar_init(&st_free[i], 4);
+      mbar_init(&st_free[i], 8);
     }
     mbar_init(dpt_full, 1);
-    mbar_init(dpt_free, 4);
-    mbar_init(ps_ready, 4);
+    mbar_init(dpt_free, 8);
+    mbar_init(ps_ready, 8);
     mbar_init(dqt_full, 1);
-    mbar_init(dqt_free, 4);
+    mbar_init(dqt_free, 8);
     fence_barrier_init();
     tma_prefetch_desc(&tmKV);
     tma_prefetch_desc(&tmQ);
@@ -460,78 +462,75 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       }
     }
   } else {
+    // Eight compute warps: two per TMEM lane quarter, each handling 32 of the step's 64 query
+    // columns, so the serial chain per step (TMEM load, exp, products, shared-memory stores,
+    // reductions) is half as long as with one warp per quarter.
     const int q = warp & 3;
+    const int half = (warp - 2) >> 2;      // 0: query columns 0..31 of the step, 1: columns 32..63
     const int t = q * 32 + lane;           // key row of this thread (also the d index for dQ^T)
     const int kvg = jb * FB_BKV + t;
     const uint32_t lane_bits = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t col_off = static_cast<uint32_t>(half * 32);
     const float log2e = 1.4426950408889634f;
     bool ok = true;
-    uint32_t dq_regs[64];
+    uint32_t dq_regs[32];
     int prev_hq = 0, prev_i = 0;
     auto flush_dq = [&](int hq, int i) {
       // lane = d: 32 consecutive floats per warp and query row -> one 128-byte reduction
-      float* base = p.dq_acc + ((static_cast<int64_t>(b) * p.S + i * FB_BQ) * Hq + hq) * FA_D + t;
+      float* base = p.dq_acc + ((static_cast<int64_t>(b) * p.S + i * FB_BQ + half * 32) * Hq + hq) * FA_D + t;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) atomicAdd(base + static_cast<int64_t>(c) * Hq * FA_D, __uint_as_float(dq_regs[c]));
+      for (int c = 0; c < 32; ++c) atomicAdd(base + static_cast<int64_t>(c) * Hq * FA_D, __uint_as_float(dq_regs[c]));
     };
     for (int n = 0; n < nsteps; ++n) {
       const int sb = n & 1;
       const int r = n / nq, i = i0 + (n - r * nq);
       const int hq = g * p.rep + r;
-      const float* lse_row = p.lse + (static_cast<int64_t>(b) * Hq + hq) * p.S + i * FB_BQ;
-      const float* delta_row = p.delta + (static_cast<int64_t>(b) * Hq + hq) * p.S + i * FB_BQ;
+      const int qcol0 = i * FB_BQ + half * 32;   // first query row (global) of this warp's columns
+      const float* lse_row = p.lse + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
+      const float* delta_row = p.delta + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
       const bool diag = i < i0 + FB_BKV / FB_BQ;
       // ---- P^T
       if (ok && !mbar_wait(&st_full[sb], (n >> 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
       tc_fence_after();
-      uint32_t pk[32], dsk[32];
+      uint32_t pk[16], dsk[16];
       {
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32(tST + lane_bits + sb * FB_BQ, s0);
-        tmem_ld_32x32(tST + lane_bits + sb * FB_BQ + 32, s1);
+        uint32_t s0[32];
+        tmem_ld_32x32(tST + lane_bits + sb * FB_BQ + col_off, s0);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&st_free[sb]);
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
+        for (int c4 = 0; c4 < 8; ++c4) {
           const float4 ls = __ldg(reinterpret_cast<const float4*>(lse_row) + c4);
           const float lv[4] = {ls.x, ls.y, ls.z, ls.w};
-          float e[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int c = c4 * 4 + u;
-            const float sv = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
-            e[u] = exp2f(sv * p.scale_log2 - lv[u] * log2e);
-            if (diag && kvg > i * FB_BQ + c) e[u] = 0.f;
+            float e = exp2f(__uint_as_float(s0[c]) * p.scale_log2 - lv[u] * log2e);
+            if (diag && kvg > qcol0 + c) e = 0.f;
+            s0[c] = __float_as_uint(e);
           }
-          // keep p in fp32 bit form in place for the dS step, pack later
-          if (c4 < 8) { s0[c4 * 4] = __float_as_uint(e[0]); s0[c4 * 4 + 1] = __float_as_uint(e[1]);
-                        s0[c4 * 4 + 2] = __float_as_uint(e[2]); s0[c4 * 4 + 3] = __float_as_uint(e[3]); }
-          else { s1[(c4 - 8) * 4] = __float_as_uint(e[0]); s1[(c4 - 8) * 4 + 1] = __float_as_uint(e[1]);
-                 s1[(c4 - 8) * 4 + 2] = __float_as_uint(e[2]); s1[(c4 - 8) * 4 + 3] = __float_as_uint(e[3]); }
         }
         // ---- dS^T
         if (ok && !mbar_wait(dpt_full, n & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
         tc_fence_after();
-        uint32_t d0[32], d1[32];
-        tmem_ld_32x32(tDPT + lane_bits, d0);
-        tmem_ld_32x32(tDPT + lane_bits + 32, d1);
+        uint32_t d0[32];
+        tmem_ld_32x32(tDPT + lane_bits + col_off, d0);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(dpt_free);
 #pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
+        for (int c4 = 0; c4 < 8; ++c4) {
           const float4 dl = __ldg(reinterpret_cast<const float4*>(delta_row) + c4);
           const float dv[4] = {dl.x, dl.y, dl.z, dl.w};
           float pe[4], de[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int c = c4 * 4 + u;
-            pe[u] = __uint_as_float(c < 32 ? s0[c] : s1[c - 32]);
-            const float dp = __uint_as_float(c < 32 ? d0[c] : d1[c - 32]);
-            de[u] = pe[u] * (dp - dv[u]) * p.scale;
+            pe[u] = __uint_as_float(s0[c]);
+            de[u] = pe[u] * (__uint_as_float(d0[c]) - dv[u]) * p.scale;
           }
           pk[c4 * 2] = pack_bf16(pe[0], pe[1]);
           pk[c4 * 2 + 1] = pack_bf16(pe[2], pe[3]);
@@ -543,22 +542,18 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       if (n > 0) {
         if (ok && !mbar_wait(dqt_full, (n - 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
         tc_fence_after();
-        uint32_t a0[32], a1[32];
-        tmem_ld_32x32(tDQT + lane_bits, a0);
-        tmem_ld_32x32(tDQT + lane_bits + 32, a1);
+        tmem_ld_32x32(tDQT + lane_bits + col_off, dq_regs);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(dqt_free);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) { dq_regs[c] = a0[c]; dq_regs[32 + c] = a1[c]; }
       }
-      // ---- publish P^T and dS^T
+      // ---- publish this warp's 32 columns (four 16-byte units per row) of P^T and dS^T
       uint8_t* prow = sPT + t * 128;
       uint8_t* drow = sDST + t * 128;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const int phys = (ch ^ (t & 7)) * 16;
+      for (int ch = 0; ch < 4; ++ch) {
+        const int phys = ((half * 4 + ch) ^ (t & 7)) * 16;
         *reinterpret_cast<uint4*>(prow + phys) = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
         *reinterpret_cast<uint4*>(drow + phys) = make_uint4(dsk[ch * 4], dsk[ch * 4 + 1], dsk[ch * 4 + 2], dsk[ch * 4 + 3]);
       }
@@ -573,15 +568,9 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     // last dQ^T, then the dK / dV accumulators
     if (ok && !mbar_wait(dqt_full, (nsteps - 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
     tc_fence_after();
-    {
-      uint32_t a0[32], a1[32];
-      tmem_ld_32x32(tDQT + lane_bits, a0);
-      tmem_ld_32x32(tDQT + lane_bits + 32, a1);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) { dq_regs[c] = a0[c]; dq_regs[32 + c] = a1[c]; }
-      if (ok) flush_dq(prev_hq, prev_i);
-    }
+    tmem_ld_32x32(tDQT + lane_bits + col_off, dq_regs);
+    tmem_ld_wait();
+    if (ok) flush_dq(prev_hq, prev_i);
     const int Hp = p.Hkv * (p.rep + 2);
     __nv_bfloat16* krow = p.dqkv + ((static_cast<int64_t>(b) * p.S + kvg) * Hp + hp_k) * FA_D;
     __nv_bfloat16* vrow = krow + FA_D;
@@ -590,7 +579,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       const uint32_t tsrc = which ? tDV : tDK;
       __nv_bfloat16* dst_row = which ? vrow : krow;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {     // this warp's half of the 128 columns
+        const int c = half * 2 + cc;
         uint32_t o[32];
         tmem_ld_32x32(tsrc + lane_bits + c * 32, o);
         tmem_ld_wait();
@@ -753,7 +743,7 @@ int mm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const 
   p.scale = 1.f / sqrtf(static_cast<float>(D));
   p.scale_log2 = p.scale * 1.4426950408889634f;
   dim3 grid(S / FB_BKV, Hkv, B);
-  flash_bwd_kernel<<<grid, FA_THREADS, FB_SMEM, stream>>>(tmKV, tmQ, tmDO, p, ds->status);
+  flash_bwd_kernel<<<grid, FB_THREADS, FB_SMEM, stream>>>(tmKV, tmQ, tmDO, p, ds->status);
   {
     const int threads = 256;
     const int64_t n = rows * (FA_D / 8);

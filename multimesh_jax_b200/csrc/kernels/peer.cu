@@ -111,6 +111,31 @@ __global__ void wait_flag_kernel(const int* flag, int value, int* err) {
   wait_flag_ge(flag, value, err);
 }
 
+// Up to eight flags at once. The wait is bounded by wall-clock time (the global timer), not
+// by a poll count: stage-boundary hand-offs may legitimately wait for a pipeline bubble.
+struct FlagList {
+  int* flag[8];
+  int n;
+};
+__global__ void set_flags_kernel(FlagList f, int value) {
+  __threadfence_system();
+  if (threadIdx.x < f.n) st_release_sys(f.flag[threadIdx.x], value);
+}
+__global__ void wait_flags_timeout_kernel(FlagList f, int value, unsigned long long limit_ns, int* err) {
+  if (threadIdx.x >= f.n) return;
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (;;) {
+    if (ld_acquire_sys(f.flag[threadIdx.x]) >= value) return;
+    __nanosleep(200);
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (t - t0 > limit_ns || *reinterpret_cast<volatile int*>(err) != 0) {
+      atomicCAS(err, 0, MM_ERR_WAIT_PEER);
+      return;
+    }
+  }
+}
+
 }  // namespace mm
 
 extern "C" {
@@ -211,6 +236,34 @@ int mm_wait_flag(const void* flag, int value, cudaStream_t stream) {
   DeviceState* ds = device_state();
   if (!ds) return -1;
   wait_flag_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<const int*>(flag), value, ds->status);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Raises up to eight flags (local or peer addresses) to `value` after all earlier work of
+// the stream.
+int mm_set_flags(const int64_t* flags, int n, int value, cudaStream_t stream) {
+  if (n < 1) return 0;
+  if (n > 8) return -2;
+  FlagList f;
+  f.n = n;
+  for (int i = 0; i < n; ++i) f.flag[i] = reinterpret_cast<int*>(flags[i]);
+  set_flags_kernel<<<1, 32, 0, stream>>>(f, value);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+// Holds the stream until up to eight local flags are >= `value`, for at most `limit_ms`
+// milliseconds; on expiry the status word gets MM_ERR_WAIT_PEER and the stream continues.
+int mm_wait_flags(const int64_t* flags, int n, int value, int limit_ms, cudaStream_t stream) {
+  if (n < 1) return 0;
+  if (n > 8) return -2;
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  FlagList f;
+  f.n = n;
+  for (int i = 0; i < n; ++i) f.flag[i] = reinterpret_cast<int*>(flags[i]);
+  wait_flags_timeout_kernel<<<1, 32, 0, stream>>>(f, value, static_cast<unsigned long long>(limit_ms) * 1000000ull,
+                                                  ds->status);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -121,3 +121,130 @@ def run_reshard_dist(topo, device: int, src_tile: Optional[torch.Tensor], send_c
         keep.append(out)
     comm.pending.append((ev, keep))
     return out, ev
+
+
+class PeerReshard:
+    """Cross-submesh reshards of a one-process-per-GPU job through peer-mapped memory.
+
+    Every distinct (source buffer, destination buffer) pair of the plan owns two staging
+    tiles in the symmetric arena plus ready / done flags. A source rank copies its tile into
+    the staging tile of the use's parity and raises the ready flags of the ranks that read
+    from it; a destination rank waits for its sources' flags and runs the pull kernel, which
+    reads the source tiles straight from peer HBM over NVLink and writes the destination
+    layout in one pass (no NCCL call, no intermediate receive buffer), then raises the done
+    flags that let the sources reuse the staging tile two uses later. Everything runs on the
+    side stream; waits are bounded by wall-clock time and report through the status word."""
+
+    MIN_BYTES = 64 << 10
+
+    def __init__(self, arena, topo, plan: dict, buffer_of: Dict[int, int], reshard_plan_of):
+        from . import symm
+        self.arena, self.topo, self.symm = arena, topo, symm
+        self.slots: Dict[tuple, dict] = {}
+        self.bytes = 0
+        for op in plan["ops"]:
+            if op["kind"] != "reshard":
+                continue
+            key = (buffer_of[op["src_store"]], buffer_of[op["dst_store"]])
+            if key in self.slots:
+                continue
+            src, dst = plan["stores"][op["src_store"]]["shape"], plan["stores"][op["dst_store"]]["shape"]
+            rplan = reshard_plan_of(op["src_store"], op["dst_store"])
+            if not self.pullable(rplan, src, dst):
+                self.slots[key] = None
+                continue
+            dtype = DTYPE_FROM_NAME[src["dtype"]]
+            srcs = list(range(src["device_start"], src["device_start"] + src["num_devices"]))
+            dsts = list(range(dst["device_start"], dst["device_start"] + dst["num_devices"]))
+            slot = {"stage": [arena.alloc(src["shard_size"], dtype) for _ in range(2)],
+                    "ready": [[arena.alloc_flag() for _ in srcs] for _ in range(2)],
+                    "done": [[arena.alloc_flag() for _ in dsts] for _ in range(2)],
+                    "srcs": srcs, "dsts": dsts, "uses": 0}
+            self.slots[key] = slot
+            n = 1
+            for s in src["shard_size"]:
+                n *= s
+            self.bytes += 2 * n * dtype.itemsize
+
+    @classmethod
+    def required_bytes(cls, plan: dict, buffer_of: Dict[int, int]) -> int:
+        """Upper bound of the arena space the staging tiles of ``plan`` need."""
+        seen, total = set(), 0
+        for op in plan["ops"]:
+            if op["kind"] != "reshard":
+                continue
+            key = (buffer_of[op["src_store"]], buffer_of[op["dst_store"]])
+            if key in seen:
+                continue
+            seen.add(key)
+            src = plan["stores"][op["src_store"]]["shape"]
+            n = DTYPE_FROM_NAME[src["dtype"]].itemsize
+            for s in src["shard_size"]:
+                n *= s
+            total += 2 * ((n + 1023) // 1024 * 1024)
+        return total
+
+    @classmethod
+    def pullable(cls, rplan: dict, src: dict, dst: dict) -> bool:
+        """Tiles the pull kernel can move: 16-byte aligned rows, at most four dimensions that
+        do not merge, and large enough for a kernel of its own to pay off."""
+        esz = DTYPE_FROM_NAME[src["dtype"]].itemsize
+        sshape, dshape = list(src["shard_size"]), list(dst["shard_size"])
+        if not sshape or not rplan["chunks"]:
+            return False
+        n = esz
+        for s in sshape:
+            n *= s
+        if n < cls.MIN_BYTES or (sshape[-1] * esz) % 16 or (dshape[-1] * esz) % 16:
+            return False
+        from .symm import build_pull_chunks
+        try:
+            recs = build_pull_chunks(rplan["chunks"], sshape, dshape, lambda d: 0, 0, esz)
+        except NotImplementedError:
+            return False
+        for r in recs:
+            ext, ss, ds = r[2:6], r[6:10], r[10:14]
+            if (r[0] % 16) or (r[1] % 16) or (ext[3] * esz) % 16:
+                return False
+            for k in range(3):
+                if ext[k] > 1 and ((ss[k] * esz) % 16 or (ds[k] * esz) % 16):
+                    return False
+        return True
+
+    def run(self, key, d: int, src_tile: Optional[torch.Tensor], chunks: List[dict], src: dict, dst: dict,
+            comm: CommStream):
+        """This rank's part of one use of ``key``. Returns ``(destination tile or None, event)``."""
+        symm, arena, slot = self.symm, self.arena, self.slots[key]
+        slot["uses"] += 1
+        e = slot["uses"]
+        par = e & 1
+        mine_src = [c for c in chunks if c["src_device"] == d]
+        mine_dst = [c for c in chunks if c["dst_device"] == d]
+        dev = self.topo.torch_device(d)
+        esz = DTYPE_FROM_NAME[src["dtype"]].itemsize
+        out = None
+        if mine_dst:
+            out = torch.empty(dst["shard_size"], dtype=DTYPE_FROM_NAME[dst["dtype"]], device=dev)
+        comm.reap()
+        comm.stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(comm.stream):
+            if mine_src:
+                readers = sorted({c["dst_device"] for c in mine_src})
+                if e > 2:   # the staging tile of this parity was last read in use e - 2
+                    symm.wait_flags(arena, [arena.flag_ptr(d, slot["done"][par][slot["dsts"].index(r)]) for r in readers],
+                                    e - 2)
+                slot["stage"][par].peer(d).copy_(src_tile)
+                symm.set_flags(arena, [arena.flag_ptr(r, slot["ready"][par][slot["srcs"].index(d)]) for r in readers], e)
+            if mine_dst:
+                writers = sorted({c["src_device"] for c in mine_dst})
+                symm.wait_flags(arena, [arena.flag_ptr(d, slot["ready"][par][slot["srcs"].index(w)]) for w in writers], e)
+                recs = symm.build_pull_chunks(mine_dst, list(src["shard_size"]), list(dst["shard_size"]),
+                                              lambda dd: slot["stage"][par].ptr(dd), out.data_ptr(), esz)
+                done = [arena.flag_ptr(w, slot["done"][par][slot["dsts"].index(d)]) for w in writers]
+                for i in range(0, len(recs), 64):
+                    last = i + 64 >= len(recs)
+                    symm.reshard_pull(recs[i:i + 64], esz, arena, done_flags=done if last else (), done_value=e)
+            ev = torch.cuda.Event()
+            ev.record(comm.stream)
+        comm.pending.append((ev, [t for t in (src_tile, out) if t is not None]))
+        return out, ev

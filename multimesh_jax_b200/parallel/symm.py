@@ -35,6 +35,8 @@ _lib.register("mm_reshard_pull", c_int, [c_void_p, c_int, c_int, c_void_p, c_int
                                          c_void_p, c_int, c_void_p])
 _lib.register("mm_set_flag", c_int, [c_void_p, c_int, c_void_p])
 _lib.register("mm_wait_flag", c_int, [c_void_p, c_int, c_void_p])
+_lib.register("mm_set_flags", c_int, [c_void_p, c_int, c_int, c_void_p])
+_lib.register("mm_wait_flags", c_int, [c_void_p, c_int, c_int, c_int, c_void_p])
 
 
 class _RawCudaBuffer:
@@ -226,3 +228,23 @@ def reshard_pull(records: List[List[int]], elem_size: int, arena: SymmetricArena
                              torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "mm_reshard_pull")
     K._count()
+
+
+def set_flags(arena: SymmetricArena, ptrs: Sequence[int], value: int) -> None:
+    """Raises the flags at ``ptrs`` (local or peer addresses) after the stream's earlier work."""
+    for i in range(0, len(ptrs), 8):
+        part = list(ptrs[i:i + 8])
+        arr = (c_int64 * len(part))(*part)
+        _lib.check(arena.lib.mm_set_flags(arr, len(part), value, torch.cuda.current_stream().cuda_stream), "mm_set_flags")
+        K._count()
+
+
+def wait_flags(arena: SymmetricArena, ptrs: Sequence[int], value: int, limit_ms: int = 30000) -> None:
+    """Holds the current stream until the local flags at ``ptrs`` reach ``value`` (bounded by
+    ``limit_ms`` of wall-clock time, after which the device status word records the expiry)."""
+    for i in range(0, len(ptrs), 8):
+        part = list(ptrs[i:i + 8])
+        arr = (c_int64 * len(part))(*part)
+        _lib.check(arena.lib.mm_wait_flags(arr, len(part), value, limit_ms, torch.cuda.current_stream().cuda_stream),
+                   "mm_wait_flags")
+        K._count()

@@ -157,7 +157,6 @@ class Executable:
         self.rendezvous = Rendezvous()
         self.dev_ctx = {d: DeviceCtx(topology, d, self.rendezvous) for d in topology.local_devices}
         topology.prepare_groups(sorted({(t["device_start"], tuple(t["mesh_dims"])) for t in plan["templates"]}))
-        self._setup_fused_tp()
         # physical buffers: stores sharing a scheduling name and layout share one id
         self.buffer_of: Dict[int, int] = {}
         names: Dict[str, int] = {}
@@ -174,11 +173,12 @@ class Executable:
             st["id"]: self._buffer_tiles.setdefault(self.buffer_of[st["id"]], {}) for st in plan["stores"]}
         self._step = 0
         self._created = False
+        self._reshard_plans: Dict[Tuple[int, int], dict] = {}
+        self._setup_fused_tp()
         # one-process-per-GPU jobs: side stream for stage-boundary messages, and the events
         # that mark the arrival of a received tile, keyed by (buffer, device)
         self._comm: Dict[int, Any] = {}
         self._arrival: Dict[Tuple[int, int], Any] = {}
-        self._reshard_plans: Dict[Tuple[int, int], dict] = {}
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
         self.donated = set(getattr(cap, "donated_inputs", ()))
@@ -201,27 +201,41 @@ class Executable:
         live_executables.add(self)
 
     def _setup_fused_tp(self) -> None:
-        """One-process-per-GPU CUDA jobs whose plan contains all-reduces of partial GEMM
-        results get a peer-mapped arena for the fused GEMM+all-reduce kernel. The arena is
-        created here, collectively, so that no rank meets the handle exchange in the middle
-        of a step. Disabled with MM_FUSED_TP=0 (then NCCL reduces the partial results)."""
+        """One-process-per-GPU CUDA jobs get a peer-mapped (IPC) arena, created here,
+        collectively, so that no rank meets the handle exchange in the middle of a step. It
+        carries (1) the receive buffers of the fused GEMM+all-reduce kernel when the plan
+        contains all-reduces of partial GEMM results (MM_FUSED_TP=0: NCCL reduces them), and
+        (2) the staging tiles and flags of cross-submesh reshards, which the destination
+        pulls straight from peer HBM (MM_P2P_RESHARD=0: NCCL point-to-point messages)."""
         import os
         topo = self.topology
+        self._fused_tp = None
+        self._peer_reshard = None
         if topo.kind != "dist" or topo.torch_device(topo.rank).type != "cuda":
             return
-        if os.environ.get("MM_FUSED_TP", "1") == "0":
-            return
         g = self.cap.graph
-        wanted = any(g.node(n)["op"] == "mm.all_reduce" for t in self.plan["templates"] for n in t["nodes"])
-        if not wanted:
+        want_tp = os.environ.get("MM_FUSED_TP", "1") != "0" and any(
+            g.node(n)["op"] == "mm.all_reduce" for t in self.plan["templates"] for n in t["nodes"])
+        want_rs = os.environ.get("MM_P2P_RESHARD", "1") != "0" and any(
+            op["kind"] == "reshard" for op in self.plan["ops"])
+        if not (want_tp or want_rs):
             return
         from ..parallel import symm
+        from ..parallel.reshard import PeerReshard
         from .collectives import FusedTP
-        mb = int(os.environ.get("MM_SYMM_ARENA_MB", "1024"))
-        arena = symm.SymmetricArena(mb << 20, topo.torch_device(topo.rank))
-        self._fused_tp = FusedTP(arena)
-        for ctx in self.dev_ctx.values():
-            ctx.fused_tp = self._fused_tp
+        nbytes = 1 << 20
+        if want_tp:
+            nbytes += int(os.environ.get("MM_SYMM_ARENA_MB", "1024")) << 20
+        if want_rs:
+            nbytes += PeerReshard.required_bytes(self.plan, self.buffer_of) + (1 << 20)
+        arena = symm.SymmetricArena(nbytes, topo.torch_device(topo.rank))
+        self._arena = arena
+        if want_rs:
+            self._peer_reshard = PeerReshard(arena, topo, self.plan, self.buffer_of, self._reshard_plan)
+        if want_tp:
+            self._fused_tp = FusedTP(arena)
+            for ctx in self.dev_ctx.values():
+                ctx.fused_tp = self._fused_tp
 
     def _comm_stream(self, d: int):
         """Side stream of device ``d`` for point-to-point messages (``None`` unless this is a
@@ -450,8 +464,14 @@ class Executable:
                     prev = self._arrival.get((self.buffer_of[src_sid], d))
                     if prev is not None:     # the source itself arrived by message
                         torch.cuda.current_stream().wait_event(prev)
-                    out, ev = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape,
-                                               self._comm_stream(d))
+                    pr = self._peer_reshard
+                    key = (self.buffer_of[src_sid], self.buffer_of[dst_sid])
+                    if pr is not None and pr.slots.get(key) is not None:
+                        out, ev = pr.run(key, d, tiles[src_sid].get(d), mine_src + [c for c in mine_dst if c not in mine_src],
+                                         src_shape, dst_shape, self._comm_stream(d))
+                    else:
+                        out, ev = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape,
+                                                   self._comm_stream(d))
                     if ev is not None and out is not None:
                         self._arrival[(self.buffer_of[dst_sid], d)] = ev
                     if out is not None:

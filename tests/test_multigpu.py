@@ -20,3 +20,27 @@ def _torchrun(script, nproc, *args, timeout=240, port=29531):
 def test_fused_gemm_allreduce_matches_nccl():
     r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "fused_tp_worker.py"), 2)
     assert "FUSED_TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def _step(nproc, *args, port):
+    import json
+    r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "step_worker.py"), nproc, *map(str, args), port=port)
+    line = next((l for l in r.stdout.splitlines() if "STEP_OK" in l), None)
+    assert line is not None, r.stdout[-2000:] + r.stderr[-3000:]
+    return json.loads(line)
+
+
+def test_pipeline_step_uses_the_peer_reshard_kernel_and_matches_eager():
+    out = _step(2, 2, 1, 1, port=29532)
+    assert out["STEP_OK"], out
+    assert out["peer_reshard_uses"] > 0          # stage-boundary tiles were pulled from peer memory
+
+
+def test_tensor_parallel_step_with_fused_all_reduce_matches_eager():
+    out = _step(2, 1, 1, 2, port=29533)
+    assert out["STEP_OK"], out
+
+
+def test_data_parallel_fsdp_step_matches_eager():
+    out = _step(2, 1, 2, 1, "fsdp", port=29534)
+    assert out["STEP_OK"], out
