@@ -187,8 +187,10 @@ def build_pull_chunks(chunks: List[dict], src_tile_shape: Sequence[int], dst_til
     """Turns planner chunks (boxes) into kernel records with at most four dimensions
     (leading dimensions are split into several records when the rank is larger)."""
     records: List[List[int]] = []
-    s_str, d_str = _strides(src_tile_shape), _strides(dst_tile_shape)
+    src_shape0, dst_shape0 = list(src_tile_shape), list(dst_tile_shape)
     for c in chunks:
+        src_tile_shape, dst_tile_shape = list(src_shape0), list(dst_shape0)   # merged per chunk below
+        s_str, d_str = _strides(src_tile_shape), _strides(dst_tile_shape)
         ext = [h - l for l, h in zip(c["lo"], c["hi"])]
         nd = len(ext)
         # merge trailing dimensions that are contiguous in both tiles
