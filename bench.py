@@ -39,7 +39,7 @@ def parse_args():
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--model", default="llama2_7b", choices=["llama2_7b", "llama3_8b", "tiny"])
+    p.add_argument("--model", default="llama2_7b", choices=["llama2_7b", "llama3_8b", "mixtral_8x7b", "tiny"])
     p.add_argument("--seq", type=int, default=2048)
     p.add_argument("--per-gpu-batch", type=int, default=8)
     p.add_argument("--microbatch", type=int, default=4)
@@ -48,6 +48,9 @@ def parse_args():
     p.add_argument("--dp", type=int, default=0, help="data-parallel degree (0 = default for N)")
     p.add_argument("--pp", type=int, default=0, help="pipeline stages (0 = N / (tp * dp))")
     p.add_argument("--fsdp", action="store_true", help="store parameters and optimizer state sharded over the data axis")
+    p.add_argument("--force-reshard", action="store_true",
+                   help="stage outputs leave sharded on the hidden dimension and enter the next stage sharded on "
+                        "the batch, so every microbatch crosses the boundary through a layout-changing reshard")
     p.add_argument("--schedule", default="1f1b")
     p.add_argument("--trace", default="", help="after the timed runs, profile one more step per rank and write "
                                                "its time breakdown to this directory (not a benchmark value)")
@@ -130,7 +133,7 @@ def main():
     import torch.distributed as dist
 
     cfg = {"llama2_7b": llama.LlamaConfig.llama2_7b, "llama3_8b": llama.LlamaConfig.llama3_8b,
-           "tiny": llama.LlamaConfig.tiny}[args.model]()
+           "mixtral_8x7b": llama.LlamaConfig.mixtral_8x7b, "tiny": llama.LlamaConfig.tiny}[args.model]()
     if args.layers:
         cfg.n_layers = args.layers
     # default layouts: tensor parallel pairs first, then data parallel (no pipeline bubble), and
@@ -140,6 +143,9 @@ def main():
     pp = args.pp or n // (tp * dp)
     if pp * dp * tp != n:
         raise SystemExit(f"pp{pp} x dp{dp} x tp{tp} != {n} GPUs")
+    if args.force_reshard and pp > 1:
+        per_stage = cfg.n_layers // pp
+        cfg.hidden_sharded_after = tuple(s * per_stage - 1 for s in range(1, pp))
     seq = args.seq
     global_batch = args.per_gpu_batch * n
     mb = min(args.microbatch, global_batch)
@@ -250,7 +256,8 @@ def main():
             "config": {"model": f"{args.model} shape ({cfg.n_layers} layers, d_model {cfg.d_model}, "
                                 f"{cfg.n_heads}q/{cfg.n_kv_heads}kv heads, ffn {cfg.d_ff}, vocab {cfg.vocab})",
                        "global_batch": global_batch, "seq_len": seq, "microbatch": mb,
-                       "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
+                       "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else "")
+                                      + ("+forced-reshard" if args.force_reshard else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
                        "l2": "working set (>= 13 GB of weights per step) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",

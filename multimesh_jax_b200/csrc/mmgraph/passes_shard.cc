@@ -616,6 +616,14 @@ bool SpmdLowering(CompileState& s) {
         g.value(out).sharding = target;
         g.value(out).has_sharding = true;
         const ShardedShape* have = Available(s, grp, in);
+        // a value that another task produced is asked for in the target layout, so that the
+        // layout changes while the value crosses between the tasks (one reshard, not two)
+        const int in_prod = g.value(in).producer;
+        if (in_prod >= 0 && g.node(in_prod).task != grp.id && !settled.count(in)) {
+          TablesOf(s).input_sharding[{grp.id, in}] = target;
+          settled.insert(in);
+          continue;
+        }
         settled.insert(in);
         if (!have) { SetAvailable(s, grp, in, target); continue; }
         if (have->mesh_dims == target.mesh_dims && have->dim_axes == target.dim_axes) continue;

@@ -43,6 +43,11 @@ class LlamaConfig:
     rope_theta: float = 1e4
     eps: float = 1e-5
     dtype: torch.dtype = torch.bfloat16
+    # layers after which the residual stream leaves its task sharded on the hidden dimension
+    # (logical axis "boundary_hidden") instead of on the batch: with the next layer on another
+    # pipeline stage, every microbatch then crosses the stage boundary through a reshard that
+    # changes the layout (hidden-sharded on the sender, batch-sharded on the receiver)
+    hidden_sharded_after: Tuple[int, ...] = ()
     n_experts: int = 0      # > 0: every feed-forward block is a sparse mixture of SwiGLU experts
     top_k: int = 2          # experts per token (softmax over the chosen router logits)
 
@@ -156,11 +161,19 @@ def forward_layers(cfg: LlamaConfig, layers: Sequence[Dict[str, torch.Tensor]], 
     layer's attention norm, or the final norm). Returns the new (x, h)."""
     for i, p in enumerate(layers):
         with named_scope(f"layers.{first_index + i}"):
+            if (first_index + i - 1) in cfg.hidden_sharded_after:
+                # receiving side of a forced boundary: batch-sharded again
+                x = mm_lib.relayout(x, ("batch", None, None))
+                h = mm_lib.relayout(h, ("batch", None, None))
             a = attention_block(cfg, p, h, cos, sin)
             x, h, _ = ops.add_rmsnorm(x, a, p["ffn_norm"], cfg.eps)
             m = mlp_block(cfg, p, h)
             x, h, _ = ops.add_rmsnorm(x, m, next_norms[i], cfg.eps)
-            x = mm_lib.with_sharding_constraint(x, ("batch", None, None))
+            if (first_index + i) in cfg.hidden_sharded_after:
+                x = mm_lib.relayout(x, (None, None, "boundary_hidden"))
+                h = mm_lib.relayout(h, (None, None, "boundary_hidden"))
+            else:
+                x = mm_lib.with_sharding_constraint(x, ("batch", None, None))
     return x, h
 
 
@@ -285,7 +298,8 @@ def make_train_step(cfg: LlamaConfig, opt: AdamWConfig, *, seq_len: int, global_
 def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                             logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
                                                                        ("mlp", "model"), ("fsdp", "data"),
-                                                                       ("expert", "data"))) -> None:
+                                                                       ("expert", "data"),
+                                                                       ("boundary_hidden", "model"))) -> None:
     """Places layer ``i`` on pipeline stage ``i // (n_layers / num_stages)`` (mesh axis
     ``stage``), the embedding on the first stage and the head / loss on the last one. The
     optimiser update of a parameter runs where its gradient lives."""

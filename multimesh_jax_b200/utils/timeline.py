@@ -30,7 +30,7 @@ _RULES: Sequence[Tuple[str, str]] = (
     (r"nccl.*AllGather", "NCCL AG"),
     (r"nccl.*(AllReduce|ReduceScatter)", "NCCL AR/RS"),
     (r"nccl", "NCCL other"),
-    (r"reshard_pull", "Reshard"),
+    (r"reshard_pull|wait_flags_timeout|set_flags_kernel|wait_flag_kernel|set_flag_kernel", "Reshard"),
     (r"AllReduceHook|allreduce|gemm_ar|allgather_gemm|moe_dispatch|moe_combine|fsdp_", "Fused comm"),
     (r"[Mm]emcpy|[Mm]emset", "Memcpy"),
 )

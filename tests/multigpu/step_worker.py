@@ -47,16 +47,20 @@ def main():
         loss_ref2, p_ref2, _ = step(p_ref, s_ref, tokens, labels, cos, sin)
     loss, p_mm, s_mm = exe(clone(params), clone(state), tokens, labels, cos, sin)
     loss2, p_mm2, _ = exe(p_mm, s_mm, tokens, labels, cos, sin)
+    # Adam's update is about lr * sign(gradient) in the first steps, so rounding differences
+    # between the two runs (bf16, other summation order over microbatches) may move single
+    # elements by up to 2 * lr per step; a wrong tile or a missing reduction moves them by far more
+    lr, nsteps = 1e-3, 2
     ok, worst = True, 0.0
-    for got, want in [(loss2, loss_ref2)] + list(zip(pytree.tree_leaves(p_mm2), pytree.tree_leaves(p_ref2))):
+    for k, (got, want) in enumerate([(loss2, loss_ref2)] + list(zip(pytree.tree_leaves(p_mm2), pytree.tree_leaves(p_ref2)))):
         got.wait()
         for d, tile in got.local_tiles().items():
             lo, hi = tile_box(got.sharding, d - got.sharding["device_start"])
             ref = want[tuple(slice(a, b) for a, b in zip(lo, hi))] if want.dim() else want
             err = (tile.float() - ref.float()).abs().max().item()
-            scale = max(ref.float().abs().max().item(), 1e-3)
-            worst = max(worst, err / scale)
-            if err / scale > 3e-2:
+            limit = 2e-2 * abs(float(ref)) if k == 0 else 2.5 * lr * nsteps + 8e-3 * ref.float().abs().max().item()
+            worst = max(worst, err / limit)
+            if err > limit:
                 ok = False
     status = K.read_status()
     pr = getattr(exe, "_peer_reshard", None)
@@ -66,7 +70,7 @@ def main():
     uses = torch.tensor([peer_uses], device=dev)
     dist.all_reduce(uses, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_rel_err_rank0": worst, "peer_reshard_uses": int(uses.item()),
+        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()),
                           "status": status, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
     dist.barrier()
     exe.shutdown()

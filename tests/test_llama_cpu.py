@@ -204,3 +204,41 @@ def test_data_parallel_and_fsdp_steps_match_eager(axes, fsdp):
     else:
         assert not sharded_on_data
     exe.shutdown()
+
+
+def test_forced_layout_change_at_the_stage_boundary():
+    """Two stages of (data 2 x model 2) devices with parameters stored FSDP-style; the first
+    stage hands its output over sharded on the hidden dimension, the second takes it sharded on
+    the batch: every microbatch crosses the boundary through a reshard that changes the layout."""
+    cfg = _cfg(n_layers=4, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128)
+    cfg.hidden_sharded_after = (1,)
+    B, S, MB = 8, 16, 4
+    params = llama.init_params(cfg)
+    opt_state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB,
+                                 fsdp=True)
+    mesh = mm.MultiMesh((2, 2, 2), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=2)
+    with mesh:
+        exe = mm.compile_function(step, (params, opt_state, tokens, labels, cos, sin), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(params, opt_state, tokens, labels, cos, sin)
+    loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)
+    plan = exe.plan
+    crossings = []
+    for op in plan["ops"]:
+        if op["kind"] != "reshard":
+            continue
+        s_, d_ = plan["stores"][op["src_store"]]["shape"], plan["stores"][op["dst_store"]]["shape"]
+        if s_["device_start"] == 0 and d_["device_start"] == 4 and s_["sizes"] == [MB, S, 64]:
+            crossings.append((s_["dim_axes"], d_["dim_axes"]))
+    # two values (residual stream and its normalised copy) per microbatch, hidden-sharded -> batch-sharded
+    assert len(crossings) == 2 * (B // MB)
+    assert all(src == [[], [], [1]] and dst == [[0], [], []] for src, dst in crossings)
+    exe.shutdown()
