@@ -40,24 +40,24 @@ def route(x2: torch.Tensor, wr: torch.Tensor, top_k: int) -> Tuple[torch.Tensor,
     return logits, topi, gates
 
 
-def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor):
-    """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D])."""
+def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor, out=None):
+    """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D]); ``out`` may be preallocated."""
     F = wgu_e.shape[1]
     gu = K.linear_fwd(rows, wgu_e.reshape(2 * F, -1))
     h = K.swiglu_fwd(gu)
-    out = K.linear_fwd(h, wdown_e)
+    out = K.linear_fwd(h, wdown_e, out=out)
     return gu, h, out
 
 
-def _expert_bwd(rows, d_out, wgu_e, wdown_e):
+def _expert_bwd(rows, d_out, wgu_e, wdown_e, dx_out=None, out=None):
     """Gradients of one expert for the rows routed to it. Returns (dx_rows, dwgu_e, dwdown_e, out)."""
     F = wgu_e.shape[1]
-    gu, h, out = _expert_fwd(rows, wgu_e, wdown_e)
+    gu, h, out = _expert_fwd(rows, wgu_e, wdown_e, out=out)
     dwdown = K.linear_wgrad(d_out, h, out_dtype=torch.float32)              # [D, F]
     dh = K.linear_dgrad(d_out, wdown_e)                                      # [M, F]
     dgu2 = K.swiglu_bwd(gu, dh)                                              # [M, 2F]
     dwgu = K.linear_wgrad(dgu2, rows, out_dtype=torch.float32).view(2, F, -1)
-    dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1))
+    dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1), out=dx_out)
     return dx, dwgu, dwdown, out
 
 
@@ -174,6 +174,16 @@ def _plan_dispatch(topi: torch.Tensor, n: int, experts_per_rank: int):
     return flat_e, order, counts
 
 
+def _peer_moe(ctx, group, x2, n_experts: int):
+    """The peer-memory implementation for this group, when the job has one (one process per
+    GPU, bf16, a symmetric arena) - otherwise ``None`` and the all-to-all form runs."""
+    reg = getattr(ctx, "peer_moe", None)
+    if reg is None or not x2.is_cuda or x2.dtype != torch.bfloat16 or x2.shape[1] % 8:
+        return None
+    ranks = tuple(ctx.device_start + o for o in group)
+    return reg.get(ranks, x2.shape[0], x2.shape[1], n_experts)
+
+
 def moe_ffn_local(ctx, axes, key, x, wr, wgu, wdown, top_k: int):
     """This device's share of ``moe_ffn``: ``x`` holds its tokens, ``wgu`` / ``wdown`` its experts."""
     group, me = ctx.group_of(axes)
@@ -183,6 +193,9 @@ def moe_ffn_local(ctx, axes, key, x, wr, wgu, wdown, top_k: int):
     D = x.shape[-1]
     x2 = x.reshape(-1, D)
     E_l = wgu.shape[0]
+    peer = _peer_moe(ctx, group, x2, E_l * n)
+    if peer is not None:
+        return peer.forward(x2, wr, wgu, wdown, top_k).view(x.shape)
     _, topi, gates = route(x2, wr, top_k)
     flat_e, order, counts = _plan_dispatch(topi, n, E_l)
     tok = torch.div(order, top_k, rounding_mode="floor")
@@ -210,6 +223,10 @@ def moe_ffn_bwd_local(ctx, axes, key, dy, x, wr, wgu, wdown, top_k: int):
     D = x.shape[-1]
     x2, dy2 = x.reshape(-1, D), dy.reshape(-1, D)
     E_l = wgu.shape[0]
+    peer = _peer_moe(ctx, group, x2, E_l * n)
+    if peer is not None:
+        dx, dwr, dwgu, dwdown = peer.backward(dy2, x2, wr, wgu, wdown, top_k)
+        return dx.view(x.shape), dwr, dwgu, dwdown
     _, topi, gates = route(x2, wr, top_k)
     flat_e, order, counts = _plan_dispatch(topi, n, E_l)
     tok = torch.div(order, top_k, rounding_mode="floor")

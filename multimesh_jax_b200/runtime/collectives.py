@@ -165,6 +165,7 @@ class DeviceCtx:
         self.torch_device = topology.torch_device(device)
         self.rendezvous = rendezvous
         self.fused_tp = None  # FusedTP registry (one-process-per-GPU CUDA jobs only)
+        self.peer_moe = None  # PeerMoERegistry (same)
         # set per task launch
         self.device_start = 0
         self.mesh_dims: Sequence[int] = (1,)

@@ -218,7 +218,10 @@ class Executable:
             g.node(n)["op"] == "mm.all_reduce" for t in self.plan["templates"] for n in t["nodes"])
         want_rs = os.environ.get("MM_P2P_RESHARD", "1") != "0" and any(
             op["kind"] == "reshard" for op in self.plan["ops"])
-        if not (want_tp or want_rs):
+        moe_nodes = [g.node(n) for t in self.plan["templates"] for n in t["nodes"]
+                     if g.node(n)["op"].startswith("mm_ops.moe_ffn.") and g.node(n)["attrs"].get("shared_axes", "[]") != "[]"]
+        want_moe = os.environ.get("MM_P2P_MOE", "1") != "0" and bool(moe_nodes)
+        if not (want_tp or want_rs or want_moe):
             return
         from ..parallel import symm
         from ..parallel.reshard import PeerReshard
@@ -228,6 +231,16 @@ class Executable:
             nbytes += int(os.environ.get("MM_SYMM_ARENA_MB", "1024")) << 20
         if want_rs:
             nbytes += PeerReshard.required_bytes(self.plan, self.buffer_of) + (1 << 20)
+        if want_moe:
+            from ..parallel.ep import PeerMoE, PeerMoERegistry
+            worst = 0
+            for nd in moe_nodes:
+                xv, wv = g.value(nd["inputs"][0]), g.value(nd["inputs"][2])
+                tokens = 1
+                for s_ in (xv["sharding"]["shard_size"] if xv["sharding"] else xv["shape"])[:-1]:
+                    tokens *= s_
+                worst = max(worst, PeerMoE.required_bytes(tokens, xv["shape"][-1], wv["shape"][0]))
+            nbytes += worst
         arena = symm.SymmetricArena(nbytes, topo.torch_device(topo.rank))
         self._arena = arena
         if want_rs:
@@ -236,6 +249,10 @@ class Executable:
             self._fused_tp = FusedTP(arena)
             for ctx in self.dev_ctx.values():
                 ctx.fused_tp = self._fused_tp
+        if want_moe:
+            self._peer_moe = PeerMoERegistry(arena)
+            for ctx in self.dev_ctx.values():
+                ctx.peer_moe = self._peer_moe
 
     def _comm_stream(self, d: int):
         """Side stream of device ``d`` for point-to-point messages (``None`` unless this is a

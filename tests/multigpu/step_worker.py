@@ -1,7 +1,7 @@
 """Worker of the multi-GPU training-step tests (one process per GPU, launched by torchrun):
 the compiled step on `pp x dp x tp` GPUs against the eager step on one GPU, in bf16.
 
-    step_worker.py <pp> <dp> <tp> [fsdp]
+    step_worker.py <pp> <dp> <tp> [fsdp|moe]
 """
 import json
 import os
@@ -16,6 +16,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 def main():
     pp, dp, tp = (int(a) for a in sys.argv[1:4])
     fsdp = len(sys.argv) > 4 and sys.argv[4] == "fsdp"
+    moe = len(sys.argv) > 4 and sys.argv[4] == "moe"
     rank = int(os.environ["RANK"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -27,7 +28,8 @@ def main():
     from torch.utils import _pytree as pytree
 
     torch.manual_seed(0)
-    cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, d_model=512, n_heads=4, n_kv_heads=2, d_ff=1024, vocab=1024)
+    cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, d_model=512, n_heads=4, n_kv_heads=2, d_ff=1024, vocab=1024,
+                                 n_experts=4 if moe else 0, top_k=2)
     B, S, MB = 8, 256, 2
     params = llama.init_params(cfg, device="cpu")
     params = pytree.tree_map(lambda t: t.to(dev), params)
@@ -63,6 +65,8 @@ def main():
             if err > limit:
                 ok = False
     status = K.read_status()
+    pm = getattr(exe, "_peer_moe", None)
+    moe_calls = sum(o.calls for o in pm._ops.values()) if pm is not None else 0
     pr = getattr(exe, "_peer_reshard", None)
     peer_uses = sum(s["uses"] for s in pr.slots.values() if s) if pr is not None else 0
     flag = torch.tensor([1 if (ok and status == 0) else 0], device=dev)
@@ -70,7 +74,7 @@ def main():
     uses = torch.tensor([peer_uses], device=dev)
     dist.all_reduce(uses, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()),
+        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls,
                           "status": status, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
     dist.barrier()
     exe.shutdown()

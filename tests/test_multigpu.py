@@ -44,3 +44,9 @@ def test_tensor_parallel_step_with_fused_all_reduce_matches_eager():
 def test_data_parallel_fsdp_step_matches_eager():
     out = _step(2, 1, 2, 1, "fsdp", port=29534)
     assert out["STEP_OK"], out
+
+
+def test_expert_parallel_step_with_fused_dispatch_matches_eager():
+    out = _step(2, 1, 2, 1, "moe", port=29535)
+    assert out["STEP_OK"], out
+    assert out["peer_moe_calls"] > 0             # router + dispatch and combine ran on the peer-memory kernels
