@@ -148,7 +148,7 @@ def main():
         cfg.hidden_sharded_after = tuple(s * per_stage - 1 for s in range(1, pp))
     seq = args.seq
     global_batch = args.per_gpu_batch * n
-    mb = min(args.microbatch, global_batch)
+    mb = min(args.microbatch * dp, global_batch)   # --microbatch counts sequences per data-parallel rank
     opt = llama.AdamWConfig()
     step_fn = llama.make_train_step(cfg, opt, seq_len=seq, global_batch=global_batch, microbatch_size=mb,
                                     schedule=args.schedule, fsdp=args.fsdp)

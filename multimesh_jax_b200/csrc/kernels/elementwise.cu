@@ -507,7 +507,9 @@ int mm_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t r
 // scratch buffer must hold mm_rmsnorm_bwd_parts(rows) * D floats.
 int mm_rmsnorm_bwd_parts(int64_t rows) {
   DeviceState* ds = device_state();
-  const int cap = ds ? ds->sm_count * 2 : 296;
+  // enough blocks for 16-24 resident warps per SM: the kernel is bound by memory latency, and
+  // the loads in flight per SM set its bandwidth
+  const int cap = ds ? ds->sm_count * 4 : 592;
   return static_cast<int>(rows < cap ? rows : cap);
 }
 
@@ -526,8 +528,8 @@ int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rs
       static_cast<int>(rows), D, add_to_dx)
   if (D <= 1024) MM_RN_BWD(128, 1);
   else if (D <= 2048) MM_RN_BWD(128, 2);
-  else if (D <= 4096) MM_RN_BWD(128, 4);
-  else if (D <= 8192) MM_RN_BWD(256, 4);
+  else if (D <= 4096) MM_RN_BWD(256, 2);
+  else if (D <= 8192) MM_RN_BWD(512, 2);
   else MM_RN_BWD(512, 4);
 #undef MM_RN_BWD
   MM_CUDA_TRY(cudaGetLastError());
