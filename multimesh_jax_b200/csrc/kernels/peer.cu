@@ -136,6 +136,49 @@ __global__ void wait_flags_timeout_kernel(FlagList f, int value, unsigned long l
   }
 }
 
+// out[v] = scale * sum over sources of src[s][v], 16-byte vectors, fp32 accumulation. Sources are
+// this GPU's own buffer and its peers' buffers (plain loads over NVLink): the reduce-scatter
+// half of an all-reduce done as a pull, and - with one source - a plain pull copy.
+struct ReducePullArgs {
+  const uint4* src[8];
+  uint4* out;
+  int nsrc;
+  int is_fp32;      // 1: fp32 elements, 0: bf16 elements
+  int64_t nvec;
+  float scale;
+};
+__global__ void __launch_bounds__(256) reduce_pull_kernel(ReducePullArgs a) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < a.nvec; v += stride) {
+    if (a.is_fp32) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < a.nsrc; ++s) {
+        const uint4 u = __ldcg(a.src[s] + v);
+        acc.x += __uint_as_float(u.x); acc.y += __uint_as_float(u.y);
+        acc.z += __uint_as_float(u.z); acc.w += __uint_as_float(u.w);
+      }
+      uint4 o;
+      o.x = __float_as_uint(acc.x * a.scale); o.y = __float_as_uint(acc.y * a.scale);
+      o.z = __float_as_uint(acc.z * a.scale); o.w = __float_as_uint(acc.w * a.scale);
+      a.out[v] = o;
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < a.nsrc; ++s) {
+        const uint4 u = __ldcg(a.src[s] + v);
+        const float2 p0 = unpack_bf16(u.x), p1 = unpack_bf16(u.y), p2 = unpack_bf16(u.z), p3 = unpack_bf16(u.w);
+        acc[0] += p0.x; acc[1] += p0.y; acc[2] += p1.x; acc[3] += p1.y;
+        acc[4] += p2.x; acc[5] += p2.y; acc[6] += p3.x; acc[7] += p3.y;
+      }
+      uint4 o;
+      o.x = pack_bf16(acc[0] * a.scale, acc[1] * a.scale);
+      o.y = pack_bf16(acc[2] * a.scale, acc[3] * a.scale);
+      o.z = pack_bf16(acc[4] * a.scale, acc[5] * a.scale);
+      o.w = pack_bf16(acc[6] * a.scale, acc[7] * a.scale);
+      a.out[v] = o;
+    }
+  }
+}
+
 }  // namespace mm
 
 extern "C" {
@@ -236,6 +279,33 @@ int mm_wait_flag(const void* flag, int value, cudaStream_t stream) {
   DeviceState* ds = device_state();
   if (!ds) return -1;
   wait_flag_kernel<<<1, 1, 0, stream>>>(reinterpret_cast<const int*>(flag), value, ds->status);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// out = scale * sum of `nsrc` buffers of `nbytes` bytes each (16-byte aligned, a multiple of 16
+// bytes); sources may be peer addresses. elem_size 4 = fp32, 2 = bf16.
+int mm_reduce_pull(const int64_t* srcs, int nsrc, void* out, int64_t nbytes, int elem_size, float scale,
+                   cudaStream_t stream) {
+  if (nbytes <= 0) return 0;
+  if (nsrc < 1 || nsrc > 8 || (nbytes & 15) || (elem_size != 4 && elem_size != 2)) return -2;
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  ReducePullArgs a;
+  for (int i = 0; i < nsrc; ++i) {
+    if (srcs[i] & 15) return -2;
+    a.src[i] = reinterpret_cast<const uint4*>(srcs[i]);
+  }
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -2;
+  a.out = reinterpret_cast<uint4*>(out);
+  a.nsrc = nsrc;
+  a.is_fp32 = elem_size == 4;
+  a.nvec = nbytes / 16;
+  a.scale = scale;
+  int64_t want = (a.nvec + 256 * 4 - 1) / (256 * 4);
+  const int cap = ds->sm_count * 8;
+  const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+  reduce_pull_kernel<<<grid, 256, 0, stream>>>(a);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

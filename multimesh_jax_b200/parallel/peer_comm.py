@@ -1,0 +1,126 @@
+"""In-task collectives over peer-mapped memory (one process per GPU).
+
+``PeerGroupComm`` serves one device group of a task (a tensor- or data-parallel group):
+
+* ``all_reduce``  - gradient sums after the microbatch loop, partial results: every rank
+  copies its tensor into a staging tile, then *pulls* its 1/g share from all members with the
+  reduce-pull kernel (the reduce-scatter half: loads over NVLink, fp32 accumulation, one pass),
+  then pulls the other members' reduced shares (the all-gather half). The volume per GPU is the
+  ring optimum, 2 (g-1)/g of the tensor, and there is no NCCL call.
+* ``reshard``     - a layout change inside the group (FSDP parameter gather before the loop,
+  batch <-> hidden transposes): staging copy, then the reshard pull kernel writes the new
+  layout directly from the members' tiles.
+
+Phases are ordered between the GPUs by flag barriers with time-bounded waits; staging tiles
+live in the symmetric arena, one pair per distinct size.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_int64, c_void_p
+from typing import Dict, List, Sequence, Tuple
+
+import torch
+
+from ..ops import _lib
+from ..ops import kernels as K
+from . import symm
+
+_lib.register("mm_reduce_pull", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_float, c_void_p])
+
+
+class PeerGroupComm:
+    MIN_BYTES = 256 << 10      # below this a library collective's latency wins
+
+    def __init__(self, arena: symm.SymmetricArena, ranks: Sequence[int], stage: Dict[int, tuple]):
+        self.arena, self.ranks = arena, list(ranks)
+        self.g = len(self.ranks)
+        self.me = self.ranks.index(arena.rank)
+        self.flag_off = [arena.alloc_flag() for _ in self.ranks]
+        self.epoch = 0
+        # staging tiles are shared by all groups of this rank: the members of a group run the same
+        # program, so they create size classes in the same order and the offsets agree
+        self.stage = stage
+        self.calls = 0
+
+    # ------------------------------------------------------------------
+    def barrier(self) -> None:
+        self.epoch += 1
+        a = self.arena
+        peers = [r for r in self.ranks if r != a.rank]
+        symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
+        symm.wait_flags(a, [a.flag_ptr(a.rank, self.flag_off[self.ranks.index(r)]) for r in peers], self.epoch)
+
+    def _tiles(self, nbytes: int):
+        """Two staging tiles of at least ``nbytes`` (sizes are rounded up so that tensors of
+        similar size share them; every member asks in the same order, so offsets agree)."""
+        size = 1 << max(20, (nbytes - 1).bit_length())
+        if size not in self.stage:
+            self.stage[size] = (self.arena.alloc((size,), torch.uint8), self.arena.alloc((size,), torch.uint8))
+        return self.stage[size]
+
+    def supports(self, x: torch.Tensor) -> bool:
+        n = x.numel() * x.element_size()
+        return (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and n >= self.MIN_BYTES
+                and n % (16 * self.g) == 0)
+
+    # ------------------------------------------------------------------
+    def all_reduce(self, x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        a, g, me = self.arena, self.g, self.me
+        x = x.contiguous()
+        nbytes = x.numel() * x.element_size()
+        s_in, s_red = self._tiles(nbytes)
+        stream = torch.cuda.current_stream().cuda_stream
+        K_lib = a.lib
+        s_in.peer(a.rank)[:nbytes].view(x.dtype).view(x.shape).copy_(x)
+        self.barrier()                                    # every member's tensor is staged
+        share = nbytes // g
+        srcs = (c_int64 * g)(*[s_in.ptr(r) + me * share for r in self.ranks])
+        rc = K_lib.mm_reduce_pull(srcs, g, s_red.ptr(a.rank) + me * share, share, x.element_size(), scale, stream)
+        _lib.check(rc, "mm_reduce_pull")
+        K._count()
+        self.barrier()                                    # every member's share is reduced
+        out = torch.empty_like(x)
+        for i, r in enumerate(self.ranks):                # all-gather half: pull each owner's share
+            one = (c_int64 * 1)(s_red.ptr(r) + i * share)
+            rc = K_lib.mm_reduce_pull(one, 1, out.data_ptr() + i * share, share, x.element_size(), 1.0, stream)
+            _lib.check(rc, "mm_reduce_pull")
+            K._count()
+        self.barrier()                                    # staging tiles may be overwritten again
+        self.calls += 1
+        return out
+
+    def reshard(self, x: torch.Tensor, src: dict, dst: dict) -> torch.Tensor:
+        """Local tile in layout ``dst`` from the members' tiles in layout ``src`` (layouts over
+        exactly this group's devices)."""
+        from .. import _mm_C
+        from ..compiler.capture import DTYPE_FROM_NAME
+        a = self.arena
+        x = x.contiguous()
+        nbytes = x.numel() * x.element_size()
+        s_in, _ = self._tiles(nbytes)
+        s_in.peer(a.rank)[:nbytes].view(x.dtype).view(x.shape).copy_(x)
+        self.barrier()
+        plan = _mm_C.plan_reshard(src, dst)
+        d = src["device_start"] + self.me
+        mine = [c for c in plan["chunks"] if c["dst_device"] == d]
+        out = torch.empty(dst["shard_size"], dtype=DTYPE_FROM_NAME[dst["dtype"]], device=x.device)
+        start = src["device_start"]
+        recs = symm.build_pull_chunks(mine, list(src["shard_size"]), list(dst["shard_size"]),
+                                      lambda dev: s_in.ptr(self.ranks[dev - start]), out.data_ptr(), x.element_size())
+        for i in range(0, len(recs), 64):
+            symm.reshard_pull(recs[i:i + 64], x.element_size(), a)
+        self.barrier()
+        self.calls += 1
+        return out
+
+
+class PeerCommRegistry:
+    def __init__(self, arena: symm.SymmetricArena):
+        self.arena = arena
+        self._ops: Dict[Tuple[int, ...], PeerGroupComm] = {}
+        self._stage: Dict[int, tuple] = {}
+
+    def get(self, ranks: Tuple[int, ...]) -> PeerGroupComm:
+        if ranks not in self._ops:
+            self._ops[ranks] = PeerGroupComm(self.arena, ranks, self._stage)
+        return self._ops[ranks]

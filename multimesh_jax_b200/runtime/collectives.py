@@ -166,6 +166,7 @@ class DeviceCtx:
         self.rendezvous = rendezvous
         self.fused_tp = None  # FusedTP registry (one-process-per-GPU CUDA jobs only)
         self.peer_moe = None  # PeerMoERegistry (same)
+        self.peer_comm = None  # PeerCommRegistry (same): in-task all-reduce / reshard over peer memory
         # set per task launch
         self.device_start = 0
         self.mesh_dims: Sequence[int] = (1,)
@@ -221,6 +222,10 @@ class DeviceCtx:
         if len(group) == 1:
             return x
         if self.topology.kind == "dist":
+            if self.peer_comm is not None:
+                comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+                if comm.supports(x):
+                    return comm.all_reduce(x)
             import torch.distributed as dist
             pg = self.topology.process_group([self.device_start + o for o in group])
             out = x.contiguous().clone()
@@ -268,6 +273,13 @@ class DeviceCtx:
         n = src["num_devices"]
         me = self.device - self.device_start
         group = list(range(n))
+        if self.topology.kind == "dist" and self.peer_comm is not None:
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            from ..parallel.reshard import PeerReshard
+            from .. import _mm_C
+            if x.is_cuda and x.numel() * x.element_size() >= comm.MIN_BYTES and \
+                    PeerReshard.pullable(_mm_C.plan_reshard(src, dst), src, dst):
+                return comm.reshard(x, src, dst)
         parts = self._exchange(("rs", key), group, x)
         full = torch.empty(src["sizes"], dtype=x.dtype, device=x.device)
         for o, p in zip(group, parts):

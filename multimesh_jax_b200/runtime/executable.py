@@ -221,7 +221,9 @@ class Executable:
         moe_nodes = [g.node(n) for t in self.plan["templates"] for n in t["nodes"]
                      if g.node(n)["op"].startswith("mm_ops.moe_ffn.") and g.node(n)["attrs"].get("shared_axes", "[]") != "[]"]
         want_moe = os.environ.get("MM_P2P_MOE", "1") != "0" and bool(moe_nodes)
-        if not (want_tp or want_rs or want_moe):
+        want_comm = os.environ.get("MM_P2P_COLLECTIVES", "1") != "0" and any(
+            g.node(n)["op"] in ("mm.all_reduce", "mm.spmd_reshard") for t in self.plan["templates"] for n in t["nodes"])
+        if not (want_tp or want_rs or want_moe or want_comm):
             return
         from ..parallel import symm
         from ..parallel.reshard import PeerReshard
@@ -231,6 +233,20 @@ class Executable:
             nbytes += int(os.environ.get("MM_SYMM_ARENA_MB", "1024")) << 20
         if want_rs:
             nbytes += PeerReshard.required_bytes(self.plan, self.buffer_of) + (1 << 20)
+        if want_comm:
+            # staging pairs of the in-task collectives: one pair per power-of-two size class
+            sizes = set()
+            for t in self.plan["templates"]:
+                for n in t["nodes"]:
+                    nd = g.node(n)
+                    if nd["op"] in ("mm.all_reduce", "mm.spmd_reshard"):
+                        v = g.value(nd["inputs"][0])
+                        nb = DTYPE_FROM_NAME[v["dtype"]].itemsize
+                        for s_ in (v["sharding"]["shard_size"] if v["sharding"] else v["shape"]):
+                            nb *= s_
+                        if nb >= (256 << 10):
+                            sizes.add(1 << max(20, (nb - 1).bit_length()))
+            nbytes += 2 * sum(sizes) + (1 << 20)
         if want_moe:
             from ..parallel.ep import PeerMoE, PeerMoERegistry
             worst = 0
@@ -249,6 +265,11 @@ class Executable:
             self._fused_tp = FusedTP(arena)
             for ctx in self.dev_ctx.values():
                 ctx.fused_tp = self._fused_tp
+        if want_comm:
+            from ..parallel.peer_comm import PeerCommRegistry
+            self._peer_comm = PeerCommRegistry(arena)
+            for ctx in self.dev_ctx.values():
+                ctx.peer_comm = self._peer_comm
         if want_moe:
             self._peer_moe = PeerMoERegistry(arena)
             for ctx in self.dev_ctx.values():

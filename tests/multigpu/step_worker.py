@@ -67,6 +67,8 @@ def main():
     status = K.read_status()
     pm = getattr(exe, "_peer_moe", None)
     moe_calls = sum(o.calls for o in pm._ops.values()) if pm is not None else 0
+    pc = getattr(exe, "_peer_comm", None)
+    comm_calls = sum(o.calls for o in pc._ops.values()) if pc is not None else 0
     pr = getattr(exe, "_peer_reshard", None)
     peer_uses = sum(s["uses"] for s in pr.slots.values() if s) if pr is not None else 0
     flag = torch.tensor([1 if (ok and status == 0) else 0], device=dev)
@@ -74,7 +76,7 @@ def main():
     uses = torch.tensor([peer_uses], device=dev)
     dist.all_reduce(uses, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls,
+        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls, "peer_collective_calls": comm_calls,
                           "status": status, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
     dist.barrier()
     exe.shutdown()

@@ -44,6 +44,7 @@ def test_tensor_parallel_step_with_fused_all_reduce_matches_eager():
 def test_data_parallel_fsdp_step_matches_eager():
     out = _step(2, 1, 2, 1, "fsdp", port=29534)
     assert out["STEP_OK"], out
+    assert out["peer_collective_calls"] > 0      # parameter gathers / gradient reductions ran on the pull kernels
 
 
 def test_expert_parallel_step_with_fused_dispatch_matches_eager():
