@@ -51,6 +51,9 @@ def parse_args():
     p.add_argument("--force-reshard", action="store_true",
                    help="stage outputs leave sharded on the hidden dimension and enter the next stage sharded on "
                         "the batch, so every microbatch crosses the boundary through a layout-changing reshard")
+    p.add_argument("--layers-per-stage", default="",
+                   help="comma-separated layer counts per pipeline stage (default: the last stage, which also "
+                        "runs the LM head and the loss, gets two layers fewer when there are four stages)")
     p.add_argument("--schedule", default="1f1b")
     p.add_argument("--trace", default="", help="after the timed runs, profile one more step per rank and write "
                                                "its time breakdown to this directory (not a benchmark value)")
@@ -146,6 +149,8 @@ def main():
     if args.force_reshard and pp > 1:
         per_stage = cfg.n_layers // pp
         cfg.hidden_sharded_after = tuple(s * per_stage - 1 for s in range(1, pp))
+        if not args.layers_per_stage:
+            args.layers_per_stage = ",".join([str(per_stage)] * pp)   # boundaries above assume equal shares
     seq = args.seq
     global_batch = args.per_gpu_batch * n
     mb = min(args.microbatch * dp, global_batch)   # --microbatch counts sequences per data-parallel rank
@@ -153,7 +158,14 @@ def main():
     step_fn = llama.make_train_step(cfg, opt, seq_len=seq, global_batch=global_batch, microbatch_size=mb,
                                     schedule=args.schedule, fsdp=args.fsdp)
     mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
-    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+    if args.layers_per_stage:
+        lps = [int(v) for v in args.layers_per_stage.split(",")]
+    elif pp == 4 and cfg.n_layers % 4 == 0 and cfg.n_layers >= 16:
+        q = cfg.n_layers // 4
+        lps = [q, q + 1, q + 1, q - 2]      # head + loss cost about 1.6 layers, the embedding about 0.7
+    else:
+        lps = None
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, layers_per_stage=lps)
 
     # abstract arguments for the capture; real tensors are created shard by shard below
     with torch.device("meta"):
@@ -256,7 +268,7 @@ def main():
             "config": {"model": f"{args.model} shape ({cfg.n_layers} layers, d_model {cfg.d_model}, "
                                 f"{cfg.n_heads}q/{cfg.n_kv_heads}kv heads, ffn {cfg.d_ff}, vocab {cfg.vocab})",
                        "global_batch": global_batch, "seq_len": seq, "microbatch": mb,
-                       "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else "")
+                       "layers_per_stage": lps, "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else "")
                                       + ("+forced-reshard" if args.force_reshard else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
                        "l2": "working set (>= 13 GB of weights per step) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks,

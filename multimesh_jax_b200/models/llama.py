@@ -299,16 +299,25 @@ def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                             logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
                                                                        ("mlp", "model"), ("fsdp", "data"),
                                                                        ("expert", "data"),
-                                                                       ("boundary_hidden", "model"))) -> None:
-    """Places layer ``i`` on pipeline stage ``i // (n_layers / num_stages)`` (mesh axis
-    ``stage``), the embedding on the first stage and the head / loss on the last one. The
-    optimiser update of a parameter runs where its gradient lives."""
-    per_stage = cfg.n_layers // num_stages
+                                                                       ("boundary_hidden", "model")),
+                            layers_per_stage: Optional[Sequence[int]] = None) -> None:
+    """Places the layers on pipeline stages (mesh axis ``stage``): ``layers_per_stage[s]``
+    consecutive layers on stage ``s`` (default: equal shares), the embedding on the first stage
+    and the head / loss on the last one - which is why the last stage may be given fewer layers.
+    The optimiser update of a parameter runs where its gradient lives."""
+    if layers_per_stage is None:
+        per = cfg.n_layers // num_stages
+        layers_per_stage = [per] * (num_stages - 1) + [cfg.n_layers - per * (num_stages - 1)]
+    if len(layers_per_stage) != num_stages or sum(layers_per_stage) != cfg.n_layers:
+        raise ValueError(f"layers_per_stage {list(layers_per_stage)} does not cover {cfg.n_layers} layers on {num_stages} stages")
+    stage_of: List[int] = []
+    for s_, cnt in enumerate(layers_per_stage):
+        stage_of.extend([s_] * cnt)
     la = [(a, b) for a, b in logical_axes if b in mesh.axis_names]
 
     def layer_task(matched: str, backprop: bool) -> Task:
         idx = int(matched.split(".")[1])
-        stage = min(idx // per_stage, num_stages - 1)
+        stage = stage_of[idx]
         return Task(name=f"stage{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage}, logical_axes=la)
 
     mesh.register_task(r"(layers\.\d+)", factory=layer_task)

@@ -31,7 +31,8 @@ _RULES: Sequence[Tuple[str, str]] = (
     (r"nccl.*(AllReduce|ReduceScatter)", "NCCL AR/RS"),
     (r"nccl", "NCCL other"),
     (r"reshard_pull|wait_flags_timeout|set_flags_kernel|wait_flag_kernel|set_flag_kernel", "Reshard"),
-    (r"AllReduceHook|allreduce|gemm_ar|allgather_gemm|moe_dispatch|moe_combine|fsdp_", "Fused comm"),
+    (r"AllReduceHook|allreduce|gemm_ar|allgather_gemm|moe_route_dispatch|moe_dispatch|moe_combine|reduce_pull|fsdp_",
+     "Fused comm"),
     (r"[Mm]emcpy|[Mm]emset", "Memcpy"),
 )
 TASK_PREFIX = "mm.task:"
