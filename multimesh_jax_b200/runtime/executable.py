@@ -429,8 +429,17 @@ class Executable:
 
         def body():
             if state.knobs["task_ranges"]:
-                with torch.profiler.record_function("mm.task:" + name):
-                    return run()
+                # one named range per task launch: visible to torch.profiler and, through NVTX, to
+                # external timeline tools
+                nvtx = dctx.torch_device.type == "cuda"
+                if nvtx:
+                    torch.cuda.nvtx.range_push("mm.task:" + name)
+                try:
+                    with torch.profiler.record_function("mm.task:" + name):
+                        return run()
+                finally:
+                    if nvtx:
+                        torch.cuda.nvtx.range_pop()
             return run()
 
         def run():

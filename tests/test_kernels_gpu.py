@@ -182,3 +182,29 @@ def test_add_and_accumulate():
     s = torch.zeros(1, device=DEV)
     K.sumsq(acc, s)
     torch.testing.assert_close(s[0], (acc.double() ** 2).sum().float(), rtol=1e-4, atol=1e-3)
+
+
+def test_bounded_flag_wait_expires_with_a_status_and_the_context_stays_usable():
+    """A wait on a flag that nothing raises gives up after its time limit, records the expiry in
+    the device status word and lets the stream continue; later kernels run normally."""
+    from multimesh_jax_b200.parallel import symm
+    dev = torch.device("cuda", 0)
+    K.read_status()                       # clear
+    arena = symm.SymmetricArena(1 << 20, dev)
+    off = arena.alloc_flag()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    symm.wait_flags(arena, [arena.flag_ptr(arena.rank, off)], 1, limit_ms=300)
+    t1.record()
+    torch.cuda.synchronize()
+    assert 250 <= t0.elapsed_time(t1) < 5000
+    assert K.read_status() == 5           # MM_ERR_WAIT_PEER; reading clears it
+    # a raised flag lets the same wait pass at once, and ordinary work still runs
+    symm.set_flags(arena, [arena.flag_ptr(arena.rank, off)], 1)
+    symm.wait_flags(arena, [arena.flag_ptr(arena.rank, off)], 1, limit_ms=300)
+    x = torch.randn(256, 512, device=dev).bfloat16()
+    y = K.linear_fwd(x, x)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0 and torch.isfinite(y.float()).all()
+    arena.close()
