@@ -141,9 +141,11 @@ def main():
         cfg.n_layers = args.layers
     # default layouts: tensor parallel pairs first, then data parallel (no pipeline bubble), and
     # the named 4-stage pipeline x TP2 configuration on 8 GPUs
-    tp = args.tp or {1: 1, 2: 2, 4: 2, 8: 2}.get(n, 1)
-    dp = args.dp or {4: 2}.get(n, 1)
-    pp = args.pp or n // (tp * dp)
+    if args.tp or args.dp or args.pp:
+        tp, dp = args.tp or 1, args.dp or 1
+        pp = args.pp or n // (tp * dp)
+    else:
+        pp, dp, tp = {1: (1, 1, 1), 2: (1, 2, 1), 4: (1, 2, 2), 8: (4, 1, 2)}.get(n, (1, n, 1))
     if pp * dp * tp != n:
         raise SystemExit(f"pp{pp} x dp{dp} x tp{tp} != {n} GPUs")
     if args.force_reshard and pp > 1:

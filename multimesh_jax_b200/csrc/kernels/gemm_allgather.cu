@@ -1,0 +1,168 @@
+// All-gather fused into a tensor-parallel GEMM (column-parallel projections whose input
+// activations are sharded by rows over the ranks, i.e. sequence-parallel activations):
+//
+//     C[M, N] = concat_r(A_r[M/g, K]) * B[N, K]^T        A_r lives on rank r
+//
+// One kernel does both. Two helper warps per CTA pull the row shards - the peers' over NVLink
+// with plain 16-byte loads, the own one from local memory - into a local [M, K] buffer, 128-row
+// block by block, and count their arrivals per block; the TMA producer of the tcgen05 main
+// loop waits (bounded) for a block's count before it loads the block's tiles from that local
+// buffer. Row blocks are visited starting with this rank's own shard and then the peers' in
+// ring order, so the tensor cores start on local rows while the first remote rows are still
+// in flight, and the transfer of block i+1 overlaps the math of block i. TMA only ever reads
+// this GPU's memory; no multicast is used.
+#include "gemm_core.cuh"
+#include "host_common.h"
+
+namespace mm {
+
+constexpr int AG_MAX_RANKS = 8;
+
+struct AllGatherHook {
+  void* C;
+  int64_t ldc;
+  bool vec_ok;
+  const uint4* a_src[AG_MAX_RANKS];  // row shard of every rank (own: local; others: peer memory), [M/g, K]
+  uint4* gathered;                   // local [M, K]
+  int* ready;                        // local, one counter per 128-row block, never reset
+  int target;                        // value a block's counter reaches when all its pieces of this call arrived
+  int nranks, me;
+  int blocks_per_shard;              // 128-row blocks per rank shard
+  int num_m;
+
+  static constexpr int kStageBytes = 0;
+  static constexpr int kAuxWarps = 2;
+  struct State {};
+  __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
+
+  // scheduler index -> row block: own shard first, then the peers' in ring order
+  __device__ __forceinline__ int map_m(int m_blk) const {
+    const int shifted = m_blk + me * blocks_per_shard;
+    return shifted >= num_m ? shifted - num_m : shifted;
+  }
+  __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
+
+  __device__ __forceinline__ bool before_tile_loads(int m_blk, int, int* err) const {
+    for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ready + m_blk) : "memory");
+      if (v >= target) {
+        fence_proxy_async_all();   // the rows were written with plain stores, TMA reads them next
+        return true;
+      }
+      if (i > 32) __nanosleep(100);
+      if ((i & 1023) == 1023 && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    }
+    atomicCAS(err, 0, MM_ERR_WAIT_PEER);
+    return false;
+  }
+
+  // Helper warps: copy this CTA's slice of every row block, in the order the blocks are used.
+  __device__ __forceinline__ void aux(int w, int lane, int M, int K, int* err) const {
+    (void)err;
+    const int64_t vec_per_block = static_cast<int64_t>(GEMM_BM) * K / 8;
+    const int64_t vec_per_shard = vec_per_block * blocks_per_shard;
+    const int workers = gridDim.x * kAuxWarps;
+    const int wid = blockIdx.x * kAuxWarps + w;
+    const int64_t per = (vec_per_block + workers - 1) / workers;
+    for (int i = 0; i < num_m; ++i) {
+      const int blk = map_m(i);
+      const int owner = blk / blocks_per_shard;
+      const int64_t in_shard = static_cast<int64_t>(blk - owner * blocks_per_shard) * vec_per_block;
+      const uint4* src = a_src[owner] + in_shard;
+      uint4* dst = gathered + static_cast<int64_t>(owner) * vec_per_shard + in_shard;
+      const int64_t lo = wid * per, hi = min(vec_per_block, lo + per);
+      int64_t v = lo + lane;
+      for (; v + 96 < hi; v += 128) {     // four loads in flight per lane
+        const uint4 x0 = __ldcg(src + v), x1 = __ldcg(src + v + 32), x2 = __ldcg(src + v + 64), x3 = __ldcg(src + v + 96);
+        dst[v] = x0; dst[v + 32] = x1; dst[v + 64] = x2; dst[v + 96] = x3;
+      }
+      for (; v < hi; v += 32) dst[v] = __ldcg(src + v);
+      fence_proxy_async_all();
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(ready + blk, 1);
+    }
+  }
+
+  __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
+                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+    (void)err; (void)stage; (void)st;
+    const int row = m_blk * GEMM_BM + q * 32 + lane;
+#pragma unroll 1
+    for (int c = 0; c < GEMM_BN / 32; ++c) {
+      const int col0 = n_blk * GEMM_BN + c * 32;
+      if (col0 >= N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(t_base + c * 32, r);
+      tmem_ld_wait();
+      if (row < M) gemm_store_chunk<OUT_BF16>(C, ldc, row, col0, N, r, vec_ok);
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(tempty);
+  }
+};
+
+int make_gemm_tmaps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, int a_mn, int64_t lda, const void* B,
+                    int b_mn, int64_t ldb, int M, int N, int K);
+
+}  // namespace mm
+
+extern "C" {
+
+// C[M, N] (bf16, row stride ldc) = concat_r(A_r) * B[N, K]^T. a_src: `nranks` addresses of the
+// [M/nranks, K] row shards (contiguous; entry `me` is local); gathered: local [M, K] buffer;
+// ready: local int counters, one per 128-row block, zero before the first call; call_index
+// counts calls on these counters from 1. M / nranks must be a multiple of 128, K of 8.
+int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathered, int* ready, int call_index,
+                           const void* B, int b_mn, int64_t ldb, void* C, int64_t ldc, int M, int N, int K,
+                           cudaStream_t stream) {
+  using namespace mm;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (nranks < 1 || nranks > AG_MAX_RANKS || (M % (nranks * GEMM_BM)) || (K % 8) || (ldb % 8) || (ldc % 8)) return -2;
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  CUtensorMap tmA, tmB;
+  int rc = make_gemm_tmaps(&tmA, &tmB, gathered, 0, K, B, b_mn, ldb, M, N, K);
+  if (rc) return rc;
+  const int num_m = M / GEMM_BM;
+  const int num_tiles = num_m * ((N + GEMM_BN - 1) / GEMM_BN);
+  const int grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;
+  AllGatherHook hook;
+  hook.C = C;
+  hook.ldc = ldc;
+  hook.vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && (ldc % 8 == 0);
+  for (int r = 0; r < nranks; ++r) hook.a_src[r] = reinterpret_cast<const uint4*>(a_src[r]);
+  hook.gathered = static_cast<uint4*>(gathered);
+  hook.ready = ready;
+  hook.target = call_index * grid * AllGatherHook::kAuxWarps;
+  hook.nranks = nranks;
+  hook.me = me;
+  hook.blocks_per_shard = num_m / nranks;
+  hook.num_m = num_m;
+  GemmShape shape{M, N, K};
+  constexpr int threads = GEMM_THREADS + 32 * AllGatherHook::kAuxWarps;
+  static bool configured[2][kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (b_mn) {
+    auto kern = gemm_bf16_kernel<false, true, AllGatherHook>;
+    if (!configured[1][dev]) {
+      MM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
+      configured[1][dev] = true;
+    }
+    kern<<<grid, threads, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, shape, hook, ds->status);
+  } else {
+    auto kern = gemm_bf16_kernel<false, false, AllGatherHook>;
+    if (!configured[0][dev]) {
+      MM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
+      configured[0][dev] = true;
+    }
+    kern<<<grid, threads, GEMM_SMEM_BYTES, stream>>>(tmA, tmB, shape, hook, ds->status);
+  }
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -40,6 +40,9 @@ struct AllReduceHook {
   int num_n;
 
   static constexpr int kStageBytes = 4 * AR_WARP_STAGE;  // 32 KiB
+  static constexpr int kAuxWarps = 0;
+  __device__ __forceinline__ int map_m(int m_blk) const { return m_blk; }
+  __device__ __forceinline__ void aux(int, int, int, int, int*) const {}
   struct State {
     int prev_m = -1, prev_n = -1;
   };

@@ -126,6 +126,10 @@ struct PlainHook {
   // Drains one 128x256 accumulator: warp `q` owns TMEM lanes [32q, 32q+32), i.e. rows
   // m_blk*128 + 32q + lane. `t_base` already points at that lane quarter.
   static constexpr int kStageBytes = 0;  // no shared-memory staging in the epilogue
+  static constexpr int kAuxWarps = 0;    // no helper warps besides producer, MMA and epilogue
+  // Row block of A / C that the scheduler's m index stands for (hooks may permute the order).
+  __device__ __forceinline__ int map_m(int m_blk) const { return m_blk; }
+  __device__ __forceinline__ void aux(int, int, int, int, int*) const {}
   struct State {};
   __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
@@ -148,7 +152,7 @@ struct PlainHook {
 };
 
 template <bool A_MN, bool B_MN, class Hook>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + 32 * Hook::kAuxWarps, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      GemmShape shape, Hook hook, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
@@ -202,6 +206,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
         gemm_tile_coords(tile, num_m, num_n, m_blk, n_blk);
+        m_blk = hook.map_m(m_blk);
         if (!hook.before_tile_loads(m_blk, n_blk, err)) { ok = false; break; }
         const int a_row0 = hook.a_row(m_blk);
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -267,6 +272,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (acc == 0) acc_phase ^= 1;
       }
     }
+  } else if (warp >= 6) {
+    hook.aux(warp - 6, lane, M, K, err);
   } else {
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
@@ -275,6 +282,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
       gemm_tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      m_blk = hook.map_m(m_blk);
       if (!mbar_wait(&tfull[acc], acc_phase, err, MM_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t t_base = tmem_base + acc * GEMM_BN + (static_cast<uint32_t>(q * 32) << 16);
