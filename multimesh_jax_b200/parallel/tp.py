@@ -81,3 +81,64 @@ class FusedLinearAllReduce:
     @staticmethod
     def supported(M: int, N: int, Kd: int, dtype: torch.dtype) -> bool:
         return dtype == torch.bfloat16 and N % 32 == 0 and Kd % 8 == 0
+
+
+_lib.register("mm_allgather_gemm_bf16", c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                                c_void_p, c_int64, c_int, c_int, c_int, c_void_p])
+
+
+class FusedAllGatherLinear:
+    """``concat_r(A_r) @ B^T`` for row-sharded (sequence-parallel) activations: the kernel pulls
+    the peers' row shards over NVLink while its tensor-core main loop already works on the rows
+    that have arrived (``mm_allgather_gemm_bf16``). One instance per tensor-parallel group.
+
+    Every rank first copies its shard into a peer-visible staging tile (double-buffered by call
+    parity) and the group passes a flag barrier; nothing else runs before the fused kernel."""
+
+    def __init__(self, arena: symm.SymmetricArena, ranks: Sequence[int]):
+        self.arena, self.ranks = arena, list(ranks)
+        self.g = len(self.ranks)
+        self.me = self.ranks.index(arena.rank)
+        self.flag_off = [arena.alloc_flag() for _ in self.ranks]
+        self.epoch = 0
+        self.sets: Dict[Tuple[int, int], dict] = {}
+        self.lib = _lib.load()
+        self.calls = 0
+
+    def _barrier(self) -> None:
+        self.epoch += 1
+        a = self.arena
+        peers = [r for r in self.ranks if r != a.rank]
+        symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
+        symm.wait_flags(a, [a.flag_ptr(a.rank, self.flag_off[self.ranks.index(r)]) for r in peers], self.epoch)
+
+    @staticmethod
+    def supported(rows_per_rank: int, Kd: int, dtype: torch.dtype) -> bool:
+        return dtype == torch.bfloat16 and rows_per_rank % BM == 0 and Kd % 8 == 0
+
+    def __call__(self, a_shard: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False):
+        """Returns ``(C [M, N], A_full [M, K])``; ``A_full`` is the gathered input (kept for the
+        weight gradient)."""
+        Ms, Kd = a_shard.shape
+        M = Ms * self.g
+        N = b.shape[1] if b_mn else b.shape[0]
+        st = self.sets.get((Ms, Kd))
+        if st is None:
+            st = self.sets[(Ms, Kd)] = {
+                "stage": [self.arena.alloc((Ms, Kd), torch.bfloat16) for _ in range(2)],
+                "ready": torch.zeros(M // BM, dtype=torch.int32, device=a_shard.device), "calls": 0}
+        st["calls"] += 1
+        par = st["calls"] & 1
+        stage = st["stage"][par]
+        stage.peer(self.arena.rank).copy_(a_shard)
+        self._barrier()
+        gathered = torch.empty((M, Kd), dtype=torch.bfloat16, device=a_shard.device)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
+        srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
+        rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), st["calls"],
+                                             b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
+                                             torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "mm_allgather_gemm_bf16")
+        K._count()
+        self.calls += 1
+        return out, gathered

@@ -35,6 +35,28 @@ def main():
         if err > 2e-2:
             ok = False
             print(f"rank {rank}: case {it} relative error {err}", flush=True)
+    # all-gather fused into the GEMM: every rank holds a row shard of the activations
+    from multimesh_jax_b200.parallel.tp import FusedAllGatherLinear
+    ag = FusedAllGatherLinear(arena, list(range(world)))
+    for it, (Ms, N, Kd, b_mn) in enumerate([(512, 1024, 512, False), (512, 1024, 512, False), (4096, 6144, 4096, False),
+                                            (1024, 768, 2048, True), (4096, 6144, 4096, False)]):
+        torch.manual_seed(1000 + 10 * it + rank)
+        a = torch.randn(Ms, Kd, device=dev).bfloat16()
+        torch.manual_seed(2000 + it)
+        b = (torch.randn(Kd, N, device=dev) if b_mn else torch.randn(N, Kd, device=dev)).bfloat16()
+        out, a_full = ag(a, b, b_mn=b_mn)
+        parts = [torch.empty_like(a) for _ in range(world)]
+        dist.all_gather(parts, a)
+        ref_a = torch.cat(parts, dim=0)
+        ref = ref_a.float() @ (b.float() if b_mn else b.float().t())
+        torch.cuda.synchronize()
+        if not torch.equal(a_full, ref_a):
+            ok = False
+            print(f"rank {rank}: all-gather case {it}: gathered rows differ", flush=True)
+        err = (out.float() - ref).abs().max().item() / ref.abs().max().item()
+        if err > 2e-2:
+            ok = False
+            print(f"rank {rank}: all-gather case {it} relative error {err}", flush=True)
     status = K.read_status()
     if status != 0:
         ok = False
