@@ -113,9 +113,10 @@ extern "C" {
 
 // C[M, N] (bf16, row stride ldc) = concat_r(A_r) * B[N, K]^T. a_src: `nranks` addresses of the
 // [M/nranks, K] row shards (contiguous; entry `me` is local); gathered: local [M, K] buffer;
-// ready: local int counters, one per 128-row block, zero before the first call; call_index
-// counts calls on these counters from 1. M / nranks must be a multiple of 128, K of 8.
-int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathered, int* ready, int call_index,
+// ready: local int counters, one per 128-row block, zero before the first call and never
+// reset; *target (host memory, 0 before the first call) carries the value the counters reach
+// after this call and is updated here. M / nranks must be a multiple of 128, K of 8.
+int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathered, int* ready, int* target,
                            const void* B, int b_mn, int64_t ldb, void* C, int64_t ldc, int M, int N, int K,
                            cudaStream_t stream) {
   using namespace mm;
@@ -136,7 +137,8 @@ int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathe
   for (int r = 0; r < nranks; ++r) hook.a_src[r] = reinterpret_cast<const uint4*>(a_src[r]);
   hook.gathered = static_cast<uint4*>(gathered);
   hook.ready = ready;
-  hook.target = call_index * grid * AllGatherHook::kAuxWarps;
+  hook.target = *target + grid * AllGatherHook::kAuxWarps;
+  *target = hook.target;
   hook.nranks = nranks;
   hook.me = me;
   hook.blocks_per_shard = num_m / nranks;

@@ -83,7 +83,7 @@ class FusedLinearAllReduce:
         return dtype == torch.bfloat16 and N % 32 == 0 and Kd % 8 == 0
 
 
-_lib.register("mm_allgather_gemm_bf16", c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+_lib.register("mm_allgather_gemm_bf16", c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
                                                 c_void_p, c_int64, c_int, c_int, c_int, c_void_p])
 
 
@@ -126,7 +126,8 @@ class FusedAllGatherLinear:
         if st is None:
             st = self.sets[(Ms, Kd)] = {
                 "stage": [self.arena.alloc((Ms, Kd), torch.bfloat16) for _ in range(2)],
-                "ready": torch.zeros(M // BM, dtype=torch.int32, device=a_shard.device), "calls": 0}
+                "ready": torch.zeros(M // BM, dtype=torch.int32, device=a_shard.device), "calls": 0,
+                "target": c_int(0)}
         st["calls"] += 1
         par = st["calls"] & 1
         stage = st["stage"][par]
@@ -135,7 +136,7 @@ class FusedAllGatherLinear:
         gathered = torch.empty((M, Kd), dtype=torch.bfloat16, device=a_shard.device)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
         srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
-        rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), st["calls"],
+        rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), ctypes.byref(st["target"]),
                                              b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
                                              torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "mm_allgather_gemm_bf16")
