@@ -188,6 +188,15 @@ def build_pull_chunks(chunks: List[dict], src_tile_shape: Sequence[int], dst_til
     (leading dimensions are split into several records when the rank is larger)."""
     records: List[List[int]] = []
     src_shape0, dst_shape0 = list(src_tile_shape), list(dst_tile_shape)
+    # The kernel walks the records in order, so at any moment a destination reads mostly from
+    # one source. Start every destination at a different source (its own ordinal first, then
+    # the next ones in ring order): otherwise all destinations would pull from source 0 first
+    # and share that GPU's NVLink egress while the other sources sit idle.
+    sources = sorted({c["src_device"] for c in chunks})
+    if len(sources) > 1:
+        pos = {d: i for i, d in enumerate(sources)}
+        chunks = [c for _, c in sorted(enumerate(chunks), key=lambda ic: (
+            (pos[ic[1]["src_device"]] - ic[1]["dst_device"]) % len(sources), ic[0]))]
     for c in chunks:
         src_tile_shape, dst_tile_shape = list(src_shape0), list(dst_shape0)   # merged per chunk below
         s_str, d_str = _strides(src_tile_shape), _strides(dst_tile_shape)
