@@ -167,7 +167,8 @@ def main():
         lps = [q, q + 1, q + 1, q - 2]      # head + loss cost about 1.6 layers, the embedding about 0.7
     else:
         lps = None
-    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, layers_per_stage=lps)
+    split = ("_act", "_wgt") if args.schedule == "zero-bubble-h2" else None
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, layers_per_stage=lps, split_backprop=split)
 
     # abstract arguments for the capture; real tensors are created shard by shard below
     with torch.device("meta"):

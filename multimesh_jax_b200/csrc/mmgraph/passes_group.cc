@@ -480,6 +480,14 @@ bool SplitCriticalPath(CompileState& s) {
       critical.insert(nid);
       for (int v : g.node(nid).inputs) { const int p = g.value(v).producer; if (p >= 0) mark(p); }
     };
+    // every value handed to that first consumer is on the critical path (a stage boundary may
+    // carry several activation gradients), not only the first one found
+    for (int id : grp.nodes)
+      for (int o : g.node(id).outputs)
+        for (int u : users[o]) {
+          const int t = g.node(u).task;
+          if (t != grp.id && t >= 0 && group_pos[t] == earliest) mark(id);
+        }
     mark(g.value(critical_value).producer);
     if (critical.size() == grp.nodes.size()) { out_groups.push_back(grp); continue; }
     const std::string base = cc.original.empty() ? grp.color : cc.original;

@@ -300,11 +300,14 @@ def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                                                                        ("mlp", "model"), ("fsdp", "data"),
                                                                        ("expert", "data"),
                                                                        ("boundary_hidden", "model")),
-                            layers_per_stage: Optional[Sequence[int]] = None) -> None:
+                            layers_per_stage: Optional[Sequence[int]] = None,
+                            split_backprop: Optional[Tuple[str, str]] = None) -> None:
     """Places the layers on pipeline stages (mesh axis ``stage``): ``layers_per_stage[s]``
     consecutive layers on stage ``s`` (default: equal shares), the embedding on the first stage
     and the head / loss on the last one - which is why the last stage may be given fewer layers.
-    The optimiser update of a parameter runs where its gradient lives."""
+    The optimiser update of a parameter runs where its gradient lives. ``split_backprop``
+    (two suffixes) splits every backward task into its activation-gradient and weight-gradient
+    halves, which the zero-bubble schedule needs."""
     if layers_per_stage is None:
         per = cfg.n_layers // num_stages
         layers_per_stage = [per] * (num_stages - 1) + [cfg.n_layers - per * (num_stages - 1)]
@@ -318,11 +321,14 @@ def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
     def layer_task(matched: str, backprop: bool) -> Task:
         idx = int(matched.split(".")[1])
         stage = stage_of[idx]
-        return Task(name=f"stage{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage}, logical_axes=la)
+        return Task(name=f"stage{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage}, logical_axes=la,
+                    split_backprop=split_backprop)
 
     mesh.register_task(r"(layers\.\d+)", factory=layer_task)
     mesh.register_task("(embed)", factory=lambda m, b: Task(name="stage0" + ("_bwd" if b else ""),
-                                                            mesh_slice={"stage": 0}, logical_axes=la))
+                                                            mesh_slice={"stage": 0}, logical_axes=la,
+                                                            split_backprop=split_backprop))
     last = num_stages - 1
     mesh.register_task("(head)", factory=lambda m, b: Task(name=f"stage{last}" + ("_bwd" if b else ""),
-                                                           mesh_slice={"stage": last}, logical_axes=la))
+                                                           mesh_slice={"stage": last}, logical_axes=la,
+                                                           split_backprop=split_backprop))

@@ -242,3 +242,36 @@ def test_forced_layout_change_at_the_stage_boundary():
     assert len(crossings) == 2 * (B // MB)
     assert all(src == [[], [], [1]] and dst == [[0], [], []] for src, dst in crossings)
     exe.shutdown()
+
+
+def test_zero_bubble_schedule_on_four_llama_stages():
+    """Both values that cross a stage boundary backwards (gradients of the residual stream and of
+    its normalised copy) stay in the activation-gradient half of the split backward task; the
+    weight-gradient halves are non-critical and results equal the eager step."""
+    cfg = _cfg(n_layers=4, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128)
+    B, S, MB = 16, 16, 2
+    params = llama.init_params(cfg)
+    opt_state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB,
+                                 schedule="zero-bubble-h2")
+    mesh = mm.MultiMesh((4, 1, 1), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=4, split_backprop=("_act", "_wgt"))
+    with mesh:
+        exe = mm.compile_function(step, (params, opt_state, tokens, labels, cos, sin), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(params, opt_state, tokens, labels, cos, sin)
+    loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)
+    loop = [t for t in exe.plan["templates"] if t["in_loop"]]
+    producer = {v: t["name"] for t in loop for v in t["outputs"]}
+    noncritical = {t["name"] for t in loop if t["noncritical"]}
+    assert len(noncritical) == 3                  # stages 1..3; stage 0 has no activation gradient to hand on
+    for t in loop:
+        if not t["noncritical"]:                  # nothing on the critical path waits for a weight-gradient task
+            assert not any(producer.get(v) in noncritical for v in t["inputs"])
+    exe.shutdown()
