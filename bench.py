@@ -7,8 +7,11 @@ AdamW, random init, synthetic token ids) through the MPMD compiler and runtime.
 
 Weak scaling: 8 sequences of 2048 tokens per GPU and step (global batch 64 at N = 8, the
 configuration named by the baseline), microbatches of 4 sequences, 1F1B schedule.
-Parallelism: N = 1 single stage; N = 2 -> 2 pipeline stages; N = 4 -> 2 stages x TP 2 (or 4
-stages with --tp 1); N = 8 -> 4 stages x TP 2.
+Default layouts: N = 1 single device; N = 2 data parallel; N = 4 data parallel 2 x tensor
+parallel 2; N = 8 the layout the baseline names, 4 pipeline stages x tensor parallel 2 with
+16 microbatches. --pp / --dp / --tp / --fsdp / --force-reshard / --model select the others
+(Llama-3-8B with FSDP and a layout-changing stage boundary, Mixtral-8x7B with expert
+parallelism over the data axis).
 
 Prints ONE JSON line (rank 0). `value` is device-timed (CUDA events around exactly K steps,
 barrier + synchronize on both sides, max over ranks); `e2e` repeats the measurement with the
@@ -25,7 +28,11 @@ import sys
 import threading
 import time
 
-import torch
+# one growing segment per stream instead of many fixed-size blocks: the step's large, short-lived
+# activations would otherwise fragment the caching allocator at this model size
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+import torch  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
