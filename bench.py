@@ -122,6 +122,8 @@ class ClockSampler:
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) != 0:
+            return 0
         print(json.dumps({"impl": "reference", "unavailable":
                           "reference cannot be installed offline: its build needs scikit-build, JAX/jaxlib patches, "
                           "Bazel and network fetches of OpenXLA, zuku and Legion (pip: ModuleNotFoundError: skbuild)"}))
