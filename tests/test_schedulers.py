@@ -172,3 +172,58 @@ def test_custom_schedule_validation():
 def test_bijective_task_requirement():
     assert C.enforce_bijective_tasks("custom") and C.enforce_bijective_tasks("zero-bubble-h2")
     assert not C.enforce_bijective_tasks("1f1b")
+
+
+def interleaved(groups, rounds, num_iters, split_bwd=False):
+    """Circular placement: ``groups * rounds`` virtual stages over ``groups`` device groups, stage s
+    on group ``s % groups`` (the interleaved cases of src/pjrt_client/loop_scheduler_test.cc)."""
+    stages = groups * rounds
+    rows, names = pipeline(stages, num_iters, split_bwd=split_bwd)
+    for row in rows:
+        for t in row:
+            s = int("".join(ch for ch in t["color"] if ch.isdigit()))
+            t["device_start"] = s % groups
+    return rows, names, stages
+
+
+@pytest.mark.parametrize("groups,rounds,n", [(2, 2, 4), (4, 2, 8), (4, 4, 8), (2, 4, 6)])
+def test_interleaved_wavefront_is_valid_and_every_group_alternates(groups, rounds, n):
+    rows, names, stages = interleaved(groups, rounds, n)
+    out = run("1f1b", rows, n)
+    order = [tuple(e) for e in out["orders"][0]]
+    check_valid(order, names, n, stages)
+    # the minibatch is as wide as the number of device groups: within one group the first
+    # `groups` microbatches pass the group's first virtual stage before any reaches its second
+    idx = {name: k for k, name in enumerate(names)}
+    pos = {e: i for i, e in enumerate(order)}
+    first_second_round = min(pos[(it, idx[f"fwd{groups}"])] for it in range(n))
+    assert sum(1 for it in range(n) if pos[(it, idx["fwd0"])] < first_second_round) >= min(groups, n)
+    # no group ever holds all microbatches in flight: a backward of the last stage is reached
+    # before the last forward of the first stage when there are more microbatches than groups
+    if n > 2 * groups * rounds:
+        assert pos[(0, idx[f"bwd{stages - 1}"])] < pos[(n - 1, idx["fwd0"])]
+
+
+def test_interleaved_wavefront_with_embeddings_prefetches_the_full_mesh_task():
+    rows, names, stages = interleaved(2, 2, 4)
+    for row in rows:
+        row.insert(0, {"color": "loop_increment", "device_start": 0, "num_devices": 2, "prefetch": True,
+                       "on_full_mesh": True, "noncritical": False, "consumes_stage": -1})
+    order = [tuple(e) for e in run("prefetch-wavefront", rows, 4)["orders"][0]]
+    assert order[:4] == [(it, 0) for it in range(4)]
+    assert len(order) == len(set(order)) == 4 * (len(names) + 1)
+
+
+@pytest.mark.parametrize("groups,rounds,n", [(2, 2, 4), (4, 2, 8), (4, 6, 8)])
+def test_zero_bubble_interleaved_keeps_dependencies_and_defers_weight_gradients(groups, rounds, n):
+    rows, names, stages = interleaved(groups, rounds, n, split_bwd=True)
+    order = [tuple(e) for e in run("zero-bubble-h2", rows, n)["orders"][0]]
+    assert len(order) == len(set(order)) == n * len(names)
+    pos = {e: i for i, e in enumerate(order)}
+    idx = {name: k for k, name in enumerate(names)}
+    for it in range(n):
+        for s in range(stages):
+            assert pos[(it, idx[f"wgrad{s}"])] > pos[(it, idx[f"bwd{s}"])]
+            if s > 0:
+                assert pos[(it, idx[f"fwd{s}"])] > pos[(it, idx[f"fwd{s - 1}"])]
+                assert pos[(it, idx[f"bwd{s - 1}"])] > pos[(it, idx[f"bwd{s}"])]
