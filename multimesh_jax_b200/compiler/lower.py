@@ -324,6 +324,11 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
     # operand afterwards (passes may have moved a reader behind it): otherwise run the plain one.
     if fast_variants:
         from ..ops.mm_ops import INPLACE_OPERANDS
+        # an input that another task reads as well (the two halves of a split backward task share
+        # the incoming boundary gradient) must survive this task unchanged
+        mine = set(template["inputs"])
+        shared_inputs = {v for t in plan["templates"] if t is not template and t["name"] != template["name"]
+                         for v in t["inputs"] if v in mine}
         index_of = {id(ins): idx for idx, ins in enumerate(instrs)}
         for ins_obj, plain, opname in fast_variants:
             idx = index_of.get(id(ins_obj))
@@ -332,7 +337,7 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                 continue
             ids = _tensor_ids_in_order(ins_obj.args, ins_obj.kwargs)
             for pos in clobbered:
-                if pos < len(ids) and (last.get(ids[pos], -1) > idx or ids[pos] in keep):
+                if pos < len(ids) and (last.get(ids[pos], -1) > idx or ids[pos] in keep or ids[pos] in shared_inputs):
                     ins_obj.fn = plain
                     break
     last_use: Dict[int, List[int]] = {}
