@@ -1,6 +1,6 @@
 """One kernel, one small case, three launches - the program to put under a profiler.
 
-    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
+    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad (each also as <case>_pair)|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
 
 Inputs are larger than the 126 MB L2 where the kernel is memory bound and a few hundred MB at
 most, so a full-metric capture of one launch finishes in seconds. Each case prints its
@@ -35,6 +35,9 @@ def main(argv=None) -> int:
     dev = torch.device("cuda")
     torch.manual_seed(0)
     out = {"case": case}
+    if case.endswith("_pair"):     # same case on the CTA-pair kernel
+        K.PAIR_MIN_M = 1
+        case = case[:-5]
     if case in ("gemm", "gemm_dgrad", "gemm_wgrad"):
         M, N, Kd = 8192, 4096, 4096
         if case == "gemm":          # y = x w^T

@@ -37,6 +37,31 @@ def test_gemm_layouts(M, N, K_, a_mn, b_mn):
     _close(out, ref)
 
 
+@pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_pair_layouts(M, N, K_, a_mn, b_mn):
+    """CTA-pair kernel (cta_group::2, 256x256 tile per pair) against the fp32 product, ragged
+    shapes included: rows of the second CTA of a pair may lie entirely outside the matrix."""
+    torch.manual_seed(0)
+    a = _rand(K_, M) if a_mn else _rand(M, K_)
+    b = _rand(K_, N) if b_mn else _rand(N, K_)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    assert K.read_status() == 0
+    _close(out, ref)
+
+
+def test_gemm_pair_accumulates_into_fp32():
+    torch.manual_seed(1)
+    T, Kd, N = 2048, 512, 768
+    x, dy = _rand(T, Kd), _rand(T, N)
+    dw = torch.zeros(N, Kd, device=DEV, dtype=torch.float32)
+    for _ in range(2):
+        K.gemm(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True, pair=True)
+    assert K.read_status() == 0
+    _close(dw, 2 * dy.float().t() @ x.float(), rtol=1e-3)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gemm_accumulate(dtype):
     torch.manual_seed(1)
