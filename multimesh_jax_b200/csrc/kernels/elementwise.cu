@@ -95,7 +95,9 @@ __global__ void __launch_bounds__(RN_THREADS)
                        const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
                        __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows,
                        int D, int add_to_dx) {
-  __shared__ float red[32];
+  // Two rows per iteration: the loads of both rows are in flight before the one block-wide sum
+  // that serves both, and the rows stay packed (bf16) in registers between the two passes.
+  __shared__ float red[64];
   const int nvec = D / 8;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
   float wreg[RN_MAX_VEC][8];
@@ -104,7 +106,7 @@ __global__ void __launch_bounds__(RN_THREADS)
   for (int i = 0; i < RN_MAX_VEC; ++i) {
     const int v = threadIdx.x + i * RN_THREADS;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    for (int j = 0; j < 8; ++j) { dwacc[i][j] = 0.f; wreg[i][j] = 0.f; }
     if (v < nvec) {
       uint4 wv = wr[v];
       float2 a = unpack_bf16(wv.x), b = unpack_bf16(wv.y), c = unpack_bf16(wv.z),
@@ -113,56 +115,85 @@ __global__ void __launch_bounds__(RN_THREADS)
       wreg[i][4] = c.x; wreg[i][5] = c.y; wreg[i][6] = d.x; wreg[i][7] = d.y;
     }
   }
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
-    uint4* dxr = reinterpret_cast<uint4*>(dx + row * D);
-    const float r = rstd[row];
-    float xf[RN_MAX_VEC][8], gf[RN_MAX_VEC][8];
-    float dot = 0.f;
+  for (int64_t row = 2 * static_cast<int64_t>(blockIdx.x); row < rows; row += 2 * static_cast<int64_t>(gridDim.x)) {
+    const int nr = (row + 1 < rows) ? 2 : 1;
+    uint4 xv[2][RN_MAX_VEC], gv[2][RN_MAX_VEC];
+    float rr[2];
 #pragma unroll
-    for (int i = 0; i < RN_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * RN_THREADS;
-      if (v < nvec) {
-        uint4 xv = xr[v], gv = gr[v];
-        float2 a;
-        a = unpack_bf16(xv.x); xf[i][0] = a.x; xf[i][1] = a.y;
-        a = unpack_bf16(xv.y); xf[i][2] = a.x; xf[i][3] = a.y;
-        a = unpack_bf16(xv.z); xf[i][4] = a.x; xf[i][5] = a.y;
-        a = unpack_bf16(xv.w); xf[i][6] = a.x; xf[i][7] = a.y;
-        a = unpack_bf16(gv.x); gf[i][0] = a.x; gf[i][1] = a.y;
-        a = unpack_bf16(gv.y); gf[i][2] = a.x; gf[i][3] = a.y;
-        a = unpack_bf16(gv.z); gf[i][4] = a.x; gf[i][5] = a.y;
-        a = unpack_bf16(gv.w); gf[i][6] = a.x; gf[i][7] = a.y;
+    for (int k = 0; k < 2; ++k) {
+      const int64_t rk = row + (k < nr ? k : 0);
+      const uint4* xr = reinterpret_cast<const uint4*>(x + rk * D);
+      const uint4* gr = reinterpret_cast<const uint4*>(dy + rk * D);
+      rr[k] = k < nr ? rstd[rk] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          dwacc[i][j] += gf[i][j] * xf[i][j] * r;
-          gf[i][j] *= wreg[i][j];
-          dot += gf[i][j] * xf[i][j];
+      for (int i = 0; i < RN_MAX_VEC; ++i) {
+        const int v = threadIdx.x + i * RN_THREADS;
+        if (v < nvec) {
+          xv[k][i] = xr[v];
+          gv[k][i] = gr[v];
+        } else {
+          xv[k][i] = make_uint4(0, 0, 0, 0);
+          gv[k][i] = make_uint4(0, 0, 0, 0);
         }
       }
     }
-    dot = block_sum<RN_THREADS>(dot, red);
-    const float c = dot * r * r * r / D;
+    float dot[2] = {0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < RN_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * RN_THREADS;
-      if (v < nvec) {
-        float o[8];
+    for (int k = 0; k < 2; ++k) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = gf[i][j] * r - xf[i][j] * c;
-        if (add_to_dx) {
-          uint4 old = dxr[v];
-          float2 a;
-          a = unpack_bf16(old.x); o[0] += a.x; o[1] += a.y;
-          a = unpack_bf16(old.y); o[2] += a.x; o[3] += a.y;
-          a = unpack_bf16(old.z); o[4] += a.x; o[5] += a.y;
-          a = unpack_bf16(old.w); o[6] += a.x; o[7] += a.y;
+      for (int i = 0; i < RN_MAX_VEC; ++i) {
+        const uint32_t xw[4] = {xv[k][i].x, xv[k][i].y, xv[k][i].z, xv[k][i].w};
+        const uint32_t gw[4] = {gv[k][i].x, gv[k][i].y, gv[k][i].z, gv[k][i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 xf = unpack_bf16(xw[j]), gf = unpack_bf16(gw[j]);
+          const float p0 = gf.x * xf.x, p1 = gf.y * xf.y;
+          dwacc[i][2 * j] += p0 * rr[k];          // rr is 0 for a missing second row
+          dwacc[i][2 * j + 1] += p1 * rr[k];
+          dot[k] += p0 * wreg[i][2 * j] + p1 * wreg[i][2 * j + 1];
         }
-        uint4 ov;
-        ov.x = pack_bf16(o[0], o[1]); ov.y = pack_bf16(o[2], o[3]);
-        ov.z = pack_bf16(o[4], o[5]); ov.w = pack_bf16(o[6], o[7]);
-        dxr[v] = ov;
+      }
+    }
+    // one pair of barriers for both rows
+    dot[0] = warp_sum(dot[0]);
+    dot[1] = warp_sum(dot[1]);
+    {
+      const int wi = threadIdx.x >> 5, l = threadIdx.x & 31;
+      __syncthreads();
+      if (l == 0) { red[wi] = dot[0]; red[32 + wi] = dot[1]; }
+      __syncthreads();
+      const float t0 = (l < RN_THREADS / 32) ? red[l] : 0.f;
+      const float t1 = (l < RN_THREADS / 32) ? red[32 + l] : 0.f;
+      dot[0] = warp_sum(t0);
+      dot[1] = warp_sum(t1);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (k < nr) {
+        const float r = rr[k];
+        const float c = dot[k] * r * r * r / D;
+        uint4* dxr = reinterpret_cast<uint4*>(dx + (row + k) * D);
+#pragma unroll
+        for (int i = 0; i < RN_MAX_VEC; ++i) {
+          const int v = threadIdx.x + i * RN_THREADS;
+          if (v < nvec) {
+            const uint32_t xw[4] = {xv[k][i].x, xv[k][i].y, xv[k][i].z, xv[k][i].w};
+            const uint32_t gw[4] = {gv[k][i].x, gv[k][i].y, gv[k][i].z, gv[k][i].w};
+            uint32_t ow[4] = {0, 0, 0, 0};
+            if (add_to_dx) {
+              const uint4 old = dxr[v];
+              ow[0] = old.x; ow[1] = old.y; ow[2] = old.z; ow[3] = old.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 xf = unpack_bf16(xw[j]), gf = unpack_bf16(gw[j]), of = unpack_bf16(ow[j]);
+              const float o0 = gf.x * wreg[i][2 * j] * r - xf.x * c + of.x;
+              const float o1 = gf.y * wreg[i][2 * j + 1] * r - xf.y * c + of.y;
+              ow[j] = pack_bf16(o0, o1);
+            }
+            dxr[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
+        }
       }
     }
   }
@@ -199,29 +230,39 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, float*
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restrict__ cs,
                             const float* __restrict__ sn, int64_t T, int S, int H, int Dh,
                             int64_t stride_t, float sign, int rot_per_group, int group_size) {
+  // one thread rotates 8 adjacent pairs: two 16-byte loads and stores of the head, and the
+  // matching 32 bytes of each table, are in flight per thread
   const int half = Dh / 2;
+  const int per_head = half / 8;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int per_tok = H * (half / 2);  // each thread handles 2 adjacent pairs (bf162)
+  const int per_tok = H * per_head;
   const int64_t total = T * per_tok;
   if (idx >= total) return;
   const int64_t t = idx / per_tok;
   const int rem = static_cast<int>(idx - t * per_tok);
-  int h = rem / (half / 2);
-  const int i = (rem - h * (half / 2)) * 2;
+  int h = rem / per_head;
+  const int i = (rem - h * per_head) * 8;
   h = (h / rot_per_group) * group_size + h % rot_per_group;
   const int pos = static_cast<int>(t % S);
   __nv_bfloat16* base = qk + t * stride_t + static_cast<int64_t>(h) * Dh;
-  __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(base + i);
-  __nv_bfloat162 hi = *reinterpret_cast<__nv_bfloat162*>(base + i + half);
-  const float2 c = *reinterpret_cast<const float2*>(cs + static_cast<int64_t>(pos) * half + i);
-  float2 s = *reinterpret_cast<const float2*>(sn + static_cast<int64_t>(pos) * half + i);
-  s.x *= sign; s.y *= sign;
-  const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
-  float2 olo, ohi;
-  olo.x = a.x * c.x - b.x * s.x; olo.y = a.y * c.y - b.y * s.y;
-  ohi.x = b.x * c.x + a.x * s.x; ohi.y = b.y * c.y + a.y * s.y;
-  *reinterpret_cast<__nv_bfloat162*>(base + i) = __floats2bfloat162_rn(olo.x, olo.y);
-  *reinterpret_cast<__nv_bfloat162*>(base + i + half) = __floats2bfloat162_rn(ohi.x, ohi.y);
+  const uint4 lo = *reinterpret_cast<const uint4*>(base + i);
+  const uint4 hi = *reinterpret_cast<const uint4*>(base + i + half);
+  const float4* cp = reinterpret_cast<const float4*>(cs + static_cast<int64_t>(pos) * half + i);
+  const float4* sp = reinterpret_cast<const float4*>(sn + static_cast<int64_t>(pos) * half + i);
+  const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+  uint32_t ol[4], oh[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 a = unpack_bf16(lw[j]), b = unpack_bf16(hw[j]);
+    const float sx = sv[2 * j] * sign, sy = sv[2 * j + 1] * sign;
+    ol[j] = pack_bf16(a.x * c[2 * j] - b.x * sx, a.y * c[2 * j + 1] - b.y * sy);
+    oh[j] = pack_bf16(b.x * c[2 * j] + a.x * sx, b.y * c[2 * j + 1] + a.y * sy);
+  }
+  *reinterpret_cast<uint4*>(base + i) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+  *reinterpret_cast<uint4*>(base + i + half) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
 }
 
 // ------------------------------------------------------------------- SwiGLU
@@ -541,9 +582,9 @@ int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rs
 
 int mm_rope(void* qk, const float* cos_t, const float* sin_t, int64_t T, int S, int H, int Dh,
             int64_t stride_t, int backward, int rot_per_group, int group_size, cudaStream_t stream) {
-  if (Dh % 4) return -2;
+  if (Dh % 16 || (stride_t % 8) || (reinterpret_cast<uintptr_t>(qk) & 15)) return -2;
   if (rot_per_group <= 0 || group_size <= 0) { rot_per_group = 1; group_size = 1; }
-  const int64_t total = T * H * (Dh / 4);
+  const int64_t total = T * H * (Dh / 16);
   if (total == 0) return 0;
   rope_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(qk), cos_t,
                                                          sin_t, T, S, H, Dh, stride_t,
