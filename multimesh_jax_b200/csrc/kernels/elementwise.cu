@@ -210,13 +210,33 @@ __global__ void __launch_bounds__(RN_THREADS)
 }
 
 // dw[j] (+)= sum_p partial[p, j]
-__global__ void colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                       int parts, int D, int accumulate) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j >= D) return;
+__global__ void __launch_bounds__(256) colsum_partials_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                                               int parts, int D, int accumulate) {
+  // 32 columns x 8 slices of the partials per block: the loads of a warp are one 128-byte line
+  // and eight of them are in flight per column before the shared-memory reduction
+  __shared__ float red[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[static_cast<int64_t>(p) * D + j];
-  dw[j] = accumulate ? dw[j] + s : s;
+  if (j < D) {
+    int p = ty;
+    for (; p + 24 < parts; p += 32) {
+      const float a0 = partial[static_cast<int64_t>(p) * D + j];
+      const float a1 = partial[static_cast<int64_t>(p + 8) * D + j];
+      const float a2 = partial[static_cast<int64_t>(p + 16) * D + j];
+      const float a3 = partial[static_cast<int64_t>(p + 24) * D + j];
+      s += (a0 + a1) + (a2 + a3);
+    }
+    for (; p < parts; p += 8) s += partial[static_cast<int64_t>(p) * D + j];
+  }
+  red[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && j < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][tx];
+    dw[j] = accumulate ? dw[j] + t : t;
+  }
 }
 
 // --------------------------------------------------------------------- RoPE
@@ -269,22 +289,37 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restr
 // gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  h = silu(gate) * up.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
                                   __nv_bfloat16* __restrict__ h, int64_t T, int F) {
+  // two 8-element groups per thread (half the array apart), all four loads issued first
   const int fv = F / 8;
+  const int64_t total = T * fv;
+  const int64_t half = (total + 1) / 2;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= T * fv) return;
-  const int64_t t = idx / fv;
-  const int v = static_cast<int>(idx - t * fv);
-  const uint4 g = reinterpret_cast<const uint4*>(gu + t * 2 * F)[v];
-  const uint4 u = reinterpret_cast<const uint4*>(gu + t * 2 * F + F)[v];
-  const uint32_t gg[4] = {g.x, g.y, g.z, g.w}, uu[4] = {u.x, u.y, u.z, u.w};
-  uint32_t oo[4];
+  if (idx >= half) return;
+  const int64_t e[2] = {idx, idx + half};
+  uint4 g[2], u[2];
+  int64_t t[2];
+  int v[2];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    float2 a = unpack_bf16(gg[j]), b = unpack_bf16(uu[j]);
-    float s0 = a.x / (1.f + __expf(-a.x)), s1 = a.y / (1.f + __expf(-a.y));
-    oo[j] = pack_bf16(s0 * b.x, s1 * b.y);
+  for (int k = 0; k < 2; ++k) {
+    const int64_t ek = e[k] < total ? e[k] : idx;
+    t[k] = ek / fv;
+    v[k] = static_cast<int>(ek - t[k] * fv);
+    g[k] = reinterpret_cast<const uint4*>(gu + t[k] * 2 * F)[v[k]];
+    u[k] = reinterpret_cast<const uint4*>(gu + t[k] * 2 * F + F)[v[k]];
   }
-  reinterpret_cast<uint4*>(h + t * F)[v] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    if (e[k] >= total) break;
+    const uint32_t gg[4] = {g[k].x, g[k].y, g[k].z, g[k].w}, uu[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+    uint32_t oo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = unpack_bf16(gg[j]), b = unpack_bf16(uu[j]);
+      float s0 = a.x / (1.f + __expf(-a.x)), s1 = a.y / (1.f + __expf(-a.y));
+      oo[j] = pack_bf16(s0 * b.x, s1 * b.y);
+    }
+    reinterpret_cast<uint4*>(h + t[k] * F)[v[k]] = make_uint4(oo[0], oo[1], oo[2], oo[3]);
+  }
 }
 
 // dgu[:, :F] = dh * up * silu'(gate),  dgu[:, F:] = dh * silu(gate)
@@ -574,7 +609,7 @@ int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rs
   else MM_RN_BWD(512, 4);
 #undef MM_RN_BWD
   MM_CUDA_TRY(cudaGetLastError());
-  colsum_partials_kernel<<<blocks_for(D, 128), 128, 0, stream>>>(scratch, dw_out, parts, D,
+  colsum_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>(scratch, dw_out, parts, D,
                                                                accumulate_dw);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
@@ -598,7 +633,7 @@ int mm_swiglu_fwd(const void* gu, void* h, int64_t T, int F, cudaStream_t stream
   if (F % 8) return -2;
   const int64_t total = T * (F / 8);
   if (total == 0) return 0;
-  swiglu_fwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
+  swiglu_fwd_kernel<<<blocks_for((total + 1) / 2, 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), T, F);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
@@ -760,7 +795,7 @@ extern "C" int mm_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* 
 #undef MM_RN_BWD_NA
   MM_CUDA_TRY(cudaGetLastError());
   // every block wrote its full row of partials above, so the reduction reads only fresh data
-  colsum_partials_kernel<<<(D + 127) / 128, 128, 0, stream>>>(scratch, dw_out, parts, D, accumulate_dw);
+  colsum_partials_kernel<<<(D + 31) / 32, 256, 0, stream>>>(scratch, dw_out, parts, D, accumulate_dw);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }
