@@ -22,7 +22,8 @@ def _load_native():
 _mm_C = _load_native()
 
 from . import state  # noqa: E402
-from .lib import (autoshard, context, enable_fast_path, enable_recomputation, ignore_transforms, mjit,  # noqa: E402
+from .lib import (autoshard, context, custom_partitioning, enable_fast_path, enable_recomputation,  # noqa: E402
+                  ignore_transforms, index_class, mjit, shard_map,
                   recompute_from_arguments_if_cost_less_than, relayout, replicate_parameters_smaller_than_num_elements,
                   should_ignore_transforms, tasks, with_sharding_constraint)
 from .no_op import mark_gradient, mark_loss, no_op  # noqa: E402
@@ -38,5 +39,5 @@ __all__ = [
     "with_sharding_constraint", "relayout", "tasks", "mjit", "shutdown", "replicate_parameters_smaller_than_num_elements",
     "recompute_from_arguments_if_cost_less_than", "clear_tasks", "no_op", "mark_gradient", "mark_loss",
     "value_and_grad", "named_scope", "module_scopes", "compile_function", "Executable", "ShardedTensor",
-    "StepFailed", "init", "init_test",
+    "StepFailed", "init", "init_test", "custom_partitioning", "index_class", "shard_map",
 ]

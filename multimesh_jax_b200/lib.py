@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import contextlib
 import json
-from typing import Any, Callable, Iterable, Optional, Sequence, Union
+from typing import Any, Callable, Dict, Iterable, Optional, Sequence, Tuple, Union
 
 import torch
 
@@ -110,6 +110,68 @@ def relayout(x: Any, spec: Sequence[AxisSpec]):
         return torch.ops.mm.marker(t, "Relayout", _json.dumps(payload))
 
     return pytree.tree_map(one, x)
+
+
+def index_class(members: Sequence[Tuple[int, int]], *, reduced_outputs: Sequence[int] = (), no_shard: bool = False,
+                shares_axes: bool = False) -> Dict[str, Any]:
+    """One index class of a sharding rule: the (slot, dimension) pairs that are indexed by the
+    same loop variable of the operator. Slots count the tensor operands first, then the results.
+    ``reduced_outputs`` lists result slots that become partial sums when the class is sharded
+    (a contraction), ``no_shard`` forbids sharding the class, ``shares_axes`` lets the class use
+    mesh axes that another class of the same operator already uses (expert dimension next to the
+    token dimension)."""
+    out = {"members": [list(m) for m in members], "no_shard": bool(no_shard),
+           "reduced_outputs": [int(r) for r in reduced_outputs]}
+    if shares_axes:
+        out["shares_axes"] = True
+    return out
+
+
+def custom_partitioning(op: Any, rule: Optional[Callable] = None):
+    """Gives a user-defined operator (a ``torch.library`` operator, or its ``namespace.name.overload``
+    string) its sharding rule, so that the compiler shards it inside whichever task it lands in,
+    on that task's own sub-mesh. ``rule(node, in_ranks, out_ranks)`` receives the graph node and the
+    shapes of the tensor operands / results and returns ``{"classes": [index_class(...), ...]}``.
+    Usable as a decorator. Counterpart of ``multimesh.jax.custom_partitioning``
+    (multimesh/jax/task.py:542-560), which re-routes JAX's partitioner callback to the task mesh;
+    here the rule is consumed by the C++ propagation pass directly."""
+    from .compiler.capture import op_name, register_shard_rule
+    name = op if isinstance(op, str) else op_name(op if isinstance(op, torch._ops.OpOverload) else op.default)
+    if rule is None:
+        return register_shard_rule(name)
+    register_shard_rule(name)(rule)
+    return rule
+
+
+def shard_map(fun: Callable, in_specs: Sequence[Optional[Sequence[AxisSpec]]],
+              out_specs: Union[Sequence[AxisSpec], Sequence[Optional[Sequence[AxisSpec]]], None] = None) -> Callable:
+    """Runs ``fun`` with its arguments and results laid out as the specs say, on the sub-mesh of
+    the task the call lands in (``multimesh.jax.shard_map``, multimesh/jax/task.py:562-577, does the
+    same re-routing for JAX's ``shard_map``). ``in_specs`` has one entry per positional argument
+    and ``out_specs`` one per result (or a single spec for a single result); an entry is a
+    per-dimension tuple of mesh axis names as in :func:`with_sharding_constraint`, or None to leave
+    that value to the propagation pass. ``fun`` is written over the global shapes and must be
+    shard-wise (every operator in it carries a sharding rule, so it is): the compiled task then
+    executes it on local tiles only, with the collectives the layouts imply. Outside a capture,
+    and under :func:`ignore_transforms`, the wrapper calls ``fun`` unchanged."""
+    def wrapped(*args):
+        if should_ignore_transforms():
+            return fun(*args)
+        if len(in_specs) != len(args):
+            raise ValueError(f"shard_map: {len(in_specs)} in_specs for {len(args)} arguments")
+        with autoshard(False):                 # the specs name mesh axes, not logical axes
+            pinned = [a if sp is None else with_sharding_constraint(a, sp) for a, sp in zip(args, in_specs)]
+            out = fun(*pinned)
+            if out_specs is None:
+                return out
+            if isinstance(out, (tuple, list)):
+                specs = list(out_specs)
+                if len(specs) != len(out):
+                    raise ValueError(f"shard_map: {len(specs)} out_specs for {len(out)} results")
+                return type(out)(o if sp is None else with_sharding_constraint(o, sp) for o, sp in zip(out, specs))
+            return with_sharding_constraint(out, out_specs)
+    wrapped.__name__ = getattr(fun, "__name__", "shard_map")
+    return wrapped
 
 
 @contextlib.contextmanager

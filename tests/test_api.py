@@ -240,3 +240,45 @@ def test_checkpoint_keeps_shard_layout_and_resumes_on_another_mesh(tmp_path):
         "float32", [3], [[]], [2], 0), topo2), "step": 0, "lr": torch.tensor(0.0)}
     again = checkpoint.load(d, like=like)
     assert torch.equal(again["w"].tile(1), full[4:]) and torch.equal(again["b"].tile(0), torch.ones(3))
+
+
+def test_custom_partitioning_and_shard_map_run_on_the_task_submesh():
+    """A user-defined operator with a sharding rule registered through ``custom_partitioning`` and a
+    ``shard_map`` region: both execute on local tiles of the task's own sub-mesh (second stage, two
+    devices) and equal the eager result."""
+    lib = torch.library.Library("mmtest_api", "DEF")
+    lib.define("scale_rows(Tensor x, Tensor s) -> Tensor")
+    torch.library.impl(lib, "scale_rows", "CompositeExplicitAutograd")(lambda x, s: x * s.unsqueeze(-1))
+    torch.library.register_fake("mmtest_api::scale_rows")(lambda x, s: torch.empty_like(x))
+    seen = []
+
+    @mm.custom_partitioning(torch.ops.mmtest_api.scale_rows)
+    def rule(node, ins, outs):
+        seen.append((tuple(ins[0]), tuple(ins[1])))
+        # slots: 0 x[r, c], 1 s[r] | 2 y[r, c]
+        return {"classes": [mm.index_class([(0, 0), (1, 0), (2, 0)]), mm.index_class([(0, 1), (2, 1)])]}
+
+    def f(x, s):
+        with mm.named_scope("first"):
+            h = torch.tanh(x)
+        with mm.named_scope("second"):
+            g = mm.shard_map(lambda a, b: torch.ops.mmtest_api.scale_rows(a, b) + 1.0,
+                             in_specs=[("model", None), ("model",)], out_specs=("model", None))
+            return g(h, s)
+
+    mesh = mm.MultiMesh((2, 2), ("stage", "model"))
+    x, s = torch.randn(8, 6), torch.randn(8)
+    with mesh:
+        mesh.register_task("first", task=mm.Task(mesh_slice={"stage": 0}))
+        mesh.register_task("second", task=mm.Task(mesh_slice={"stage": 1}))
+        exe = mm.compile_function(f, (x, s), mesh=mesh, backend="cpu")
+    out = exe(x, s)
+    torch.testing.assert_close(out.full_tensor(), torch.tanh(x) * s.unsqueeze(-1) + 1.0)
+    assert seen, "the sharding rule of the user-defined operator was not consulted"
+    second = [t for t in exe.plan["templates"] if "second" in t["name"]][0]
+    assert second["device_start"] == 2 and second["num_devices"] == 2
+    sh = out.sharding
+    assert sh["dim_axes"][0] and sh["shard_size"][0] == 4      # rows split over the two devices of stage 1
+    with mm.ignore_transforms():
+        torch.testing.assert_close(f(x, s), torch.tanh(x) * s.unsqueeze(-1) + 1.0)
+    exe.shutdown()
