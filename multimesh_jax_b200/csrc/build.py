@@ -91,7 +91,10 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(cus))) as ex:
         objs = list(ex.map(compile_one, cus))
-    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-lcudart"])
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = target.with_name(target.name + ".tmp")
+    _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lcudart"])
+    os.replace(tmp, target)
     return target
 
 

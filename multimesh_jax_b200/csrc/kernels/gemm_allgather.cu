@@ -86,7 +86,7 @@ struct AllGatherHook {
   }
 
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
-                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+                                           int* err, uint8_t* stage, State& st, const TmemRelease& rel) const {
     (void)err; (void)stage; (void)st;
     const int row = m_blk * GEMM_BM + q * 32 + lane;
 #pragma unroll 1
@@ -100,7 +100,7 @@ struct AllGatherHook {
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(tempty);
+    if (lane == 0) rel.arrive();
   }
 };
 

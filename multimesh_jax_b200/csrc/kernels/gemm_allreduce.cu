@@ -18,7 +18,10 @@
 // Ranks walk the tiles in the same order. Receive buffers are double-buffered by call
 // parity; flags carry the call's epoch and are never reset. No TMA load touches peer
 // memory and no multicast is used.
+#include <cstdlib>
+
 #include "gemm_core.cuh"
+#include "gemm_pair_core.cuh"
 #include "host_common.h"
 
 namespace mm {
@@ -108,7 +111,7 @@ struct AllReduceHook {
   }
 
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
-                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+                                           int* err, uint8_t* stage, State& st, const TmemRelease& rel) const {
     uint8_t* ws = stage + q * AR_WARP_STAGE;          // this warp's 32 rows x 256 B
     const int row0 = m_blk * GEMM_BM + q * 32;
     const int tile = m_blk * num_n + n_blk;
@@ -138,7 +141,7 @@ struct AllReduceHook {
         // accumulator fully drained: hand it back to the MMA warp before touching NVLink
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty);
+        if (lane == 0) rel.arrive();
       } else {
         __syncwarp();
       }
@@ -239,6 +242,21 @@ int mm_gemm_allreduce_bf16(const void* A, int a_mn, int64_t lda, const void* B, 
   hook.npeers = npeers;
   hook.epoch = epoch;
   hook.num_n = (N + GEMM_BN - 1) / GEMM_BN;
+  // CTA pairs (256x256 tile per two SMs) from 256 rows on; MM_AR_PAIR=0 keeps the single-CTA loop
+  static const bool pair_ok = [] {
+    const char* e = getenv("MM_AR_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  if (pair_ok && M >= 2 * GEMM_BM) {
+    DeviceState* ds = device_state();
+    if (!ds) return -1;
+    rc = make_pair_tmaps(&tmA, &tmB, A, a_mn, lda, B, b_mn, ldb, M, N, K);
+    if (rc) return rc;
+    if (!a_mn && !b_mn) return launch_pair_kernel<false, false>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+    if (!a_mn && b_mn) return launch_pair_kernel<false, true>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+    if (a_mn && b_mn) return launch_pair_kernel<true, true>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+    return launch_pair_kernel<true, false>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+  }
   if (!a_mn && !b_mn) return launch_ar<false, false>(tmA, tmB, hook, M, N, K, stream);
   if (!a_mn && b_mn) return launch_ar<false, true>(tmA, tmB, hook, M, N, K, stream);
   if (a_mn && b_mn) return launch_ar<true, true>(tmA, tmB, hook, M, N, K, stream);

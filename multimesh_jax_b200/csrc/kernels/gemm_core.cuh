@@ -113,6 +113,19 @@ __device__ __forceinline__ void gemm_store_chunk(void* C, int64_t ldc, int row, 
   }
 }
 
+// How an epilogue warp hands a drained accumulator back to the MMA lane: an arrival on the
+// accumulator-empty barrier of its own CTA, or - in a CTA pair - of the pair's leader.
+struct TmemRelease {
+  uint32_t addr;   // shared::cta address (own CTA) or shared::cluster address (leader CTA)
+  bool remote;
+  __device__ __forceinline__ void arrive() const {
+    if (remote)
+      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+    else
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+  }
+};
+
 // Default hook: plain GEMM writing to local memory.
 template <int OUT>
 struct PlainHook {
@@ -133,7 +146,7 @@ struct PlainHook {
   struct State {};
   __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
-                                           int* err, uint8_t* stage, State& st, uint64_t* tempty) const {
+                                           int* err, uint8_t* stage, State& st, const TmemRelease& rel) const {
     (void)err; (void)stage; (void)st;
     const int row = m_blk * GEMM_BM + q * 32 + lane;
 #pragma unroll 1
@@ -147,7 +160,7 @@ struct PlainHook {
     }
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(tempty);
+    if (lane == 0) rel.arrive();
   }
 };
 
@@ -287,7 +300,8 @@ __global__ void __launch_bounds__(GEMM_THREADS + 32 * Hook::kAuxWarps, 1)
       tc_fence_after();
       const uint32_t t_base = tmem_base + acc * GEMM_BN + (static_cast<uint32_t>(q * 32) << 16);
       // the hook arrives on tempty[acc] itself as soon as it has drained the accumulator
-      hook.epilogue(t_base, m_blk, n_blk, q, lane, M, N, err, epi_stage, hstate, &tempty[acc]);
+      const TmemRelease rel{smem_u32(&tempty[acc]), false};
+      hook.epilogue(t_base, m_blk, n_blk, q, lane, M, N, err, epi_stage, hstate, rel);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
