@@ -315,7 +315,16 @@ bool Coloring(CompileState& s) {
   auto votes = [&](int id) { return !props.derived_constant[id] && !props.derived_parameter[id]; };
   const std::string prio = s.config.color_propagation_priority;
 
-  // (1) inside the loop body: forward, favouring the most recent coloured operand; then backward
+  // (1) inside the loop body: forward, favouring the most recent coloured operand; then backward.
+  //     A node of the backward pass takes its colour only from operands whose colour itself comes
+  //     from the backward pass (a gradient), never from a saved forward value: otherwise an
+  //     activation derivative written outside every scope would land in the forward task of its
+  //     layer and split the backward task around it.
+  std::vector<char> from_bwd(g.nodes.size(), 0);
+  for (int id : g.order) {
+    const Node& n = g.node(id);
+    if (!n.dead && n.backprop && !n.color.empty()) from_bwd[id] = 1;
+  }
   for (int id : g.order) {
     Node& n = g.node(id);
     if (n.dead || n.loop < 0 || !n.color.empty() || !votes(id)) continue;
@@ -323,9 +332,13 @@ bool Coloring(CompileState& s) {
     for (int v : n.inputs) {
       const int p = g.value(v).producer;
       if (p < 0 || g.node(p).loop < 0 || g.node(p).color.empty()) continue;
+      if (n.backprop && !from_bwd[p]) continue;
       if (best < 0 || props.topo_index[p] > props.topo_index[best]) best = p;
     }
-    if (best >= 0) n.color = g.node(best).color;
+    if (best >= 0) {
+      n.color = g.node(best).color;
+      from_bwd[id] = from_bwd[best];
+    }
   }
   for (auto it = g.order.rbegin(); it != g.order.rend(); ++it) {
     Node& n = g.node(*it);
@@ -336,7 +349,10 @@ bool Coloring(CompileState& s) {
         if (g.node(u).loop < 0 || g.node(u).color.empty()) continue;
         if (best < 0 || props.topo_index[u] < props.topo_index[best]) best = u;
       }
-    if (best >= 0) n.color = g.node(best).color;
+    if (best >= 0) {
+      n.color = g.node(best).color;
+      from_bwd[*it] = from_bwd[best];
+    }
   }
 
   // (2) neighbour voting, three widening filters, to a fixed point

@@ -316,7 +316,17 @@ bool InstructionDelayRecolor(CompileState& s) {
     n.task = to.id;
     changed = true;
   }
-  if (changed) s.Note("delay-recolor moved instructions to later tasks");
+  if (changed) {
+    // keep the groups' member lists in step with the nodes' new tasks (in graph order)
+    for (auto& grp : s.groups) grp.nodes.clear();
+    for (int id : g.order) {
+      const Node& n = g.node(id);
+      if (n.dead || n.task < 0) continue;
+      auto it = group_pos.find(n.task);
+      if (it != group_pos.end()) s.groups[it->second].nodes.push_back(id);
+    }
+    s.Note("delay-recolor moved instructions to later tasks");
+  }
   return changed;
 }
 
