@@ -132,6 +132,59 @@ def build_host(force: bool = False) -> Path:
     return target
 
 
+SANITIZER_FLAGS = {
+    "address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"],
+    "thread": ["-fsanitize=thread"],
+    "none": [],
+}
+
+
+class SanitizerUnavailable(RuntimeError):
+    """No installed C++ compiler can link with the requested sanitizer runtime."""
+
+
+def _compiler_with(flags, scratch: Path) -> str:
+    """First of $CXX, g++, /usr/bin/g++, clang++ that links a trivial program with ``flags``."""
+    probe = scratch / "probe.cc"
+    probe.write_text("int main() { return 0; }\n")
+    seen = []
+    for cxx in [os.environ.get("CXX"), "g++", "/usr/bin/g++", "clang++"]:
+        if not cxx or cxx in seen or not shutil.which(cxx):
+            continue
+        seen.append(cxx)
+        proc = subprocess.run([cxx, "-pthread", *flags, str(probe), "-o", str(scratch / "probe")],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        if proc.returncode == 0:
+            return cxx
+    raise SanitizerUnavailable(f"no compiler among {seen} links with {' '.join(flags)}")
+
+
+def build_selftest(sanitizer: str = "address", force: bool = False) -> Path:
+    """Builds ``selftest/host_selftest.cc`` with the compiler and runtime sources into a
+    stand-alone program instrumented by ``sanitizer`` (``address`` = ASan + UBSan, ``thread`` =
+    TSan, ``none``); one object per source, compiled in parallel. Returns the program's path."""
+    flags = SANITIZER_FLAGS[sanitizer]
+    out_dir = BUILD_DIR / f"selftest_{sanitizer}"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    srcs = [HERE / "selftest" / "host_selftest.cc"] + sorted((HERE / "mmgraph").glob("*.cc")) + [HERE / "mmrt" / "runtime.cc"]
+    hdrs = sorted((HERE / "mmgraph").glob("*.h")) + sorted((HERE / "mmrt").glob("*.h"))
+    target = out_dir / "host_selftest"
+    if not force and not _newer(srcs + hdrs, target):
+        return target
+    cxx = _compiler_with(flags, out_dir)
+
+    def compile_one(src: Path) -> Path:
+        obj = out_dir / (src.stem + ".o")
+        if force or _newer([src] + hdrs, obj):
+            _run([cxx, "-std=c++17", "-O0", "-g1", "-pthread", *flags, "-c", str(src), "-o", str(obj)])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    _run([cxx, "-pthread", *flags, "-o", str(target), *map(str, objs)])
+    return target
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force=force)
     build_host(force=force)

@@ -265,17 +265,20 @@ Plan BuildPlan(CompileState& s) {
     auto key = std::make_pair(src_store, want.Key());
     auto hit = reshard_cache.find(key);
     if (hit != reshard_cache.end()) return hit->second;
-    const Store& src = plan.stores[src_store];
-    const int dst = new_store(Store::TEMP, temp_counter++, src.value, src.iteration, want);
+    // by value: new_store() grows the store table and would leave a reference dangling
+    const int src_value = plan.stores[src_store].value;
+    const int src_iteration = plan.stores[src_store].iteration;
+    const DeviceRange src_devices = plan.stores[src_store].shape.devices;
+    const int dst = new_store(Store::TEMP, temp_counter++, src_value, src_iteration, want);
     PlanOp op;
     op.kind = PlanOp::RESHARD;
     op.src_store = src_store;
     op.dst_store = dst;
     op.name = "reshard";
-    op.iteration = src.iteration;
+    op.iteration = src_iteration;
     // every device of either layout takes part
-    const int lo = std::min(src.shape.devices.start, want.devices.start);
-    const int hi = std::max(src.shape.devices.stop(), want.devices.stop());
+    const int lo = std::min(src_devices.start, want.devices.start);
+    const int hi = std::max(src_devices.stop(), want.devices.stop());
     op.devices = DeviceRange{lo, hi - lo};
     plan.ops.push_back(op);
     reshard_cache[key] = dst;

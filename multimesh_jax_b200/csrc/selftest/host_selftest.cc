@@ -1,0 +1,251 @@
+// Stand-alone self test of the C++ compiler (mmgraph) and task runtime (mmrt), meant to be built
+// with -fsanitize=address,undefined or -fsanitize=thread (no Python in the process):
+//
+//   1. builds a microbatched P-stage pipeline graph with forward, backward and weight-gradient
+//      work, compiles it with every pipeline schedule and checks plan invariants;
+//   2. executes each plan on a ThreadedContext with one worker thread per virtual device. Task
+//      and reshard bodies read and write plain host buffers (one per physical buffer and device,
+//      shared by every store with the same scheduling name) WITHOUT locks, so a missing
+//      dependency edge is a data race the thread sanitizer reports and a wrong checksum here;
+//   3. replays the submission log through the hazard checker;
+//   4. injects host-side faults (a task body that throws, a dropped task) and checks that the
+//      error surfaces as a status and that the context stays usable.
+//
+// Exit code 0 = all checks passed. The reference gets the same assurance from its ASAN build type
+// (CMakeLists.txt:12-17) over the mock-runtime tests.
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../mmgraph/graph.h"
+#include "../mmgraph/passes.h"
+#include "../mmrt/runtime.h"
+
+using namespace mmg;
+
+static int g_failures = 0;
+#define CHECK(cond, msg)                                                \
+  do {                                                                  \
+    if (!(cond)) {                                                      \
+      std::fprintf(stderr, "CHECK failed (%s:%d): %s\n", __FILE__, __LINE__, msg); \
+      ++g_failures;                                                     \
+    }                                                                   \
+  } while (0)
+
+static std::string TaskJson(const std::string& name, int device, bool split) {
+  std::string s = "{\"name\":\"" + name + "\",\"devices\":[" + std::to_string(device) + "],\"dims\":[1],"
+                  "\"device_axes\":[\"x\"],\"logical_axes\":[],\"split_backprop\":[";
+  if (split) s += "\"_act\",\"_wgt\"";
+  s += "],\"loop_dependent_devices\":[]}";
+  return s;
+}
+
+static int AddOp(Graph& g, const std::string& op, const std::vector<int>& in, std::vector<int64_t> shape, int loop,
+                 const std::string& task, bool backprop) {
+  const int id = g.AddNode(op, in, {shape}, {DType::F32}, {{"args", "[]"}});
+  Node& n = g.node(id);
+  n.loop = loop;
+  n.explicit_task = task;
+  n.backprop = backprop;
+  return n.outputs[0];
+}
+
+// x -> P stages of (mm, tanh) -> loss; backward chain with input and weight gradients per stage.
+static void BuildPipeline(Graph& g, int stages, int microbatches, const std::string& schedule, bool split) {
+  const int64_t B = 4 * microbatches, D = 8;
+  LoopConfig loop;
+  loop.id = 0;
+  loop.num_microbatches = microbatches;
+  loop.slice_dim = 0;
+  loop.size = 4;
+  loop.schedule = schedule;
+  g.loops.push_back(loop);
+  const int x = g.AddInput("x", {B, D}, DType::F32);
+  std::vector<int> w(stages);
+  for (int s = 0; s < stages; ++s) w[s] = g.AddInput("w" + std::to_string(s), {D, D}, DType::F32);
+  const int slice_node = g.AddNode("mm.microbatch_slice.default", {x}, {{4, D}}, {DType::F32}, {{"args", "[0, 4, 0]"}});
+  g.node(slice_node).loop = 0;
+  int h = g.node(slice_node).outputs[0];
+  std::vector<int> acts;
+  for (int s = 0; s < stages; ++s) {
+    const std::string t = TaskJson("stage" + std::to_string(s), s, false);
+    acts.push_back(h);
+    h = AddOp(g, "aten.mm.default", {h, w[s]}, {4, D}, 0, t, false);
+    h = AddOp(g, "aten.tanh.default", {h}, {4, D}, 0, t, false);
+  }
+  int grad = AddOp(g, "aten.ones_like.default", {h}, {4, D}, 0, TaskJson("stage" + std::to_string(stages - 1) + "_bwd",
+                                                                          stages - 1, split), true);
+  std::vector<int> outs;
+  for (int s = stages - 1; s >= 0; --s) {
+    const std::string t = TaskJson("stage" + std::to_string(s) + "_bwd", s, split);
+    const int dw = AddOp(g, "aten.mm.default", {acts[s], grad}, {D, D}, 0, t, true);   // weight gradient
+    if (s > 0) grad = AddOp(g, "aten.mm.default", {grad, w[s]}, {4, D}, 0, t, true);   // input gradient
+    const int out_node = g.AddNode("mm.microbatch_out.default", {dw}, {{D, D}}, {DType::F32}, {{"args", "[0, \"\"]"}});
+    g.node(out_node).loop = 0;
+    outs.push_back(g.node(out_node).outputs[0]);
+  }
+  g.SetOutputs(outs);
+}
+
+struct RunResult {
+  double checksum = 0;
+  std::string hazards;
+  mmrt::Status status = mmrt::Status::kOk;
+};
+
+// Executes the plan's operation list with synthetic bodies over unlocked host buffers.
+static RunResult Execute(const Plan& plan, int num_devices, bool inject_throw) {
+  std::vector<int> devices(num_devices);
+  for (int d = 0; d < num_devices; ++d) devices[d] = d;
+  mmrt::ThreadedContext ctx(devices, /*inline_execution=*/false, /*record_submissions=*/true);
+  std::map<std::string, int> buffer_of_name;
+  auto buffer_id = [&](const Store& st) {
+    const std::string key = std::to_string(static_cast<int>(st.kind)) + ":" + st.name;
+    auto it = buffer_of_name.find(key);
+    if (it == buffer_of_name.end()) it = buffer_of_name.emplace(key, static_cast<int>(buffer_of_name.size())).first;
+    return it->second;
+  };
+  // one cell of payload per (buffer, device); sized up front so bodies never rehash the map
+  std::map<std::pair<int, int>, double> cells;
+  for (const Store& st : plan.stores)
+    for (int d = st.shape.devices.start; d < st.shape.devices.stop(); ++d) cells[{buffer_id(st), d}] = 0.0;
+  for (size_t i = 0; i < plan.param_stores.size(); ++i) {
+    if (plan.param_stores[i] < 0) continue;
+    const Store& st = plan.stores[plan.param_stores[i]];
+    for (int d = st.shape.devices.start; d < st.shape.devices.stop(); ++d) cells[{buffer_id(st), d}] = 1.0 + 0.25 * i;
+  }
+  auto tiles = [&](int store, int device_filter) {
+    std::vector<mmrt::TileRef> t;
+    const Store& st = plan.stores[store];
+    for (int d = st.shape.devices.start; d < st.shape.devices.stop(); ++d)
+      if (device_filter < 0 || d == device_filter) t.push_back({buffer_id(st), d});
+    return t;
+  };
+  if (inject_throw) {
+    mmrt::FaultSpec f;
+    f.kind = mmrt::FaultSpec::kThrow;
+    f.name_substring = "_bwd";
+    f.remaining = 1;
+    ctx.InjectFault(f);
+  }
+  ctx.OpenWindow();
+  int k = 0;
+  for (const PlanOp& op : plan.ops) {
+    ++k;
+    if (op.kind == PlanOp::TASK) {
+      for (int d = op.devices.start; d < op.devices.stop(); ++d) {
+        std::vector<mmrt::TileRef> reads, writes;
+        for (int s : op.inputs) for (auto& t : tiles(s, d)) reads.push_back(t);
+        for (size_t o = 0; o < op.outputs.size(); ++o) {
+          for (auto& t : tiles(op.outputs[o], d)) {
+            writes.push_back(t);
+            if (!op.accumulate.empty() && op.accumulate[o] == 2) reads.push_back(t);
+          }
+        }
+        const std::vector<int> acc = op.accumulate;
+        mmrt::ExecuteOptions eo;
+        eo.name = op.name;
+        eo.priority = op.priority;
+        eo.strict_ordering = op.strict_ordering;
+        ctx.CreateExecuteTask(d, reads, writes, [&cells, reads, writes, acc, k] {
+          double v = 0.001 * k;
+          for (auto& r : reads) v += 0.5 * cells.at({r.buffer, r.device});
+          size_t o = 0;
+          for (auto& wt : writes) {
+            double& c = cells.at({wt.buffer, wt.device});
+            c = (!acc.empty() && o < acc.size() && acc[o] == 2) ? c + std::tanh(v) : std::tanh(v);
+            ++o;
+          }
+        }, eo);
+      }
+    } else if (op.kind == PlanOp::RESHARD) {
+      const Store& dst = plan.stores[op.dst_store];
+      for (int d = dst.shape.devices.start; d < dst.shape.devices.stop(); ++d) {
+        std::vector<mmrt::TileRef> reads = tiles(op.src_store, -1), writes = tiles(op.dst_store, d);
+        mmrt::ExecuteOptions eo;
+        eo.name = "reshard";
+        eo.kind = 1;
+        ctx.Reshard(d, reads, writes, [&cells, reads, writes] {
+          double v = 0;
+          for (auto& r : reads) v += cells.at({r.buffer, r.device});
+          for (auto& wt : writes) cells.at({wt.buffer, wt.device}) = v / static_cast<double>(reads.size());
+        }, eo);
+      }
+    }
+  }
+  ctx.CloseWindow();
+  RunResult res;
+  std::string message;
+  res.status = ctx.WaitAll(&message);
+  res.hazards = mmrt::CheckHazards(ctx.Submissions());
+  for (int r : plan.root_stores)
+    for (auto& t : tiles(r, -1)) res.checksum += cells.at({t.buffer, t.device});
+  if (inject_throw) {
+    // the context must stay usable after a failed step
+    ctx.ResetError();
+    mmrt::ExecuteOptions eo;
+    eo.name = "after_failure";
+    double probe = 0;
+    ctx.CreateExecuteTask(0, {}, {}, [&probe] { probe = 42.0; }, eo);
+    std::string m2;
+    CHECK(ctx.WaitAll(&m2) == mmrt::Status::kOk && probe == 42.0, "context unusable after an injected fault");
+  }
+  ctx.Shutdown();
+  return res;
+}
+
+int main(int argc, char** argv) {
+  const int repeats = argc > 1 ? std::atoi(argv[1]) : 3;
+  const char* schedules[] = {"gpipe", "1f1b", "wavefront", "zero-bubble-h2"};
+  for (const char* schedule : schedules) {
+    const bool split = std::string(schedule) == "zero-bubble-h2";
+    for (int stages : {2, 4}) {
+      const int microbatches = 2 * stages;
+      Graph g;
+      BuildPipeline(g, stages, microbatches, schedule, split);
+      Partition part(DeviceRange::Create(0, stages));
+      PartitionConfig cfg;
+      std::vector<std::string> log;
+      Plan plan = MpmdPartition(g, part, cfg, &log);
+      int tasks = 0, reshards = 0;
+      for (const PlanOp& op : plan.ops) {
+        tasks += op.kind == PlanOp::TASK;
+        reshards += op.kind == PlanOp::RESHARD;
+        if (op.kind == PlanOp::TASK) {
+          CHECK(op.inputs.size() == plan.templates[op.task_template].inputs.size(), "task inputs do not match template");
+          CHECK(op.outputs.size() == plan.templates[op.task_template].outputs.size(), "task outputs do not match template");
+        }
+      }
+      CHECK(tasks >= 2 * stages * microbatches, "fewer tasks than forward + backward per stage and microbatch");
+      CHECK(reshards > 0, "a pipeline without stage-boundary reshards");
+      // determinism: compiling the same graph again gives the same plan
+      Graph g2;
+      BuildPipeline(g2, stages, microbatches, schedule, split);
+      Partition part2(DeviceRange::Create(0, stages));
+      CHECK(MpmdPartition(g2, part2, cfg).Hash() == plan.Hash(), "plan hash is not deterministic");
+
+      double first = 0;
+      for (int r = 0; r < repeats; ++r) {
+        RunResult res = Execute(plan, stages, false);
+        CHECK(res.status == mmrt::Status::kOk, "execution reported an error");
+        CHECK(res.hazards.empty(), res.hazards.c_str());
+        CHECK(std::isfinite(res.checksum) && res.checksum != 0.0, "degenerate checksum");
+        if (r == 0) first = res.checksum;
+        CHECK(std::fabs(res.checksum - first) < 1e-12, "results differ between runs: tasks raced");
+      }
+      RunResult failed = Execute(plan, stages, true);
+      CHECK(failed.status != mmrt::Status::kOk, "an injected fault did not surface as a status");
+      std::printf("%-15s stages=%d microbatches=%d: %d tasks, %d reshards, checksum %.9f\n", schedule, stages,
+                  microbatches, tasks, reshards, first);
+    }
+  }
+  if (g_failures) {
+    std::fprintf(stderr, "%d check(s) failed\n", g_failures);
+    return 1;
+  }
+  std::printf("host selftest ok\n");
+  return 0;
+}
