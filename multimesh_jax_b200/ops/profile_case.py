@@ -1,6 +1,6 @@
 """One kernel, one small case, three launches - the program to put under a profiler.
 
-    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad (each also as <case>_pair)|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
+    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad (each also as <case>_pair)|gemm_allreduce_loopback|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
 
 Inputs are larger than the 126 MB L2 where the kernel is memory bound and a few hundred MB at
 most, so a full-metric capture of one launch finishes in seconds. Each case prints its
@@ -55,6 +55,36 @@ def main(argv=None) -> int:
             fn = lambda: K.linear_wgrad(a, b, out=acc, accumulate=True)
         ms = _time(fn)
         out.update(shape=[M, N, Kd], ms=ms, tflops=2.0 * M * N * Kd / ms / 1e9)
+    elif case == "gemm_allreduce_loopback":
+        # The fused GEMM + all-reduce kernel on ONE GPU: its single peer slot is this GPU's own
+        # receive buffer and flag array, so every tile is pushed to local memory, flagged, waited
+        # for and added back (out = 2 A B^T). Same kernel and instruction stream as the 2-GPU call
+        # with NVLink replaced by local HBM; no launch waits on another launch.
+        from ctypes import c_int64
+        from ..parallel import tp  # noqa: F401 - registers the entry point's signature
+        from . import _lib
+        M, N, Kd = 8192, 4096, 2048
+        a = torch.randn(M, Kd, device=dev).bfloat16()
+        b = torch.randn(N, Kd, device=dev).bfloat16()
+        tiles = 4 * ((M + 127) // 128) * ((N + 255) // 256)
+        recv = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+        flags = torch.zeros(tiles, device=dev, dtype=torch.int32)
+        res = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        epoch = [0]
+        lib = _lib.load()
+
+        def fn():
+            epoch[0] += 1
+            one = lambda t: (c_int64 * 1)(t.data_ptr())
+            rc = lib.mm_gemm_allreduce_bf16(a.data_ptr(), 0, a.stride(0), b.data_ptr(), 0, b.stride(0), res.data_ptr(),
+                                            res.stride(0), M, N, Kd, one(recv), one(recv), one(flags), one(flags), 1,
+                                            epoch[0], torch.cuda.current_stream().cuda_stream)
+            _lib.check(rc, "mm_gemm_allreduce_bf16")
+        ms = _time(fn)
+        ref = 2.0 * (a.float() @ b.float().t())
+        err = float((res.float() - ref).abs().max() / ref.abs().max())
+        out.update(shape=[M, N, Kd], ms=ms, tflops=2.0 * M * N * Kd / ms / 1e9, max_rel_err=err,
+                   bytes_pushed=M * N * 2)
     elif case in ("flash_fwd", "flash_bwd"):
         B, S, H, D = 2, 2048, 16, 128
         qkv = (torch.randn(B, S, 3 * H, D, device=dev) * 0.5).bfloat16()
