@@ -227,3 +227,50 @@ def test_sixteen_virtual_devices_pipeline_on_the_mock_runtime():
         assert 0 < mock.max_device_high_water < 64 << 20
         hashes.append((mock.operation_hash, plan["hash"]))
     assert hashes[0] == hashes[1]
+
+
+@pytest.mark.parametrize("dp,pp,tp,layers", [(2, 2, 8, 4), (1, 8, 2, 8), (4, 4, 8, 4)],
+                         ids=["DP2_PP2_TP8_32dev", "Pipeline8x2_16dev", "DP4_PP4_TP8_128dev"])
+def test_multi_node_layouts_on_the_mock_runtime(dp, pp, tp, layers):
+    """One process plans and 'runs' a multi-node job on virtual devices (the method of
+    src/pjrt_client/mm_pjrt_executable_test.cc: DP2_PP2_TP8_4nodes, Pipeline2x8Stages, Gpt3_16nodes):
+    the mock checks the protocol (local tiles exist, nothing is read while offloaded, writes stay on
+    the task's device), the hazard checker replays the submissions, and all devices take part."""
+    from multimesh_jax_b200.models import llama
+    from multimesh_jax_b200.runtime.collectives import Topology
+    n = dp * pp * tp
+    cfg = llama.LlamaConfig.tiny(n_layers=layers, n_heads=8, n_kv_heads=8, d_model=64, d_ff=128, vocab=256)
+    cfg.dtype = torch.float32
+    B, S = 8 * dp, 8
+    MB = 2 * dp
+    step = llama.make_train_step(cfg, llama.AdamWConfig(), seq_len=S, global_batch=B, microbatch_size=MB)
+    with torch.device("meta"):
+        params = llama.init_params(cfg, device="meta")
+        state = llama.init_opt_state(params)
+    tok = torch.empty(B, S, dtype=torch.int64, device="meta")
+    cos = torch.empty(S, cfg.head_dim // 2, device="meta")
+    mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+    mock = C.MockContext(n)
+    with mesh:
+        exe = mm.compile_function(step, (params, state, tok, tok, cos, cos), mesh=mesh, context=mock,
+                                  topology=Topology("cpu", n))
+    plan = exe.plan
+    from torch.utils import _pytree as pytree
+    real = [torch.zeros(plan["stores"][s]["shape"]["sizes"], dtype=getattr(torch, plan["stores"][s]["shape"]["dtype"]))
+            if s >= 0 else torch.zeros(1) for s in plan["param_stores"]]
+    exe(*pytree.tree_unflatten(real, exe.cap.in_spec))
+    assert mock.violation == "" and mock.hazard_report() == ""
+    assert {r["device"] for r in mock.event_log()} == set(range(n))
+    # every stage runs forward and backward of every microbatch on each of its devices
+    per_device = mock.num_tasks / n
+    assert per_device >= 2 * (B // MB)
+    # tensor- and data-parallel ranks of a stage hold equal shares: the busiest device stays within
+    # a small factor of the mean
+    assert mock.max_device_high_water < 8 << 20
+    stage_of = lambda d: d // (dp * tp)
+    tasks_per_stage = {}
+    for r in mock.event_log():
+        if r["kind"] == 0:
+            tasks_per_stage[stage_of(r["device"])] = tasks_per_stage.get(stage_of(r["device"]), 0) + 1
+    assert set(tasks_per_stage) == set(range(pp))
