@@ -8,14 +8,13 @@ Counterpart of the reference's ``multimesh/jax/lib.py``: ``ignore_transforms``
 from __future__ import annotations
 
 import contextlib
-import json
-from typing import Any, Callable, Dict, Iterable, Optional, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, Optional, Sequence, Tuple, Union
 
 import torch
 
 from . import no_op as _no_op
 from . import state
-from .task import Context, MultiMesh, Task, register_task
+from .task import Context, MultiMesh, Task
 
 _auto_sharding = _no_op.no_op(_no_op.AUTO_SHARDING)
 

@@ -27,7 +27,7 @@ from .. import lib as mm_lib
 from ..ops import kernels as K
 from ..ops import mm_ops  # noqa: F401  (registers the operators)
 from ..ops import moe as _moe  # noqa: F401  (registers the mixture-of-experts operators)
-from ..task import MultiMesh, Task, microbatch, named_scope, register_task, value_and_grad
+from ..task import MultiMesh, Task, microbatch, named_scope, value_and_grad
 
 ops = torch.ops.mm_ops
 

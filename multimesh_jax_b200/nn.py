@@ -14,7 +14,7 @@ Counterpart of the Flax helpers of the reference (``multimesh/jax/flax/task.py:2
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Optional, Sequence, Tuple, Type
+from typing import Any, Dict, Optional, Sequence, Tuple, Type
 
 import torch
 

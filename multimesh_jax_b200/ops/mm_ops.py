@@ -17,8 +17,7 @@ weight-gradient GEMM adds into the fp32 accumulator in its epilogue.
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, List, Optional, Tuple
+from typing import Dict
 
 import torch
 

@@ -23,7 +23,7 @@ expert projections run on the tcgen05 GEMM kernels; dispatch and combine go thro
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import Dict, Tuple
 
 import torch
 

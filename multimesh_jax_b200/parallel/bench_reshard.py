@@ -21,7 +21,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import sys
 
 import torch
 import torch.distributed as dist
@@ -61,7 +60,6 @@ def main():
     dist.init_process_group("nccl")
     from .. import _mm_C
     from ..runtime.collectives import Topology
-    from ..compiler.capture import DTYPE_FROM_NAME
     from . import symm
     from .reshard import run_reshard_dist
 

@@ -10,9 +10,8 @@ weighting them with its gates. Three flag barriers per call order the phases bet
 """
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_int, c_int64, c_void_p
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 import torch
 

@@ -17,7 +17,7 @@ live in the symmetric arena, one pair per distinct size.
 from __future__ import annotations
 
 from ctypes import c_float, c_int, c_int64, c_void_p
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, Sequence, Tuple
 
 import torch
 

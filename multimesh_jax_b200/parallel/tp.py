@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_int, c_int64, c_void_p
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, Sequence, Tuple
 
 import torch
 

@@ -11,7 +11,7 @@ have run (reading one blocks, nothing else does).
 """
 from __future__ import annotations
 
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 from torch.utils import _pytree as pytree

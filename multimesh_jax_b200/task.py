@@ -12,15 +12,13 @@ Outside a capture (or under ``ignore_transforms()``) ``task`` and
 from __future__ import annotations
 
 import contextlib
-import json
 import re
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 from torch.utils import _pytree as pytree
 
-from . import no_op as _no_op
 from . import state
 
 # ----------------------------------------------------------------------------
