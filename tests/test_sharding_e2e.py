@@ -1,0 +1,139 @@
+"""End-to-end sharding behaviour on virtual CPU devices, after the case lists of the reference's
+mpmd_logical_to_gspmd_sharding_test.cc (TransposeOperandAutoShardParam, GradientAutoShardParam,
+GradientMultiTaskAutoShard), mpmd_sharding_propagation_test.cc (ShardReplicatedIntermediates) and
+mpmd_shard_map_loop_reduce_test.cc (SimpleShardedContraction, DataParallelTransformer)."""
+import torch
+
+import multimesh_jax_b200 as mm
+
+
+def _ops(exe):
+    g = exe.cap.graph
+    return {t["name"]: [g.node(n)["op"] for n in t["nodes"]] for t in exe.plan["templates"]}
+
+
+def _node_dicts(exe, op):
+    g = exe.cap.graph
+    return [(t["name"], g.node(n)) for t in exe.plan["templates"] for n in t["nodes"] if g.node(n)["op"] == op]
+
+
+def test_data_parallel_gradient_sums_are_reduced_once_per_step_outside_the_loop():
+    mm.init(cpus=4)
+
+    def loss_fn(params, batch):
+        x, y = batch
+        with mm.named_scope("net"):
+            x = mm.with_sharding_constraint(x, ("batch", None))
+            h = torch.tanh(x @ params[0])
+            return (((h @ params[1]) - y) ** 2).sum()
+
+    def step(params, batch):
+        return mm.microbatch(mm.value_and_grad(loss_fn), size=4, argnum=1, schedule="gpipe")(params, batch)
+
+    torch.manual_seed(0)
+    params = [torch.randn(8, 16), torch.randn(16, 4)]
+    batch = (torch.randn(16, 8), torch.randn(16, 4))
+    mesh = mm.MultiMesh((1, 4), ("stage", "data"))
+    with mesh:
+        mesh.register_task("net", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("batch", "data")]))
+        exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="cpu")
+    loss, grads = exe(params, batch)
+    with mm.ignore_transforms():
+        ref_loss, ref_grads = step(params, batch)
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-4)
+    for g, r in zip(grads, ref_grads):
+        torch.testing.assert_close(g.full_tensor(), r, rtol=1e-4, atol=1e-4)
+    reduces = [name for name, ops in _ops(exe).items() if name.endswith("_reduce")]
+    assert len(reduces) == len(params)                       # one hoisted reduction per weight gradient
+    hoisted = [n for _, n in _node_dicts(exe, "mm.all_reduce") if n["attrs"].get("hoisted") == "1"]
+    assert len(hoisted) == len(params)
+    in_loop = [name for name, n in _node_dicts(exe, "mm.all_reduce") if name.endswith("_loop")]
+    assert len(in_loop) <= 1                                 # at most the scalar loss, never a weight gradient
+    # parameters and their gradients are replicated over the data axis; the batch is split 4 ways
+    ins = exe.input_shardings()
+    assert ins[0]["shard_size"] == [8, 16] and ins[2]["shard_size"] == [4, 8]
+    exe.shutdown()
+
+
+def test_gradient_of_a_sharded_parameter_has_the_parameters_layout():
+    mm.init(cpus=2)
+
+    def loss_fn(w1, w2, x):
+        with mm.named_scope("mlp"):
+            w1 = mm.with_sharding_constraint(w1, ("mlp", None))      # column parallel: [F, D] split on F
+            w2 = mm.with_sharding_constraint(w2, (None, "mlp"))      # row parallel:    [D, F] split on F
+            return (torch.tanh(x @ w1.t()) @ w2.t()).sum()
+
+    def step(w1, w2, x):
+        return mm.value_and_grad(loss_fn, argnums=(0, 1))(w1, w2, x)
+
+    torch.manual_seed(0)
+    w1, w2, x = torch.randn(16, 8), torch.randn(8, 16), torch.randn(6, 8)
+    mesh = mm.MultiMesh((1, 2), ("stage", "model"))
+    with mesh:
+        mesh.register_task("mlp", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("mlp", "model")]))
+        exe = mm.compile_function(step, (w1, w2, x), mesh=mesh, backend="cpu")
+    loss, (g1, g2) = exe(w1, w2, x)
+    with mm.ignore_transforms():
+        ref_loss, (r1, r2) = step(w1, w2, x)
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(g1.full_tensor(), r1, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(g2.full_tensor(), r2, rtol=1e-4, atol=1e-5)
+    ins = exe.input_shardings()
+    assert ins[0]["shard_size"] == [8, 8] and ins[1]["shard_size"] == [8, 8]
+    # the gradients come out in the layouts of their parameters: the optimizer update needs no collective
+    assert g1.sharding["dim_axes"] == ins[0]["dim_axes"] and g2.sharding["dim_axes"] == ins[1]["dim_axes"]
+    # column- then row-parallel: the activation between the two products stays sharded (no gather) and the
+    # forward pass needs exactly one all-reduce, after the second product
+    fwd = [ops for name, ops in _ops(exe).items() if not name.endswith("_bwd")][0]
+    assert fwd.count("mm.all_reduce") == 1 and "mm.spmd_reshard" not in fwd
+    exe.shutdown()
+
+
+def test_transposed_use_of_a_sharded_operand_shards_the_result():
+    mm.init(cpus=2)
+
+    def f(w, x):
+        with mm.named_scope("proj"):
+            w = mm.with_sharding_constraint(w, ("hidden", None))
+            return torch.relu(x @ w.t())
+
+    w, x = torch.randn(8, 4), torch.randn(5, 4)
+    mesh = mm.MultiMesh((1, 2), ("stage", "model"))
+    with mesh:
+        mesh.register_task("proj", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("hidden", "model")]))
+        exe = mm.compile_function(f, (w, x), mesh=mesh, backend="cpu")
+    out = exe(w, x)
+    torch.testing.assert_close(out.full_tensor(), torch.relu(x @ w.t()))
+    assert out.sharding["shard_size"] == [5, 4] and out.sharding["dim_axes"][1]      # columns follow w's rows
+    assert not _node_dicts(exe, "mm.all_reduce") and not _node_dicts(exe, "mm.spmd_reshard")
+    exe.shutdown()
+
+
+def test_parameter_shared_by_two_tasks_gets_the_sum_of_both_gradients():
+    mm.init(cpus=2)
+
+    def loss_fn(w, x):
+        with mm.named_scope("first"):
+            h = torch.tanh(x @ w)
+        with mm.named_scope("second"):
+            return (h @ w.t()).sum()                 # the same matrix again, on the other device
+
+    def step(w, x):
+        return mm.value_and_grad(loss_fn)(w, x)
+
+    torch.manual_seed(0)
+    w, x = torch.randn(6, 6), torch.randn(4, 6)
+    mesh = mm.MultiMesh((2,), ("stage",))
+    with mesh:
+        mesh.register_task("first", task=mm.Task(mesh_slice={"stage": 0}))
+        mesh.register_task("second", task=mm.Task(mesh_slice={"stage": 1}))
+        exe = mm.compile_function(step, (w, x), mesh=mesh, backend="cpu")
+    loss, grad = exe(w, x)
+    with mm.ignore_transforms():
+        ref_loss, ref_grad = step(w, x)
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(grad.full_tensor(), ref_grad, rtol=1e-4, atol=1e-5)
+    devices = {op["device_start"] for op in exe.plan["ops"] if op["kind"] == "task"}
+    assert devices == {0, 1}
+    exe.shutdown()
