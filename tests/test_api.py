@@ -282,3 +282,35 @@ def test_custom_partitioning_and_shard_map_run_on_the_task_submesh():
     with mm.ignore_transforms():
         torch.testing.assert_close(f(x, s), torch.tanh(x) * s.unsqueeze(-1) + 1.0)
     exe.shutdown()
+
+
+def test_explicitly_sharded_argument_is_resharded_at_the_call():
+    """An argument that arrives as a ShardedTensor in another layout (here: the column-sharded
+    result of one compiled function) is re-laid-out to what the next compiled function expects."""
+    mm.init(cpus=2)
+    mesh = mm.MultiMesh((1, 2), ("stage", "model"))
+
+    def producer(w, x):
+        with mm.named_scope("p"):
+            w = mm.with_sharding_constraint(w, ("hidden", None))
+            return x @ w.t()                                  # [5, 8], columns sharded
+
+    def consumer(h, v):
+        with mm.named_scope("c"):
+            h = mm.with_sharding_constraint(h, ("batch", None))    # rows sharded
+            return torch.tanh(h) @ v
+
+    w, x, v = torch.randn(8, 4), torch.randn(6, 4), torch.randn(8, 3)
+    with mesh:
+        mesh.register_task("p", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("hidden", "model")]))
+        mesh.register_task("c", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("batch", "model")]))
+        first = mm.compile_function(producer, (w, x), mesh=mesh, backend="cpu")
+        h = first(w, x)
+        second = mm.compile_function(consumer, (h.full_tensor(), v), mesh=mesh, backend="cpu")
+    assert h.sharding["shard_size"] == [6, 4]
+    want = second.input_shardings()[0]
+    assert want["shard_size"] == [3, 8] and want["key"] != h.sharding["key"]
+    out = second(h, v)                                        # ShardedTensor in, different layout
+    torch.testing.assert_close(out.full_tensor(), torch.tanh(x @ w.t()) @ v, rtol=1e-5, atol=1e-5)
+    first.shutdown()
+    second.shutdown()
