@@ -64,6 +64,9 @@ def parse_args():
     p.add_argument("--schedule", default="",
                    help="microbatch schedule: 1f1b, gpipe, zero-bubble-h2 (split backward tasks) or auto (zero-bubble-h2 "
                         "when there are pipeline stages, with 1f1b as the fallback); empty = the default of the layout")
+    p.add_argument("--plan-only", action="store_true",
+                   help="compile the step for --gpus virtual devices on the mock runtime (no CUDA device is "
+                        "touched, nothing is allocated), print the plan's statistics as one JSON line and exit")
     p.add_argument("--trace", default="", help="after the timed runs, profile one more step per rank and write "
                                                "its time breakdown to this directory (not a benchmark value)")
     return p.parse_args()
@@ -121,6 +124,23 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def default_layout(n: int):
+    """(pipeline stages, data parallel, tensor parallel, schedule) used when no layout flag is given:
+    the fastest measured layout per GPU count, except at 8 GPUs where the named layout and schedule
+    are kept - 4 stages x TP2, 1F1B with 16 microbatches."""
+    return {1: (1, 1, 1, "1f1b"), 2: (1, 2, 1, "1f1b"), 4: (4, 1, 1, "zero-bubble-h2"),
+            8: (4, 1, 2, "1f1b")}.get(n, (1, n, 1, "1f1b"))
+
+
+def default_layers_per_stage(n_layers: int, pp: int, schedule: str):
+    """Measured on 4 GPUs: 1F1B runs 2.3 % faster with a lighter last stage (it owns the output
+    projection and the loss), zero-bubble runs 4.8 % faster with equal shares (None)."""
+    if pp == 4 and n_layers % 4 == 0 and n_layers >= 16 and schedule == "1f1b":
+        q = n_layers // 4
+        return [q, q + 1, q + 1, q - 2]
+    return None
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -135,32 +155,28 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     n = args.gpus
-    if world != n and not (world == 1 and n == 1):
+    if world != n and not (world == 1 and n == 1) and not args.plan_only:
         raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
     import multimesh_jax_b200 as mm
     from multimesh_jax_b200.models import llama
     from multimesh_jax_b200.ops import kernels as K
-    if n > 1:
-        mm.init(gpus=n, distributed=True)
+    if not args.plan_only:
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
+        if n > 1:
+            mm.init(gpus=n, distributed=True)
     import torch.distributed as dist
 
     cfg = {"llama2_7b": llama.LlamaConfig.llama2_7b, "llama3_8b": llama.LlamaConfig.llama3_8b,
            "mixtral_8x7b": llama.LlamaConfig.mixtral_8x7b, "tiny": llama.LlamaConfig.tiny}[args.model]()
     if args.layers:
         cfg.n_layers = args.layers
-    # default layouts: tensor parallel pairs first, then data parallel (no pipeline bubble), and
-    # the named 4-stage pipeline x TP2 configuration on 8 GPUs
     if args.tp or args.dp or args.pp:
         tp, dp = args.tp or 1, args.dp or 1
         pp = args.pp or n // (tp * dp)
         default_schedule = "1f1b"
     else:
-        # fastest measured layout per GPU count, except at 8 GPUs where the named layout and
-        # schedule are kept: 4 stages x TP2, 1F1B with 16 microbatches
-        pp, dp, tp, default_schedule = {1: (1, 1, 1, "1f1b"), 2: (1, 2, 1, "1f1b"), 4: (4, 1, 1, "zero-bubble-h2"),
-                                        8: (4, 1, 2, "1f1b")}.get(n, (1, n, 1, "1f1b"))
+        pp, dp, tp, default_schedule = default_layout(n)
     args.schedule = args.schedule or default_schedule
     if pp * dp * tp != n:
         raise SystemExit(f"pp{pp} x dp{dp} x tp{tp} != {n} GPUs")
@@ -175,13 +191,8 @@ def main():
     opt = llama.AdamWConfig()
     if args.layers_per_stage:
         lps = [int(v) for v in args.layers_per_stage.split(",")]
-    elif pp == 4 and cfg.n_layers % 4 == 0 and cfg.n_layers >= 16 and args.schedule == "1f1b":
-        # measured on 4 GPUs: 1F1B runs 2.3 % faster with a lighter last stage (it owns the output
-        # projection and the loss), zero-bubble runs 4.8 % faster with equal shares
-        q = cfg.n_layers // 4
-        lps = [q, q + 1, q + 1, q - 2]
     else:
-        lps = None
+        lps = default_layers_per_stage(cfg.n_layers, pp, args.schedule)
 
     # abstract arguments for the capture; real tensors are created shard by shard below
     with torch.device("meta"):
@@ -197,6 +208,12 @@ def main():
         split = ("_act", "_wgt") if schedule == "zero-bubble-h2" else None
         llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, layers_per_stage=lps, split_backprop=split)
         with mesh:
+            if args.plan_only:
+                from multimesh_jax_b200 import _mm_C
+                from multimesh_jax_b200.runtime.collectives import Topology
+                return mm.compile_function(step_fn, (a_params, a_state, a_tok, a_tok, a_cos, a_cos), mesh=mesh,
+                                           donate_argnums=(0, 1), context=_mm_C.MockContext(n),
+                                           topology=Topology("cpu", n), name="train_step")
             return mm.compile_function(step_fn, (a_params, a_state, a_tok, a_tok, a_cos, a_cos), mesh=mesh,
                                        donate_argnums=(0, 1), backend="dist" if n > 1 else "cuda", name="train_step")
 
@@ -215,6 +232,16 @@ def main():
     else:
         exe = compile_with(args.schedule)
     compile_s = time.time() - t0
+    if args.plan_only:
+        plan = exe.plan
+        print(json.dumps({"plan_only": True, "n_gpus": n, "parallelism": f"pp{pp}xdp{dp}xtp{tp}", "schedule": args.schedule,
+                          "layers_per_stage": lps, "microbatches": global_batch // mb, "compile_s": round(compile_s, 2),
+                          "tasks": sum(1 for op in plan["ops"] if op["kind"] == "task"),
+                          "reshards": sum(1 for op in plan["ops"] if op["kind"] == "reshard"),
+                          "temp_gb_per_device": round(plan["temp_bytes_per_device_max"] / 2 ** 30, 1),
+                          "plan_hash": plan["hash"], "stats": plan["stats"]}))
+        exe.shutdown()
+        return 0
 
     from multimesh_jax_b200.models.init_sharded import init_sharded_llama
     params, state = init_sharded_llama(cfg, exe, dev, seed=1234)
