@@ -214,6 +214,8 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                 if gshape != lshape:
                     args = tuple(_fix_sizes(a, gshape, lshape) for a in args)
             fn = fxn.target
+            if n["attrs"].get("zero_result") == "1":
+                fn = _zeroed(fxn.target)
             if fast_ops and op in fast_ops:
                 fn = fast_ops[op]
                 fast_pending = (fxn.target, op)
@@ -347,6 +349,13 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
     prog = TemplateProgram(template, instrs, list(template["inputs"]), list(template["outputs"]), last_use)
     prog.fused_acc = fused_acc
     return prog
+
+
+def _zeroed(target: Callable) -> Callable:
+    """``target`` with its tensor result replaced by zeros of the same shape and type."""
+    def run(*args, **kwargs):
+        return torch.zeros_like(target(*args, **kwargs))
+    return run
 
 
 def _ir_value_of(cap: Captured, node: fx.Node) -> Optional[int]:

@@ -368,6 +368,8 @@ PYBIND11_MODULE(_mm_C, m) {
       .def_readwrite("recompute_from_arguments_if_cost_less_than", &PartitionConfig::recompute_from_arguments_if_cost_less_than)
       .def_readwrite("argument_recompute", &PartitionConfig::argument_recompute)
       .def_readwrite("minimize_cut_size", &PartitionConfig::minimize_cut_size)
+      .def_readwrite("zero_arguments", &PartitionConfig::zero_arguments)
+      .def_readwrite("dynamic_schedule_post_loop_tasks", &PartitionConfig::dynamic_schedule_post_loop_tasks)
       .def_readwrite("loop_increment_color", &PartitionConfig::loop_increment_color)
       .def_readwrite("enable_recomputation", &PartitionConfig::enable_recomputation)
       .def_readwrite("color_propagation_priority", &PartitionConfig::color_propagation_priority)

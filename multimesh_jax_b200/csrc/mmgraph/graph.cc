@@ -330,6 +330,8 @@ PartitionConfig PartitionConfig::FromEnv() {
   c.loop_increment_color = GetEnvBool("MULTIMESH_LOOP_INCREMENT_COLOR", false);
   c.argument_recompute = GetEnvBool("MULTIMESH_ARGUMENT_RECOMPUTE", true);
   c.minimize_cut_size = GetEnvBool("MULTIMESH_MINIMIZE_CUT_SIZE", true);
+  c.zero_arguments = GetEnvBool("MULTIMESH_ZERO_ARGUMENTS", false);
+  c.dynamic_schedule_post_loop_tasks = GetEnvBool("MULTIMESH_DYNAMIC_SCHEDULE_POST_LOOP_TASKS", true);
   c.color_propagation_priority = GetEnvString("MULTIMESH_COLOR_PROPAGATION_PRIORITY", "WEIGHT");
   return c;
 }

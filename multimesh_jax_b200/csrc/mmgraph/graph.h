@@ -193,6 +193,11 @@ struct PartitionConfig {
   bool minimize_cut_size = true;
   bool loop_increment_color = false;
   bool enable_recomputation = true;
+  // hoisted parameter casts produce zeros (debugging aid: isolates the cost / effect of the casts)
+  bool zero_arguments = false;
+  // tasks outside the microbatch loop that contain no collective may overtake one another;
+  // false = every task keeps its submission order on its device
+  bool dynamic_schedule_post_loop_tasks = true;
   std::string color_propagation_priority = "WEIGHT";  // WEIGHT | DEPTH | TOPOLOGICAL
   std::string dump_dir;
   bool dump_all_passes = false;

@@ -558,6 +558,7 @@ bool HoistLoopConvert(CompileState& s) {
     }
     if (invariant) {
       n.loop = -1;  // cast weights once per step, not once per microbatch
+      if (s.config.zero_arguments && IsConvert(n)) n.attrs["zero_result"] = "1";
       changed = true;
     }
   }

@@ -295,7 +295,7 @@ Plan BuildPlan(CompileState& s) {
     op.loop = t.in_loop;
     op.iteration = inst.iteration;
     op.priority = t.in_loop ? 10 : 0;
-    op.strict_ordering = t.in_loop || t.has_collectives;
+    op.strict_ordering = t.in_loop || t.has_collectives || !s.config.dynamic_schedule_post_loop_tasks;
     if (t.in_loop) op.scalars.push_back(static_cast<int64_t>(inst.iteration) * loop.size);
     // inputs
     for (int v : t.inputs) {

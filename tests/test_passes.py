@@ -488,3 +488,26 @@ def test_plan_hash_is_deterministic():
         two_stage_graph(b, loop=True)
         hashes.append(C.mpmd_partition(b.g, b.part, b.cfg)["hash"])
     assert hashes[0] == hashes[1]
+
+
+def test_environment_options_for_zeroed_arguments_and_static_post_loop_schedule(monkeypatch):
+    monkeypatch.setenv("MULTIMESH_ZERO_ARGUMENTS", "1")
+    monkeypatch.setenv("MULTIMESH_DYNAMIC_SCHEDULE_POST_LOOP_TASKS", "0")
+    cfg = C.PartitionConfig.from_env()
+    assert cfg.zero_arguments and not cfg.dynamic_schedule_post_loop_tasks
+    monkeypatch.delenv("MULTIMESH_ZERO_ARGUMENTS")
+    monkeypatch.delenv("MULTIMESH_DYNAMIC_SCHEDULE_POST_LOOP_TASKS")
+    cfg = C.PartitionConfig.from_env()
+    assert not cfg.zero_arguments and cfg.dynamic_schedule_post_loop_tasks
+
+
+def test_static_schedule_keeps_every_task_in_submission_order():
+    def plan_with(dynamic):
+        b = G()
+        two_stage_graph(b)
+        b.cfg.dynamic_schedule_post_loop_tasks = dynamic
+        return C.mpmd_partition(b.g, b.part, b.cfg)
+    dyn = [op["strict_ordering"] for op in plan_with(True)["ops"] if op["kind"] == "task"]
+    sta = [op["strict_ordering"] for op in plan_with(False)["ops"] if op["kind"] == "task"]
+    assert dyn == [False, False]      # no loop, no collectives: free to overtake
+    assert sta == [True, True]

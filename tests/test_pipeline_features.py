@@ -155,3 +155,35 @@ def test_fast_path_runs_tiny_functions_eagerly():
         out = f(a, b)
     got = out.full_tensor() if isinstance(out, mm.ShardedTensor) else out
     assert torch.equal(got, a * 2 + b)
+
+
+def test_zero_arguments_option_zeroes_hoisted_parameter_casts():
+    """With hoisted parameter casts switched on and the zero-arguments debugging option set, the
+    cast of a weight (done once per step, outside the microbatch loop) yields zeros: the loss of
+    ``sum((x @ w.to(float64)) ** 2)`` becomes 0 while the untouched run matches eager."""
+    from multimesh_jax_b200 import _mm_C
+
+    def loss_fn(w, batch):
+        with mm.named_scope("blk.0"):
+            return ((batch @ w.to(torch.float64)) ** 2).sum()
+
+    def step(w, batch):
+        return mm.microbatch(loss_fn, size=2, argnum=1, schedule="gpipe")(w, batch)
+
+    torch.manual_seed(0)
+    w, x = torch.randn(D, D), torch.randn(8, D, dtype=torch.float64)
+    results = {}
+    for zero in (False, True):
+        mesh = mm.MultiMesh((1,), ("stage",))
+        mesh.register_task(r"(blk\.\d+)", task=mm.Task(mesh_slice={"stage": 0}))
+        with mesh:
+            exe = mm.compile_function(step, (w, x), mesh=mesh, backend="cpu",
+                                      config_overrides={"hoist_loop_convert": True, "zero_arguments": zero})
+        results[zero] = float(exe(w, x).full_tensor())
+        g = exe.cap.graph
+        casts = [g.node(n) for t in exe.plan["templates"] for n in t["nodes"] if g.node(n)["op"].startswith("aten._to_copy")]
+        assert casts and all(c["loop"] < 0 for c in casts)           # hoisted out of the loop
+        exe.shutdown()
+    with mm.ignore_transforms():
+        ref = float(step(w, x))
+    assert abs(results[False] - ref) < 1e-6 * abs(ref) and results[True] == 0.0
