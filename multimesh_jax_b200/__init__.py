@@ -31,7 +31,7 @@ from .task import (Context, MultiMesh, Task, TaskMesh, clear_tasks, microbatch, 
                    parallelize, register_task, slice_global_mesh, task, value_and_grad)
 from .runtime.executable import Executable, ShardedTensor, StepFailed  # noqa: E402
 from .compiler.api import compile_function  # noqa: E402
-from .init import init, init_test, shutdown  # noqa: E402
+from .init import detect_cluster, init, init_test, shutdown  # noqa: E402
 
 __all__ = [
     "task", "microbatch", "parallelize", "register_task", "slice_global_mesh", "Task", "TaskMesh", "Context",
@@ -39,5 +39,5 @@ __all__ = [
     "with_sharding_constraint", "relayout", "tasks", "mjit", "shutdown", "replicate_parameters_smaller_than_num_elements",
     "recompute_from_arguments_if_cost_less_than", "clear_tasks", "no_op", "mark_gradient", "mark_loss",
     "value_and_grad", "named_scope", "module_scopes", "compile_function", "Executable", "ShardedTensor",
-    "StepFailed", "init", "init_test", "custom_partitioning", "index_class", "shard_map",
+    "StepFailed", "init", "init_test", "custom_partitioning", "index_class", "shard_map", "detect_cluster",
 ]

@@ -314,3 +314,21 @@ def test_explicitly_sharded_argument_is_resharded_at_the_call():
     torch.testing.assert_close(out.full_tensor(), torch.tanh(x @ w.t()) @ v, rtol=1e-5, atol=1e-5)
     first.shutdown()
     second.shutdown()
+
+
+def test_cluster_detection_reads_the_launchers_environment(monkeypatch):
+    for var in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID",
+                "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE", "OMPI_COMM_WORLD_LOCAL_RANK"):
+        monkeypatch.delenv(var, raising=False)
+    assert mm.detect_cluster() is None
+    monkeypatch.setenv("SLURM_PROCID", "5")
+    monkeypatch.setenv("SLURM_NTASKS", "16")
+    monkeypatch.setenv("SLURM_LOCALID", "1")
+    assert mm.detect_cluster() == (5, 16, 1) == mm.detect_cluster("slurm")
+    monkeypatch.setenv("RANK", "2")
+    monkeypatch.setenv("WORLD_SIZE", "4")
+    assert mm.detect_cluster() == (2, 4, 0)              # the torchrun variables come first
+    with pytest.raises(RuntimeError):
+        mm.detect_cluster("ompi")
+    with pytest.raises(ValueError):
+        mm.detect_cluster("kubernetes")
