@@ -182,21 +182,28 @@ class Executable:
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
         self.donated = set(getattr(cap, "donated_inputs", ()))
-        # temporaries whose last reader is task op k (and that no reshard reads later)
+        # Temporaries handed over to their last reader (task op k), which frees each one right after
+        # its last use. Readers of one tile are not ordered among themselves by the dependence
+        # analysis, so this is only safe when they cannot overtake one another: every reader is a
+        # task of a strict-order chain (on one device those run in plan order) and no reshard -
+        # which runs on its own thread - reads the store at all.
         last_read: Dict[int, int] = {}
+        unsafe: set = set()
         for k, op in enumerate(plan["ops"]):
             if op["kind"] == "task":
                 for sid in op["inputs"]:
                     last_read[sid] = k
+                    if not op["strict_ordering"]:
+                        unsafe.add(sid)
                 for sid, m in zip(op["outputs"], op["accumulate"]):
                     if m:
-                        last_read[sid] = -1          # accumulators are read-modify-written: never hand over
+                        unsafe.add(sid)              # accumulators are read-modify-written: never hand over
             elif op["kind"] == "reshard":
-                last_read[op["src_store"]] = -1
+                unsafe.add(op["src_store"])
         self._dying_inputs: Dict[int, set] = {}
         for sid, k in last_read.items():
             st = plan["stores"][sid]
-            if k >= 0 and st["kind"] == "TEMP" and st["alias_of"] < 0:
+            if sid not in unsafe and st["kind"] == "TEMP" and st["alias_of"] < 0:
                 self._dying_inputs.setdefault(k, set()).add(sid)
         live_executables.add(self)
 

@@ -13,6 +13,20 @@ from multimesh_jax_b200.models import llama
 torch.manual_seed(0)
 
 
+
+LR = 1e-2      # learning rate of every AdamW step in this file
+
+
+def _adam_close(got: torch.Tensor, want: torch.Tensor, lr: float):
+    """Parameters after one AdamW step. Adam's first step is lr * sign(g) for every element, so an
+    element whose gradient is zero up to rounding can land 2 * lr away when the summation order of
+    the gradient differs; such elements must stay rare (< 0.2 %) and within 2.2 * lr, all others
+    must agree to 1e-3."""
+    diff = (got - want).abs()
+    loose = diff > 1e-3 + 1e-3 * want.abs()
+    assert float(diff.max()) <= 2.2 * lr + 1e-6, f"max difference {float(diff.max())}"
+    assert int(loose.sum()) <= max(1, int(0.002 * diff.numel())), f"{int(loose.sum())} of {diff.numel()} elements differ"
+
 def _cfg(**kw):
     cfg = llama.LlamaConfig.tiny(**kw)
     cfg.dtype = torch.float32
@@ -178,7 +192,7 @@ def test_data_parallel_and_fsdp_steps_match_eager(axes, fsdp):
     loss, p_mm, s_mm = exe(params, opt_state, tokens, labels, cos, sin)
     torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
     for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
-        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)   # Adam's first step is sign-like: tiny gradients amplify rounding
+        _adam_close(a.full_tensor(), b, LR)
     for a, b in zip(pytree.tree_leaves(s_mm["m"]), pytree.tree_leaves(s_ref["m"])):
         torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-5)
     g = exe.cap.graph
@@ -229,7 +243,7 @@ def test_forced_layout_change_at_the_stage_boundary():
     loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
     torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
     for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
-        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)
+        _adam_close(a.full_tensor(), b, LR)
     plan = exe.plan
     crossings = []
     for op in plan["ops"]:
@@ -266,7 +280,7 @@ def test_zero_bubble_schedule_on_four_llama_stages():
     loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
     torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
     for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
-        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-3)
+        _adam_close(a.full_tensor(), b, LR)
     loop = [t for t in exe.plan["templates"] if t["in_loop"]]
     producer = {v: t["name"] for t in loop for v in t["outputs"]}
     noncritical = {t["name"] for t in loop if t["noncritical"]}
