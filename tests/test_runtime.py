@@ -274,3 +274,34 @@ def test_multi_node_layouts_on_the_mock_runtime(dp, pp, tp, layers):
         if r["kind"] == 0:
             tasks_per_stage[stage_of(r["device"])] = tasks_per_stage.get(stage_of(r["device"]), 0) + 1
     assert set(tasks_per_stage) == set(range(pp))
+
+
+def test_temporaries_are_handed_over_only_when_their_readers_are_ordered():
+    """A task may free an input after its last use only if no other reader of that tile can run
+    later than it: readers are not ordered among themselves, so a store that a reshard also reads
+    (its body runs on another worker thread), or that a task outside the strict-order chains reads,
+    stays in the table."""
+    from multimesh_jax_b200.models import llama
+    cfg = llama.LlamaConfig.tiny(n_layers=4, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128)
+    cfg.dtype = torch.float32
+    B, S, MB = 8, 16, 2
+    params = llama.init_params(cfg)
+    state = llama.init_opt_state(params)
+    tok = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(), seq_len=S, global_batch=B, microbatch_size=MB)
+    mesh = mm.MultiMesh((2, 1, 1), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=2)
+    with mesh:
+        exe = mm.compile_function(step, (params, state, tok, tok, cos, sin), mesh=mesh, backend="cpu")
+    ops = exe.plan["ops"]
+    reshard_sources = {op["src_store"] for op in ops if op["kind"] == "reshard"}
+    handed_over = set().union(*exe._dying_inputs.values()) if exe._dying_inputs else set()
+    assert handed_over, "nothing is freed early: the hand-over is switched off altogether"
+    assert not (handed_over & reshard_sources)
+    for k, stores in exe._dying_inputs.items():
+        for sid in stores:
+            readers = [op for op in ops if op["kind"] == "task" and sid in op["inputs"]]
+            assert all(op["strict_ordering"] for op in readers)
+            assert ops[k] is readers[-1]
+    exe.shutdown()
