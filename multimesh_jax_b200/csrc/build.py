@@ -17,6 +17,7 @@ import shutil
 import subprocess
 import sys
 import sysconfig
+import tempfile
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
@@ -164,7 +165,8 @@ def build_selftest(sanitizer: str = "address", force: bool = False) -> Path:
     stand-alone program instrumented by ``sanitizer`` (``address`` = ASan + UBSan, ``thread`` =
     TSan, ``none``); one object per source, compiled in parallel. Returns the program's path."""
     flags = SANITIZER_FLAGS[sanitizer]
-    out_dir = BUILD_DIR / f"selftest_{sanitizer}"
+    # outside the source tree: the instrumented objects are large and of no use to anyone else
+    out_dir = Path(tempfile.gettempdir()) / f"mm_selftest_{os.getuid()}" / sanitizer
     out_dir.mkdir(parents=True, exist_ok=True)
     srcs = [HERE / "selftest" / "host_selftest.cc"] + sorted((HERE / "mmgraph").glob("*.cc")) + [HERE / "mmrt" / "runtime.cc"]
     hdrs = sorted((HERE / "mmgraph").glob("*.h")) + sorted((HERE / "mmrt").glob("*.h"))
