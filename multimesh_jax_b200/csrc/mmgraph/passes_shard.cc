@@ -783,11 +783,45 @@ bool HoistShardMapReduce(CompileState& s) {
   for (int id : std::vector<int>(g.order)) {
     Node& ar = g.node(id);
     if (ar.dead || ar.op != "mm.all_reduce" || ar.loop < 0) continue;
+    // The reduced value must end in exactly one microbatch accumulator, directly or through
+    // view-like operators (the detach autograd puts on a returned loss); any other user may
+    // only look at its shape (the ones_like that seeds the backward pass).
     const auto& us = users[ar.outputs[0]];
-    if (us.size() != 1 || g.node(us[0]).op != "mm.accumulate") continue;
-    const int acc_id = us[0];
+    int acc_id = -1, chain_head = -1;
+    std::vector<int> shape_only;
+    bool ok = !us.empty();
+    for (int u : us) {
+      const Node& un = g.node(u);
+      if (un.op == "mm.accumulate" && acc_id < 0) {
+        acc_id = u;
+      } else if (un.op == "aten.ones_like.default" || un.op == "aten.zeros_like.default" ||
+                 un.op == "aten.empty_like.default") {
+        shape_only.push_back(u);
+      } else if (IsAliasOp(un) && acc_id < 0 && un.loop == ar.loop) {
+        int cur = u;
+        while (true) {   // follow the chain of single-user views down to the accumulator
+          const auto& cu = users[g.node(cur).outputs[0]];
+          if (cu.size() != 1) { ok = false; break; }
+          const Node& next = g.node(cu[0]);
+          if (next.op == "mm.accumulate") { acc_id = cu[0]; chain_head = u; break; }
+          if (!IsAliasOp(next) || next.loop != ar.loop) { ok = false; break; }
+          cur = cu[0];
+        }
+      } else {
+        ok = false;
+      }
+      if (!ok) break;
+    }
+    if (!ok || acc_id < 0) continue;
     // accumulate the partial value; reduce its sum once, after the loop
-    g.node(acc_id).inputs[0] = ar.inputs[0];
+    const int partial = ar.inputs[0];
+    if (chain_head >= 0) {
+      for (int& in : g.node(chain_head).inputs) if (in == ar.outputs[0]) in = partial;
+    } else {
+      g.node(acc_id).inputs[0] = partial;
+    }
+    for (int u : shape_only)
+      for (int& in : g.node(u).inputs) if (in == ar.outputs[0]) in = partial;
     const int acc_out = g.node(acc_id).outputs[0];
     if (s.config.remove_hoisted_reduces) {  // performance upper-bound experiment: drop it entirely
       ar.dead = true;

@@ -1,7 +1,7 @@
 """Worker of the multi-process tests (gloo ranks on CPU, one process per virtual device).
 
 Modes:
-  step   - pipeline x tensor parallel training step through the "dist" topology; every rank
+  step   - pipeline x data x tensor parallel training step through the "dist" topology; every rank
            checks its tiles of the loss and of the updated parameters against the eager step.
   leave  - the last rank exits cleanly between steps; the others see their next collective
            end with an error within the process-group timeout and report it as a status.
@@ -18,7 +18,7 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 
-def build(pp, tp):
+def build(pp, tp, dp=1):
     import multimesh_jax_b200 as mm
     from multimesh_jax_b200.models import llama
     torch.manual_seed(0)
@@ -31,7 +31,7 @@ def build(pp, tp):
     labels = torch.randint(0, cfg.vocab, (B, S))
     cos, sin = llama.rope_tables(cfg, S, "cpu")
     step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB)
-    mesh = mm.MultiMesh((pp, tp), ("stage", "model"))
+    mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
     llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
     args = (params, state, tokens, labels, cos, sin)
     with mesh:
@@ -39,10 +39,10 @@ def build(pp, tp):
     return mm, exe, step, args
 
 
-def mode_step(pp, tp):
+def mode_step(pp, tp, dp=1):
     from torch.utils import _pytree as pytree
     rank = dist.get_rank()
-    mm, exe, step, args = build(pp, tp)
+    mm, exe, step, args = build(pp, tp, dp)
     with mm.ignore_transforms():
         loss_ref, p_ref, _ = step(*args)
     loss, p_mm, _ = exe(*args)
@@ -89,7 +89,11 @@ def mode_leave(pp, tp):
 
 if __name__ == "__main__":
     mode, pp, tp = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
+    dp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
     timeout = datetime.timedelta(seconds=8 if mode == "leave" else 120)
     dist.init_process_group("gloo", timeout=timeout)
-    {"step": mode_step, "leave": mode_leave}[mode](pp, tp)
+    if mode == "step":
+        mode_step(pp, tp, dp)
+    else:
+        mode_leave(pp, tp)
     dist.destroy_process_group()

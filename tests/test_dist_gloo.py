@@ -27,9 +27,9 @@ def _run(nproc, *args, timeout=420):
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
 
 
-@pytest.mark.parametrize("pp,tp", [(2, 1), (2, 2)])
-def test_dist_topology_step_matches_eager(pp, tp):
-    r = _run(pp * tp, "step", pp, tp)
+@pytest.mark.parametrize("pp,tp,dp", [(2, 1, 1), (2, 2, 1), (1, 1, 2), (2, 1, 2)])
+def test_dist_topology_step_matches_eager(pp, tp, dp):
+    r = _run(pp * tp * dp, "step", pp, tp, dp)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     line = next(l for l in r.stdout.splitlines() if "DIST_STEP_OK" in l)
     assert json.loads(line)["DIST_STEP_OK"] is True
