@@ -156,6 +156,26 @@ def tile_box(shape_dict: dict, ordinal: int) -> Tuple[List[int], List[int]]:
     return _mm_C.tile_box(shape_dict, ordinal)
 
 
+_LOCAL_PLANS: Dict[Tuple[str, str], Optional[Dict[int, list]]] = {}
+
+
+def _local_only_chunks(src: dict, dst: dict) -> Optional[Dict[int, list]]:
+    """Chunks of the reshard ``src`` -> ``dst`` per destination device when each of them comes
+    from that same device's source tile; None when any piece has to cross devices."""
+    key = (src["key"], dst["key"])
+    if key not in _LOCAL_PLANS:
+        from .. import _mm_C
+        chunks = _mm_C.plan_reshard(src, dst)["chunks"]
+        if all(c["src_device"] == c["dst_device"] for c in chunks):
+            per: Dict[int, list] = {}
+            for c in chunks:
+                per.setdefault(c["dst_device"], []).append(c)
+            _LOCAL_PLANS[key] = per
+        else:
+            _LOCAL_PLANS[key] = None
+    return _LOCAL_PLANS[key]
+
+
 class DeviceCtx:
     """What a task body sees of the device it runs on."""
 
@@ -273,6 +293,18 @@ class DeviceCtx:
         n = src["num_devices"]
         me = self.device - self.device_start
         group = list(range(n))
+        local = _local_only_chunks(src, dst)
+        if local is not None:
+            # every destination tile is made of pieces of the same device's source tile (replicated
+            # -> sharded, or a coarser -> finer split): a slice, no exchange. All members take this
+            # branch together because the plan depends on the two layouts only.
+            out = torch.empty(dst["shard_size"], dtype=x.dtype, device=x.device)
+            for c in local.get(self.device, ()):
+                ext = [h - l for l, h in zip(c["lo"], c["hi"])]
+                s_box = tuple(slice(o, o + e) for o, e in zip(c["src_offset"], ext))
+                d_box = tuple(slice(o, o + e) for o, e in zip(c["dst_offset"], ext))
+                out[d_box] = x[s_box]
+            return out
         if self.topology.kind == "dist" and self.peer_comm is not None:
             comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
             from ..parallel.reshard import PeerReshard

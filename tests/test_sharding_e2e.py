@@ -135,3 +135,33 @@ def test_parameter_shared_by_two_tasks_gets_the_sum_of_both_gradients():
     devices = {op["device_start"] for op in exe.plan["ops"] if op["kind"] == "task"}
     assert devices == {0, 1}
     exe.shutdown()
+
+
+def test_layout_change_made_of_local_pieces_needs_no_exchange(monkeypatch):
+    """replicated -> sharded (and coarser -> finer) layout changes inside a task are slices of the
+    device's own tile: no data is exchanged between the devices, the result equals the slice of the
+    global tensor. sharded -> replicated still gathers."""
+    from multimesh_jax_b200 import _mm_C as C
+    from multimesh_jax_b200.runtime import collectives as col
+    from test_sharding import shape
+
+    topo = col.Topology("cpu", 4)
+    ctxs = [col.DeviceCtx(topo, d, col.Rendezvous()) for d in range(4)]
+    exchanged = []
+    monkeypatch.setattr(col.DeviceCtx, "_exchange", lambda self, *a, **k: exchanged.append(a) or (_ for _ in ()).throw(
+        AssertionError("exchange called")))
+    full = torch.arange(8 * 12, dtype=torch.float32).reshape(8, 12)
+    rep = shape("float32", [8, 12], [[], []], [4], 0)
+    rows = shape("float32", [8, 12], [[0], []], [4], 0)
+    halves = shape("float32", [8, 12], [[0], []], [2, 2], 0)         # rows over the first mesh axis only
+    grid = shape("float32", [8, 12], [[0], [1]], [2, 2], 0)
+    for src, dst in ((rep, rows), (rep, grid), (halves, grid)):
+        for d, ctx in enumerate(ctxs):
+            ctx.device_start = 0
+            lo, hi = C.tile_box(src, d)
+            x = full[lo[0]:hi[0], lo[1]:hi[1]].contiguous()
+            out = ctx.spmd_reshard(x, src, dst, key=("t", d))
+            lo, hi = C.tile_box(dst, d)
+            torch.testing.assert_close(out, full[lo[0]:hi[0], lo[1]:hi[1]])
+    assert not exchanged
+    assert col._local_only_chunks(rows, rep) is None                  # the gather direction is not local
