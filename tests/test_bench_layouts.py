@@ -41,3 +41,11 @@ def test_llama3_fsdp_tp_forced_reshard_and_mixtral_expert_parallel_plans():
     moe = _plan("--gpus", "8", "--model", "mixtral_8x7b", "--seq", "4096", "--per-gpu-batch", "2", "--microbatch", "1",
                 "--pp", "2", "--dp", "4", "--tp", "1")
     assert moe["parallelism"] == "pp2xdp4xtp1" and moe["microbatches"] == 4 and moe["reshards"] > 0
+
+
+def test_reference_arm_reports_why_it_is_unavailable():
+    proc = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1"],
+                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300, cwd=str(ROOT))
+    assert proc.returncode == 0
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line and len(line["unavailable"]) > 10
