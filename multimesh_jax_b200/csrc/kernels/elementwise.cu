@@ -595,6 +595,7 @@ int mm_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rs
                    float* dw_out, float* scratch, int64_t rows, int D, int accumulate_dw,
                    int add_to_dx, cudaStream_t stream) {
   if (D % 8 || D > 16384) return -2;
+  if (rows < 0 || rows > 2147483647LL) return -2;   // the kernel indexes rows with an int
   if (rows == 0) return 0;
   const int parts = mm_rmsnorm_bwd_parts(rows);
 #define MM_RN_BWD(TH, VPT)                                                                   \
@@ -777,7 +778,11 @@ extern "C" int mm_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* 
             D, MM_NOALLOC_MAX_D);
     return -2;
   }
-  if (rows < 0) return -2;
+  if (rows < 0 || rows > 2147483647LL) {
+    fprintf(stderr, "[mm_kernels] rmsnorm_bwd_noalloc: %lld rows are not supported (0 .. 2^31 - 1)\n",
+            static_cast<long long>(rows));
+    return -2;
+  }
   if (rows == 0) return 0;
   int rc = 0;
   float* scratch = noalloc_scratch_for_current_device(&rc);

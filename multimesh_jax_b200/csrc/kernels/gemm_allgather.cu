@@ -43,7 +43,8 @@ struct AllGatherHook {
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
 
   __device__ __forceinline__ bool before_tile_loads(int m_blk, int, int* err) const {
-    for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
+    unsigned long long t0 = 0, limit = 0;
+    for (uint32_t i = 0;; ++i) {
       int v;
       asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ready + m_blk) : "memory");
       if (v >= target) {
@@ -51,7 +52,15 @@ struct AllGatherHook {
         return true;
       }
       if (i > 32) __nanosleep(100);
-      if ((i & 1023) == 1023 && *reinterpret_cast<volatile int*>(err) != 0) return false;
+      if ((i & 255) == 255) {
+        if (*reinterpret_cast<volatile int*>(err) != 0) return false;
+        if (t0 == 0) {
+          t0 = global_timer_ns();
+          limit = status_wait_limit_ns(err);
+        } else if (global_timer_ns() - t0 > limit) {
+          break;
+        }
+      }
     }
     atomicCAS(err, 0, MM_ERR_WAIT_PEER);
     return false;

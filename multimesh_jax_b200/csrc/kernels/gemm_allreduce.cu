@@ -112,6 +112,17 @@ struct AllReduceHook {
 
   __device__ __forceinline__ void epilogue(uint32_t t_base, int m_blk, int n_blk, int q, int lane, int M, int N,
                                            int* err, uint8_t* stage, State& st, const TmemRelease& rel) const {
+    if (m_blk * GEMM_BM >= M) {
+      // A CTA pair covers 256 rows: with an odd number of 128-row blocks the second CTA of the last
+      // pair has no rows. It owns no flags and no receive rows either, so it only hands the
+      // accumulator back (the MMA lane counts its arrival) and reduces what it pushed before.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) rel.arrive();
+      if (st.prev_m >= 0) reduce_tile(st.prev_m, st.prev_n, q, lane, M, N, err);
+      st.prev_m = -1;
+      return;
+    }
     uint8_t* ws = stage + q * AR_WARP_STAGE;          // this warp's 32 rows x 256 B
     const int row0 = m_blk * GEMM_BM + q * 32;
     const int tile = m_blk * num_n + n_blk;

@@ -1,5 +1,6 @@
 #include "host_common.h"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace mm {
@@ -18,6 +19,15 @@ DeviceState* device_state() {
     return nullptr;
   if (cudaMalloc(&s->status, 64) != cudaSuccess) return nullptr;
   if (cudaMemset(s->status, 0, 64) != cudaSuccess) return nullptr;
+  // bytes 8..15: time limit of peer waits in nanoseconds (MM_PEER_WAIT_MS, default 20 s)
+  unsigned long long limit_ns = 20000ull * 1000000ull;
+  if (const char* e = getenv("MM_PEER_WAIT_MS")) {
+    const long long ms = atoll(e);
+    if (ms > 0) limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  }
+  if (cudaMemcpy(reinterpret_cast<char*>(s->status) + 8, &limit_ns, sizeof(limit_ns), cudaMemcpyHostToDevice) !=
+      cudaSuccess)
+    return nullptr;
   s->ready = true;
   return s;
 }
@@ -95,6 +105,24 @@ int mm_read_status(int clear) {
   if (cudaMemcpy(&v, s->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
   if (clear && v != 0) cudaMemset(s->status, 0, sizeof(int));
   return v;
+}
+
+// Sets the time limit of peer waits on the current device (milliseconds; takes effect for kernels
+// launched afterwards).
+int mm_set_peer_wait_ms(int ms) {
+  mm::DeviceState* s = mm::device_state();
+  if (!s || ms <= 0) return -1;
+  const unsigned long long limit_ns = static_cast<unsigned long long>(ms) * 1000000ull;
+  if (cudaMemcpy(reinterpret_cast<char*>(s->status) + 8, &limit_ns, sizeof(limit_ns), cudaMemcpyHostToDevice) !=
+      cudaSuccess)
+    return -2;
+  return 0;
+}
+
+// Device address of the current device's 64-byte status block (word 0 = status).
+void* mm_status_ptr() {
+  mm::DeviceState* s = mm::device_state();
+  return s ? s->status : nullptr;
 }
 
 int mm_sm_count() {

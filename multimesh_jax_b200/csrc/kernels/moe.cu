@@ -27,7 +27,7 @@ struct RouteDispatchArgs {
   const __nv_bfloat16* x;      // [T, D]
   const __nv_bfloat16* wr;     // [E, D]
   const __nv_bfloat16* other;  // optional [T, D]: second row per token (scaled by the gate)
-  int T, D, E, k, experts_per_rank, capacity;
+  int T, D, E, k, experts_per_rank, capacity, nranks;
   __nv_bfloat16* recv[MOE_MAX_RANKS];        // [experts_per_rank][capacity][D] in every owner's memory
   __nv_bfloat16* recv_other[MOE_MAX_RANKS];  // same shape, for `other`
   int* counter[MOE_MAX_RANKS];               // [experts_per_rank] in every owner's memory
@@ -72,6 +72,16 @@ __global__ void __launch_bounds__(256)
       for (int i = 0; i < j; ++i) taken |= chosen[i] == e;
       if (!taken && logit[e] > bv) { bv = logit[e]; best = e; }
     }
+    if (best < 0) {
+      // no logit compares greater than -inf (all NaN or -inf, a diverging run): the choice must
+      // still be an expert, so take the lowest index not chosen yet, with a neutral logit
+      for (int e = 0; e < a.E && best < 0; ++e) {
+        bool taken = false;
+        for (int i = 0; i < j; ++i) taken |= chosen[i] == e;
+        if (!taken) best = e;
+      }
+      bv = 0.f;
+    }
     chosen[j] = best;
     val[j] = bv;
     mx = fmaxf(mx, bv);
@@ -83,6 +93,16 @@ __global__ void __launch_bounds__(256)
   for (int j = 0; j < a.k; ++j) {
     const float gate = val[j] / den;
     const int e = chosen[j];
+    if (e < 0 || e >= a.E || e / a.experts_per_rank >= a.nranks) {
+      // cannot happen with a total selection; checked because the stores below go to a peer
+      if (lane == 0) {
+        atomicCAS(err, 0, MM_ERR_BOUNDS);
+        a.idx[t * a.k + j] = 0;
+        a.gates[t * a.k + j] = 0.f;
+        a.slot[t * a.k + j] = a.capacity;    // marks "no row": combine skips it
+      }
+      continue;
+    }
     const int owner = e / a.experts_per_rank, el = e - owner * a.experts_per_rank;
     int s = 0;
     if (lane == 0) s = atomicAdd_system(a.counter[owner] + el, 1);
@@ -92,8 +112,8 @@ __global__ void __launch_bounds__(256)
       a.gates[t * a.k + j] = gate;
       a.slot[t * a.k + j] = s;
     }
-    if (s >= a.capacity) {
-      if (lane == 0) atomicCAS(err, 0, MM_ERR_MOE_CAPACITY);
+    if (s < 0 || s >= a.capacity) {
+      if (lane == 0) atomicCAS(err, 0, s < 0 ? static_cast<int>(MM_ERR_BOUNDS) : MM_ERR_MOE_CAPACITY);
       continue;
     }
     const int64_t off = (static_cast<int64_t>(el) * a.capacity + s) * a.D;
@@ -123,7 +143,7 @@ struct CombineArgs {
   const __nv_bfloat16* other;  // optional [T, D] for the dot products
   float* dots;          // optional out [T, k]: <other[t], row_k>
   __nv_bfloat16* y;     // optional out [T, D]: sum_k w_k * row_k
-  int T, D, k, experts_per_rank, capacity;
+  int T, D, k, experts_per_rank, capacity, nranks;
 };
 
 __global__ void __launch_bounds__(256) moe_combine_kernel(CombineArgs a) {
@@ -137,7 +157,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(CombineArgs a) {
   for (int j = 0; j < a.k; ++j) {
     const int e = a.idx[t * a.k + j], s = a.slot[t * a.k + j];
     const int owner = e / a.experts_per_rank, el = e - owner * a.experts_per_rank;
-    const bool valid = s < a.capacity;
+    const bool valid = s >= 0 && s < a.capacity && e >= 0 && owner < a.nranks;
     rows[j] = valid ? reinterpret_cast<const uint4*>(a.buf[owner] + (static_cast<int64_t>(el) * a.capacity + s) * a.D)
                     : nullptr;
     w[j] = a.gates ? a.gates[t * a.k + j] : 1.f;
@@ -202,6 +222,7 @@ int mm_moe_route_dispatch(const void* x, const void* wr, const void* other, int 
   a.wr = static_cast<const __nv_bfloat16*>(wr);
   a.other = static_cast<const __nv_bfloat16*>(other);
   a.T = T; a.D = D; a.E = E; a.k = k; a.experts_per_rank = experts_per_rank; a.capacity = capacity;
+  a.nranks = nranks;
   for (int r = 0; r < nranks; ++r) {
     a.recv[r] = reinterpret_cast<__nv_bfloat16*>(recv[r]);
     a.recv_other[r] = recv_other ? reinterpret_cast<__nv_bfloat16*>(recv_other[r]) : nullptr;
@@ -229,6 +250,7 @@ int mm_moe_combine(const int64_t* buf, int nranks, const int* idx, const int* sl
   a.dots = dots;
   a.y = static_cast<__nv_bfloat16*>(y);
   a.T = T; a.D = D; a.k = k; a.experts_per_rank = experts_per_rank; a.capacity = capacity;
+  a.nranks = nranks;
   const int threads = 256;
   const int blocks = (T * 32 + threads - 1) / threads;
   moe_combine_kernel<<<blocks, threads, 0, stream>>>(a);

@@ -13,13 +13,18 @@
 // Limits and rules
 //   * hidden size D: a multiple of 8, at most MM_NOALLOC_MAX_D (8192). Larger or
 //     unaligned sizes are refused with a message on stderr and a non-zero return code.
-//   * any number of rows; at most MM_NOALLOC_MAX_PARTS (128) blocks share the rows, so the
-//     scratch is MM_NOALLOC_MAX_PARTS * MM_NOALLOC_MAX_D floats = 4 MiB. Every GPU that
-//     loads the library holds this array until the process exits.
-//   * the first call on each device looks up the device address of the array (one
-//     `cudaGetSymbolAddress`, with that device current) and remembers it. Make that first
-//     call before starting a stream capture on the device.
-//   * the function never calls cudaMalloc, cudaFree or any routine that allocates.
+//   * up to 2^31 - 1 rows (more are refused); at most MM_NOALLOC_MAX_PARTS (128) blocks share
+//     the rows, so the scratch is MM_NOALLOC_MAX_PARTS * MM_NOALLOC_MAX_D floats = 4 MiB. Every
+//     GPU that loads the library holds this array until the process exits.
+//   * the first call on each device is a set-up call: it looks up the device address of the
+//     array (one `cudaGetSymbolAddress`, with that device current) and remembers it. With lazy
+//     module loading that look-up, or the first kernel launch, can make the CUDA driver load
+//     the library's code image onto the device - the 4 MiB array included - which is an
+//     allocation made by the driver. So make one call per device during ordinary start-up:
+//     before the region in which nothing may be allocated begins, and before any stream
+//     capture on that device.
+//   * apart from that driver-side loading on the first call, the function itself calls no
+//     cudaMalloc, no cudaFree and no library routine that allocates.
 //   * all calls on a device share the one array, and it keeps whatever the previous call
 //     left in it. The kernels overwrite every element they later read, so nothing has to
 //     be cleared, but two calls whose kernels overlap on the GPU (different streams

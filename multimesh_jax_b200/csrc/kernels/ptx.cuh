@@ -2,9 +2,14 @@
 // mbarriers with bounded waits, TMA tensor copies, tcgen05 tensor-core MMA
 // with TMEM accumulators, and system-scope flag accesses for peer memory.
 //
-// Every wait in this header is bounded: after MM_SPIN_LIMIT polls it records
-// an error code in a caller-supplied global word and returns false so the
-// kernel can unwind (free TMEM, return) instead of spinning forever.
+// Every wait in this header is bounded by wall-clock time (the global timer): when the
+// limit runs out it records an error code in a caller-supplied global status word and
+// returns false so the kernel can unwind (free TMEM, return) instead of spinning forever.
+// The limit lives next to the status word (`status_wait_limit_ns`), so the host sets it per
+// device. Once a status word is non-zero every later wait gives up at its first check: the
+// step that saw the expiry has failed anyway, and the rest of its kernels must drain in
+// milliseconds, not one time limit each. The host reads and clears the word when the step's
+// results are awaited and reports the failure there.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -14,7 +19,10 @@
 namespace mm {
 
 #ifndef MM_SPIN_LIMIT
-#define MM_SPIN_LIMIT (1u << 22)
+#define MM_SPIN_LIMIT (1u << 22)   // poll bound of the few waits that have no status word
+#endif
+#ifndef MM_DEFAULT_WAIT_NS
+#define MM_DEFAULT_WAIT_NS 20000000000ull   // used when the status block carries no limit
 #endif
 
 // Error codes written to the kernel's status word.
@@ -27,6 +35,19 @@ enum : int {
   MM_ERR_WAIT_PEER = 5,      // a peer flag never reached the expected value
   MM_ERR_BOUNDS = 6,         // a checked index was out of range
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// The status block of a device is 64 bytes: word 0 is the status, bytes 8..15 hold the time limit
+// of peer waits in nanoseconds (0: the default).
+__device__ __forceinline__ unsigned long long status_wait_limit_ns(const int* err) {
+  if (!err) return MM_DEFAULT_WAIT_NS;
+  const unsigned long long v = *reinterpret_cast<const volatile unsigned long long*>(err + 2);
+  return v ? v : MM_DEFAULT_WAIT_NS;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -73,13 +94,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false (and records `code`) when the limit is reached.
+// Bounded wait. Returns false (and records `code`) when the limit is reached. The limit is twice
+// that of a peer wait: a role that waits for another role which itself waits for a peer must
+// not give up first, or the status would name the wrong cause.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-  for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
+  unsigned long long t0 = 0, limit = 0;
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 128) __nanosleep(64);
-    // once any wait of the kernel has expired, the others give up at once
-    if ((i & 1023) == 1023 && err && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    if ((i & 1023) == 1023) {
+      // once any wait has expired, the others give up at once
+      if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
+      if (t0 == 0) {
+        t0 = global_timer_ns();
+        limit = 2 * status_wait_limit_ns(err);
+      } else if (global_timer_ns() - t0 > limit) {
+        break;
+      }
+    }
   }
   if (err) atomicCAS(err, 0, code);
   return false;
@@ -234,12 +266,21 @@ __device__ __forceinline__ int atom_add_release_sys(int* p, int v) {
   asm volatile("atom.add.release.sys.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
   return old;
 }
-// Wait (bounded) until *p >= target. Returns false on expiry.
+// Wait until *p >= target, for at most the device's peer-wait time limit. Returns false on expiry.
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int target, int* err) {
-  for (uint32_t i = 0; i < MM_SPIN_LIMIT; ++i) {
+  unsigned long long t0 = 0, limit = 0;
+  for (uint32_t i = 0;; ++i) {
     if (ld_acquire_sys(p) >= target) return true;
     if (i > 32) __nanosleep(100);
-    if ((i & 1023) == 1023 && err && *reinterpret_cast<volatile int*>(err) != 0) return false;
+    if ((i & 255) == 255) {
+      if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;
+      if (t0 == 0) {
+        t0 = global_timer_ns();
+        limit = status_wait_limit_ns(err);
+      } else if (global_timer_ns() - t0 > limit) {
+        break;
+      }
+    }
   }
   if (err) atomicCAS(err, 0, MM_ERR_WAIT_PEER);
   return false;

@@ -17,6 +17,8 @@ _P = c_void_p
 _SIGS = {
     "mm_read_status": (c_int, [c_int]),
     "mm_sm_count": (c_int, []),
+    "mm_status_ptr": (c_void_p, []),
+    "mm_set_peer_wait_ms": (c_int, [c_int]),
     "mm_gemm_bf16": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int, c_int64,
                              c_int, c_int, c_int, _P]),
     "mm_gemm_pair_bf16": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int, c_int64,

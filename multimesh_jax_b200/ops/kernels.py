@@ -43,6 +43,67 @@ def read_status(clear: bool = True) -> int:
     return _lib.load().mm_read_status(1 if clear else 0)
 
 
+STATUS_NAMES = {1: "a GEMM consumer gave up waiting for a TMA stage", 2: "a TMA producer gave up waiting for a free stage",
+                3: "an epilogue gave up waiting for its accumulator", 4: "an MMA lane gave up waiting for a drained accumulator",
+                5: "a wait for a peer GPU's flag ran out of time", 6: "a checked index was out of range",
+                9: "a token overflowed the capacity of an expert's receive region"}
+
+
+class StatusProbe:
+    """Non-blocking view of one device's kernel status word.
+
+    ``record()`` queues, on the current stream, a 4-byte copy of the word into pinned host
+    memory followed by an event; ``poll()`` looks at the copies whose event has fired (all of
+    them after a synchronisation when ``block``) and returns the first non-zero code it finds,
+    clearing the device word so that the next step starts clean. The host thus learns of an
+    expired bounded wait or a capacity overflow without ever stalling the stream."""
+
+    SLOTS = 16
+
+    def __init__(self, device: torch.device):
+        from ..parallel.symm import tensor_from_ptr
+        self.device = device
+        with torch.cuda.device(device):
+            ptr = _lib.load().mm_status_ptr()
+        if not ptr:
+            raise RuntimeError("the kernel library has no status block on this device")
+        self.word = tensor_from_ptr(ptr, (1,), torch.int32, device)
+        self.host = torch.zeros(self.SLOTS, dtype=torch.int32).pin_memory()
+        self.events = [None] * self.SLOTS
+        self.next = 0
+        self._pending_code = 0
+
+    def record(self) -> None:
+        i = self.next % self.SLOTS
+        if self.events[i] is not None and not self.events[i].query():
+            self.events[i].synchronize()      # the ring is full: only then wait for the oldest copy
+            self._take(i)
+        self.host[i:i + 1].copy_(self.word, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.events[i] = ev
+        self.next += 1
+
+    def _take(self, i: int) -> None:
+        code = int(self.host[i])
+        self.events[i] = None
+        if code and not self._pending_code:
+            self._pending_code = code
+
+    def poll(self, block: bool = False) -> int:
+        if block:
+            torch.cuda.synchronize(self.device)
+        for i, ev in enumerate(self.events):
+            if ev is not None and ev.query():
+                self._take(i)
+        code = self._pending_code
+        if code:
+            self._pending_code = 0
+            with torch.cuda.device(self.device):
+                read_status(clear=True)
+        return code
+
+
 # --------------------------------------------------------------------- GEMM
 _OUT_MODE = {(bf16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2, (bf16, True): 3}
 

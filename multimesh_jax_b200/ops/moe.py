@@ -40,6 +40,30 @@ def route(x2: torch.Tensor, wr: torch.Tensor, top_k: int) -> Tuple[torch.Tensor,
     return logits, topi, gates
 
 
+def select_experts(logits: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The selection rule of ``moe_route_dispatch_kernel`` restated on tensors: per choice the
+    largest logit not taken yet, ties to the lowest index; when no remaining logit compares
+    greater than -inf (all NaN or -inf) the lowest free index with a neutral logit of 0. The
+    result is always ``top_k`` distinct experts in ``[0, E)`` - the kernel stores rows into the
+    owner's memory at offsets derived from them. Returns (experts [T, k], chosen logits [T, k])."""
+    T, E = logits.shape
+    work = logits.float().clone()
+    work[torch.isnan(work)] = float("-inf")
+    idx = torch.empty(T, top_k, dtype=torch.int64)
+    val = torch.empty(T, top_k, dtype=torch.float32)
+    taken = torch.zeros(T, E, dtype=torch.bool)
+    for j in range(top_k):
+        masked = torch.where(taken, torch.full_like(work, float("-inf")), work)
+        best_v, best_i = masked.max(dim=-1)                    # max returns the first maximal index
+        none = ~(best_v > float("-inf"))
+        first_free = (~taken).float().argmax(dim=-1)
+        best_i = torch.where(none, first_free, best_i)
+        best_v = torch.where(none, torch.zeros_like(best_v), best_v)
+        idx[:, j], val[:, j] = best_i, best_v
+        taken[torch.arange(T), best_i] = True
+    return idx, val
+
+
 def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor, out=None):
     """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D]); ``out`` may be preallocated."""
     F = wgu_e.shape[1]

@@ -142,6 +142,8 @@ class PeerReshard:
         self.arena, self.topo, self.symm = arena, topo, symm
         self.slots: Dict[tuple, dict] = {}
         self.bytes = 0
+        # every pull of this object runs on the side stream, one after the other: one counter word
+        self.counter = arena.alloc_counter("PeerReshard")
         for op in plan["ops"]:
             if op["kind"] != "reshard":
                 continue
@@ -243,7 +245,8 @@ class PeerReshard:
                 done = [arena.flag_ptr(w, slot["done"][par][slot["dsts"].index(d)]) for w in writers]
                 for i in range(0, len(recs), 64):
                     last = i + 64 >= len(recs)
-                    symm.reshard_pull(recs[i:i + 64], esz, arena, done_flags=done if last else (), done_value=e)
+                    symm.reshard_pull(recs[i:i + 64], esz, arena, done_flags=done if last else (), done_value=e,
+                                       counter=self.counter)
             ev = torch.cuda.Event()
             ev.record(comm.stream)
         comm.pending.append((ev, [t for t in (src_tile, out) if t is not None]))

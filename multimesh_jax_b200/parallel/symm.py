@@ -39,6 +39,32 @@ _lib.register("mm_set_flags", c_int, [c_void_p, c_int, c_int, c_void_p])
 _lib.register("mm_wait_flags", c_int, [c_void_p, c_int, c_int, c_int, c_void_p])
 
 
+class WordAllocator:
+    """Bookkeeping of the 4-byte words at the start of an arena: the first ``NUM_COUNTERS`` are
+    CTA counters (one per launcher, handed out once, never shared), the rest are flags."""
+
+    NUM_COUNTERS = 64
+
+    def __init__(self, total_words: int):
+        self.total_words = total_words
+        self.counter_owner: Dict[int, str] = {}
+        self._next_flag = self.NUM_COUNTERS
+
+    def alloc_counter(self, owner: str) -> int:
+        index = len(self.counter_owner)
+        if index >= self.NUM_COUNTERS:
+            raise MemoryError("all CTA-counter words of the arena are taken")
+        self.counter_owner[index] = owner
+        return index
+
+    def alloc_flag(self) -> int:
+        off = self._next_flag * 4
+        self._next_flag += 1
+        if self._next_flag > self.total_words:
+            raise MemoryError("flag area exhausted")
+        return off
+
+
 class _RawCudaBuffer:
     """Exposes a raw device pointer through ``__cuda_array_interface__``."""
 
@@ -86,7 +112,7 @@ class SymmetricArena:
                 self._opened.append(out.value)
         self._offset = FLAG_BYTES
         self._named: Dict[str, Tuple[int, int]] = {}
-        self._next_flag = 64  # the first words are reserved (CTA counters)
+        self.words = WordAllocator(FLAG_BYTES // 4)
         self.epoch = 0
 
     # -- allocation (must be called in the same order with the same sizes on every rank) ----
@@ -114,16 +140,18 @@ class SymmetricArena:
 
     def alloc_flag(self) -> int:
         """Offset (bytes) of a fresh 4-byte flag in the flag area."""
-        off = self._next_flag * 4
-        self._next_flag += 1
-        if off + 4 > FLAG_BYTES:
-            raise MemoryError("flag area exhausted")
-        return off
+        return self.words.alloc_flag()
 
     def flag_ptr(self, rank: int, offset: int) -> int:
         return self.peer_base[rank] + offset
 
-    def counter_ptr(self, index: int = 0) -> int:
+    def alloc_counter(self, owner: str) -> int:
+        """Index of a zero-initialised CTA-counter word that belongs to ``owner`` alone. A pull
+        kernel counts its finished CTAs in the word it is given; two launchers whose kernels can
+        overlap on the GPU (different streams) must therefore never share one."""
+        return self.words.alloc_counter(owner)
+
+    def counter_ptr(self, index: int) -> int:
         return self.base + 4 * index
 
     def barrier(self) -> None:
@@ -228,14 +256,19 @@ def build_pull_chunks(chunks: List[dict], src_tile_shape: Sequence[int], dst_til
 
 
 def reshard_pull(records: List[List[int]], elem_size: int, arena: SymmetricArena, wait_flags: Sequence[int] = (),
-                 wait_value: int = 0, done_flags: Sequence[int] = (), done_value: int = 0, max_ctas: int = 0) -> None:
-    """Launches the pull kernel on the current stream."""
+                 wait_value: int = 0, done_flags: Sequence[int] = (), done_value: int = 0, max_ctas: int = 0,
+                 counter: Optional[int] = None) -> None:
+    """Launches the pull kernel on the current stream. ``counter`` is the caller's own CTA-counter
+    word (``arena.alloc_counter``); it is needed only with ``done_flags``, which the last CTA to
+    finish raises."""
     lib = arena.lib
+    if done_flags and counter is None:
+        raise ValueError("a pull that raises done flags needs the launcher's own counter word")
     flat = (c_int64 * (14 * len(records)))(*[x for r in records for x in r])
     waits = (c_int64 * max(1, len(wait_flags)))(*wait_flags) if wait_flags else None
     dones = (c_int64 * max(1, len(done_flags)))(*done_flags) if done_flags else None
     rc = lib.mm_reshard_pull(flat, len(records), elem_size, waits, len(wait_flags), wait_value, dones,
-                             len(done_flags), done_value, arena.counter_ptr(0), max_ctas,
+                             len(done_flags), done_value, arena.counter_ptr(counter) if done_flags else None, max_ctas,
                              torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, "mm_reshard_pull")
     K._count()

@@ -39,11 +39,12 @@ class ShardedTensor:
     sizes, mesh axes per dimension, mesh shape, device range). Only tiles of
     devices local to this process are held."""
 
-    def __init__(self, sharding: dict, tiles: Dict[int, torch.Tensor], topology: Topology, waiter=None):
+    def __init__(self, sharding: dict, tiles: Dict[int, torch.Tensor], topology: Topology, waiter=None, checker=None):
         self.sharding = sharding
         self._tiles = tiles
         self.topology = topology
         self._waiter = waiter
+        self._checker = checker     # checker(block): raises if a kernel of the producing step failed
 
     @property
     def shape(self) -> Tuple[int, ...]:
@@ -78,6 +79,8 @@ class ShardedTensor:
     def full_tensor(self) -> torch.Tensor:
         """Assembles the global value (on the first local device, or CPU)."""
         self.wait()
+        if self._checker is not None:
+            self._checker(True)     # the value is about to be read: make sure no kernel reported a failure
         topo = self.topology
         sizes = self.sharding["sizes"]
         start = self.sharding["device_start"]
@@ -181,6 +184,9 @@ class Executable:
         self._arrival: Dict[Tuple[int, int], Any] = {}
         self.launches = 0
         self._inline = len(topology.local_devices) == 1
+        # kernel status words of the local CUDA devices, read without stalling the streams
+        self._probes = {d: K.StatusProbe(topology.torch_device(d)) for d in topology.local_devices
+                        if topology.torch_device(d).type == "cuda"}
         self.donated = set(getattr(cap, "donated_inputs", ()))
         # Temporaries handed over to their last reader (task op k), which frees each one right after
         # its last use. Readers of one tile are not ordered among themselves by the dependence
@@ -341,7 +347,14 @@ class Executable:
         self._step += 1
         if not self._inline:
             # parameter tiles are rebound below: the previous step must not be reading them any more
-            self.wait()
+            status, msg = ctx.wait_all()
+            if int(status) != 0:
+                ctx.reset_error()
+                raise StepFailed(f"{self.name}: {status.name}: {msg}")
+            for probe in self._probes.values():
+                with torch.cuda.device(probe.device):
+                    probe.record()
+        self._check_kernel_status(block=False)
         ctx.open_window()
         ctx.start_timer(self.name)
         ctx.mark_profile(f"start {self.name}")
@@ -389,6 +402,9 @@ class Executable:
         ctx.stop_timer(self.name)
         ctx.close_window()
         ctx.mark_profile(f"finish {self.name}")
+        if self._probes and self._inline:
+            for d, probe in self._probes.items():
+                probe.record()      # bodies ran inline: the step's kernels are all queued
         # results
         waited = {"done": False}
 
@@ -400,6 +416,7 @@ class Executable:
             if int(status) != 0:
                 ctx.reset_error()
                 raise StepFailed(f"{self.name}: {status.name}: {msg}")
+            self._check_kernel_status(block=False)
 
         outs: List[Any] = []
         it = iter(plan["root_stores"])
@@ -409,7 +426,8 @@ class Executable:
                 outs.append(cap.output_constants[pos])
                 continue
             sid = next(it)
-            outs.append(ShardedTensor(plan["stores"][sid]["shape"], root_tiles[sid], topo, waiter))
+            outs.append(ShardedTensor(plan["stores"][sid]["shape"], root_tiles[sid], topo, waiter,
+                                      self._check_kernel_status if self._probes else None))
         return pytree.tree_unflatten(outs, cap.out_spec)
 
     # ------------------------------------------------------------------ tasks
@@ -552,11 +570,28 @@ class Executable:
             self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
 
     # ------------------------------------------------------------------ misc
+    def _check_kernel_status(self, block: bool) -> None:
+        """Raises :class:`StepFailed` when a kernel of an earlier step recorded an expired bounded
+        wait or an overflow in its device's status word. Without ``block`` only status copies that
+        have already arrived on the host are looked at (the stream is never stalled); with it the
+        device is synchronised first, so every queued step is covered."""
+        for d, probe in self._probes.items():
+            if block:
+                with torch.cuda.device(probe.device):
+                    probe.record()      # covers whatever was queued after the step's own probe
+            code = probe.poll(block)
+            if code:
+                raise StepFailed(f"{self.name}: kernel status {code} on device {d}: "
+                                 f"{K.STATUS_NAMES.get(code, 'unknown code')}")
+
     def wait(self):
+        """Blocks until every submitted task has run and the devices are idle; raises
+        :class:`StepFailed` if a task or a kernel reported an error."""
         status, msg = self.context.wait_all()
         if int(status) != 0:
             self.context.reset_error()
             raise StepFailed(f"{self.name}: {status.name}: {msg}")
+        self._check_kernel_status(block=True)
 
     def event_log(self):
         return self.context.event_log()

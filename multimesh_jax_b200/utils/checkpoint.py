@@ -11,7 +11,9 @@ layout for :class:`ShardedTensor` pytrees:
 <dir>/<leaf>.<ordinal>.pt      one tile (written by the process that owns the device)
 ```
 
-Every process writes only the tiles of its own devices; rank 0 writes the manifest. Loading
+Every process writes only the tiles of its own devices, each to a temporary name that is
+renamed into place; rank 0 writes the manifest after a barrier over all ranks, so a manifest
+on disk means that every tile it names is complete. Loading
 into the same layout reads each tile straight into place; loading into a different layout
 (other mesh shape, other device count) assembles every destination tile from the boxes that
 intersect it, reading only the files it needs.
@@ -46,16 +48,29 @@ def _replica_owner(sharding: dict, ordinal: int) -> int:
     return ordinal
 
 
+def _atomic_save(tensor: torch.Tensor, path: str) -> None:
+    tmp = f"{path}.tmp.{os.getpid()}"
+    torch.save(tensor, tmp)
+    os.replace(tmp, path)
+
+
+def _shard_size(sh: dict) -> List[int]:
+    """Tile extents of a layout (every tile of a layout has the same shape)."""
+    if "shard_size" in sh:
+        return list(sh["shard_size"])
+    lo, hi = tile_box(sh, 0)
+    return [b - a for a, b in zip(lo, hi)]
+
+
 def save(directory: str, tree: Any, *, step: Optional[int] = None, rank: Optional[int] = None) -> dict:
     """Writes ``tree`` (a pytree of :class:`ShardedTensor`, tensors and plain values). Returns
     the manifest. In one-process-per-device jobs every rank must call this."""
     os.makedirs(directory, exist_ok=True)
     leaves, spec = pytree.tree_flatten(tree, is_leaf=_is_leaf)
+    import torch.distributed as dist
+    distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
     if rank is None:
-        rank = 0
-        import torch.distributed as dist
-        if dist.is_available() and dist.is_initialized():
-            rank = dist.get_rank()
+        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
     entries: List[dict] = []
     for i, leaf in enumerate(leaves):
         name = f"leaf{i:05d}"
@@ -70,23 +85,28 @@ def save(directory: str, tree: Any, *, step: Optional[int] = None, rank: Optiona
                 fname = f"{name}.{owner}.pt"
                 tiles.append({"ordinal": o, "lo": list(lo), "hi": list(hi), "file": fname})
                 if owner == o and (start + o) in local:
-                    torch.save(local[start + o].detach().cpu(), os.path.join(directory, fname))
+                    _atomic_save(local[start + o].detach().cpu(), os.path.join(directory, fname))
             entries.append({"kind": "sharded", "dtype": sh["dtype"], "sizes": list(sh["sizes"]),
-                            "sharding": {k: sh[k] for k in ("dim_axes", "mesh_dims", "device_start", "num_devices", "key")},
+                            "sharding": dict({k: sh[k] for k in ("dim_axes", "mesh_dims", "device_start", "num_devices",
+                                                                 "key")}, shard_size=_shard_size(sh)),
                             "tiles": tiles})
         elif isinstance(leaf, torch.Tensor):
             fname = f"{name}.full.pt"
             if rank == 0:
-                torch.save(leaf.detach().cpu(), os.path.join(directory, fname))
+                _atomic_save(leaf.detach().cpu(), os.path.join(directory, fname))
             entries.append({"kind": "tensor", "file": fname})
         else:
             entries.append({"kind": "value", "value": leaf})
     manifest = {"format": FORMAT_VERSION, "step": step, "treespec": pytree.treespec_dumps(spec), "leaves": entries}
+    if distributed:
+        dist.barrier()      # every rank's tiles are in place before the manifest can appear
     if rank == 0:
         tmp = os.path.join(directory, MANIFEST + ".tmp")
         with open(tmp, "w") as f:
             json.dump(manifest, f)
         os.replace(tmp, os.path.join(directory, MANIFEST))   # the manifest appears last and atomically
+    if distributed:
+        dist.barrier()      # no rank returns (and possibly loads) before the manifest exists
     return manifest
 
 
@@ -148,6 +168,7 @@ def load(directory: str, *, like: Any = None, shardings: Optional[List[Optional[
             topo = topology
             if sh is None:
                 sh = dict(e["sharding"], dtype=e["dtype"], sizes=e["sizes"])
+                sh.setdefault("shard_size", _shard_size(sh))   # manifests written before the field existed
             if topo is None:
                 raise ValueError("load() needs `like` or `topology` to place sharded leaves")
         if list(sh["sizes"]) != list(e["sizes"]):

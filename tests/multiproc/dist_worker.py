@@ -5,6 +5,8 @@ Modes:
            checks its tiles of the loss and of the updated parameters against the eager step.
   leave  - the last rank exits cleanly between steps; the others see their next collective
            end with an error within the process-group timeout and report it as a status.
+  ckpt   - every rank saves its tiles of the updated parameters, the job reloads them (stored layout
+           and the compiled step's layout) and compares; the manifest names only complete tiles.
 """
 import datetime
 import json
@@ -62,6 +64,36 @@ def mode_step(pp, tp, dp=1):
     exe.shutdown()
 
 
+def mode_ckpt(pp, tp, directory):
+    from torch.utils import _pytree as pytree
+    from multimesh_jax_b200.utils import checkpoint
+    from multimesh_jax_b200.runtime.executable import ShardedTensor
+    rank = dist.get_rank()
+    mm, exe, step, args = build(pp, tp)
+    loss, p_mm, s_mm = exe(*args)
+    loss.wait()
+    manifest = checkpoint.save(directory, {"params": p_mm, "step": 3}, step=3)
+    # after save() returns on any rank the manifest exists and every file it names is complete
+    assert os.path.exists(os.path.join(directory, checkpoint.MANIFEST))
+    names = {t["file"] for e in manifest["leaves"] if e["kind"] == "sharded" for t in e["tiles"]}
+    assert all(os.path.exists(os.path.join(directory, n)) for n in names)
+    assert not [f for f in os.listdir(directory) if ".tmp" in f]
+    is_leaf = lambda x: isinstance(x, ShardedTensor)
+    back = checkpoint.load(directory, topology=exe.topology)
+    checked = 0
+    for got, want in zip(pytree.tree_flatten(back["params"], is_leaf=is_leaf)[0],
+                         pytree.tree_flatten(p_mm, is_leaf=is_leaf)[0]):
+        assert "shard_size" in got.sharding and list(got.sharding["shard_size"]) == list(want.sharding["shard_size"])
+        for d, tile in want.local_tiles().items():
+            torch.testing.assert_close(got.tile(d), tile, rtol=0, atol=0)
+            checked += 1
+    ok = torch.tensor([1 if checked > 0 and back["step"] == 3 else 0])
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"DIST_CKPT_OK": bool(ok.item()), "tiles_checked_rank0": checked}), flush=True)
+    exe.shutdown()
+
+
 def mode_leave(pp, tp):
     rank, world = dist.get_rank(), dist.get_world_size()
     mm, exe, step, args = build(pp, tp)
@@ -89,11 +121,13 @@ def mode_leave(pp, tp):
 
 if __name__ == "__main__":
     mode, pp, tp = sys.argv[1], int(sys.argv[2]), int(sys.argv[3])
-    dp = int(sys.argv[4]) if len(sys.argv) > 4 else 1
+    dp = int(sys.argv[4]) if len(sys.argv) > 4 and mode == "step" else 1
     timeout = datetime.timedelta(seconds=8 if mode == "leave" else 120)
     dist.init_process_group("gloo", timeout=timeout)
     if mode == "step":
         mode_step(pp, tp, dp)
+    elif mode == "ckpt":
+        mode_ckpt(pp, tp, sys.argv[4])
     else:
         mode_leave(pp, tp)
     dist.destroy_process_group()

@@ -42,3 +42,10 @@ def test_rank_leaving_between_steps_is_reported_on_the_host():
     survivors = [l for l in lines if "outcome" in l]
     assert survivors and all(l["outcome"].startswith("error") for l in survivors), lines
     assert all(l["seconds"] < 60 for l in survivors)
+
+
+def test_two_ranks_save_and_reload_a_checkpoint(tmp_path):
+    r = _run(2, "ckpt", 2, 1, str(tmp_path / "ckpt"), timeout=240)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = next(l for l in r.stdout.splitlines() if "DIST_CKPT_OK" in l)
+    assert json.loads(line)["DIST_CKPT_OK"] is True

@@ -55,3 +55,34 @@ def test_compiled_step_matches_eager_on_gpu():
         torch.testing.assert_close(a.full_tensor().float(), b.float(), rtol=2e-2, atol=2e-3)
     assert K.read_status() == 0
     exe.shutdown()
+
+
+def test_expired_kernel_wait_fails_the_step_and_the_next_step_runs():
+    """A bounded device wait that runs out during a step (here: a flag that nothing raises, with a
+    300 ms limit, queued behind the step's kernels) is reported when the step is awaited -
+    ``StepFailed`` naming the status code - and the status is cleared, so the next step is clean."""
+    from multimesh_jax_b200.parallel import symm
+    torch.manual_seed(2)
+    cfg = llama.LlamaConfig.tiny(n_layers=1, d_model=256, n_heads=2, n_kv_heads=2, d_ff=512, vocab=512)
+    B, S = 2, 128
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-3), seq_len=S, global_batch=B, microbatch_size=B)
+    params = llama.init_params(cfg, device="cuda")
+    state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S), device="cuda")
+    cos, sin = llama.rope_tables(cfg, S, "cuda")
+    mesh = mm.MultiMesh((1, 1), ("stage", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=1)
+    with mesh:
+        exe = mm.compile_function(step, (params, state, tokens, tokens, cos, sin), mesh=mesh, backend="cuda")
+    K.read_status()
+    arena = symm.SymmetricArena(1 << 20, torch.device("cuda", 0))
+    off = arena.alloc_flag()
+    loss, p1, s1 = exe(params, state, tokens, tokens, cos, sin)
+    symm.wait_flags(arena, [arena.flag_ptr(arena.rank, off)], 1, limit_ms=300)   # expires: nothing raises it
+    with pytest.raises(mm.StepFailed, match="kernel status 5"):
+        exe.wait()
+    loss2, p2, s2 = exe(params, state, tokens, tokens, cos, sin)
+    exe.wait()                                                                   # clean again
+    assert torch.isfinite(loss2.full_tensor()).all()
+    arena.close()
+    exe.shutdown()

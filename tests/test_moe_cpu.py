@@ -81,3 +81,25 @@ def test_mixtral_shape_parameter_count():
     cfg = llama.LlamaConfig.mixtral_8x7b()
     assert abs(cfg.num_params() / 1e9 - 46.7) < 0.5       # 8x7B has about 46.7 B parameters
     assert abs(cfg.active_params() / 1e9 - 12.9) < 0.5     # about 12.9 B of them touch each token
+
+
+def test_expert_selection_is_total_for_nan_and_infinite_logits():
+    """The dispatch kernel derives peer-memory offsets from the chosen experts, so the selection
+    must yield valid, distinct experts whatever the logits are."""
+    inf, nan = float("inf"), float("nan")
+    logits = torch.tensor([[0.1, 0.7, 0.7, -0.2],          # tie: lowest index first
+                           [nan, nan, nan, nan],           # nothing comparable
+                           [-inf, -inf, -inf, -inf],
+                           [nan, 0.3, -inf, nan],          # one finite logit only
+                           [inf, 1.0, inf, 0.0]])
+    idx, val = moe.select_experts(logits, 2)
+    assert idx.tolist() == [[1, 2], [0, 1], [0, 1], [1, 0], [0, 2]]
+    for row in idx.tolist():
+        assert len(set(row)) == 2 and all(0 <= e < 4 for e in row)
+    assert val[1].tolist() == [0.0, 0.0] and val[3].tolist() == [pytest.approx(0.3), 0.0]
+    # on ordinary logits the rule is torch.topk
+    torch.manual_seed(3)
+    rnd = torch.randn(64, 8)
+    idx, val = moe.select_experts(rnd, 2)
+    topv, topi = rnd.topk(2, dim=-1)
+    assert torch.equal(idx, topi) and torch.equal(val, topv)

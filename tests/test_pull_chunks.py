@@ -77,3 +77,19 @@ def test_destinations_start_pulling_from_different_sources():
                                       lambda d: 1000 * (d + 1) * ELEM, 0, ELEM)
         first_sources.append(recs[0][0] // (1000 * ELEM) - 1)
     assert sorted(first_sources) == [0, 1, 2, 3]                 # no two destinations begin at the same source
+
+
+def test_counter_words_are_never_shared_between_launchers():
+    """Every launcher of the pull kernel counts finished CTAs in a word of its own: two kernels
+    that overlap on the GPU would otherwise mix their counts and raise done flags early."""
+    import pytest
+    words = symm.WordAllocator(1 << 14)
+    owners = [f"launcher{i}" for i in range(symm.WordAllocator.NUM_COUNTERS)]
+    got = [words.alloc_counter(o) for o in owners]
+    assert len(set(got)) == len(got) and all(0 <= i < symm.WordAllocator.NUM_COUNTERS for i in got)
+    assert words.counter_owner == dict(zip(got, owners))
+    with pytest.raises(MemoryError):
+        words.alloc_counter("one too many")
+    # flags live behind the counter words and never overlap them
+    flag = words.alloc_flag()
+    assert flag >= 4 * symm.WordAllocator.NUM_COUNTERS
