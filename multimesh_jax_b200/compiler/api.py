@@ -17,6 +17,7 @@ from torch.utils import _pytree as pytree
 from .. import state
 from ..runtime.collectives import Topology
 from ..runtime.executable import Executable, ShardedTensor
+from ..runtime.wrapper import WrapperExecutable
 from ..task import MultiMesh
 from .capture import Captured, capture, make_partition
 
@@ -60,7 +61,7 @@ def _apply_shardings(cap: Captured, in_shardings, example_args) -> None:
 def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optional[MultiMesh] = None,
                      num_devices: Optional[int] = None, donate_argnums: Sequence[int] = (),
                      backend: Optional[str] = None, in_shardings=None, context=None, topology: Optional[Topology] = None,
-                     name: Optional[str] = None, config_overrides: Optional[Dict[str, Any]] = None) -> Executable:
+                     name: Optional[str] = None, config_overrides: Optional[Dict[str, Any]] = None):
     from .. import _mm_C
     mesh = mesh or MultiMesh.current()
     if num_devices is None:
@@ -92,9 +93,49 @@ def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optiona
     part = make_partition(num_devices, mesh, nmb)
     cfg = _partition_config(**(config_overrides or {}))
     plan = _mm_C.mpmd_partition(cap.graph, part, cfg)
-    exe = Executable(cap, plan, topology, context=context, name=name or getattr(fn, "__name__", "step"))
+    name = name or getattr(fn, "__name__", "step")
+    reason = bypass_reason(cap, plan, num_devices, donate_argnums, context)
+    if reason is not None:
+        exe = WrapperExecutable(cap, plan, topology, name=name, reason=reason, num_devices=num_devices)
+    else:
+        exe = Executable(cap, plan, topology, context=context, name=name)
     exe.partition = part
     return exe
+
+
+def bypass_reason(cap: Captured, plan: dict, num_devices: int, donate_argnums, context) -> Optional[str]:
+    """Why a compiled program does not need the MPMD runtime, or None when it does.
+
+    ``"fast-path"``: the plan is a single task without reshards, the program has fewer than
+    ``FAST_PATH_MAX_NODES`` operators and none of them is a marker (``mm.*``: task, microbatch
+    or sharding annotations) - ``src/pjrt_client/mm_pjrt_client.cc:587-617``.
+    ``"single-device"``: the device assignment is one device and the program has no marker and
+    no microbatch loop, so there is nothing to partition, schedule or reshard -
+    ``src/pjrt_client/mm_pjrt_client.cc:525-534``.
+    Both are switched off by ``enable_fast_path(False)`` (the differential test harness does
+    that to force every program through the partitioner), by donated arguments (in-place
+    reuse of their tiles is a service of the partitioned executable) and by an explicitly
+    given runtime context (mock runs want to see the submissions)."""
+    if not state.flags.fast_path or context is not None or donate_argnums or cap.loop_configs:
+        return None
+    g = cap.graph
+    ops = [op for op in plan["ops"] if op["kind"] in ("task", "reshard")]
+    if len(ops) != 1 or ops[0]["kind"] != "task":
+        return None
+    if any(t["name"].split(".", 1)[-1] != "global" for t in plan["templates"]):
+        return None                      # the user placed the work in a task of their own
+    node_ids = [n for t in plan["templates"] for n in t["nodes"]]
+    names = [g.node(n)["op"] for n in node_ids]
+    if any(nm.startswith("mm.") for nm in names):
+        return None
+    if any(len(ax) > 0 for sid in plan["param_stores"] + plan["root_stores"] if sid >= 0
+           for ax in plan["stores"][sid]["shape"]["dim_axes"]):
+        return None                      # a sharded argument or result: the partitioned path owns layouts
+    if len(names) < FAST_PATH_MAX_NODES:
+        return "fast-path"
+    if num_devices == 1:
+        return "single-device"
+    return None
 
 
 class JitFunction:

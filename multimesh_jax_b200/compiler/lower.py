@@ -127,9 +127,11 @@ class TemplateProgram:
                 x = env[ins.args]
                 env[ins.outs[0]] = x.narrow(dim, scalars[0] // shards, size // shards)
             elif kind == 4:  # all-reduce over mesh axes
-                axes, scale = ins.extra
-                y = ctx.all_reduce(env[ins.args], axes, ins.node_id)
-                env[ins.outs[0]] = y if scale == 1.0 else y * scale
+                axes, scale, in_place = ins.extra
+                y = ctx.all_reduce(env[ins.args], axes, ins.node_id, in_place=in_place)
+                if scale != 1.0:
+                    y = y.mul_(scale) if in_place else y * scale
+                env[ins.outs[0]] = y
             elif kind == 5:  # local reshard
                 src, dst = ins.extra
                 env[ins.outs[0]] = ctx.spmd_reshard(env[ins.args], src, dst, ins.node_id)
@@ -258,7 +260,8 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             instrs.append(Instr(3, None, n["inputs"][0], None, n["outputs"], None, nid, (dim, size, shards)))
         elif op == "mm.all_reduce":
             axes = json.loads(attrs["axes"])
-            instrs.append(Instr(4, None, n["inputs"][0], None, n["outputs"], None, nid, (axes, float(attrs["scale"]))))
+            instrs.append(Instr(4, None, n["inputs"][0], None, n["outputs"], None, nid,
+                                (axes, float(attrs["scale"]), attrs.get("in_place") == "1")))
         elif op == "mm.spmd_reshard":
             from .. import _mm_C
             src = _mm_C.sharded_shape_from_json(attrs["from"])
@@ -285,7 +288,7 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             if len(rd) != 1 or rd[0].kind != 4 or v in outputs_set:
                 continue
             ar = rd[0]
-            axes, scale = ar.extra
+            axes, scale, _ = ar.extra
             ins.kind = 7
             ins.extra = (axes, scale, opname == "mm_ops.linear_dgrad.default")
             ins.outs = ar.outs

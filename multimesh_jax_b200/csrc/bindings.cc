@@ -136,6 +136,7 @@ struct Compiler {
     else if (name == "microbatch_loop_canonicalizer") changed = MicrobatchLoopCanonicalizer(s);
     else if (name == "simple_loop_increment_coloring") changed = SimpleLoopIncrementColoring(s);
     else if (name == "coloring") changed = Coloring(s);
+    else if (name == "unused_loop_output_remover") changed = UnusedLoopOutputRemover(s);
     else if (name == "logical_sharding_propagation") changed = LogicalShardingPropagation(s);
     else if (name == "hoist_loop_convert") changed = HoistLoopConvert(s);
     else if (name == "parameter_replication") changed = ParameterReplication(s);
@@ -334,6 +335,7 @@ PYBIND11_MODULE(_mm_C, m) {
       .def("add_task", [](Partition& p, const std::string& json, bool backprop) {
         return p.Add(TaskOptions::FromJson(Json::parse(json)), backprop).name;
       })
+      .def("recolor", &Partition::Recolor)
       .def("compute_scope_color", &Partition::ComputeScopeColor)
       .def("has", &Partition::Has)
       .def("color", [](const Partition& p, const std::string& name) {

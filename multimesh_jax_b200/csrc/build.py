@@ -128,8 +128,11 @@ def build_host(force: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, srcs))
-    _run([cxx, "-shared", "-o", str(target), *map(str, objs), *extra,
+    # link beside the target and rename: a process that has the old module mapped keeps its file
+    tmp = target.with_name(target.name + ".tmp")
+    _run([cxx, "-shared", "-o", str(tmp), *map(str, objs), *extra,
           "-L", str(cuda / "lib64"), "-lcudart", "-Wl,-rpath," + str(cuda / "lib64"), "-pthread"])
+    os.replace(tmp, target)
     return target
 
 

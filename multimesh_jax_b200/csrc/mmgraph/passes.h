@@ -64,6 +64,7 @@ bool ConstantOutputCopy(CompileState& s);
 bool RepeatedOutputCopy(CompileState& s);
 bool MicrobatchLoopCanonicalizer(CompileState& s);
 bool SimpleLoopIncrementColoring(CompileState& s);
+bool UnusedLoopOutputRemover(CompileState& s);
 bool Coloring(CompileState& s);
 bool LogicalShardingPropagation(CompileState& s);
 bool HoistLoopConvert(CompileState& s);

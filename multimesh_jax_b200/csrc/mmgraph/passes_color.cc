@@ -264,6 +264,34 @@ bool MicrobatchLoopCanonicalizer(CompileState& s) {
   return changed;
 }
 
+// Loop-carried sums that nobody reads after the loop (a gradient the optimizer ignores, an
+// auxiliary output the caller drops) are removed together with the loop work that only fed
+// them (src/pjrt_client/mpmd_unused_loop_output_remover.cc:39). It runs after colouring, as
+// in the reference: colouring may have cloned or rewired users, so an accumulator that had a
+// reader at capture time can be dead by now.
+bool UnusedLoopOutputRemover(CompileState& s) {
+  Graph& g = *s.graph;
+  const auto users = g.ComputeUsers();
+  std::set<int> outputs(g.outputs.begin(), g.outputs.end());
+  int removed_outputs = 0;
+  for (auto& n : g.nodes) {
+    if (n.dead || n.op != "mm.accumulate" || n.loop < 0) continue;
+    bool used = false;
+    for (int o : n.outputs) used = used || outputs.count(o) || !users[o].empty();
+    if (used) continue;
+    n.dead = true;
+    ++removed_outputs;
+  }
+  if (!removed_outputs) return false;
+  std::vector<int> keep;
+  for (int id : g.order) if (!g.node(id).dead) keep.push_back(id);
+  g.order = keep;
+  const int swept = g.DeadCodeElimination();
+  s.log.push_back("unused_loop_output_remover: dropped " + std::to_string(removed_outputs) + " loop outputs and " +
+                  std::to_string(swept) + " operators that only fed them");
+  return true;
+}
+
 bool SimpleLoopIncrementColoring(CompileState& s) {
   if (!s.config.loop_increment_color) return false;
   Graph& g = *s.graph;

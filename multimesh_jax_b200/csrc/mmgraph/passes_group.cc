@@ -200,7 +200,11 @@ bool ComputationFusion(CompileState& s, FusionMode mode) {
       switch (mode) {
         case FusionMode::kMatchingColor: return a.color == b.color;
         case FusionMode::kOriginalColor:
-          return (ca.original.empty() ? ca.name : ca.original) == (cb.original.empty() ? cb.name : cb.original);
+          // colours that descend from one user-visible task (recolouring and regrouping split it);
+          // descendants always share the parent's devices, the test only guards against a table
+          // that was edited by hand
+          return (ca.original.empty() ? ca.name : ca.original) == (cb.original.empty() ? cb.name : cb.original) &&
+                 ca.devices == cb.devices && ca.backprop == cb.backprop;
         case FusionMode::kMatchingDevices:
           return a.region == 1 && ca.devices == cb.devices && ca.backprop == cb.backprop;
       }

@@ -56,6 +56,7 @@ Plan MpmdPartition(Graph& g, Partition& part, const PartitionConfig& cfg, std::v
   Dump(s, "after_mpmd_preprocess", &counter);
   RunPass(s, "simple_loop_increment_coloring", [&] { return SimpleLoopIncrementColoring(s); }, &counter);
   RunPass(s, "coloring", [&] { return Coloring(s); }, &counter);
+  RunPass(s, "unused_loop_output_remover", [&] { return UnusedLoopOutputRemover(s); }, &counter);
   RunPass(s, "logical_sharding_propagation", [&] { return LogicalShardingPropagation(s); }, &counter);
   RunPass(s, "hoist_loop_convert", [&] { return HoistLoopConvert(s); }, &counter);
   RunPass(s, "parameter_replication", [&] { return ParameterReplication(s); }, &counter);
@@ -71,8 +72,10 @@ Plan MpmdPartition(Graph& g, Partition& part, const PartitionConfig& cfg, std::v
   if (recolored) {
     s.groups.clear();
     RunPass(s, "computation_grouper_2", [&] { return ComputationGrouper(s); }, &counter);
-    RunPass(s, "computation_fusion_matching_color_2", [&] { return ComputationFusion(s, FusionMode::kMatchingColor); }, &counter);
   }
+  // after the regrouping: call sites that descend from the same user task fuse again where the
+  // dependencies allow it (src/pjrt_client/mpmd_partition.cc:946)
+  RunPass(s, "computation_fusion_original_color", [&] { return ComputationFusion(s, FusionMode::kOriginalColor); }, &counter);
   RunPass(s, "split_critical_path", [&] { return SplitCriticalPath(s); }, &counter);
   std::string schedule = g.loops.empty() ? "" : g.loops[0].schedule;
   if (!EnforceBijectiveTasks(schedule))

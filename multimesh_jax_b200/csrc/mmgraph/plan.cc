@@ -396,6 +396,45 @@ Plan BuildPlan(CompileState& s) {
     plan.ops = reordered;
   }
 
+  // ---------------------------------------------------------------- in-place collectives
+  // A task outside the loop that is nothing but an all-reduce of one of its inputs (the
+  // once-per-step reduction of a gradient accumulator) writes its result over that input when
+  // nothing else reads the input: the output store reuses the input's buffer and the runtime
+  // reduces in place (src/pjrt_client/mpmd_inplace_collectives.cc:20-76).
+  {
+    std::vector<int> readers(plan.stores.size(), 0), writers(plan.stores.size(), 0);
+    for (const PlanOp& op : plan.ops) {
+      if (op.kind == PlanOp::TASK) {
+        for (int sid : op.inputs) ++readers[sid];
+        for (int sid : op.outputs) ++writers[sid];
+      } else if (op.kind == PlanOp::RESHARD) {
+        ++readers[op.src_store];
+        ++writers[op.dst_store];
+      }
+    }
+    int count = 0;
+    for (const PlanOp& op : plan.ops) {
+      if (op.kind != PlanOp::TASK || op.loop) continue;
+      const TaskTemplate& t = plan.templates[op.task_template];
+      int reduce = -1, others = 0;
+      for (int id : t.nodes) {
+        const Node& n = g.node(id);
+        if (n.op == "mm.all_reduce") reduce = reduce < 0 ? id : -2;
+        else if (n.op != "mm.accumulate" && n.op != "mm.relayout" && n.op.rfind("mm.marker", 0) != 0) ++others;
+      }
+      if (reduce < 0 || others > 0 || t.inputs.size() != 1 || t.outputs.size() != 1) continue;
+      const int in_sid = op.inputs[0], out_sid = op.outputs[0];
+      const Store& in = plan.stores[in_sid];
+      Store& out = plan.stores[out_sid];
+      if (in.kind != Store::TEMP || out.kind != Store::TEMP || in.alias_of >= 0 || out.alias_of >= 0) continue;
+      if (readers[in_sid] != 1 || writers[out_sid] != 1 || !(in.shape == out.shape)) continue;
+      out.alias_of = in_sid;
+      g.node(reduce).attrs["in_place"] = "1";
+      ++count;
+    }
+    plan.stats["in_place_collectives"] = std::to_string(count);
+  }
+
   // ---------------------------------------------------------------- buffer names
   // last use of every store in op order; reshards tick the clock twice so that a buffer
   // released by a reshard is not handed out again immediately
@@ -419,6 +458,9 @@ Plan BuildPlan(CompileState& s) {
     }
   }
   for (int sid : plan.root_stores) if (sid >= 0) last_use[sid] = 1 << 30;
+  // a store that reuses another temporary's buffer keeps that buffer alive for its own lifetime
+  for (auto& st : plan.stores)
+    if (st.kind == Store::TEMP && st.alias_of >= 0) last_use[st.alias_of] = std::max(last_use[st.alias_of], last_use[st.id]);
   {
     std::map<std::string, std::vector<std::pair<int, std::string>>> pools;  // shape key -> (free-at clock, name)
     std::vector<int> temps;
@@ -427,6 +469,10 @@ Plan BuildPlan(CompileState& s) {
     int fresh = 0;
     for (int sid : temps) {
       Store& st = plan.stores[sid];
+      if (st.alias_of >= 0) {           // in-place result: the name of the buffer it overwrites
+        st.name = plan.stores[st.alias_of].name;
+        continue;
+      }
       auto& pool = pools[st.shape.Key()];
       std::string name;
       for (size_t i = 0; i < pool.size(); ++i)

@@ -17,7 +17,7 @@ live in the symmetric arena, one pair per distinct size.
 from __future__ import annotations
 
 from ctypes import c_float, c_int, c_int64, c_void_p
-from typing import Dict, Sequence, Tuple
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -64,7 +64,7 @@ class PeerGroupComm:
                 and n % (16 * self.g) == 0)
 
     # ------------------------------------------------------------------
-    def all_reduce(self, x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    def all_reduce(self, x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         a, g, me = self.arena, self.g, self.me
         x = x.contiguous()
         nbytes = x.numel() * x.element_size()
@@ -79,7 +79,8 @@ class PeerGroupComm:
         _lib.check(rc, "mm_reduce_pull")
         K._count()
         self.barrier()                                    # every member's share is reduced
-        out = torch.empty_like(x)
+        if out is None:
+            out = torch.empty_like(x)                     # else in place: x was staged above, its buffer is free
         for i, r in enumerate(self.ranks):                # all-gather half: pull each owner's share
             one = (c_int64 * 1)(s_red.ptr(r) + i * share)
             rc = K_lib.mm_reduce_pull(one, 1, out.data_ptr() + i * share, share, x.element_size(), 1.0, stream)

@@ -236,7 +236,10 @@ class DeviceCtx:
         mine = [p.to(self.torch_device) if p.device != self.torch_device else p for p in mine]
         return torch.cat(mine, dim=0), [int(p.shape[0]) for p in mine]
 
-    def all_reduce(self, x: torch.Tensor, axes: Sequence[int], key) -> torch.Tensor:
+    def all_reduce(self, x: torch.Tensor, axes: Sequence[int], key, in_place: bool = False) -> torch.Tensor:
+        """Sum of ``x`` over the devices that differ from this one along ``axes``. With
+        ``in_place`` (the planner found that nothing else reads the operand: the once-per-step
+        reduction of a gradient accumulator) the result overwrites ``x``'s buffer."""
         me = self.device - self.device_start
         group = mesh_group(me, self.mesh_dims, list(axes))
         if len(group) == 1:
@@ -245,16 +248,22 @@ class DeviceCtx:
             if self.peer_comm is not None:
                 comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
                 if comm.supports(x):
-                    return comm.all_reduce(x)
+                    return comm.all_reduce(x, out=x if in_place and x.is_contiguous() else None)
             import torch.distributed as dist
             pg = self.topology.process_group([self.device_start + o for o in group])
-            out = x.contiguous().clone()
+            out = x if in_place and x.is_contiguous() else x.contiguous().clone()
             dist.all_reduce(out, group=pg)
             return out
         parts = self._exchange(("ar", key), group, x)
         acc = parts[0].float() if x.dtype in (torch.bfloat16, torch.float16) else parts[0].clone()
         for p in parts[1:]:
             acc = acc + (p.float() if acc.dtype != p.dtype else p)
+        if in_place:
+            # every member has read the others' tensors (the exchange above returns after all
+            # members arrived); wait for all of them to finish summing before overwriting
+            self.rendezvous.exchange((self.key_prefix, "ar-done", key, tuple(group)), group, me, None)
+            x.copy_(acc.to(x.dtype))
+            return x
         return acc.to(x.dtype)
 
     def linear_all_reduce(self, x: torch.Tensor, w: torch.Tensor, axes: Sequence[int], is_dgrad: bool, key

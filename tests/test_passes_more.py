@@ -154,3 +154,114 @@ def test_loop_dependent_task_alternates_between_submeshes_and_feeds_a_fixed_task
     back = [r for r in _ops(plan, "reshard") if stores[r["src_store"]]["shape"]["device_start"] == 2
             and stores[r["dst_store"]]["shape"]["device_start"] == 0]
     assert len(back) == 2
+
+
+# ---------------------------------------------------------------------------- fusion by original colour
+def test_fusion_by_original_colour_rejoins_call_sites_of_one_user_task():
+    """Two call sites whose colours differ only because one was recoloured (``s0`` and its
+    descendant ``s0_late``) are not fused by the matching-colour round but are by the
+    original-colour round that follows the regrouping (src/pjrt_client/mpmd_partition.cc:946);
+    a pair whose fusion would contradict the dependencies stays apart."""
+    from test_passes import G, task_json
+    b = G(2)
+    x, y = b.inp("x", [4]), b.inp("y", [4])
+    b.part.add_task(task_json("s0", [0]), False)
+    late = b.part.recolor("s0", "s0_late")
+    assert b.part.color(late)["original"] == "s0"
+    a = b.op("aten.relu.default", [x], [4], task=task_json("s0", [0]))
+    m = b.op("aten.gelu.default", [y], [4], task=task_json("s1", [1]))
+    c = b.op("aten.neg.default", [a], [4], color=late)
+    e = b.op("aten.add.Tensor", [c, m], [4], task=task_json("s1", [1]))
+    b.g.set_outputs([e])
+    comp = b.compiler()
+    comp.run("coloring")
+    comp.run("computation_grouper")
+    comp.run("computation_fusion_matching_color")
+    assert [(g["color"], g["nodes"]) for g in comp.groups()] == [("s0", [0]), ("s0_late", [2]), ("s1", [1, 3])]
+    assert comp.run("computation_fusion_original_color")
+    assert [(g["color"], g["nodes"]) for g in comp.groups()] == [("s0", [0, 2]), ("s1", [1, 3])]
+    assert b.g.node(2)["color"] == "s0"
+
+    # s0 -> s1 -> s0_late: the middle task depends on the first and feeds the last; no fusion
+    b = G(2)
+    x = b.inp("x", [4])
+    b.part.add_task(task_json("s0", [0]), False)
+    late = b.part.recolor("s0", "s0_late")
+    a = b.op("aten.relu.default", [x], [4], task=task_json("s0", [0]))
+    m = b.op("aten.gelu.default", [a], [4], task=task_json("s1", [1]))
+    c = b.op("aten.neg.default", [m], [4], color=late)
+    b.g.set_outputs([c])
+    comp = b.compiler()
+    comp.run("coloring")
+    comp.run("computation_grouper")
+    assert not comp.run("computation_fusion_original_color")
+    assert len(comp.groups()) == 3
+
+
+# ---------------------------------------------------------------------------- unused loop outputs
+def test_unused_loop_output_is_removed_with_the_work_that_only_fed_it():
+    from test_passes import G, task_json
+    b = G(1)
+    b.g.add_loop(json.dumps({"id": 0, "num_microbatches": 2, "slice_dim": 0, "size": 2, "schedule": "gpipe"}))
+    x = b.inp("x", [4, 8])
+    xs = b.op("mm.microbatch_slice.default", [x], [2, 8], loop=0, args=[0, 2, 0])
+    h = b.op("aten.relu.default", [xs], [2, 8], loop=0, task=task_json("t", [0]))
+    used = b.op("aten.sum.default", [h], [], loop=0, task=task_json("t", [0]))
+    aux = b.op("aten.exp.default", [h], [2, 8], loop=0, task=task_json("t", [0]))       # feeds only the dropped output
+    aux_sum = b.op("aten.sum.default", [aux], [], loop=0, task=task_json("t", [0]))
+    out_used = b.op("mm.microbatch_out.default", [used], [], loop=0, args=[0, ""])
+    out_dropped = b.op("mm.microbatch_out.default", [aux_sum], [], loop=0, args=[0, ""])
+    b.g.set_outputs([out_used])
+    comp = b.compiler()
+    comp.run("microbatch_loop_canonicalizer")
+    comp.run("coloring")
+    assert comp.run("unused_loop_output_remover")
+    dead = {i for i in range(7) if b.g.node(i)["dead"]}
+    assert dead == {b.g.value(aux)["producer"], b.g.value(aux_sum)["producer"], b.g.value(out_dropped)["producer"]}
+    assert any("dropped 1 loop outputs and 2 operators" in line for line in comp.log())
+    assert not comp.run("unused_loop_output_remover")          # nothing left to drop
+
+
+# ---------------------------------------------------------------------------- in-place collectives
+def test_hoisted_gradient_reduction_reuses_the_accumulator_buffer():
+    """The once-per-step all-reduce of a gradient accumulator is a task of its own whose only
+    input dies there: its output store takes the accumulator's buffer and the all-reduce node is
+    marked in-place (src/pjrt_client/mpmd_inplace_collectives.cc:20-76). Numerics are unchanged."""
+    import torch
+    import multimesh_jax_b200 as mm
+    from multimesh_jax_b200.models import llama
+    torch.manual_seed(0)
+    cfg = llama.LlamaConfig.tiny(n_layers=1, n_heads=2, n_kv_heads=2, d_model=32, d_ff=48, vocab=64)
+    cfg.dtype = torch.float32
+    B, S = 8, 8
+    params = llama.init_params(cfg)
+    state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=4)
+    mesh = mm.MultiMesh((1, 2, 1), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=1)
+    args = (params, state, tokens, tokens, cos, sin)
+    with mesh:
+        exe = mm.compile_function(step, args, mesh=mesh, backend="cpu")
+    plan, g = exe.plan, exe.cap.graph
+    n_inplace = int(plan["stats"]["in_place_collectives"])
+    assert n_inplace > 0
+    marked = [n for t in plan["templates"] for n in t["nodes"]
+              if g.node(n)["op"] == "mm.all_reduce" and g.node(n)["attrs"].get("in_place") == "1"]
+    assert len(marked) == n_inplace
+    aliased = [st for st in plan["stores"] if st["kind"] == "TEMP" and st["alias_of"] >= 0]
+    assert len(aliased) == n_inplace
+    for st in aliased:
+        src = plan["stores"][st["alias_of"]]
+        assert src["name"] == st["name"] and src["shape"]["key"] == st["shape"]["key"]
+        assert exe.buffer_of[st["id"]] == exe.buffer_of[src["id"]]
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(*args)
+    loss, p_mm, _ = exe(*args)
+    from torch.utils import _pytree as pytree
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, r in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        torch.testing.assert_close(a.full_tensor(), r, rtol=1e-3, atol=2e-4)
+    assert not exe.context.hazard_report()        # every conflicting pair of accesses is ordered
+    exe.shutdown()

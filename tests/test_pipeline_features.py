@@ -146,15 +146,59 @@ def test_recomputation_between_tasks_keeps_results():
     exe.shutdown()
 
 
-def test_fast_path_runs_tiny_functions_eagerly():
+def test_fast_path_runs_tiny_functions_without_the_mpmd_runtime():
+    """One small task without markers is dispatched to the wrapper executable: no task-graph
+    context exists, nothing is submitted, and the result is the plain function's. With the fast
+    path switched off the same function goes through the partitioned executable."""
+    from multimesh_jax_b200.runtime.wrapper import WrapperExecutable
+
     def tiny(a, b):
         return a * 2 + b
     a, b = torch.ones(4), torch.arange(4.0)
+    before = WrapperExecutable.total_calls
     with mm.enable_fast_path(True):
+        exe = mm.compile_function(tiny, (a, b), num_devices=2, backend="cpu")
+        assert isinstance(exe, WrapperExecutable) and exe.reason == "fast-path" and exe.context is None
+        out = exe(a, b)
         f = mm.mjit(tiny, backend="cpu")
-        out = f(a, b)
-    got = out.full_tensor() if isinstance(out, mm.ShardedTensor) else out
-    assert torch.equal(got, a * 2 + b)
+        out2 = f(a, b)
+    assert WrapperExecutable.total_calls == before + 2
+    assert isinstance(out, mm.ShardedTensor) and sorted(out.local_tiles()) == [0, 1]     # replicated on the assignment
+    assert torch.equal(out.full_tensor(), a * 2 + b) and torch.equal(out2.full_tensor(), a * 2 + b)
+    with mm.enable_fast_path(False):
+        slow = mm.compile_function(tiny, (a, b), num_devices=2, backend="cpu")
+    assert isinstance(slow, mm.Executable) and slow.context is not None
+    got = slow(a, b)
+    assert torch.equal(got.full_tensor(), a * 2 + b)
+    assert slow.launches > 0 and WrapperExecutable.total_calls == before + 2
+    slow.shutdown()
+
+
+def test_single_device_programs_without_markers_bypass_the_mpmd_runtime():
+    """A device assignment of one device and nothing to partition: the wrapper runs the captured
+    graph even when it is larger than the fast-path limit; an explicit task, a microbatch loop
+    or a donated argument keeps the partitioned executable."""
+    from multimesh_jax_b200.runtime.wrapper import WrapperExecutable
+
+    def big(x):
+        for i in range(30):
+            x = torch.tanh(x) + i
+        return x.sum()
+    x = torch.randn(8)
+    exe = mm.compile_function(big, (x,), num_devices=1, backend="cpu")
+    assert isinstance(exe, WrapperExecutable) and exe.reason == "single-device"
+    torch.testing.assert_close(exe(x).full_tensor(), big(x))
+    # the same program on two devices is partitioned (one task, replicated)
+    two = mm.compile_function(big, (x,), num_devices=2, backend="cpu")
+    assert isinstance(two, mm.Executable)
+    torch.testing.assert_close(two(x).full_tensor(), big(x))
+    two.shutdown()
+
+    def tasked(x):
+        return mm.task(lambda t: t * 2, name="dbl", devices=[0])(x).sum()
+    assert isinstance(mm.compile_function(tasked, (x,), num_devices=1, backend="cpu"), mm.Executable)
+    donated = mm.compile_function(big, (x,), num_devices=1, backend="cpu", donate_argnums=(0,))
+    assert isinstance(donated, mm.Executable)
 
 
 def test_zero_arguments_option_zeroes_hoisted_parameter_casts():
