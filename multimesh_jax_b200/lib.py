@@ -90,13 +90,18 @@ def with_sharding_constraint(x: Any, spec: Sequence[AxisSpec]):
     return pytree.tree_map(one, x)
 
 
-def relayout(x: Any, spec: Sequence[AxisSpec]):
+def relayout(x: Any, spec: Sequence[AxisSpec], grad_spec: Optional[Sequence[AxisSpec]] = None):
     """A layout change point: the result equals ``x`` but is laid out as ``spec`` says (same
     conventions as :func:`with_sharding_constraint`; all ``None`` = replicated), while ``x``
     itself keeps the layout it has. Where the two differ the compiled task gathers or slices
     at this point. Typical use: parameters stored sharded over the data-parallel ranks
     (``with_sharding_constraint(w, (..., "fsdp"))``) and gathered once per step before the
-    microbatch loop (``relayout(w, (..., None))``)."""
+    microbatch loop (``relayout(w, (..., None))``).
+
+    ``grad_spec`` gives the layout of the cotangent that flows back through this point (the
+    layout ``x`` has, normally): the backward pass then changes layout at the mirrored point,
+    e.g. the all-gather of a sequence-sharded activation in front of a tensor-parallel
+    projection turns into the reduce-scatter of that activation's gradient."""
     if should_ignore_transforms():
         return x
     from torch.utils import _pytree as pytree
@@ -106,6 +111,8 @@ def relayout(x: Any, spec: Sequence[AxisSpec]):
         if not isinstance(t, torch.Tensor):
             return t
         payload = {"axes": _canonical_axes(spec, t.dim()), "logical": bool(state.flags.autoshard)}
+        if grad_spec is not None:
+            payload["grad_axes"] = _canonical_axes(grad_spec, t.dim())
         return torch.ops.mm.marker(t, "Relayout", _json.dumps(payload))
 
     return pytree.tree_map(one, x)

@@ -43,6 +43,12 @@ def _marker_setup_context(ctx, inputs, output):
 def _marker_backward(ctx, grad):
     if ctx.kind in _SELF_TRANSPOSING:
         return torch.ops.mm.marker(grad, ctx.kind, ctx.payload), None, None
+    if ctx.kind == "Relayout" and ctx.payload:
+        # a layout change point with a stated cotangent layout is mirrored in the backward pass
+        p = json.loads(ctx.payload)
+        if "grad_axes" in p:
+            back = {"axes": p["grad_axes"], "logical": p.get("logical", True), "grad_axes": p["axes"]}
+            return torch.ops.mm.marker(grad, "Relayout", json.dumps(back)), None, None
     return grad, None, None
 
 
