@@ -150,6 +150,20 @@ class TemplateProgram:
                 x, w = _materialize(ins.args, env, ctx)
                 y = ctx.linear_all_reduce(x, w, axes, is_dgrad, ins.node_id)
                 env[ins.outs[0]] = y if scale == 1.0 else y * scale
+            elif kind == 9:  # reduce-scatter of a partial result
+                axes, scale, dim, src, dst = ins.extra
+                y = ctx.reduce_scatter(env[ins.args], axes, dim, src, dst, ins.node_id)
+                env[ins.outs[0]] = y if scale == 1.0 else y.mul_(scale)
+            elif kind == 10:  # linear whose partial result is reduce-scattered: one fused kernel
+                axes, scale, is_dgrad, dim, src, dst = ins.extra
+                x, w = _materialize(ins.args, env, ctx)
+                y = ctx.linear_reduce_scatter(x, w, axes, is_dgrad, dim, src, dst, ins.node_id)
+                env[ins.outs[0]] = y if scale == 1.0 else y.mul_(scale)
+            elif kind == 11:  # all-gather of the row-sharded activation fused into the linear that reads it
+                is_dgrad, axes, dim, src, dst, gathered_vid, x_vid, w_vid = ins.extra
+                y, full = ctx.all_gather_linear(env[x_vid], env[w_vid], is_dgrad, axes, dim, src, dst, ins.node_id)
+                env[gathered_vid] = full
+                env[ins.outs[0]] = y
             # free values whose last use was this instruction (keeps peak memory low)
             dead = self._last_use.get(idx)
             if dead:
@@ -267,8 +281,35 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             src = _mm_C.sharded_shape_from_json(attrs["from"])
             dst = _mm_C.sharded_shape_from_json(attrs["to"])
             instrs.append(Instr(5, None, n["inputs"][0], None, n["outputs"], None, nid, (src, dst)))
+        elif op == "mm.reduce_scatter":
+            from .. import _mm_C
+            src = _mm_C.sharded_shape_from_json(attrs["from"])
+            dst = _mm_C.sharded_shape_from_json(attrs["to"])
+            instrs.append(Instr(9, None, n["inputs"][0], None, n["outputs"], None, nid,
+                                (json.loads(attrs["axes"]), float(attrs["scale"]), int(attrs["dim"]), src, dst)))
         else:
             raise NotImplementedError(f"no lowering for compiler-generated op {op}")
+    # identity-like instructions (layout markers, accumulate markers) only rename a value: readers
+    # take the operand directly, so that the fusions below see producer and consumer side by side
+    if not single_device:
+        outputs_set = set(template["outputs"])
+        rename: Dict[int, int] = {}
+        kept: List[Instr] = []
+        tail: List[Instr] = []
+        for ins in instrs:
+            if rename:
+                if ins.kind in (0, 6):
+                    ins.args = _remap(ins.args, rename)
+                    ins.kwargs = _remap(ins.kwargs, rename)
+                elif isinstance(ins.args, int) and ins.args in rename:
+                    ins.args = rename[ins.args]
+            if ins.kind == 1 and g.node(ins.node_id)["op"] != "mm.accumulate":
+                rename[ins.outs[0]] = ins.args
+                if ins.outs[0] in outputs_set:
+                    tail.append(ins)        # still defines a task output: bound at the end of the program
+                continue
+            kept.append(ins)
+        instrs = kept + tail
     # fuse "linear -> all-reduce of its partial result" into one GEMM+collective kernel
     if not single_device:
         readers: Dict[int, List[Instr]] = {}
@@ -285,14 +326,73 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
                 continue
             v = ins.outs[0]
             rd = readers.get(v, [])
-            if len(rd) != 1 or rd[0].kind != 4 or v in outputs_set:
+            if len(rd) != 1 or rd[0].kind not in (4, 9) or v in outputs_set:
                 continue
             ar = rd[0]
-            axes, scale, _ = ar.extra
-            ins.kind = 7
-            ins.extra = (axes, scale, opname == "mm_ops.linear_dgrad.default")
+            is_dgrad = opname == "mm_ops.linear_dgrad.default"
+            if ar.kind == 4:
+                axes, scale, _ = ar.extra
+                ins.kind = 7
+                ins.extra = (axes, scale, is_dgrad)
+            else:
+                axes, scale, dim, src, dst = ar.extra
+                # the scattered dimension must be one of the row dimensions of the product
+                wv = g.value(g.node(ins.node_id)["inputs"][1])
+                n_rows_dims = len(g.value(v)["shape"]) - ((len(wv["shape"]) - 1) if not is_dgrad else 1)
+                if dim >= n_rows_dims:
+                    continue
+                ins.kind = 10
+                ins.extra = (axes, scale, is_dgrad, dim, src, dst)
             ins.outs = ar.outs
             removed.add(id(ar))
+        if removed:
+            instrs = [i for i in instrs if id(i) not in removed]
+        # fuse "all-gather of a row-sharded activation -> linear" into one kernel that also
+        # returns the gathered activation (the backward pass needs it for the weight gradient)
+        removed = set()
+        position = {id(ins): k for k, ins in enumerate(instrs)}
+        for ins in instrs:
+            if ins.kind != 5:
+                continue
+            gattrs = g.node(ins.node_id)["attrs"]
+            if "gather_dim" not in gattrs:
+                continue
+            gv = ins.outs[0]
+            rd = readers.get(gv, [])
+            live = sorted((r for r in rd if id(r) in position), key=lambda r: position[id(r)])
+            def_pos = {v: position[id(i2)] for i2 in instrs for v in (i2.outs or ()) if id(i2) in position}
+            first, ids = None, None
+            task_inputs = set(template["inputs"])
+            for k_r, r in enumerate(live):
+                if r.kind != 0 or r.slots is not None:
+                    continue
+                if g.node(r.node_id)["op"] not in ("mm_ops.linear.default", "mm_ops.linear_dgrad.default"):
+                    continue
+                r_ids = _tensor_ids_in_order(r.args, r.kwargs)
+                if len(r_ids) != 2 or r_ids[0] != gv or r_ids[1] == gv:
+                    continue
+                # a later reader can take the first reader's place when its other operand exists
+                # from the start of the task (a weight)
+                if k_r > 0 and r_ids[1] not in task_inputs and def_pos.get(r_ids[1], 1 << 30) > position[id(live[0])]:
+                    continue
+                first, ids = r, r_ids
+                break
+            if first is None:
+                continue
+            opname = g.node(first.node_id)["op"]
+            if first is not live[0]:
+                instrs.remove(first)
+                instrs.insert(instrs.index(live[0]), first)
+                position = {id(i2): k2 for k2, i2 in enumerate(instrs)}
+            dim = int(gattrs["gather_dim"])
+            if dim >= len(g.value(gv)["shape"]) - 1:
+                continue                                  # only row dimensions of the activation
+            src, dst = ins.extra
+            first.kind = 11
+            first.extra = (opname == "mm_ops.linear_dgrad.default", json.loads(gattrs["gather_axes"]), dim, src, dst,
+                           gv, ins.args, ids[1])
+            first.static = False
+            removed.add(id(ins))
         if removed:
             instrs = [i for i in instrs if id(i) not in removed]
     # fuse "operator -> accumulate -> task output" into the operator's own epilogue
@@ -404,6 +504,8 @@ def _fix_sizes(arg, gshape, lshape):
 
 
 def _reads(ins: Instr) -> List[int]:
-    if ins.kind in (0, 6, 7):
+    if ins.kind == 11:      # reads the row shard (not the gathered value its operator names) and the weight
+        return [ins.extra[6], ins.extra[7]]
+    if ins.kind in (0, 6, 7, 10):
         return _tensor_ids_in_order(ins.args, ins.kwargs)
     return [ins.args]

@@ -156,6 +156,7 @@ struct Compiler {
     else if (name == "sharding_propagation_forward_full") changed = ShardingPropagation(s, PropagationMode::kForwardFull);
     else if (name == "spmd_lowering") changed = SpmdLowering(s);
     else if (name == "hoist_shard_map_reduce") changed = HoistShardMapReduce(s);
+    else if (name == "reduce_scatter_creator") changed = ReduceScatterCreator(s);
     else if (name == "unused_param_output_remover") changed = UnusedParamOutputRemover(s);
     else throw std::runtime_error("unknown pass '" + name + "'");
     ValidateCircularDependencies(s, name);

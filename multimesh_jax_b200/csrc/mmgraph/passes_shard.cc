@@ -772,6 +772,146 @@ bool SpmdLowering(CompileState& s) {
 }
 
 // ---------------------------------------------------------------------------
+// Collective folding: all-reduce followed by a slice over the same mesh axes becomes a
+// reduce-scatter, and layout changes that only drop mesh axes from one dimension are tagged as
+// all-gathers (the role of AllReduceFolder / ReduceScatterCreator behind
+// src/pjrt_client/mpmd_shard_map_loop_reduce.cc:137-147, and of the splice at :234-301). The
+// lowering can then fuse either one into the tensor-core GEMM next to it.
+// ---------------------------------------------------------------------------
+namespace {
+
+// `to` equals `from` except that dimension *dim additionally carries exactly `axes` (appended
+// after the axes it already has, i.e. every `from` tile is cut into |axes| consecutive parts).
+bool IsScatterOf(const ShardedShape& from, const ShardedShape& to, const std::vector<int>& axes, int* dim) {
+  if (from.mesh_dims != to.mesh_dims || from.rank() != to.rank() || axes.empty()) return false;
+  int found = -1;
+  for (int d = 0; d < from.rank(); ++d) {
+    if (from.dim_axes[d] == to.dim_axes[d]) continue;
+    if (found >= 0) return false;
+    std::vector<int> want = from.dim_axes[d];
+    want.insert(want.end(), axes.begin(), axes.end());
+    if (to.dim_axes[d] != want) return false;
+    found = d;
+  }
+  if (found < 0) return false;
+  for (int d = 0; d < from.rank(); ++d)
+    for (int a : from.dim_axes[d])
+      if (std::find(axes.begin(), axes.end(), a) != axes.end()) return false;
+  *dim = found;
+  return true;
+}
+
+std::vector<int> IntList(const std::string& json) {
+  std::vector<int> out;
+  for (auto v : Json::parse(json).as_int_vector()) out.push_back(static_cast<int>(v));
+  return out;
+}
+
+}  // namespace
+
+bool ReduceScatterCreator(CompileState& s) {
+  Graph& g = *s.graph;
+  const auto users = g.ComputeUsers();
+  std::set<int> graph_outputs(g.outputs.begin(), g.outputs.end());
+  int scatters = 0, gathers = 0;
+  for (int id : std::vector<int>(g.order)) {
+    Node& n = g.node(id);
+    if (n.dead) continue;
+    if (n.op == "mm.spmd_reshard" && !n.attrs.count("gather_dim")) {
+      // pure all-gather: the target drops trailing mesh axes of one dimension
+      const ShardedShape from = ShardedShape::FromJson(Json::parse(n.attrs.at("from")));
+      const ShardedShape to = ShardedShape::FromJson(Json::parse(n.attrs.at("to")));
+      if (from.mesh_dims == to.mesh_dims && from.rank() == to.rank()) {
+        int dim = -1;
+        bool ok = true;
+        std::vector<int> dropped;
+        for (int d = 0; d < from.rank() && ok; ++d) {
+          if (from.dim_axes[d] == to.dim_axes[d]) continue;
+          if (dim >= 0 || to.dim_axes[d].size() >= from.dim_axes[d].size()) { ok = false; break; }
+          for (size_t k = 0; k < to.dim_axes[d].size(); ++k) ok = ok && to.dim_axes[d][k] == from.dim_axes[d][k];
+          dropped.assign(from.dim_axes[d].begin() + to.dim_axes[d].size(), from.dim_axes[d].end());
+          dim = d;
+        }
+        if (ok && dim >= 0) {
+          Json axes = Json::array();
+          for (int a : dropped) axes.push(Json::number(a));
+          n.attrs["gather_dim"] = std::to_string(dim);
+          n.attrs["gather_axes"] = axes.dump();
+          ++gathers;
+        }
+      }
+      continue;
+    }
+    if (n.op != "mm.all_reduce") continue;
+    const int out = n.outputs[0];
+    if (graph_outputs.count(out) || !g.value(out).has_sharding) continue;
+    const std::vector<int> axes = IntList(n.Attr("axes", "[]"));
+    const ShardedShape from = g.value(out).sharding;
+    // (a) the only reader is a local slice of the reduced value, in the same task
+    if (users[out].size() == 1) {
+      Node& u = g.node(users[out][0]);
+      if (u.op == "mm.spmd_reshard" && u.task == n.task && !u.dead) {
+        const ShardedShape to = ShardedShape::FromJson(Json::parse(u.attrs.at("to")));
+        int dim = -1;
+        if (IsScatterOf(from, to, axes, &dim)) {
+          n.op = "mm.reduce_scatter";
+          n.attrs["dim"] = std::to_string(dim);
+          n.attrs["from"] = from.ToJson().dump();
+          n.attrs["to"] = to.ToJson().dump();
+          g.value(out).sharding = to;
+          const int sliced = u.outputs[0];
+          g.value(out).axes = g.value(sliced).axes;
+          g.value(out).has_axes = g.value(sliced).has_axes;
+          g.value(out).axes_logical = g.value(sliced).axes_logical;
+          g.ReplaceAllUses(sliced, out);
+          u.dead = true;
+          ++scatters;
+          continue;
+        }
+      }
+    }
+    // (b) a reduction that runs once per step in a task of its own (a hoisted gradient sum) and
+    // whose readers, in other tasks, all ask for the same finer layout: the FSDP case, where
+    // every data-parallel rank only needs the gradient of the parameter shard it owns
+    if (n.Attr("hoisted") == "1" && !users[out].empty()) {
+      const ShardedShape* want = nullptr;
+      bool same = true;
+      for (int u : users[out]) {
+        const Node& un = g.node(u);
+        if (un.task == n.task) { same = false; break; }
+        const ShardedShape* w = InputShardingOf(s, un.task, out);
+        if (!w) { same = false; break; }
+        if (want && !(*want == *w)) { same = false; break; }
+        want = w;
+      }
+      int dim = -1;
+      if (same && want && IsScatterOf(from, *want, axes, &dim)) {
+        n.op = "mm.reduce_scatter";
+        n.attrs["dim"] = std::to_string(dim);
+        n.attrs["from"] = from.ToJson().dump();
+        n.attrs["to"] = want->ToJson().dump();
+        g.value(out).sharding = *want;
+        ++scatters;
+      }
+    }
+  }
+  if (!scatters && !gathers) return false;
+  if (scatters) {
+    std::vector<int> keep;
+    for (int id : g.order) if (!g.node(id).dead) keep.push_back(id);
+    g.order = keep;
+    for (auto& grp : s.groups) {
+      std::vector<int> nodes;
+      for (int id : grp.nodes) if (!g.node(id).dead) nodes.push_back(id);
+      grp.nodes = nodes;
+    }
+  }
+  s.Note("collective folding: " + std::to_string(scatters) + " reduce-scatters, " + std::to_string(gathers) +
+         " all-gathers");
+  return true;
+}
+
+// ---------------------------------------------------------------------------
 // Hoist reductions of gradient accumulators out of the loop
 // (src/pjrt_client/mpmd_hoist_shard_map_reduce.cc:49-189): an all-reduce whose only
 // consumer is the loop-carried sum runs once after the loop on the accumulated value.

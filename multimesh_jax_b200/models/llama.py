@@ -50,6 +50,17 @@ class LlamaConfig:
     hidden_sharded_after: Tuple[int, ...] = ()
     n_experts: int = 0      # > 0: every feed-forward block is a sparse mixture of SwiGLU experts
     top_k: int = 2          # experts per token (softmax over the chosen router logits)
+    # Megatron-style sequence parallelism: between the tensor-parallel projections the residual
+    # stream, the norms and their gradients are sharded on the sequence dimension over the
+    # tensor-parallel mesh axis (logical axis "seq"). The layout changes in front of the
+    # column-parallel projections (an all-gather, fused into the GEMM that reads the activation)
+    # and behind the row-parallel ones (a reduce-scatter, fused into the GEMM that produces the
+    # partial sums) instead of an all-reduce of replicated activations.
+    sequence_parallel: bool = False
+    # output projection and loss sharded on the vocabulary over the tensor-parallel axis (logical
+    # axis "vocab"): every rank computes its slice of the logits; the softmax statistics are
+    # exchanged between the ranks inside the loss operator
+    vocab_parallel: bool = False
 
     @property
     def head_dim(self) -> int:
@@ -133,13 +144,30 @@ def rope_tables(cfg: LlamaConfig, seq_len: int, device) -> Tuple[torch.Tensor, t
     return K.rope_tables(seq_len, cfg.head_dim, cfg.rope_theta, device)
 
 
+def sp_enter(cfg: LlamaConfig, h: torch.Tensor) -> torch.Tensor:
+    """Sequence-sharded activation -> full sequence, in front of a tensor-parallel projection.
+    The cotangent takes the opposite way (full -> sequence-sharded: a reduce-scatter of the
+    projection's partial input gradients)."""
+    if not cfg.sequence_parallel:
+        return h
+    return mm_lib.relayout(h, ("batch", None, None), grad_spec=("batch", "seq", None))
+
+
+def sp_leave(cfg: LlamaConfig, y: torch.Tensor) -> torch.Tensor:
+    """Output of a row-parallel projection (partial sums over the tensor-parallel ranks) ->
+    sequence-sharded; its cotangent is gathered back to the full sequence."""
+    if not cfg.sequence_parallel:
+        return y
+    return mm_lib.relayout(y, ("batch", "seq", None), grad_spec=("batch", None, None))
+
+
 def attention_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor, cos, sin) -> torch.Tensor:
     """h: normalised activations [B, S, D] -> attention branch output [B, S, D]."""
     B, S, D = h.shape
-    qkv = ops.linear(h, p["wqkv"])                       # [B, S, H_total, Dh]
+    qkv = ops.linear(sp_enter(cfg, h), p["wqkv"])        # [B, S, H_total, Dh]
     qkv = mm_lib.with_sharding_constraint(qkv, ("batch", None, "heads", None))
     out, _, _ = ops.attention(qkv, cos, sin, cfg.n_heads // cfg.n_kv_heads)
-    return ops.linear(out.flatten(2), p["wo"])
+    return sp_leave(cfg, ops.linear(out.flatten(2), p["wo"]))
 
 
 def mlp_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor) -> torch.Tensor:
@@ -149,9 +177,9 @@ def mlp_block(cfg: LlamaConfig, p: Dict[str, torch.Tensor], h: torch.Tensor) -> 
         wgu = mm_lib.with_sharding_constraint(p["wgu"], ("expert", None, None, None))
         wdown = mm_lib.with_sharding_constraint(p["wdown"], ("expert", None, None))
         return ops.moe_ffn(h, p["router"], wgu, wdown, cfg.top_k)
-    gu = ops.linear(h, p["wgu"])                          # [B, S, 2, F]
+    gu = ops.linear(sp_enter(cfg, h), p["wgu"])           # [B, S, 2, F]
     gu = mm_lib.with_sharding_constraint(gu, ("batch", None, None, "mlp"))
-    return ops.linear(ops.swiglu(gu), p["wdown"])
+    return sp_leave(cfg, ops.linear(ops.swiglu(gu), p["wdown"]))
 
 
 def forward_layers(cfg: LlamaConfig, layers: Sequence[Dict[str, torch.Tensor]], x: torch.Tensor, h: torch.Tensor,
@@ -172,6 +200,9 @@ def forward_layers(cfg: LlamaConfig, layers: Sequence[Dict[str, torch.Tensor]], 
             if (first_index + i) in cfg.hidden_sharded_after:
                 x = mm_lib.relayout(x, (None, None, "boundary_hidden"))
                 h = mm_lib.relayout(h, (None, None, "boundary_hidden"))
+            elif cfg.sequence_parallel and not cfg.n_experts:
+                x = mm_lib.with_sharding_constraint(x, ("batch", "seq", None))
+                h = mm_lib.with_sharding_constraint(h, ("batch", "seq", None))
             else:
                 x = mm_lib.with_sharding_constraint(x, ("batch", None, None))
     return x, h
@@ -181,13 +212,21 @@ def loss_fn(cfg: LlamaConfig, params: Dict[str, Any], tokens: torch.Tensor, labe
             loss_scale: float) -> torch.Tensor:
     """Sum over tokens of the next-token cross-entropy, times ``loss_scale``."""
     layers = params["layers"]
+    sp = cfg.sequence_parallel and not cfg.n_experts
     with named_scope("embed"):
         x = ops.embedding(params["embed"], tokens)         # [B, S, D]
+        if sp:
+            x = mm_lib.with_sharding_constraint(x, ("batch", "seq", None))
         h, _ = ops.rmsnorm(x, layers[0]["attn_norm"], cfg.eps)
     next_norms = [l["attn_norm"] for l in layers[1:]] + [params["final_norm"]]
     x, h = forward_layers(cfg, layers, x, h, cos, sin, next_norms)
     with named_scope("head"):
-        logits = ops.linear(h, params["lm_head"])          # [B, S, V]
+        w_out = params["lm_head"]
+        if cfg.vocab_parallel:
+            w_out = mm_lib.with_sharding_constraint(w_out, ("vocab", None))
+        logits = ops.linear(sp_enter(cfg, h) if sp else h, w_out)   # [B, S, V]
+        if cfg.vocab_parallel:
+            logits = mm_lib.with_sharding_constraint(logits, ("batch", None, "vocab"))
         loss, _ = ops.cross_entropy(logits, labels, loss_scale)
     return loss
 
@@ -299,7 +338,8 @@ def register_pipeline_tasks(cfg: LlamaConfig, mesh: MultiMesh, num_stages: int,
                             logical_axes: Sequence[Tuple[str, str]] = (("batch", "data"), ("heads", "model"),
                                                                        ("mlp", "model"), ("fsdp", "data"),
                                                                        ("expert", "data"),
-                                                                       ("boundary_hidden", "model")),
+                                                                       ("boundary_hidden", "model"),
+                                                                       ("seq", "model"), ("vocab", "model")),
                             layers_per_stage: Optional[Sequence[int]] = None,
                             split_backprop: Optional[Tuple[str, str]] = None) -> None:
     """Places the layers on pipeline stages (mesh axis ``stage``): ``layers_per_stage[s]``

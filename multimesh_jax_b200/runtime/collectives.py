@@ -296,6 +296,100 @@ class DeviceCtx:
         y = mm_ops.linear_dgrad_impl(x, w) if is_dgrad else mm_ops.linear_impl(x, w)
         return self.all_reduce(y, axes, key)
 
+    def _scatter_slice(self, full: torch.Tensor, src: dict, dst: dict) -> torch.Tensor:
+        """This device's tile of layout ``dst`` cut out of its tile of the coarser layout ``src``."""
+        local = _local_only_chunks(src, dst)
+        if local is None:
+            raise RuntimeError("reduce-scatter target is not a refinement of the source layout")
+        out = torch.empty(dst["shard_size"], dtype=full.dtype, device=full.device)
+        for c in local.get(self.device, ()):
+            ext = [h - l for l, h in zip(c["lo"], c["hi"])]
+            s_box = tuple(slice(o, o + e) for o, e in zip(c["src_offset"], ext))
+            d_box = tuple(slice(o, o + e) for o, e in zip(c["dst_offset"], ext))
+            out[d_box] = full[s_box]
+        return out
+
+    def reduce_scatter(self, x: torch.Tensor, axes: Sequence[int], dim: int, src: dict, dst: dict, key) -> torch.Tensor:
+        """Sum of ``x`` over the devices along ``axes``, of which this device keeps its part of
+        dimension ``dim`` (layout ``dst``, a refinement of ``src``). One-process-per-GPU jobs pull
+        only their own share from the peers (half of an all-reduce's traffic); elsewhere the sum
+        is formed by the all-reduce and sliced."""
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        if len(group) == 1:
+            return x
+        if self.topology.kind == "dist" and self.peer_comm is not None:
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            if comm.supports_scatter(x, dim):
+                return comm.reduce_scatter(x, dim, group.index(me))
+        return self._scatter_slice(self.all_reduce(x, axes, key), src, dst)
+
+    def linear_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, axes: Sequence[int], is_dgrad: bool, dim: int,
+                              src: dict, dst: dict, key) -> torch.Tensor:
+        """``reduce_scatter(linear(x, w))`` (or of the input gradient) over ``axes`` along the row
+        dimension ``dim`` of the product. One-process-per-GPU jobs run the fused tcgen05 GEMM whose
+        epilogue pushes each tile's partial sums to the rank that owns those rows."""
+        from ..ops import mm_ops
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        fused = self.fused_tp
+        if fused is not None and len(group) > 1 and x.is_cuda and x.dtype == torch.bfloat16:
+            ranks = tuple(self.device_start + o for o in group)
+            op = fused.get_scatter(ranks)
+            if is_dgrad:
+                w2 = w.reshape(-1, w.shape[-1])
+                a2 = x.reshape(-1, w2.shape[0])
+                out_shape = list(x.shape[:x.dim() - (w.dim() - 1)]) + [w2.shape[1]]
+                N, Kd = w2.shape[1], w2.shape[0]
+            else:
+                w2 = w.reshape(-1, w.shape[-1])
+                a2 = x.reshape(-1, x.shape[-1])
+                out_shape = list(x.shape[:-1]) + list(w.shape[:-1])
+                N, Kd = w2.shape[0], a2.shape[1]
+            M = a2.shape[0]
+            outer = 1
+            for s_ in out_shape[:dim]:
+                outer *= s_
+            rows_per_outer = M // outer
+            if op.supported(M, N, Kd, outer, x.dtype):
+                y = op(a2, w2, b_mn=is_dgrad, outer=outer)          # [M / g, N]
+                out_shape[dim] //= len(group)
+                return y.view(out_shape)
+        y = mm_ops.linear_dgrad_impl(x, w) if is_dgrad else mm_ops.linear_impl(x, w)
+        return self.reduce_scatter(y, axes, dim, src, dst, key)
+
+    def all_gather_linear(self, x: torch.Tensor, w: torch.Tensor, is_dgrad: bool, axes: Sequence[int], dim: int,
+                          src: dict, dst: dict, key) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``linear(all_gather(x), w)`` for an activation whose row dimension ``dim`` is sharded
+        over ``axes``; returns the product and the gathered activation. One-process-per-GPU jobs
+        run the fused kernel that pulls the peers' rows while the tensor cores already work on
+        the rows that have arrived."""
+        from ..ops import mm_ops
+        me = self.device - self.device_start
+        group = mesh_group(me, self.mesh_dims, list(axes))
+        fused = self.fused_tp
+        if fused is not None and len(group) > 1 and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous():
+            ranks = tuple(self.device_start + o for o in group)
+            op = fused.get_gather(ranks)
+            outer = 1
+            for s_ in x.shape[:dim]:
+                outer *= s_
+            a2 = x.reshape(-1, x.shape[-1])
+            w2 = w.reshape(-1, w.shape[-1])
+            if is_dgrad and w.dim() == 2 and op.supported(a2.shape[0], a2.shape[1], outer, x.dtype):
+                y, full = op(a2, w2, b_mn=True, outer=outer)
+                full_shape = list(x.shape)
+                full_shape[dim] *= len(group)
+                return y.view(*full_shape[:-1], w2.shape[1]), full.view(full_shape)
+            if not is_dgrad and op.supported(a2.shape[0], a2.shape[1], outer, x.dtype):
+                y, full = op(a2, w2, outer=outer)
+                full_shape = list(x.shape)
+                full_shape[dim] *= len(group)
+                return y.view(*full_shape[:-1], *w.shape[:-1]), full.view(full_shape)
+        full = self.spmd_reshard(x, src, dst, key)
+        y = mm_ops.linear_dgrad_impl(full, w) if is_dgrad else mm_ops.linear_impl(full, w)
+        return y, full
+
     def spmd_reshard(self, x: torch.Tensor, src: dict, dst: dict, key) -> torch.Tensor:
         """Local tile of layout ``dst`` from tiles in layout ``src`` (same
         devices): gather every tile, assemble the global array, slice."""
