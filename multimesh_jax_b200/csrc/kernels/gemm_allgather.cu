@@ -1,7 +1,11 @@
 // All-gather fused into a tensor-parallel GEMM (column-parallel projections whose input
 // activations are sharded by rows over the ranks, i.e. sequence-parallel activations):
 //
-//     C[M, N] = concat_r(A_r[M/g, K]) * B[N, K]^T        A_r lives on rank r
+//     C[M, N] = gather_r(A_r[M/g, K]) * B[N, K]^T        A_r lives on rank r
+//
+// The shards interleave in chunks of `chunk_rows` rows: chunk c of the gathered matrix is chunk
+// c / g of rank c % g (one chunk per rank = plain concatenation; for a [B, S, .] activation
+// sharded on S a chunk is the S / g rows of one sequence).
 //
 // One kernel does both. Two helper warps per CTA pull the row shards - the peers' over NVLink
 // with plain 16-byte loads, the own one from local memory - into a local [M, K] buffer, 128-row
@@ -11,7 +15,10 @@
 // ring order, so the tensor cores start on local rows while the first remote rows are still
 // in flight, and the transfer of block i+1 overlaps the math of block i. TMA only ever reads
 // this GPU's memory; no multicast is used.
+#include <cstdlib>
+
 #include "gemm_core.cuh"
+#include "gemm_pair_core.cuh"
 #include "host_common.h"
 
 namespace mm {
@@ -28,6 +35,7 @@ struct AllGatherHook {
   int target;                        // value a block's counter reaches when all its pieces of this call arrived
   int nranks, me;
   int blocks_per_shard;              // 128-row blocks per rank shard
+  int chunk_blocks;                  // 128-row blocks per chunk
   int num_m;
 
   static constexpr int kStageBytes = 0;
@@ -35,14 +43,20 @@ struct AllGatherHook {
   struct State {};
   __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
 
-  // scheduler index -> row block: own shard first, then the peers' in ring order
+  // scheduler index -> row block of the gathered matrix: the blocks of this rank's own shard
+  // first, then the peers' in ring order
   __device__ __forceinline__ int map_m(int m_blk) const {
-    const int shifted = m_blk + me * blocks_per_shard;
-    return shifted >= num_m ? shifted - num_m : shifted;
+    if (m_blk >= num_m) return m_blk;     // the empty half of the last CTA pair
+    const int hop = m_blk / blocks_per_shard, in_shard = m_blk - hop * blocks_per_shard;
+    int owner = me + hop;
+    if (owner >= nranks) owner -= nranks;
+    const int chunk = in_shard / chunk_blocks, within = in_shard - chunk * chunk_blocks;
+    return (chunk * nranks + owner) * chunk_blocks + within;
   }
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
 
   __device__ __forceinline__ bool before_tile_loads(int m_blk, int, int* err) const {
+    if (m_blk >= num_m) return true;
     unsigned long long t0 = 0, limit = 0;
     for (uint32_t i = 0;; ++i) {
       int v;
@@ -74,12 +88,14 @@ struct AllGatherHook {
     const int workers = gridDim.x * kAuxWarps;
     const int wid = blockIdx.x * kAuxWarps + w;
     const int64_t per = (vec_per_block + workers - 1) / workers;
+    (void)vec_per_shard;
     for (int i = 0; i < num_m; ++i) {
       const int blk = map_m(i);
-      const int owner = blk / blocks_per_shard;
-      const int64_t in_shard = static_cast<int64_t>(blk - owner * blocks_per_shard) * vec_per_block;
-      const uint4* src = a_src[owner] + in_shard;
-      uint4* dst = gathered + static_cast<int64_t>(owner) * vec_per_shard + in_shard;
+      const int hop = i / blocks_per_shard;
+      int owner = me + hop;
+      if (owner >= nranks) owner -= nranks;
+      const uint4* src = a_src[owner] + static_cast<int64_t>(i - hop * blocks_per_shard) * vec_per_block;
+      uint4* dst = gathered + static_cast<int64_t>(blk) * vec_per_block;
       const int64_t lo = wid * per, hi = min(vec_per_block, lo + per);
       int64_t v = lo + lane;
       for (; v + 96 < hi; v += 128) {     // four loads in flight per lane
@@ -124,21 +140,38 @@ extern "C" {
 // [M/nranks, K] row shards (contiguous; entry `me` is local); gathered: local [M, K] buffer;
 // ready: local int counters, one per 128-row block, zero before the first call and never
 // reset; *target (host memory, 0 before the first call) carries the value the counters reach
-// after this call and is updated here. M / nranks must be a multiple of 128, K of 8.
+// after this call and is updated here. chunk_rows (0: M / nranks) must be a multiple of 128 and
+// M a multiple of nranks * chunk_rows; K a multiple of 8.
 int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathered, int* ready, int* target,
                            const void* B, int b_mn, int64_t ldb, void* C, int64_t ldc, int M, int N, int K,
-                           cudaStream_t stream) {
+                           int chunk_rows, cudaStream_t stream) {
   using namespace mm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (nranks < 1 || nranks > AG_MAX_RANKS || (M % (nranks * GEMM_BM)) || (K % 8) || (ldb % 8) || (ldc % 8)) return -2;
+  if (nranks < 1 || nranks > AG_MAX_RANKS || (K % 8) || (ldb % 8) || (ldc % 8)) return -2;
+  if (chunk_rows <= 0) chunk_rows = M / nranks;
+  if ((chunk_rows % GEMM_BM) || (M % (nranks * chunk_rows))) return -2;
   DeviceState* ds = device_state();
   if (!ds) return -1;
+  // CTA pairs (256x256 tile per two SMs) from 256 rows on; MM_AG_PAIR=0 keeps the single-CTA loop
+  static const bool pair_ok = [] {
+    const char* e = getenv("MM_AG_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  const bool pair = pair_ok && M >= 2 * GEMM_BM;
   CUtensorMap tmA, tmB;
-  int rc = make_gemm_tmaps(&tmA, &tmB, gathered, 0, K, B, b_mn, ldb, M, N, K);
+  int rc = pair ? make_pair_tmaps(&tmA, &tmB, gathered, 0, K, B, b_mn, ldb, M, N, K)
+                : make_gemm_tmaps(&tmA, &tmB, gathered, 0, K, B, b_mn, ldb, M, N, K);
   if (rc) return rc;
   const int num_m = M / GEMM_BM;
-  const int num_tiles = num_m * ((N + GEMM_BN - 1) / GEMM_BN);
-  const int grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;
+  int grid;
+  if (pair) {
+    const int num_tiles = ((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((N + GEMM_BN - 1) / GEMM_BN);
+    const int max_pairs = ds->sm_count / 2;
+    grid = 2 * (num_tiles < max_pairs ? num_tiles : max_pairs);
+  } else {
+    const int num_tiles = num_m * ((N + GEMM_BN - 1) / GEMM_BN);
+    grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;
+  }
   AllGatherHook hook;
   hook.C = C;
   hook.ldc = ldc;
@@ -151,7 +184,12 @@ int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathe
   hook.nranks = nranks;
   hook.me = me;
   hook.blocks_per_shard = num_m / nranks;
+  hook.chunk_blocks = chunk_rows / GEMM_BM;
   hook.num_m = num_m;
+  if (pair) {
+    if (b_mn) return launch_pair_kernel<false, true>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+    return launch_pair_kernel<false, false>(tmA, tmB, hook, M, N, K, ds->sm_count, ds->status, stream);
+  }
   GemmShape shape{M, N, K};
   constexpr int threads = GEMM_THREADS + 32 * AllGatherHook::kAuxWarps;
   static bool configured[2][kMaxDevices] = {};

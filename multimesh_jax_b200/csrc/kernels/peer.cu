@@ -144,16 +144,19 @@ struct ReducePullArgs {
   uint4* out;
   int nsrc;
   int is_fp32;      // 1: fp32 elements, 0: bf16 elements
-  int64_t nvec;
+  int64_t nvec;     // vectors written (all chunks)
+  int64_t chunk_vecs, src_stride_vecs;   // the sources are read in chunks of chunk_vecs, src_stride_vecs apart
   float scale;
 };
 __global__ void __launch_bounds__(256) reduce_pull_kernel(ReducePullArgs a) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < a.nvec; v += stride) {
+    const int64_t chunk = v / a.chunk_vecs;
+    const int64_t sv = chunk * a.src_stride_vecs + (v - chunk * a.chunk_vecs);
     if (a.is_fp32) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int s = 0; s < a.nsrc; ++s) {
-        const uint4 u = __ldcg(a.src[s] + v);
+        const uint4 u = __ldcg(a.src[s] + sv);
         acc.x += __uint_as_float(u.x); acc.y += __uint_as_float(u.y);
         acc.z += __uint_as_float(u.z); acc.w += __uint_as_float(u.w);
       }
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(256) reduce_pull_kernel(ReducePullArgs a) {
     } else {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int s = 0; s < a.nsrc; ++s) {
-        const uint4 u = __ldcg(a.src[s] + v);
+        const uint4 u = __ldcg(a.src[s] + sv);
         const float2 p0 = unpack_bf16(u.x), p1 = unpack_bf16(u.y), p2 = unpack_bf16(u.z), p3 = unpack_bf16(u.w);
         acc[0] += p0.x; acc[1] += p0.y; acc[2] += p1.x; acc[3] += p1.y;
         acc[4] += p2.x; acc[5] += p2.y; acc[6] += p3.x; acc[7] += p3.y;
@@ -285,10 +288,23 @@ int mm_wait_flag(const void* flag, int value, cudaStream_t stream) {
 
 // out = scale * sum of `nsrc` buffers of `nbytes` bytes each (16-byte aligned, a multiple of 16
 // bytes); sources may be peer addresses. elem_size 4 = fp32, 2 = bf16.
+int mm_reduce_pull_chunked(const int64_t* srcs, int nsrc, void* out, int64_t chunk_bytes, int64_t nchunks,
+                           int64_t src_stride_bytes, int elem_size, float scale, cudaStream_t stream);
+
 int mm_reduce_pull(const int64_t* srcs, int nsrc, void* out, int64_t nbytes, int elem_size, float scale,
                    cudaStream_t stream) {
+  return mm_reduce_pull_chunked(srcs, nsrc, out, nbytes, 1, nbytes, elem_size, scale, stream);
+}
+
+// Chunked form: `nchunks` pieces of `chunk_bytes` bytes, `src_stride_bytes` apart in every source,
+// written back to back to `out` (the reduce-scatter of an inner dimension: every outer index
+// contributes one piece of this rank's share).
+int mm_reduce_pull_chunked(const int64_t* srcs, int nsrc, void* out, int64_t chunk_bytes, int64_t nchunks,
+                           int64_t src_stride_bytes, int elem_size, float scale, cudaStream_t stream) {
+  const int64_t nbytes = chunk_bytes * nchunks;
   if (nbytes <= 0) return 0;
-  if (nsrc < 1 || nsrc > 8 || (nbytes & 15) || (elem_size != 4 && elem_size != 2)) return -2;
+  if (nsrc < 1 || nsrc > 8 || (chunk_bytes & 15) || (src_stride_bytes & 15) || (elem_size != 4 && elem_size != 2))
+    return -2;
   DeviceState* ds = device_state();
   if (!ds) return -1;
   ReducePullArgs a;
@@ -301,6 +317,8 @@ int mm_reduce_pull(const int64_t* srcs, int nsrc, void* out, int64_t nbytes, int
   a.nsrc = nsrc;
   a.is_fp32 = elem_size == 4;
   a.nvec = nbytes / 16;
+  a.chunk_vecs = chunk_bytes / 16;
+  a.src_stride_vecs = src_stride_bytes / 16;
   a.scale = scale;
   int64_t want = (a.nvec + 256 * 4 - 1) / (256 * 4);
   const int cap = ds->sm_count * 8;

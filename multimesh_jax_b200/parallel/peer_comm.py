@@ -26,6 +26,7 @@ from ..ops import kernels as K
 from . import symm
 
 _lib.register("mm_reduce_pull", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_float, c_void_p])
+_lib.register("mm_reduce_pull_chunked", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int, c_float, c_void_p])
 
 
 class PeerGroupComm:
@@ -87,6 +88,44 @@ class PeerGroupComm:
             _lib.check(rc, "mm_reduce_pull")
             K._count()
         self.barrier()                                    # staging tiles may be overwritten again
+        self.calls += 1
+        return out
+
+    def supports_scatter(self, x: torch.Tensor, dim: int) -> bool:
+        """Reduce-scatter along ``dim`` as a pull of this rank's share: the share of every outer
+        index must be a whole number of 16-byte vectors."""
+        if not (x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.is_contiguous()):
+            return False
+        if x.numel() * x.element_size() < self.MIN_BYTES or dim >= x.dim() or x.shape[dim] % self.g:
+            return False
+        inner = x.element_size() * (x.shape[dim] // self.g)
+        for s_ in x.shape[dim + 1:]:
+            inner *= s_
+        return inner % 16 == 0
+
+    def reduce_scatter(self, x: torch.Tensor, dim: int, index: int, scale: float = 1.0) -> torch.Tensor:
+        """Sum of the members' ``x`` restricted to part ``index`` (of ``g``) of dimension ``dim``:
+        staging copy, one barrier, one pull kernel that reads only this rank's share from every
+        member (a (g-1)/g-th of the tensor crosses NVLink into this GPU), one barrier."""
+        a, g = self.arena, self.g
+        nbytes = x.numel() * x.element_size()
+        s_in, _ = self._tiles(nbytes)
+        s_in.peer(a.rank)[:nbytes].view(x.dtype).view(x.shape).copy_(x)
+        self.barrier()
+        outer = 1
+        for s_ in x.shape[:dim]:
+            outer *= s_
+        stride = nbytes // outer                      # bytes of one outer index in the source
+        chunk = stride // g                           # this rank's share of it
+        out_shape = list(x.shape)
+        out_shape[dim] //= g
+        out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+        srcs = (c_int64 * g)(*[s_in.ptr(r) + index * chunk for r in self.ranks])
+        rc = a.lib.mm_reduce_pull_chunked(srcs, g, out.data_ptr(), chunk, outer, stride, x.element_size(), scale,
+                                          torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "mm_reduce_pull_chunked")
+        K._count()
+        self.barrier()                                # staging tiles may be overwritten again
         self.calls += 1
         return out
 

@@ -83,8 +83,77 @@ class FusedLinearAllReduce:
         return dtype == torch.bfloat16 and N % 32 == 0 and Kd % 8 == 0
 
 
+_lib.register("mm_gemm_reducescatter_bf16", c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64,
+                                                    c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                    c_int, c_int, c_int, c_void_p])
+
+
+class _ScatterBufferSet:
+    def __init__(self, arena: symm.SymmetricArena, Ms: int, N: int, g: int):
+        self.tiles = 4 * ((Ms + BM - 1) // BM) * ((N + BN - 1) // BN)   # one flag per 32-row quarter of a shard tile
+        self.recv = [arena.alloc((g - 1, Ms, N), torch.bfloat16) for _ in range(2)]
+        self.flags = [arena.alloc((g - 1, self.tiles), torch.int32) for _ in range(2)]
+        self.epoch = 0
+
+
+class FusedLinearReduceScatter:
+    """``reduce_scatter(A @ B^T)`` over one tensor-parallel group with this rank's K-shard of
+    both operands (``mm_gemm_reducescatter_bf16``): the tcgen05 GEMM whose epilogue pushes the
+    partial sums of every tile to the rank that owns those rows and adds what it receives for
+    its own rows. Rows are owned in chunks (``outer`` chunks per rank: ``outer`` = 1 for a plain
+    split of the rows, the number of sequences for a [B, S, .] activation sharded on S)."""
+
+    def __init__(self, arena: symm.SymmetricArena, ranks: Sequence[int]):
+        self.arena, self.ranks = arena, list(ranks)
+        self.g = len(self.ranks)
+        self.me = self.ranks.index(arena.rank)
+        self.sets: Dict[Tuple[int, int], _ScatterBufferSet] = {}
+        self.lib = _lib.load()
+        self.calls = 0
+
+    def supported(self, M: int, N: int, Kd: int, outer: int, dtype: torch.dtype) -> bool:
+        if dtype != torch.bfloat16 or N % 32 or Kd % 8 or outer < 1 or M % (self.g * outer):
+            return False
+        return (M // (self.g * outer)) % BM == 0
+
+    def _sender_slot(self, sender: int, owner: int) -> int:
+        """Index of rank position ``sender`` among the senders of ``owner``."""
+        return sender if sender < owner else sender - 1
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, outer: int = 1
+                 ) -> torch.Tensor:
+        M, Kd = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+        N = b.shape[1] if b_mn else b.shape[0]
+        g, me = self.g, self.me
+        Ms = M // g
+        chunk_rows = M // (g * outer)
+        bs = self.sets.get((Ms, N))
+        if bs is None:
+            bs = self.sets[(Ms, N)] = _ScatterBufferSet(self.arena, Ms, N, g)
+        bs.epoch += 1
+        par = bs.epoch & 1
+        recv, flags = bs.recv[par], bs.flags[par]
+        slot_bytes, flag_bytes = Ms * N * 2, bs.tiles * 4
+        my_rank = self.arena.rank
+        recv_local = (c_int64 * (g - 1))(*[recv.ptr(my_rank) + p * slot_bytes for p in range(g - 1)])
+        flag_local = (c_int64 * (g - 1))(*[flags.ptr(my_rank) + p * flag_bytes for p in range(g - 1)])
+        recv_peer = (c_int64 * g)(*[0 if r == me else recv.ptr(self.ranks[r]) + self._sender_slot(me, r) * slot_bytes
+                                   for r in range(g)])
+        flag_peer = (c_int64 * g)(*[0 if r == me else flags.ptr(self.ranks[r]) + self._sender_slot(me, r) * flag_bytes
+                                   for r in range(g)])
+        out = torch.empty((Ms, N), dtype=torch.bfloat16, device=a.device)
+        rc = self.lib.mm_gemm_reducescatter_bf16(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
+                                                 out.data_ptr(), out.stride(0), M, N, Kd, recv_local, recv_peer,
+                                                 flag_local, flag_peer, g, me, chunk_rows, bs.epoch,
+                                                 torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "mm_gemm_reducescatter_bf16")
+        K._count()
+        self.calls += 1
+        return out
+
+
 _lib.register("mm_allgather_gemm_bf16", c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
-                                                c_void_p, c_int64, c_int, c_int, c_int, c_void_p])
+                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p])
 
 
 class FusedAllGatherLinear:
@@ -113,10 +182,13 @@ class FusedAllGatherLinear:
         symm.wait_flags(a, [a.flag_ptr(a.rank, self.flag_off[self.ranks.index(r)]) for r in peers], self.epoch)
 
     @staticmethod
-    def supported(rows_per_rank: int, Kd: int, dtype: torch.dtype) -> bool:
-        return dtype == torch.bfloat16 and rows_per_rank % BM == 0 and Kd % 8 == 0
+    def supported(rows_per_rank: int, Kd: int, outer: int = 1, dtype: torch.dtype = torch.bfloat16) -> bool:
+        """``outer`` chunks per rank (1: the shards concatenate; the number of sequences for a
+        [B, S, .] activation sharded on S); a chunk must be a whole number of 128-row blocks."""
+        return (dtype == torch.bfloat16 and outer >= 1 and rows_per_rank % outer == 0
+                and (rows_per_rank // outer) % BM == 0 and Kd % 8 == 0)
 
-    def __call__(self, a_shard: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False):
+    def __call__(self, a_shard: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False, outer: int = 1):
         """Returns ``(C [M, N], A_full [M, K])``; ``A_full`` is the gathered input (kept for the
         weight gradient)."""
         Ms, Kd = a_shard.shape
@@ -138,7 +210,7 @@ class FusedAllGatherLinear:
         srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
         rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), ctypes.byref(st["target"]),
                                              b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
-                                             torch.cuda.current_stream().cuda_stream)
+                                             Ms // outer, torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "mm_allgather_gemm_bf16")
         K._count()
         self.calls += 1

@@ -132,6 +132,22 @@ class FusedTP:
             self._ops[ranks] = FusedLinearAllReduce(self.arena, ranks)
         return self._ops[ranks]
 
+    def get_scatter(self, ranks: Tuple[int, ...]):
+        """GEMM -> reduce-scatter operator of a group (its members create it at the same point of
+        the same program, so the arena offsets agree)."""
+        from ..parallel.tp import FusedLinearReduceScatter
+        key = ("rs",) + tuple(ranks)
+        if key not in self._ops:
+            self._ops[key] = FusedLinearReduceScatter(self.arena, ranks)
+        return self._ops[key]
+
+    def get_gather(self, ranks: Tuple[int, ...]):
+        from ..parallel.tp import FusedAllGatherLinear
+        key = ("ag",) + tuple(ranks)
+        if key not in self._ops:
+            self._ops[key] = FusedAllGatherLinear(self.arena, ranks)
+        return self._ops[key]
+
 
 def mesh_group(ordinal: int, mesh_dims: Sequence[int], axes: Sequence[int]) -> List[int]:
     """Ordinals (within the task's device list) that differ from ``ordinal``

@@ -228,14 +228,16 @@ class Executable:
             return
         g = self.cap.graph
         want_tp = os.environ.get("MM_FUSED_TP", "1") != "0" and any(
-            g.node(n)["op"] == "mm.all_reduce" for t in self.plan["templates"] for n in t["nodes"])
+            g.node(n)["op"] in ("mm.all_reduce", "mm.reduce_scatter") or "gather_dim" in g.node(n)["attrs"]
+            for t in self.plan["templates"] for n in t["nodes"])
         want_rs = os.environ.get("MM_P2P_RESHARD", "1") != "0" and any(
             op["kind"] == "reshard" for op in self.plan["ops"])
         moe_nodes = [g.node(n) for t in self.plan["templates"] for n in t["nodes"]
                      if g.node(n)["op"].startswith("mm_ops.moe_ffn.") and g.node(n)["attrs"].get("shared_axes", "[]") != "[]"]
         want_moe = os.environ.get("MM_P2P_MOE", "1") != "0" and bool(moe_nodes)
         want_comm = os.environ.get("MM_P2P_COLLECTIVES", "1") != "0" and any(
-            g.node(n)["op"] in ("mm.all_reduce", "mm.spmd_reshard") for t in self.plan["templates"] for n in t["nodes"])
+            g.node(n)["op"] in ("mm.all_reduce", "mm.reduce_scatter", "mm.spmd_reshard")
+            for t in self.plan["templates"] for n in t["nodes"])
         if not (want_tp or want_rs or want_moe or want_comm):
             return
         from ..parallel import symm
@@ -252,7 +254,7 @@ class Executable:
             for t in self.plan["templates"]:
                 for n in t["nodes"]:
                     nd = g.node(n)
-                    if nd["op"] in ("mm.all_reduce", "mm.spmd_reshard"):
+                    if nd["op"] in ("mm.all_reduce", "mm.reduce_scatter", "mm.spmd_reshard"):
                         v = g.value(nd["inputs"][0])
                         nb = DTYPE_FROM_NAME[v["dtype"]].itemsize
                         for s_ in (v["sharding"]["shard_size"] if v["sharding"] else v["shape"]):

@@ -1,7 +1,7 @@
 """Worker of the multi-GPU training-step tests (one process per GPU, launched by torchrun):
 the compiled step on `pp x dp x tp` GPUs against the eager step on one GPU, in bf16.
 
-    step_worker.py <pp> <dp> <tp> [fsdp|moe]
+    step_worker.py <pp> <dp> <tp> [fsdp|moe|sp]      (sp: sequence-parallel tensor parallelism with a vocabulary-sharded loss)
 """
 import json
 import os
@@ -17,6 +17,7 @@ def main():
     pp, dp, tp = (int(a) for a in sys.argv[1:4])
     fsdp = len(sys.argv) > 4 and sys.argv[4] == "fsdp"
     moe = len(sys.argv) > 4 and sys.argv[4] == "moe"
+    sp = len(sys.argv) > 4 and sys.argv[4] == "sp"
     rank = int(os.environ["RANK"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -30,6 +31,7 @@ def main():
     torch.manual_seed(0)
     cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, d_model=512, n_heads=4, n_kv_heads=2, d_ff=1024, vocab=1024,
                                  n_experts=4 if moe else 0, top_k=2)
+    cfg.sequence_parallel = cfg.vocab_parallel = sp
     B, S, MB = 8, 256, 2
     params = llama.init_params(cfg, device="cpu")
     params = pytree.tree_map(lambda t: t.to(dev), params)
@@ -69,6 +71,11 @@ def main():
     moe_calls = sum(o.calls for o in pm._ops.values()) if pm is not None else 0
     pc = getattr(exe, "_peer_comm", None)
     comm_calls = sum(o.calls for o in pc._ops.values()) if pc is not None else 0
+    ft = getattr(exe, "_fused_tp", None)
+    fused = {}
+    for key, o in (ft._ops.items() if ft is not None else ()):
+        kind = key[0] if isinstance(key[0], str) else "ar"
+        fused[kind] = fused.get(kind, 0) + o.calls
     pr = getattr(exe, "_peer_reshard", None)
     peer_uses = sum(s["uses"] for s in pr.slots.values() if s) if pr is not None else 0
     flag = torch.tensor([1 if (ok and status == 0) else 0], device=dev)
@@ -76,7 +83,7 @@ def main():
     uses = torch.tensor([peer_uses], device=dev)
     dist.all_reduce(uses, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls, "peer_collective_calls": comm_calls,
+        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls, "peer_collective_calls": comm_calls, "fused_calls": fused,
                           "status": status, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
     dist.barrier()
     exe.shutdown()

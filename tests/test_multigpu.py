@@ -51,3 +51,11 @@ def test_expert_parallel_step_with_fused_dispatch_matches_eager():
     out = _step(2, 1, 2, 1, "moe", port=29535)
     assert out["STEP_OK"], out
     assert out["peer_moe_calls"] > 0             # router + dispatch and combine ran on the peer-memory kernels
+
+
+def test_sequence_parallel_step_with_fused_reduce_scatter_and_all_gather_matches_eager():
+    out = _step(2, 1, 1, 2, "sp", port=29536)
+    assert out["STEP_OK"], out
+    # the projections ran on the GEMM + reduce-scatter and all-gather + GEMM kernels, none on the all-reduce one
+    assert out["fused_calls"].get("rs", 0) > 0 and out["fused_calls"].get("ag", 0) > 0, out
+    assert out["fused_calls"].get("ar", 0) == 0, out
