@@ -55,6 +55,10 @@ def parse_args():
     p.add_argument("--dp", type=int, default=0, help="data-parallel degree (0 = default for N)")
     p.add_argument("--pp", type=int, default=0, help="pipeline stages (0 = N / (tp * dp))")
     p.add_argument("--fsdp", action="store_true", help="store parameters and optimizer state sharded over the data axis")
+    p.add_argument("--sp", type=int, default=-1,
+                   help="1: sequence-parallel layout of the tensor-parallel region (GEMM + reduce-scatter and "
+                        "all-gather + GEMM kernels, vocabulary-sharded output projection and loss); 0: replicated "
+                        "activations with GEMM + all-reduce; -1: on whenever the tensor-parallel degree is above 1")
     p.add_argument("--force-reshard", action="store_true",
                    help="stage outputs leave sharded on the hidden dimension and enter the next stage sharded on "
                         "the batch, so every microbatch crosses the boundary through a layout-changing reshard")
@@ -180,6 +184,8 @@ def main():
     args.schedule = args.schedule or default_schedule
     if pp * dp * tp != n:
         raise SystemExit(f"pp{pp} x dp{dp} x tp{tp} != {n} GPUs")
+    sp = (tp > 1 and not cfg.n_experts and not args.force_reshard) if args.sp < 0 else bool(args.sp)
+    cfg.sequence_parallel = cfg.vocab_parallel = sp
     if args.force_reshard and pp > 1:
         per_stage = cfg.n_layers // pp
         cfg.hidden_sharded_after = tuple(s * per_stage - 1 for s in range(1, pp))
@@ -333,7 +339,7 @@ def main():
                                 f"{cfg.n_heads}q/{cfg.n_kv_heads}kv heads, ffn {cfg.d_ff}, vocab {cfg.vocab})",
                        "global_batch": global_batch, "seq_len": seq, "microbatch": mb,
                        "layers_per_stage": lps, "parallelism": f"pp{pp}xdp{dp}xtp{tp}" + ("+fsdp" if args.fsdp else "")
-                                      + ("+forced-reshard" if args.force_reshard else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
+                                      + ("+forced-reshard" if args.force_reshard else "") + ("+sp" if sp else ""), "schedule": args.schedule, "optimizer": "AdamW (fp32 master)",
                        "l2": "working set (>= 13 GB of weights per step) far exceeds the 126 MB L2; no flush needed"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
@@ -341,7 +347,7 @@ def main():
             "gpu_launches": launches, "library_kernel_calls": lib_calls,
             "tflops_per_gpu": round(flops / (ms / args.steps / 1e3) / n / 1e12, 1),
             "loss": round(loss_val, 4), "compile_s": round(compile_s, 1), "kernel_status": status,
-            "fused_gemm_allreduce_calls": sum(o.calls for o in getattr(getattr(exe, "_fused_tp", None), "_ops", {}).values()),
+            "fused_gemm_collective_calls": sum(o.calls for o in getattr(getattr(exe, "_fused_tp", None), "_ops", {}).values()),
             "impl": "ours",
         }
         print(json.dumps(out), flush=True)

@@ -251,7 +251,8 @@ def build_program(cap: Captured, plan: dict, template: dict, fast_ops: Optional[
             instrs.append(Instr(0, fn, args, kwargs, n["outputs"], None if single else slots, nid))
             shared = n["attrs"].get("shared_axes")
             if shared is not None and not single_device and json.loads(shared):
-                from ..ops.moe import CTX_OPS
+                from ..ops import moe as _moe  # noqa: F401  (registers its entries)
+                from ..ops.mm_ops import CTX_OPS
                 if op in CTX_OPS:
                     instrs[-1].kind = 8
                     instrs[-1].extra = (CTX_OPS[op][0], json.loads(shared))

@@ -350,6 +350,30 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
   reinterpret_cast<uint4*>(dgu + t * 2 * F + F)[v] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
 }
 
+struct CeCombineArgs {
+  const float* stats[8];
+  int nranks;
+};
+__global__ void __launch_bounds__(256)
+    ce_combine_kernel(CeCombineArgs a, const int64_t* __restrict__ targets, float* __restrict__ stats2,
+                      float* __restrict__ loss, int64_t rows) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float m[8], s[8], tl = 0.f, mx = -INFINITY;
+  for (int r = 0; r < a.nranks; ++r) {
+    // written by another GPU: read past L1
+    m[r] = __ldcg(a.stats[r] + row * 3);
+    s[r] = __ldcg(a.stats[r] + row * 3 + 1);
+    tl += __ldcg(a.stats[r] + row * 3 + 2);
+    mx = fmaxf(mx, m[r]);
+  }
+  float se = 0.f;
+  for (int r = 0; r < a.nranks; ++r) se += (m[r] == -INFINITY) ? 0.f : s[r] * __expf(m[r] - mx);
+  stats2[row * 2] = mx;
+  stats2[row * 2 + 1] = se;
+  loss[row] = targets[row] >= 0 ? logf(se) + mx - tl : 0.f;
+}
+
 // ----------------------------------------------------------- cross-entropy
 // One block per row. Pass 1: online max / sum-exp. Pass 2 (optional): write
 // dlogits = (softmax - onehot) * grad_scale in place of the logits.
@@ -658,6 +682,22 @@ int mm_cross_entropy(void* logits, const int64_t* targets, float* loss, float* s
   cross_entropy_kernel<<<static_cast<unsigned>(rows), CE_THREADS, 0, stream>>>(
       static_cast<__nv_bfloat16*>(logits), targets, loss, stats_out, stats_in, V, ld, vocab_start,
       grad_scale, write_grad);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
+
+// Combines the per-shard softmax statistics of a vocabulary-sharded cross-entropy: stats[r] is
+// rank r's [rows, 3] array of (max, sum-exp relative to that max, target logit or 0) - local
+// memory for this rank, peer memory for the others. Writes the global (max, sum-exp) per row
+// to stats2 [rows, 2] and the loss per row (0 for ignored rows).
+int mm_ce_combine(const int64_t* stats, int nranks, const int64_t* targets, float* stats2, float* loss,
+                  int64_t rows, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (nranks < 1 || nranks > 8) return -2;
+  CeCombineArgs a;
+  for (int r = 0; r < nranks; ++r) a.stats[r] = reinterpret_cast<const float*>(stats[r]);
+  a.nranks = nranks;
+  ce_combine_kernel<<<blocks_for(rows, 256), 256, 0, stream>>>(a, targets, stats2, loss, rows);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -165,9 +165,12 @@ int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathe
   const int num_m = M / GEMM_BM;
   int grid;
   if (pair) {
-    const int num_tiles = ((M + 2 * GEMM_BM - 1) / (2 * GEMM_BM)) * ((N + GEMM_BN - 1) / GEMM_BN);
-    const int max_pairs = ds->sm_count / 2;
-    grid = 2 * (num_tiles < max_pairs ? num_tiles : max_pairs);
+    // the same number of pairs the launch below will use: every launched CTA's helper warps
+    // contribute to each block's arrival count
+    const int pairs = b_mn ? pair_kernel_pairs<false, true, AllGatherHook>(M, N, ds->sm_count)
+                           : pair_kernel_pairs<false, false, AllGatherHook>(M, N, ds->sm_count);
+    if (pairs < 1) return -1;
+    grid = 2 * pairs;
   } else {
     const int num_tiles = num_m * ((N + GEMM_BN - 1) / GEMM_BN);
     grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;

@@ -261,23 +261,52 @@ __global__ void __launch_bounds__(G2_THREADS + 32 * Hook::kAuxWarps, 1)
   }
 }
 
-// Launches the pair kernel: clusters of two CTAs, at most one pair per two SMs.
+// Number of CTA pairs the kernel runs for an M x N problem on the current device: one per output
+// tile, but never more than can be resident at the same time (hooks whose CTAs wait for one
+// another - the all-gather prologue, the peers of a fused collective - rely on every launched
+// pair running). The residency limit comes from the occupancy query for clusters of two and is
+// cached per device. Returns 0 on failure.
+template <bool A_MN, bool B_MN, class Hook>
+static int pair_kernel_pairs(int M, int N, int sm_count) {
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, Hook>;
+  constexpr int smem_bytes = G2_SMEM_BYTES + Hook::kStageBytes;
+  static_assert(smem_bytes <= 232448, "shared memory of the paired GEMM exceeds the CTA limit");
+  static int resident[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 0;
+  if (resident[dev] == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return 0;
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2 * (sm_count / 2), 1, 1);
+    q.blockDim = dim3(G2_THREADS + 32 * Hook::kAuxWarps, 1, 1);
+    q.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    q.attrs = qa;
+    q.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &q) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = sm_count / 2;      // the query is advisory: fall back to one pair per two SMs
+    }
+    resident[dev] = clusters < sm_count / 2 ? clusters : sm_count / 2;
+  }
+  const int num_tiles = ((M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((N + G2_BN - 1) / G2_BN);
+  return num_tiles < resident[dev] ? num_tiles : resident[dev];
+}
+
+// Launches the pair kernel: clusters of two CTAs, at most as many as are resident together.
 template <bool A_MN, bool B_MN, class Hook>
 static int launch_pair_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const Hook& hook, int M, int N, int K,
                               int sm_count, int* status, cudaStream_t stream) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, Hook>;
   constexpr int smem_bytes = G2_SMEM_BYTES + Hook::kStageBytes;
-  static_assert(smem_bytes <= 232448, "shared memory of the paired GEMM exceeds the CTA limit");
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) return -1;
-    configured[dev] = true;
-  }
-  const int num_tiles = ((M + 2 * G2_BM - 1) / (2 * G2_BM)) * ((N + G2_BN - 1) / G2_BN);
-  const int max_pairs = sm_count / 2;
-  const int pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
+  const int pairs = pair_kernel_pairs<A_MN, B_MN, Hook>(M, N, sm_count);
+  if (pairs < 1) return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(G2_THREADS + 32 * Hook::kAuxWarps, 1, 1);

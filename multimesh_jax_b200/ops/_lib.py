@@ -31,6 +31,7 @@ _SIGS = {
     "mm_swiglu_bwd": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
     "mm_cross_entropy": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int64, c_int, c_float,
                                  c_int, _P]),
+    "mm_ce_combine": (c_int, [_P, c_int, _P, _P, _P, c_int64, _P]),
     "mm_embedding_fwd": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
     "mm_embedding_bwd": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, _P]),
     "mm_add_bf16": (c_int, [_P, _P, _P, c_int64, _P]),

@@ -336,6 +336,70 @@ def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, grad_scal
     return loss
 
 
+def cross_entropy_stats(logits: torch.Tensor, targets: torch.Tensor, vocab_start: int) -> torch.Tensor:
+    """First pass of a vocabulary-sharded cross-entropy: per row (max, sum-exp relative to that
+    max, logit of the target if it lies in this shard else 0) of this shard's logits [rows, V_local]."""
+    rows, V = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        mx = lf.max(dim=-1).values
+        se = torch.exp(lf - mx[:, None]).sum(-1)
+        local = targets - vocab_start
+        has = (targets >= 0) & (local >= 0) & (local < V)
+        tl = torch.where(has, lf.gather(1, local.clamp(0, V - 1)[:, None]).squeeze(1), torch.zeros_like(mx))
+        return torch.stack([mx, se, tl], dim=1)
+    stats = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+    rc = _lib.load().mm_cross_entropy(logits.data_ptr(), targets.data_ptr(), None, stats.data_ptr(), None, rows, V,
+                                      logits.stride(0), vocab_start, 0.0, 0, _stream())
+    _lib.check(rc, "mm_cross_entropy")
+    _count()
+    return stats
+
+
+def cross_entropy_combine(all_stats, targets: torch.Tensor, stat_ptrs=None):
+    """Global (max, sum-exp) per row [rows, 2] and the loss per row from the shards' statistics.
+    ``all_stats``: list of [rows, 3] tensors (CPU path), or with ``stat_ptrs`` the device
+    addresses of the shards' arrays - this GPU's and its peers' - read by one kernel."""
+    rows = targets.numel()
+    if stat_ptrs is None:
+        st = torch.stack(list(all_stats), dim=0)                       # [g, rows, 3]
+        mx = st[..., 0].max(dim=0).values
+        se = (st[..., 1] * torch.exp(st[..., 0] - mx)).sum(0)
+        tl = st[..., 2].sum(0)
+        loss = torch.where(targets >= 0, torch.log(se) + mx - tl, torch.zeros_like(mx))
+        return torch.stack([mx, se], dim=1).contiguous(), loss
+    import ctypes
+    dev = targets.device
+    stats2 = torch.empty((rows, 2), dtype=torch.float32, device=dev)
+    loss = torch.empty(rows, dtype=torch.float32, device=dev)
+    arr = (ctypes.c_int64 * len(stat_ptrs))(*stat_ptrs)
+    rc = _lib.load().mm_ce_combine(arr, len(stat_ptrs), targets.data_ptr(), stats2.data_ptr(), loss.data_ptr(), rows,
+                                   _stream())
+    _lib.check(rc, "mm_ce_combine")
+    _count()
+    return stats2, loss
+
+
+def cross_entropy_apply(logits: torch.Tensor, targets: torch.Tensor, stats2: torch.Tensor, vocab_start: int,
+                        grad_scale: float) -> None:
+    """Second pass: overwrites this shard's logits with d(loss * grad_scale)/dlogits given the
+    global statistics."""
+    rows, V = logits.shape
+    if not logits.is_cuda:
+        lf = logits.float()
+        g = torch.exp(lf - stats2[:, :1]) / stats2[:, 1:2]
+        local = targets - vocab_start
+        has = (targets >= 0) & (local >= 0) & (local < V)
+        g[has.nonzero().flatten(), local[has]] -= 1.0
+        g = g * grad_scale * (targets >= 0)[:, None]
+        logits.copy_(g.to(logits.dtype))
+        return
+    rc = _lib.load().mm_cross_entropy(logits.data_ptr(), targets.data_ptr(), None, None, stats2.data_ptr(), rows, V,
+                                      logits.stride(0), vocab_start, grad_scale, 1, _stream())
+    _lib.check(rc, "mm_cross_entropy")
+    _count()
+
+
 # ---------------------------------------------------------------- embedding
 def embedding_fwd(table: torch.Tensor, ids: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
     V, D = table.shape

@@ -447,12 +447,44 @@ def _rule_attention_bwd(node, ins, outs):
 
 @register_shard_rule("mm_ops.cross_entropy.default")
 def _rule_cross_entropy(node, ins, outs):
+    # slots: 0 logits, 1 targets | 2 loss, 3 dlogits. The vocabulary dimension may be sharded: the
+    # per-device form of the operator (``cross_entropy_local``) then exchanges the softmax
+    # statistics with the other shards itself, so the loss is not a partial sum over that axis.
     r = len(ins[0])
     classes = []
     for d in range(r - 1):
         classes.append(_cls([(0, d), (1, d), (3, d)], reduced=[0]))
-    classes.append(_cls([(0, r - 1), (3, r - 1)], no_shard=True))
+    vocab = _cls([(0, r - 1), (3, r - 1)])
+    vocab["shares_axes"] = True
+    classes.append(vocab)
     return {"classes": classes}
+
+
+def cross_entropy_local(ctx, axes, key, logits, targets, scale: float):
+    """This device's share of a cross-entropy whose vocabulary is sharded over the mesh axes
+    ``axes``: local statistics (max, sum-exp, target logit), exchange with the other shards
+    (peer memory on GPUs: every rank's combine kernel reads the others' statistics directly),
+    then the gradient of the local slice from the global statistics. Returns (loss summed over
+    the local rows times ``scale`` - the same on every shard -, d loss / d logits slice)."""
+    group, me = ctx.group_of(axes)
+    if len(group) == 1:
+        return cross_entropy_impl(logits, targets, scale, False)
+    V_local = logits.shape[-1]
+    buf = logits.clone()
+    flat = buf.view(-1, V_local)
+    tflat = targets.reshape(-1)
+    stats = K.cross_entropy_stats(flat, tflat, me * V_local)
+    stats2, loss_rows = ctx.combine_softmax_stats(stats, tflat, group, key)
+    K.cross_entropy_apply(flat, tflat, stats2, me * V_local, scale)
+    return loss_rows.sum() * scale, buf
+
+
+# Operators whose per-device form talks to the other devices of the task over the mesh axes of the
+# index class marked ``shares_axes``: operator name -> (function(ctx, axes, key, *args), slot of the
+# tensor argument that carries that class). Other modules add their own entries.
+CTX_OPS: Dict[str, tuple] = {
+    "mm_ops.cross_entropy.default": (cross_entropy_local, 0),
+}
 
 
 @register_shard_rule("mm_ops.embedding.default")

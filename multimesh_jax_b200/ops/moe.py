@@ -288,7 +288,9 @@ def moe_ffn_bwd_local(ctx, axes, key, dy, x, wr, wgu, wdown, top_k: int):
 
 # operators whose per-device form talks to the other devices of the task: name -> (function,
 # index of the tensor argument whose leading dimension tells over which mesh axes)
-CTX_OPS: Dict[str, tuple] = {
+from .mm_ops import CTX_OPS  # noqa: E402  (the registry lives with the operator definitions)
+
+CTX_OPS.update({
     "mm_ops.moe_ffn.default": (moe_ffn_local, 2),
     "mm_ops.moe_ffn_bwd.default": (moe_ffn_bwd_local, 3),
-}
+})

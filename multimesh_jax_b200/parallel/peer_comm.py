@@ -91,6 +91,26 @@ class PeerGroupComm:
         self.calls += 1
         return out
 
+    SMALL_BYTES = 1 << 20
+
+    def share_small(self, x: torch.Tensor):
+        """Makes a small tensor (statistics, counts; at most ``SMALL_BYTES``) readable by the
+        group: copies it into this rank's slot of a double-buffered symmetric tile and passes a
+        flag barrier. Returns the device addresses of every member's copy, in group order; they
+        stay valid until this rank's next call but one."""
+        a = self.arena
+        nbytes = x.numel() * x.element_size()
+        if nbytes > self.SMALL_BYTES:
+            raise ValueError("share_small is for small tensors")
+        if not hasattr(self, "_small"):
+            self._small = [a.alloc((self.SMALL_BYTES,), torch.uint8) for _ in range(2)]
+            self._small_calls = 0
+        self._small_calls += 1
+        buf = self._small[self._small_calls & 1]
+        buf.peer(a.rank)[:nbytes].view(x.dtype).view(x.shape).copy_(x)
+        self.barrier()
+        return [buf.ptr(r) for r in self.ranks]
+
     def supports_scatter(self, x: torch.Tensor, dim: int) -> bool:
         """Reduce-scatter along ``dim`` as a pull of this rank's share: the share of every outer
         index must be a whole number of 16-byte vectors."""

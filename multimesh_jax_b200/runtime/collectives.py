@@ -312,6 +312,17 @@ class DeviceCtx:
         y = mm_ops.linear_dgrad_impl(x, w) if is_dgrad else mm_ops.linear_impl(x, w)
         return self.all_reduce(y, axes, key)
 
+    def combine_softmax_stats(self, stats: torch.Tensor, targets: torch.Tensor, group: List[int], key):
+        """Global softmax statistics of a vocabulary-sharded cross-entropy from this shard's
+        [rows, 3] array (see ``kernels.cross_entropy_stats``): returns ([rows, 2], loss per row)."""
+        from ..ops import kernels as K
+        if self.topology.kind == "dist" and self.peer_comm is not None and stats.is_cuda:
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            ptrs = comm.share_small(stats)
+            return K.cross_entropy_combine(None, targets, stat_ptrs=ptrs)
+        parts = self._exchange(("ce", key), group, stats)
+        return K.cross_entropy_combine(parts, targets)
+
     def _scatter_slice(self, full: torch.Tensor, src: dict, dst: dict) -> torch.Tensor:
         """This device's tile of layout ``dst`` cut out of its tile of the coarser layout ``src``."""
         local = _local_only_chunks(src, dst)

@@ -289,3 +289,57 @@ def test_zero_bubble_schedule_on_four_llama_stages():
         if not t["noncritical"]:                  # nothing on the critical path waits for a weight-gradient task
             assert not any(producer.get(v) in noncritical for v in t["inputs"])
     exe.shutdown()
+
+
+@pytest.mark.parametrize("pp,dp,tp,vocab", [(1, 1, 2, False), (1, 1, 2, True), (2, 2, 2, True), (1, 1, 4, True)])
+def test_sequence_parallel_tensor_parallel_step_matches_eager(pp, dp, tp, vocab):
+    """Sequence-parallel layout of the tensor-parallel region: the residual stream and the norms
+    are sharded on the sequence over the `model` axis; the compiler turns "partial projection ->
+    all-reduce -> slice" into reduce-scatters and the layout changes in front of the column-
+    parallel projections into all-gathers, and the lowering fuses each of them into the GEMM
+    beside it. With a vocabulary-sharded output projection the loss exchanges its softmax
+    statistics instead of gathering the logits. Results equal the eager step."""
+    import collections
+    cfg = _cfg(n_layers=2 * pp, n_heads=4, n_kv_heads=4 if tp > 2 else 2, d_model=64, d_ff=96, vocab=128)
+    cfg.sequence_parallel = True
+    cfg.vocab_parallel = vocab
+    B, S, MB = 8, 16, 4
+    params = llama.init_params(cfg)
+    opt_state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=LR), seq_len=S, global_batch=B, microbatch_size=MB)
+    mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp)
+    with mesh:
+        exe = mm.compile_function(step, (params, opt_state, tokens, labels, cos, sin), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        loss_ref, p_ref, _ = step(params, opt_state, tokens, labels, cos, sin)
+    loss, p_mm, _ = exe(params, opt_state, tokens, labels, cos, sin)
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        _adam_close(a.full_tensor(), b, LR)
+    g = exe.cap.graph
+    loop_ops, kinds = collections.Counter(), collections.Counter()
+    for t in exe.plan["templates"]:
+        if "_loop" in t["name"]:
+            loop_ops.update(g.node(n)["op"] for n in t["nodes"])
+            kinds.update(i.kind for i in exe.programs[t["id"]].instrs)
+    layers = cfg.n_layers
+    # per layer: attention-out and FFN-down forward, QKV and gate/up input gradients (+ the head's)
+    assert loop_ops["mm.reduce_scatter"] >= 4 * layers
+    assert loop_ops["mm.all_reduce"] == 0                  # no activation is all-reduced any more
+    gathers = sum(1 for t in exe.plan["templates"] for n in t["nodes"] if "gather_dim" in g.node(n)["attrs"])
+    assert gathers >= 4 * layers
+    # the lowering fused them: kind 10 = GEMM + reduce-scatter, kind 11 = all-gather + GEMM
+    assert kinds[10] >= 4 * layers and kinds[11] >= 4 * layers
+    assert kinds[9] == 0
+    if vocab:
+        # the logits are never gathered: their only consumer is the loss operator in its exchanging form
+        assert kinds[8] >= pp // pp
+        head = [s_ for s_ in exe.output_shardings()][0]
+        assert head is not None
+    log = "\n".join(exe.plan.get("log", []))
+    assert "collective folding" in log
+    exe.shutdown()
