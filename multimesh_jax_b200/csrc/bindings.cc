@@ -10,6 +10,7 @@
 #include "mmgraph/passes.h"
 #include "mmgraph/schedule.h"
 #include "mmgraph/sharding.h"
+#include "mmrt/cuda_context.h"
 #include "mmrt/runtime.h"
 
 namespace py = pybind11;
@@ -570,6 +571,109 @@ PYBIND11_MODULE(_mm_C, m) {
            py::arg("kind"), py::arg("name"), py::arg("device") = -1, py::arg("count") = 1, py::arg("delay_ms") = 0)
       .def("hazard_report", [](const mmrt::ThreadedContext& c) { return mmrt::CheckHazards(c.Submissions()); })
       .def_property_readonly("device_bytes_high_water", &mmrt::ThreadedContext::device_bytes_high_water);
+
+  // CUDA streams, events and the scratch tile behind the same submission interface. With
+  // `fake=True` every CUDA call goes to a recording stand-in (no GPU needed): `fake_trace()`
+  // returns what was called.
+  struct PyCudaContext {
+    std::unique_ptr<mmrt::FakeGpuApi> fake;
+    std::unique_ptr<mmrt::CudaContext> ctx;
+  };
+  py::class_<PyCudaContext>(m, "CudaContext")
+      .def(py::init([](std::vector<int> local_devices, std::vector<int> ordinals, std::vector<uintptr_t> compute_streams,
+                       bool fake, bool record_submissions) {
+             auto p = std::make_unique<PyCudaContext>();
+             if (fake) p->fake = std::make_unique<mmrt::FakeGpuApi>();
+             mmrt::GpuApi* api = fake ? static_cast<mmrt::GpuApi*>(p->fake.get()) : mmrt::CudaRuntimeApi();
+             p->ctx = std::make_unique<mmrt::CudaContext>(std::move(local_devices), std::move(ordinals),
+                                                          std::move(compute_streams), api, record_submissions);
+             return p;
+           }),
+           py::arg("local_devices"), py::arg("ordinals"), py::arg("compute_streams"), py::arg("fake") = false,
+           py::arg("record_submissions") = false)
+      .def("create_execute_task",
+           [](PyCudaContext& c, int device, const std::vector<std::pair<int, int>>& reads,
+              const std::vector<std::pair<int, int>>& writes, py::object body, const std::string& name, bool strict,
+              int priority, int step, int stream) {
+             mmrt::Body b = WrapBody(std::move(body));
+             mmrt::ExecuteOptions o = Options(name, strict, priority, step);
+             o.stream = stream;
+             py::gil_scoped_release rel;
+             return c.ctx->CreateExecuteTask(device, Tiles(reads), Tiles(writes), std::move(b), o);
+           },
+           py::arg("device"), py::arg("reads"), py::arg("writes"), py::arg("body"), py::arg("name") = "",
+           py::arg("strict_ordering") = false, py::arg("priority") = 0, py::arg("step") = 0, py::arg("stream") = 0)
+      .def("reshard",
+           [](PyCudaContext& c, int device, const std::vector<std::pair<int, int>>& reads,
+              const std::vector<std::pair<int, int>>& writes, py::object body, const std::string& name, int step,
+              int stream) {
+             mmrt::Body b = WrapBody(std::move(body));
+             mmrt::ExecuteOptions o = Options(name, false, 0, step);
+             o.stream = stream;
+             py::gil_scoped_release rel;
+             return c.ctx->Reshard(device, Tiles(reads), Tiles(writes), std::move(b), o);
+           },
+           py::arg("device"), py::arg("reads"), py::arg("writes"), py::arg("body"), py::arg("name") = "reshard",
+           py::arg("step") = 0, py::arg("stream") = 1)
+      .def("create_store", [](PyCudaContext& c, int b, int d, int64_t bytes, bool host) { c.ctx->CreateStore(b, d, bytes, host); })
+      .def("free_store", [](PyCudaContext& c, int b, int d) { c.ctx->FreeStore(b, d); })
+      .def("open_window", [](PyCudaContext& c) { py::gil_scoped_release rel; c.ctx->OpenWindow(); })
+      .def("close_window", [](PyCudaContext& c) { c.ctx->CloseWindow(); })
+      .def("run_after_all_tasks", [](PyCudaContext& c, py::object body) {
+        mmrt::Body b = WrapBody(std::move(body));
+        py::gil_scoped_release rel;
+        c.ctx->RunAfterAllTasks(std::move(b));
+      })
+      .def("start_timer", [](PyCudaContext& c, const std::string& n) { c.ctx->StartTimer(n); })
+      .def("stop_timer", [](PyCudaContext& c, const std::string& n) { c.ctx->StopTimer(n); })
+      .def("mark_profile", [](PyCudaContext& c, const std::string& n) { c.ctx->MarkProfile(n); })
+      .def("wait_all", [](PyCudaContext& c) {
+        std::string msg;
+        mmrt::Status st = c.ctx->WaitAll(&msg);
+        return std::make_pair(st, msg);
+      })
+      .def("reset_error", [](PyCudaContext& c) { c.ctx->ResetError(); })
+      .def("shutdown", [](PyCudaContext& c) { py::gil_scoped_release rel; c.ctx->Shutdown(); })
+      .def("synchronize", [](PyCudaContext& c) { py::gil_scoped_release rel; return c.ctx->Synchronize(); })
+      .def("event_log", [](const PyCudaContext& c) { return LogToList(c.ctx->EventLog()); })
+      .def("clear_event_log", [](PyCudaContext& c) { c.ctx->ClearEventLog(); })
+      .def("timer_results_ms", [](PyCudaContext& c) { return c.ctx->TimerResultsMs(); })
+      .def("stream_handle", [](const PyCudaContext& c, int device, int kind) { return c.ctx->StreamHandle(device, kind); })
+      .def("set_task_ranges", [](PyCudaContext& c, bool on) { c.ctx->set_task_ranges(on); })
+      .def("reserve_scratch", [](PyCudaContext& c, int device, int64_t bytes) { return c.ctx->ReserveScratch(device, bytes); })
+      .def("scratch_bytes", [](const PyCudaContext& c, int device) { return c.ctx->ScratchBytes(device); })
+      .def("edges", [](const PyCudaContext& c) {
+        py::list out;
+        for (auto& e : c.ctx->Edges()) {
+          py::dict d;
+          d["from_task"] = e.from_task;
+          d["to_task"] = e.to_task;
+          d["device"] = e.device;
+          d["from_stream"] = e.from_stream;
+          d["to_stream"] = e.to_stream;
+          d["from_name"] = e.from_name;
+          d["to_name"] = e.to_name;
+          out.append(d);
+        }
+        return out;
+      })
+      .def("inject_fault",
+           [](PyCudaContext& c, const std::string& kind, const std::string& name, int device, int count, int delay_ms) {
+             mmrt::FaultSpec f;
+             f.kind = kind == "drop" ? mmrt::FaultSpec::kDrop : (kind == "delay" ? mmrt::FaultSpec::kDelay : mmrt::FaultSpec::kThrow);
+             f.name_substring = name;
+             f.device = device;
+             f.remaining = count;
+             f.delay_ms = delay_ms;
+             c.ctx->InjectFault(f);
+           },
+           py::arg("kind"), py::arg("name"), py::arg("device") = -1, py::arg("count") = 1, py::arg("delay_ms") = 0)
+      .def("hazard_report", [](const PyCudaContext& c) { return mmrt::CheckHazards(c.ctx->Submissions()); })
+      .def("fake_trace", [](const PyCudaContext& c) { return c.fake ? c.fake->trace : std::vector<std::string>(); })
+      .def("fake_stream_priorities", [](const PyCudaContext& c) { return c.fake ? c.fake->stream_priorities : std::vector<int>(); })
+      .def_property_readonly("open_windows", [](const PyCudaContext& c) { return c.ctx->open_windows(); })
+      .def_property_readonly("host_blocks", [](const PyCudaContext& c) { return c.ctx->host_blocks(); })
+      .def_property_readonly("device_bytes_high_water", [](const PyCudaContext& c) { return c.ctx->device_bytes_high_water(); });
 
   py::class_<mmrt::MockContext>(m, "MockContext")
       .def(py::init<int>())

@@ -7,14 +7,16 @@
 // c / g of rank c % g (one chunk per rank = plain concatenation; for a [B, S, .] activation
 // sharded on S a chunk is the S / g rows of one sequence).
 //
-// One kernel does both. Two helper warps per CTA pull the row shards - the peers' over NVLink
+// One kernel does both. Helper warps of every CTA pull the row shards - the peers' over NVLink
 // with plain 16-byte loads, the own one from local memory - into a local [M, K] buffer, 128-row
 // block by block, and count their arrivals per block; the TMA producer of the tcgen05 main
-// loop waits (bounded) for a block's count before it loads the block's tiles from that local
-// buffer. Row blocks are visited starting with this rank's own shard and then the peers' in
-// ring order, so the tensor cores start on local rows while the first remote rows are still
-// in flight, and the transfer of block i+1 overlaps the math of block i. TMA only ever reads
-// this GPU's memory; no multicast is used.
+// loop waits (bounded) for a remote block's count before it loads the block's tiles from that
+// local buffer. The tensor cores start with this rank's own rows, which the producer loads
+// straight from the shard through a second tensor map (nothing to wait for, no copy on the
+// critical path), while the helper warps - six per CTA, eight 16-byte loads in flight per lane -
+// bring in the peers' rows in the order the main loop will ask for them; the own rows are
+// copied into the gathered buffer last, for the caller. TMA only ever reads this GPU's memory;
+// no multicast is used.
 #include <cstdlib>
 
 #include "gemm_core.cuh"
@@ -24,25 +26,36 @@
 namespace mm {
 
 constexpr int AG_MAX_RANKS = 8;
+constexpr int AG_ROUND = 4;   // row blocks the helper warps of the grid copy at the same time
 
 struct AllGatherHook {
   void* C;
   int64_t ldc;
   bool vec_ok;
+  CUtensorMap tm_own;                // this rank's own row shard [M/g, K]: its blocks are loaded from where they are
   const uint4* a_src[AG_MAX_RANKS];  // row shard of every rank (own: local; others: peer memory), [M/g, K]
-  uint4* gathered;                   // local [M, K]
+  uint4* gathered;                   // local [M, K]: the gathered matrix (an output; the peers' rows are read from it)
   int* ready;                        // local, one counter per 128-row block, never reset
-  int target;                        // value a block's counter reaches when all its pieces of this call arrived
+  int target;                        // value a remote block's counter reaches when all its pieces of this call arrived
   int nranks, me;
   int blocks_per_shard;              // 128-row blocks per rank shard
   int chunk_blocks;                  // 128-row blocks per chunk
   int num_m;
+  int workers_per_block;             // helper warps that copy (and signal) each row block
 
   static constexpr int kStageBytes = 0;
-  static constexpr int kAuxWarps = 2;
+  static constexpr int kAuxWarps = 6;
   struct State {};
   __device__ __forceinline__ void finish(State&, uint8_t*, int, int, int, int, int*) const {}
 
+  // gathered row block -> (hop along the ring from this rank, block inside that rank's shard)
+  __device__ __forceinline__ void locate(int blk, int& hop, int& in_shard) const {
+    const int chunk = blk / chunk_blocks, within = blk - chunk * chunk_blocks;
+    const int owner = chunk % nranks;
+    hop = owner - me;
+    if (hop < 0) hop += nranks;
+    in_shard = (chunk / nranks) * chunk_blocks + within;
+  }
   // scheduler index -> row block of the gathered matrix: the blocks of this rank's own shard
   // first, then the peers' in ring order
   __device__ __forceinline__ int map_m(int m_blk) const {
@@ -53,10 +66,23 @@ struct AllGatherHook {
     const int chunk = in_shard / chunk_blocks, within = in_shard - chunk * chunk_blocks;
     return (chunk * nranks + owner) * chunk_blocks + within;
   }
-  __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
+  __device__ __forceinline__ bool own_block(int m_blk) const {
+    if (m_blk >= num_m) return false;
+    return (m_blk / chunk_blocks) % nranks == me;
+  }
+  // own rows come straight from the shard (no copy on the critical path), the peers' from `gathered`
+  __device__ __forceinline__ const CUtensorMap* a_map(int m_blk, const CUtensorMap* dflt) const {
+    return own_block(m_blk) ? &tm_own : dflt;
+  }
+  __device__ __forceinline__ int a_row(int m_blk) const {
+    if (!own_block(m_blk)) return m_blk * GEMM_BM;
+    int hop, in_shard;
+    locate(m_blk, hop, in_shard);
+    return in_shard * GEMM_BM;
+  }
 
   __device__ __forceinline__ bool before_tile_loads(int m_blk, int, int* err) const {
-    if (m_blk >= num_m) return true;
+    if (m_blk >= num_m || own_block(m_blk)) return true;
     unsigned long long t0 = 0, limit = 0;
     for (uint32_t i = 0;; ++i) {
       int v;
@@ -80,33 +106,44 @@ struct AllGatherHook {
     return false;
   }
 
-  // Helper warps: copy this CTA's slice of every row block, in the order the blocks are used.
+  // Helper warps copy the row blocks into `gathered` - the peers' blocks first, in the order the
+  // tensor cores will want them (they are what the main loop waits for), this rank's own blocks
+  // last (only the caller needs them in `gathered`). Blocks are taken AG_ROUND at a time: in a
+  // round every helper warp of the grid copies one contiguous piece of one of the round's blocks
+  // with up to eight 16-byte loads in flight per lane, so a round costs about one NVLink round
+  // trip whatever the block size, and `workers_per_block` warps signal each block.
   __device__ __forceinline__ void aux(int w, int lane, int M, int K, int* err) const {
-    (void)err;
-    const int64_t vec_per_block = static_cast<int64_t>(GEMM_BM) * K / 8;
-    const int64_t vec_per_shard = vec_per_block * blocks_per_shard;
-    const int workers = gridDim.x * kAuxWarps;
+    (void)err; (void)M;
     const int wid = blockIdx.x * kAuxWarps + w;
-    const int64_t per = (vec_per_block + workers - 1) / workers;
-    (void)vec_per_shard;
-    for (int i = 0; i < num_m; ++i) {
+    if (wid >= workers_per_block * AG_ROUND) return;
+    const int slot = wid % AG_ROUND, sub = wid / AG_ROUND;
+    const int64_t vec_per_block = static_cast<int64_t>(GEMM_BM) * K / 8;
+    const int64_t per = (vec_per_block + workers_per_block - 1) / workers_per_block;
+    const int64_t lo = sub * per, hi = min(vec_per_block, lo + per);
+    for (int k = slot; k < num_m; k += AG_ROUND) {
+      int i = k + blocks_per_shard;                    // scheduler index: remote blocks, then own ones
+      if (i >= num_m) i -= num_m;
       const int blk = map_m(i);
       const int hop = i / blocks_per_shard;
       int owner = me + hop;
       if (owner >= nranks) owner -= nranks;
       const uint4* src = a_src[owner] + static_cast<int64_t>(i - hop * blocks_per_shard) * vec_per_block;
       uint4* dst = gathered + static_cast<int64_t>(blk) * vec_per_block;
-      const int64_t lo = wid * per, hi = min(vec_per_block, lo + per);
-      int64_t v = lo + lane;
-      for (; v + 96 < hi; v += 128) {     // four loads in flight per lane
-        const uint4 x0 = __ldcg(src + v), x1 = __ldcg(src + v + 32), x2 = __ldcg(src + v + 64), x3 = __ldcg(src + v + 96);
-        dst[v] = x0; dst[v + 32] = x1; dst[v + 64] = x2; dst[v + 96] = x3;
+      for (int64_t v = lo + lane; v < hi; v += 256) {
+        uint4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (v + 32 * u < hi) x[u] = __ldcg(src + v + 32 * u);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (v + 32 * u < hi) dst[v + 32 * u] = x[u];
       }
-      for (; v < hi; v += 32) dst[v] = __ldcg(src + v);
-      fence_proxy_async_all();
-      __threadfence();
-      __syncwarp();
-      if (lane == 0) atomicAdd(ready + blk, 1);
+      if (hop != 0) {
+        fence_proxy_async_all();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(ready + blk, 1);
+      }
     }
   }
 
@@ -176,13 +213,19 @@ int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathe
     grid = num_tiles < ds->sm_count ? num_tiles : ds->sm_count;
   }
   AllGatherHook hook;
+  // this rank's own rows are read where they are: same box as the map of the gathered matrix
+  rc = encode_tmap_2d_bf16(&hook.tm_own, reinterpret_cast<const void*>(a_src[me]), K, M / nranks,
+                           static_cast<uint64_t>(K) * 2, GEMM_BK, GEMM_BM);
+  if (rc) return rc;
   hook.C = C;
   hook.ldc = ldc;
   hook.vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && (ldc % 8 == 0);
   for (int r = 0; r < nranks; ++r) hook.a_src[r] = reinterpret_cast<const uint4*>(a_src[r]);
   hook.gathered = static_cast<uint4*>(gathered);
   hook.ready = ready;
-  hook.target = *target + grid * AllGatherHook::kAuxWarps;
+  hook.workers_per_block = grid * AllGatherHook::kAuxWarps / AG_ROUND;
+  if (hook.workers_per_block < 1) return -2;
+  hook.target = *target + hook.workers_per_block;
   *target = hook.target;
   hook.nranks = nranks;
   hook.me = me;

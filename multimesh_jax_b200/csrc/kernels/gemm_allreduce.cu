@@ -52,6 +52,7 @@ struct AllReduceHook {
 
   __device__ __forceinline__ bool before_tile_loads(int, int, int*) const { return true; }
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
+  __device__ __forceinline__ const CUtensorMap* a_map(int, const CUtensorMap* dflt) const { return dflt; }
 
   // out[tile] += sum of the peers' partials of that tile (rows of warp q).
   __device__ __forceinline__ void reduce_tile(int m_blk, int n_blk, int q, int lane, int M, int N, int* err) const {
@@ -223,6 +224,7 @@ struct ReduceScatterHook {
   };
   __device__ __forceinline__ bool before_tile_loads(int, int, int*) const { return true; }
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
+  __device__ __forceinline__ const CUtensorMap* a_map(int, const CUtensorMap* dflt) const { return dflt; }
 
   // out[tile of my shard] += the other ranks' partials of that tile (rows of warp q)
   __device__ __forceinline__ void reduce_tile(int local_m, int n_blk, int q, int lane, int Ms, int N, int* err) const {

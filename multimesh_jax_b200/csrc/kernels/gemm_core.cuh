@@ -136,6 +136,9 @@ struct PlainHook {
   __device__ __forceinline__ bool before_tile_loads(int, int, int*) const { return true; }
   // Row of A (in the tensor map's coordinates) where tile row-block m_blk starts.
   __device__ __forceinline__ int a_row(int m_blk) const { return m_blk * GEMM_BM; }
+  // Tensor map the rows of block m_blk are loaded through (hooks whose A lives in two buffers
+  // carry a second map; the kernel's own one is the default).
+  __device__ __forceinline__ const CUtensorMap* a_map(int, const CUtensorMap* dflt) const { return dflt; }
   // Drains one 128x256 accumulator: warp `q` owns TMEM lanes [32q, 32q+32), i.e. rows
   // m_blk*128 + 32q + lane. `t_base` already points at that lane quarter.
   static constexpr int kStageBytes = 0;  // no shared-memory staging in the epilogue
@@ -167,7 +170,7 @@ struct PlainHook {
 template <bool A_MN, bool B_MN, class Hook>
 __global__ void __launch_bounds__(GEMM_THREADS + 32 * Hook::kAuxWarps, 1)
     gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     GemmShape shape, Hook hook, int* __restrict__ err) {
+                     GemmShape shape, const __grid_constant__ Hook hook, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -222,17 +225,18 @@ __global__ void __launch_bounds__(GEMM_THREADS + 32 * Hook::kAuxWarps, 1)
         m_blk = hook.map_m(m_blk);
         if (!hook.before_tile_loads(m_blk, n_blk, err)) { ok = false; break; }
         const int a_row0 = hook.a_row(m_blk);
+        const CUtensorMap* mapA = hook.a_map(m_blk, &tmA);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, err, MM_ERR_WAIT_EMPTY)) { ok = false; break; }
           mbar_expect_tx(&full[stage], GEMM_A_STAGE + GEMM_B_STAGE);
           uint8_t* a_dst = sA + stage * GEMM_A_STAGE;
           uint8_t* b_dst = sB + stage * GEMM_B_STAGE;
           if (!A_MN) {
-            tma_load_2d(a_dst, &tmA, &full[stage], kb * GEMM_BK, a_row0);
+            tma_load_2d(a_dst, mapA, &full[stage], kb * GEMM_BK, a_row0);
           } else {
 #pragma unroll
             for (int i = 0; i < GEMM_BM / 64; ++i)
-              tma_load_2d(a_dst + i * (GEMM_BK * 128), &tmA, &full[stage], a_row0 + i * 64,
+              tma_load_2d(a_dst + i * (GEMM_BK * 128), mapA, &full[stage], a_row0 + i * 64,
                           kb * GEMM_BK);
           }
           if (!B_MN) {

@@ -101,7 +101,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
 template <bool A_MN, bool B_MN, class Hook>
 __global__ void __launch_bounds__(G2_THREADS + 32 * Hook::kAuxWarps, 1)
     gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      GemmShape shape, Hook hook, int* __restrict__ err) {
+                      GemmShape shape, const __grid_constant__ Hook hook, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   // the pair's descriptors name the same offsets in both CTAs: align on the shared-window offset
   const uint32_t raw = smem_u32(smem_raw);
@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(G2_THREADS + 32 * Hook::kAuxWarps, 1)
         const int m128 = hook.map_m(m_blk * 2 + static_cast<int>(rank));   // this CTA's 128-row block
         if (!hook.before_tile_loads(m128, n_blk, err)) { ok = false; break; }
         const int a_row0 = hook.a_row(m128);
+        const CUtensorMap* mapA = hook.a_map(m128, &tmA);
         const int b_row0 = n_blk * G2_BN + static_cast<int>(rank) * G2_BNH;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, err, MM_ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -171,11 +172,11 @@ __global__ void __launch_bounds__(G2_THREADS + 32 * Hook::kAuxWarps, 1)
           uint8_t* a_dst = sA + stage * G2_A_STAGE;
           uint8_t* b_dst = sB + stage * G2_B_STAGE;
           if (!A_MN) {
-            tma_load_2d_pair(a_dst, &tmA, bar, kb * G2_BK, a_row0);
+            tma_load_2d_pair(a_dst, mapA, bar, kb * G2_BK, a_row0);
           } else {
 #pragma unroll
             for (int i = 0; i < G2_BM / 64; ++i)
-              tma_load_2d_pair(a_dst + i * (G2_BK * 128), &tmA, bar, a_row0 + i * 64, kb * G2_BK);
+              tma_load_2d_pair(a_dst + i * (G2_BK * 128), mapA, bar, a_row0 + i * 64, kb * G2_BK);
           }
           if (!B_MN) {
             tma_load_2d_pair(b_dst, &tmB, bar, kb * G2_BK, b_row0);

@@ -892,6 +892,35 @@ bool ReduceScatterCreator(CompileState& s) {
         n.attrs["to"] = want->ToJson().dump();
         g.value(out).sharding = *want;
         ++scatters;
+        continue;
+      }
+      // (c) the readers take the reduced value as it is and slice it themselves, all to the same
+      // finer layout (the reader's task had already settled on the coarse layout when the slice
+      // was inserted): reduce-scatter here, and the slices become the identity
+      bool all_slices = true;
+      std::string to_json;
+      for (int u : users[out]) {
+        const Node& un = g.node(u);
+        if (un.dead || un.op != "mm.spmd_reshard" || un.task == n.task) { all_slices = false; break; }
+        if (to_json.empty()) to_json = un.attrs.at("to");
+        else if (to_json != un.attrs.at("to")) { all_slices = false; break; }
+      }
+      if (all_slices && !to_json.empty()) {
+        const ShardedShape to = ShardedShape::FromJson(Json::parse(to_json));
+        if (IsScatterOf(from, to, axes, &dim)) {
+          n.op = "mm.reduce_scatter";
+          n.attrs["dim"] = std::to_string(dim);
+          n.attrs["from"] = from.ToJson().dump();
+          n.attrs["to"] = to.ToJson().dump();
+          g.value(out).sharding = to;
+          for (int u : std::vector<int>(users[out])) {
+            Node& un = g.node(u);
+            SetInputSharding(s, un.task, out, to);
+            g.ReplaceAllUses(un.outputs[0], out);
+            un.dead = true;
+          }
+          ++scatters;
+        }
       }
     }
   }

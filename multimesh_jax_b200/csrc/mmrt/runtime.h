@@ -49,6 +49,7 @@ struct ExecuteOptions {
   int priority = 0;
   int kind = 0;  // 0 task, 1 reshard, 2 host callback, 3 marker
   int step = 0;
+  int stream = 0;  // contexts with several streams per device: 0 compute, 1 communication, 2 auxiliary
 };
 
 struct TaskRecord {  // one entry of the event log

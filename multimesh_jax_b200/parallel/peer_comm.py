@@ -178,9 +178,13 @@ class PeerCommRegistry:
     def __init__(self, arena: symm.SymmetricArena):
         self.arena = arena
         self._ops: Dict[Tuple[int, ...], PeerGroupComm] = {}
-        self._stage: Dict[int, tuple] = {}
+        self._stage: Dict[int, Dict[int, tuple]] = {}     # stream kind -> size class -> staging pair
 
-    def get(self, ranks: Tuple[int, ...]) -> PeerGroupComm:
-        if ranks not in self._ops:
-            self._ops[ranks] = PeerGroupComm(self.arena, ranks, self._stage)
-        return self._ops[ranks]
+    def get(self, ranks: Tuple[int, ...], stream_kind: int = 0) -> PeerGroupComm:
+        """The group's communicator for tasks of one stream kind. Collectives queued on different
+        streams can overlap on the GPU, so each kind gets its own flags, epochs and staging tiles;
+        the members of a group ask in the same program order, so the arena offsets agree."""
+        key = (tuple(ranks), stream_kind)
+        if key not in self._ops:
+            self._ops[key] = PeerGroupComm(self.arena, ranks, self._stage.setdefault(stream_kind, {}))
+        return self._ops[key]

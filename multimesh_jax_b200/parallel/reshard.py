@@ -214,8 +214,11 @@ class PeerReshard:
         return True
 
     def run(self, key, d: int, src_tile: Optional[torch.Tensor], chunks: List[dict], src: dict, dst: dict,
-            comm: CommStream):
-        """This rank's part of one use of ``key``. Returns ``(destination tile or None, event)``."""
+            comm: Optional[CommStream]):
+        """This rank's part of one use of ``key``. With a :class:`CommStream` the work is queued
+        on that side stream and ``(destination tile or None, event)`` is returned; with ``None``
+        it is queued on the current stream (the runtime context chose it and orders the readers
+        of the tile behind it) and the event is ``None``."""
         symm, arena, slot = self.symm, self.arena, self.slots[key]
         slot["uses"] += 1
         e = slot["uses"]
@@ -227,9 +230,14 @@ class PeerReshard:
         out = None
         if mine_dst:
             out = torch.empty(dst["shard_size"], dtype=DTYPE_FROM_NAME[dst["dtype"]], device=dev)
-        comm.reap()
-        comm.stream.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(comm.stream):
+        if comm is None:
+            import contextlib
+            scope = contextlib.nullcontext()
+        else:
+            comm.reap()
+            comm.stream.wait_stream(torch.cuda.current_stream(dev))
+            scope = torch.cuda.stream(comm.stream)
+        with scope:
             if mine_src:
                 readers = sorted({c["dst_device"] for c in mine_src})
                 if e > 2:   # the staging tile of this parity was last read in use e - 2
@@ -247,7 +255,10 @@ class PeerReshard:
                     last = i + 64 >= len(recs)
                     symm.reshard_pull(recs[i:i + 64], esz, arena, done_flags=done if last else (), done_value=e,
                                        counter=self.counter)
-            ev = torch.cuda.Event()
-            ev.record(comm.stream)
-        comm.pending.append((ev, [t for t in (src_tile, out) if t is not None]))
+            ev = None
+            if comm is not None:
+                ev = torch.cuda.Event()
+                ev.record(comm.stream)
+        if comm is not None:
+            comm.pending.append((ev, [t for t in (src_tile, out) if t is not None]))
         return out, ev

@@ -207,6 +207,7 @@ class DeviceCtx:
         self.device_start = 0
         self.mesh_dims: Sequence[int] = (1,)
         self.key_prefix: Tuple = ()
+        self.stream_kind = 0      # 0 compute, 1 communication, 2 auxiliary stream of the runtime context
 
     # ------------------------------------------------------------------
     def _exchange(self, key, group_ordinals: List[int], tensor: torch.Tensor) -> List[torch.Tensor]:
@@ -262,7 +263,7 @@ class DeviceCtx:
             return x
         if self.topology.kind == "dist":
             if self.peer_comm is not None:
-                comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+                comm = self.peer_comm.get(tuple(self.device_start + o for o in group), self.stream_kind)
                 if comm.supports(x):
                     return comm.all_reduce(x, out=x if in_place and x.is_contiguous() else None)
             import torch.distributed as dist
@@ -317,7 +318,7 @@ class DeviceCtx:
         [rows, 3] array (see ``kernels.cross_entropy_stats``): returns ([rows, 2], loss per row)."""
         from ..ops import kernels as K
         if self.topology.kind == "dist" and self.peer_comm is not None and stats.is_cuda:
-            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group), self.stream_kind)
             ptrs = comm.share_small(stats)
             return K.cross_entropy_combine(None, targets, stat_ptrs=ptrs)
         parts = self._exchange(("ce", key), group, stats)
@@ -346,7 +347,7 @@ class DeviceCtx:
         if len(group) == 1:
             return x
         if self.topology.kind == "dist" and self.peer_comm is not None:
-            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group), self.stream_kind)
             if comm.supports_scatter(x, dim):
                 return comm.reduce_scatter(x, dim, group.index(me))
         return self._scatter_slice(self.all_reduce(x, axes, key), src, dst)
@@ -436,7 +437,7 @@ class DeviceCtx:
                 out[d_box] = x[s_box]
             return out
         if self.topology.kind == "dist" and self.peer_comm is not None:
-            comm = self.peer_comm.get(tuple(self.device_start + o for o in group))
+            comm = self.peer_comm.get(tuple(self.device_start + o for o in group), self.stream_kind)
             from ..parallel.reshard import PeerReshard
             from .. import _mm_C
             if x.is_cuda and x.numel() * x.element_size() >= comm.MIN_BYTES and \

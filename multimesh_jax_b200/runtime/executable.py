@@ -153,10 +153,36 @@ class Executable:
             local = any(topology.is_local(d) for d in self._template_devices(t))
             if local or topology.kind != "dist":
                 self.programs[t["id"]] = build_program(cap, plan, t, fast_ops, acc_fusable)
+        # A process that drives exactly one CUDA device gets the context that owns the device's
+        # streams: tasks on the caller's compute stream, reshards and once-per-step collectives on
+        # a communication stream, ordered by CUDA events wherever the dependence analysis finds a
+        # pair of conflicting accesses on different streams (MM_CUDA_CONTEXT=0: everything on one
+        # stream through the host-side context).
+        self._streams: Dict[int, Any] = {}
+        self._cuda_ctx = False
         if context is None:
+            import os
             inline = len(topology.local_devices) == 1
-            context = _mm_C.ThreadedContext(topology.local_devices, inline, False)
+            dev0 = topology.torch_device(topology.local_devices[0])
+            if inline and dev0.type == "cuda" and os.environ.get("MM_CUDA_CONTEXT", "1") != "0":
+                d0 = topology.local_devices[0]
+                ordinal = dev0.index if dev0.index is not None else torch.cuda.current_device()
+                with torch.cuda.device(dev0):
+                    compute = torch.cuda.current_stream(dev0).cuda_stream
+                context = _mm_C.CudaContext([d0], [ordinal], [compute])
+                context.set_task_ranges(bool(state.knobs["task_ranges"]))
+                for kind in (1, 2):
+                    self._streams[kind] = torch.cuda.ExternalStream(context.stream_handle(d0, kind), device=dev0)
+                self._cuda_ctx = True
+            else:
+                context = _mm_C.ThreadedContext(topology.local_devices, inline, False)
         self.context = context
+        import os as _os
+        self._overlap_reduce = _os.environ.get("MM_OVERLAP_REDUCE", "1") != "0"
+        self._compute_stream = None
+        if self._cuda_ctx:
+            dev0 = topology.torch_device(topology.local_devices[0])
+            self._compute_stream = torch.cuda.current_stream(dev0)
         self.rendezvous = Rendezvous()
         self.dev_ctx = {d: DeviceCtx(topology, d, self.rendezvous) for d in topology.local_devices}
         topology.prepare_groups(sorted({(t["device_start"], tuple(t["mesh_dims"])) for t in plan["templates"]}))
@@ -295,6 +321,8 @@ class Executable:
         one-process-per-GPU CUDA job; MM_COMM_STREAM=0 keeps messages on the compute stream)."""
         import os
         topo = self.topology
+        if self._cuda_ctx:
+            return None       # the runtime context owns the communication stream and orders the readers
         if topo.kind != "dist" or topo.torch_device(d).type != "cuda" or os.environ.get("MM_COMM_STREAM", "1") == "0":
             return None
         if d not in self._comm:
@@ -453,6 +481,12 @@ class Executable:
         in_keys = [(buf[s], d) for s in in_ids] + [(buf[s], d) for s, m in zip(out_ids, modes) if m == 2]
 
         name = op["name"]
+        # once-per-step reductions that are tasks of their own run on the communication stream:
+        # the reduction of one gradient overlaps the optimizer update of the previous ones
+        kind = 0
+        if self._cuda_ctx and name.endswith("_reduce") and self._overlap_reduce:
+            kind = 1
+        side = self._streams.get(kind)
 
         def body():
             if state.knobs["task_ranges"]:
@@ -470,9 +504,16 @@ class Executable:
             return run()
 
         def run():
+            if side is None:
+                return run_on_current_stream()
+            with torch.cuda.stream(side):
+                return run_on_current_stream()
+
+        def run_on_current_stream():
             dctx.device_start = dev_start
             dctx.mesh_dims = mesh_dims
             dctx.key_prefix = (step, k)
+            dctx.stream_kind = kind
             if dctx.torch_device.type == "cuda":
                 torch.cuda.set_device(dctx.torch_device)
             if arrival:
@@ -484,6 +525,9 @@ class Executable:
             # inputs read for the last time here are handed over: the program frees each one
             # right after its last use instead of keeping it alive for the whole task
             ins = [tiles[s].pop(d) if s in dying else tiles[s][d] for s in in_ids]
+            if side is not None:
+                for t_in in ins:            # allocated on another stream: keep its memory until this one is done
+                    t_in.record_stream(side)
             for s, t_in, want in zip(in_ids, ins, in_shapes):
                 if tuple(t_in.shape) != want:
                     raise RuntimeError(f"task {name}: store {s} ({stores[s]['shape']['key']}) holds a tile of shape "
@@ -499,11 +543,18 @@ class Executable:
                     tiles[s][d] = o.to(acc_dtypes[oi], copy=True)
                 else:
                     tiles[s][d] = o
+                if side is not None and isinstance(tiles[s][d], torch.Tensor) and tiles[s][d].is_cuda:
+                    tiles[s][d].record_stream(torch.cuda.default_stream(dctx.torch_device) if self._compute_stream is None
+                                              else self._compute_stream)
                 if s in root_tiles:
                     root_tiles[s][d] = tiles[s][d]
 
         self.launches += 1
-        self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step)
+        if self._cuda_ctx:
+            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step,
+                                             kind)
+        else:
+            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step)
 
     # ------------------------------------------------------------------ reshards
     def _reshard_plan(self, src_sid: int, dst_sid: int) -> dict:
@@ -535,20 +586,32 @@ class Executable:
                 writes = [(buf[dst_sid], d)] if mine_dst else []
 
                 def body(d=d, mine_dst=mine_dst, mine_src=mine_src):
+                    side = self._streams.get(1) if self._cuda_ctx else None
+                    if side is None:
+                        return move(d, mine_dst, mine_src, None)
+                    with torch.cuda.stream(side):       # the context ordered this stream behind the producer
+                        return move(d, mine_dst, mine_src, side)
+
+                def move(d, mine_dst, mine_src, side):
                     prev = self._arrival.get((self.buffer_of[src_sid], d))
                     if prev is not None:     # the source itself arrived by message
                         torch.cuda.current_stream().wait_event(prev)
                     pr = self._peer_reshard
                     key = (self.buffer_of[src_sid], self.buffer_of[dst_sid])
+                    src_tile = tiles[src_sid].get(d)
+                    if side is not None and src_tile is not None and src_tile.is_cuda:
+                        src_tile.record_stream(side)
                     if pr is not None and pr.slots.get(key) is not None:
-                        out, ev = pr.run(key, d, tiles[src_sid].get(d), mine_src + [c for c in mine_dst if c not in mine_src],
+                        out, ev = pr.run(key, d, src_tile, mine_src + [c for c in mine_dst if c not in mine_src],
                                          src_shape, dst_shape, self._comm_stream(d))
                     else:
-                        out, ev = run_reshard_dist(topo, d, tiles[src_sid].get(d), mine_src, mine_dst, dst_shape,
+                        out, ev = run_reshard_dist(topo, d, src_tile, mine_src, mine_dst, dst_shape,
                                                    self._comm_stream(d))
                     if ev is not None and out is not None:
                         self._arrival[(self.buffer_of[dst_sid], d)] = ev
                     if out is not None:
+                        if side is not None and self._compute_stream is not None:
+                            out.record_stream(self._compute_stream)   # allocated here, read by tasks of the compute stream
                         tiles[dst_sid][d] = out
                         if dst_sid in root_tiles:
                             root_tiles[dst_sid][d] = out
@@ -569,7 +632,10 @@ class Executable:
                     with torch.profiler.record_function(label):
                         inner()
             self.launches += 1
-            self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
+            if self._cuda_ctx:
+                self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step, 1)
+            else:
+                self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
 
     # ------------------------------------------------------------------ misc
     def _check_kernel_status(self, block: bool) -> None:

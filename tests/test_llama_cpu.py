@@ -200,11 +200,18 @@ def test_data_parallel_and_fsdp_steps_match_eager(axes, fsdp):
     for t in exe.plan["templates"]:
         for n in t["nodes"]:
             op = g.node(n)["op"]
-            if op in ("mm.all_reduce", "mm.spmd_reshard", "mm.relayout"):
+            if op in ("mm.all_reduce", "mm.reduce_scatter", "mm.spmd_reshard", "mm.relayout"):
                 kind = "loop" if "_loop" in t["name"] else ("reduce" if t["name"].endswith("_reduce") else "other")
                 by_task[(kind, op)] = by_task.get((kind, op), 0) + 1
     # every weight gradient is reduced over `data` once per step, after the loop
-    assert by_task.get(("reduce", "mm.all_reduce"), 0) >= 6 * cfg.n_layers
+    hoisted = by_task.get(("reduce", "mm.all_reduce"), 0) + by_task.get(("reduce", "mm.reduce_scatter"), 0)
+    assert hoisted >= 6 * cfg.n_layers
+    if fsdp:
+        # a rank only needs the gradient of the parameter shard it owns: the reductions of the
+        # sharded weights are reduce-scatters (half the traffic of an all-reduce at two ranks)
+        assert by_task.get(("reduce", "mm.reduce_scatter"), 0) >= 4 * cfg.n_layers
+    else:
+        assert by_task.get(("reduce", "mm.reduce_scatter"), 0) == 0
     w = p_mm["layers"][0]["wgu"]
     data_axis = 1 if axes[0] == 1 else 0   # index of `data` inside the stage's sub-mesh
     data_axis = list(mesh.slice(stage=0).axis_names).index("data")

@@ -305,3 +305,72 @@ def test_temporaries_are_handed_over_only_when_their_readers_are_ordered():
             assert all(op["strict_ordering"] for op in readers)
             assert ops[k] is readers[-1]
     exe.shutdown()
+
+
+# ---------------------------------------------------------------------------- CUDA context (against a recording stand-in)
+def _fake_cuda_context(record=True):
+    return C.CudaContext([0], [0], [0], fake=True, record_submissions=record)
+
+
+def test_cuda_context_turns_cross_stream_conflicts_into_event_waits():
+    """Tasks on one stream are ordered by the stream; a conflicting pair on two streams gets an
+    event wait (and only such pairs do): producer (compute) -> reshard (communication) ->
+    consumer (compute), then a task that overwrites the reshard's source."""
+    c = _fake_cuda_context()
+    assert c.fake_stream_priorities() == [-5, 0]           # communication stream: highest priority; auxiliary: lowest
+    comm, aux = c.stream_handle(0, 1), c.stream_handle(0, 2)
+    assert c.stream_handle(0, 0) == 0 and comm != aux
+    ran = []
+    c.open_window()
+    c.create_execute_task(0, [], [(1, 0)], lambda: ran.append("produce"), "produce", True, 10, 0, 0)
+    c.create_execute_task(0, [(1, 0)], [(5, 0)], lambda: ran.append("same-stream"), "same-stream", True, 10, 0, 0)
+    c.reshard(0, [(1, 0)], [(2, 0)], lambda: ran.append("reshard"), "reshard", 0, 1)
+    c.create_execute_task(0, [(2, 0)], [(3, 0)], lambda: ran.append("consume"), "consume", True, 10, 0, 0)
+    c.create_execute_task(0, [], [(1, 0)], lambda: ran.append("overwrite"), "overwrite", False, 0, 0, 0)
+    c.close_window()
+    assert ran == ["produce", "same-stream", "reshard", "consume", "overwrite"]     # bodies run at submission, in plan order
+    edges = [(e["from_name"], e["to_name"], e["from_stream"], e["to_stream"]) for e in c.edges()]
+    assert ("produce", "reshard", 0, 1) in edges            # read after write across streams
+    assert ("reshard", "consume", 1, 0) in edges            # read after write back on the compute stream
+    assert ("reshard", "overwrite", 1, 0) in edges          # write after read
+    assert not any(e[0] == "produce" and e[1] == "same-stream" for e in edges)     # same stream: no event
+    trace = c.fake_trace()
+    waits = [t for t in trace if t.startswith("wait")]
+    assert f"wait s{comm} e1" in waits                      # the reshard's stream waits for the producer's event
+    assert any(t.startswith("wait s0 ") for t in waits)
+    # the window's end joins the communication stream into the compute stream
+    assert trace[-2].startswith("wait s0 ") and trace[-1].startswith("record ") and trace[-1].endswith(" s0")
+    assert c.hazard_report() == ""                          # every conflicting pair is ordered by a recorded edge
+    c.shutdown()
+
+
+def test_cuda_context_windows_scratch_and_status():
+    c = _fake_cuda_context(record=False)
+    for step in range(12):                                  # the stand-in's events complete at once: never more than 8 open
+        c.open_window()
+        c.create_execute_task(0, [], [(1, 0)], lambda: None, "t", False, 0, step, 0)
+        c.close_window()
+        assert c.open_windows <= 8
+    assert c.host_blocks == 0
+    base = c.reserve_scratch(0, 1000)
+    assert base != 0 and c.scratch_bytes(0) >= 1000
+    assert c.reserve_scratch(0, 500) == base                # never shrinks, never reallocates for a smaller task
+    bigger = c.reserve_scratch(0, 8 << 20)
+    assert bigger != 0 and c.scratch_bytes(0) >= (8 << 20)
+    assert any(t.startswith("sync s") for t in c.fake_trace())    # the old tile was in use: streams drained before the free
+    # a body that raises fails its step: later tasks of the step are skipped, the status names the cause
+    ran = []
+
+    def boom():
+        raise RuntimeError("kernel launch refused")
+    c.create_execute_task(0, [], [(1, 0)], boom, "bad", False, 0, 99, 0)
+    c.create_execute_task(0, [(1, 0)], [(2, 0)], lambda: ran.append(1), "after", False, 0, 99, 0)
+    status, msg = c.wait_all()
+    assert status == C.Status.TASK_FAILED and "refused" in msg and ran == []
+    c.reset_error()
+    c.create_execute_task(0, [], [(1, 0)], lambda: ran.append(2), "next-step", False, 0, 100, 0)
+    assert ran == [2] and c.wait_all()[0] == C.Status.OK
+    c.inject_fault("throw", "victim", -1, 1, 0)
+    c.create_execute_task(0, [], [(1, 0)], lambda: ran.append(3), "victim", False, 0, 101, 0)
+    assert c.wait_all()[0] == C.Status.INJECTED_FAULT
+    c.shutdown()
