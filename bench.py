@@ -7,7 +7,8 @@ AdamW, random init, synthetic token ids) through the MPMD compiler and runtime.
 
 Weak scaling: 8 sequences of 2048 tokens per GPU and step (global batch 64 at N = 8, the
 configuration named by the baseline), microbatches of 4 sequences per data-parallel rank.
-Default layouts: N = 1 single device; N = 2 data parallel; N = 4 four pipeline stages with
+Default layouts: N = 1 single device; N = 2 tensor parallel with sequence-sharded activations
+(GEMM + reduce-scatter and all-gather + GEMM kernels; the fastest measured layout on 2 GPUs); N = 4 four pipeline stages with
 the zero-bubble-H2 schedule (the fastest measured layout on 4 GPUs); N = 8 the layout the
 baseline names, 4 pipeline stages x tensor parallel 2, 1F1B with 16 microbatches. --pp / --dp / --tp / --fsdp / --force-reshard / --model select the others
 (Llama-3-8B with FSDP and a layout-changing stage boundary, Mixtral-8x7B with expert
@@ -132,7 +133,7 @@ def default_layout(n: int):
     """(pipeline stages, data parallel, tensor parallel, schedule) used when no layout flag is given:
     the fastest measured layout per GPU count, except at 8 GPUs where the named layout and schedule
     are kept - 4 stages x TP2, 1F1B with 16 microbatches."""
-    return {1: (1, 1, 1, "1f1b"), 2: (1, 2, 1, "1f1b"), 4: (4, 1, 1, "zero-bubble-h2"),
+    return {1: (1, 1, 1, "1f1b"), 2: (1, 1, 2, "1f1b"), 4: (4, 1, 1, "zero-bubble-h2"),
             8: (4, 1, 2, "1f1b")}.get(n, (1, n, 1, "1f1b"))
 
 

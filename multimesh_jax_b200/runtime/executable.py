@@ -275,9 +275,11 @@ class Executable:
         if want_rs:
             nbytes += PeerReshard.required_bytes(self.plan, self.buffer_of) + (1 << 20)
         if want_comm:
-            # staging pairs of the in-task collectives: one pair per power-of-two size class
+            # staging pairs of the in-task collectives: one pair per power-of-two size class and per
+            # stream kind (once-per-step reductions run on the communication stream with tiles of their own)
             sizes = set()
             for t in self.plan["templates"]:
+                kind = 1 if (self._cuda_ctx and self._overlap_reduce and t["name"].endswith("_reduce")) else 0
                 for n in t["nodes"]:
                     nd = g.node(n)
                     if nd["op"] in ("mm.all_reduce", "mm.reduce_scatter", "mm.spmd_reshard"):
@@ -286,8 +288,8 @@ class Executable:
                         for s_ in (v["sharding"]["shard_size"] if v["sharding"] else v["shape"]):
                             nb *= s_
                         if nb >= (256 << 10):
-                            sizes.add(1 << max(20, (nb - 1).bit_length()))
-            nbytes += 2 * sum(sizes) + (1 << 20)
+                            sizes.add((kind, 1 << max(20, (nb - 1).bit_length())))
+            nbytes += 2 * sum(sz for _, sz in sizes) + (4 << 20)
         if want_moe:
             from ..parallel.ep import PeerMoE, PeerMoERegistry
             worst = 0

@@ -20,7 +20,7 @@ def _plan(*flags):
 
 
 @pytest.mark.parametrize("n,parallelism,schedule,microbatches", [
-    (1, "pp1xdp1xtp1", "1f1b", 2), (2, "pp1xdp2xtp1", "1f1b", 2), (4, "pp4xdp1xtp1", "zero-bubble-h2", 8),
+    (1, "pp1xdp1xtp1", "1f1b", 2), (2, "pp1xdp1xtp2", "1f1b", 4), (4, "pp4xdp1xtp1", "zero-bubble-h2", 8),
     (8, "pp4xdp1xtp2", "1f1b", 16)])
 def test_default_layouts_compile_for_the_full_llama2_shape(n, parallelism, schedule, microbatches):
     p = _plan("--gpus", str(n))
