@@ -11,6 +11,7 @@
 #include "mmgraph/schedule.h"
 #include "mmgraph/sharding.h"
 #include "mmrt/cuda_context.h"
+#include "mmrt/launcher.h"
 #include "mmrt/runtime.h"
 
 namespace py = pybind11;
@@ -674,6 +675,56 @@ PYBIND11_MODULE(_mm_C, m) {
       .def_property_readonly("open_windows", [](const PyCudaContext& c) { return c.ctx->open_windows(); })
       .def_property_readonly("host_blocks", [](const PyCudaContext& c) { return c.ctx->host_blocks(); })
       .def_property_readonly("device_bytes_high_water", [](const PyCudaContext& c) { return c.ctx->device_bytes_high_water(); });
+
+  // ------------------------------------------------------------ native task launcher
+  py::class_<mmrt::KernelProgram>(m, "KernelProgram")
+      .def(py::init<>())
+      // args: list of tuples ("p", slot, offset[, scalar, scale]) | ("i", value) | ("f", value) | ("s",)
+      .def("add_call",
+           [](mmrt::KernelProgram& p, uintptr_t fn, const std::string& name, const py::list& args) {
+             std::vector<mmrt::LaunchArg> out;
+             for (auto item : args) {
+               py::tuple t = item.cast<py::tuple>();
+               const std::string kind = t[0].cast<std::string>();
+               mmrt::LaunchArg a;
+               if (kind == "p") {
+                 a.kind = mmrt::LaunchArg::kPtr;
+                 a.slot = t[1].cast<int>();
+                 a.value = t.size() > 2 ? t[2].cast<int64_t>() : 0;
+                 if (t.size() > 4) {
+                   a.scalar = t[3].cast<int>();
+                   a.scalar_scale = t[4].cast<int64_t>();
+                 }
+               } else if (kind == "i") {
+                 a.kind = mmrt::LaunchArg::kInt;
+                 a.value = t[1].cast<int64_t>();
+               } else if (kind == "f") {
+                 a.kind = mmrt::LaunchArg::kFloat;
+                 a.fvalue = t[1].cast<double>();
+               } else if (kind == "s") {
+                 a.kind = mmrt::LaunchArg::kStream;
+               } else {
+                 throw std::runtime_error("unknown launch argument kind '" + kind + "'");
+               }
+               out.push_back(a);
+             }
+             p.AddCall(fn, name, std::move(out));
+           })
+      .def("launch",
+           [](const mmrt::KernelProgram& p, const std::vector<uintptr_t>& bases, const std::vector<int64_t>& scalars,
+              uintptr_t stream) {
+             std::string err;
+             int rc;
+             {
+               py::gil_scoped_release rel;
+               rc = p.Launch(bases, scalars, stream, &err);
+             }
+             if (rc != 0) throw std::runtime_error("native task launch failed: " + err);
+           })
+      .def("__len__", &mmrt::KernelProgram::size)
+      .def("describe", &mmrt::KernelProgram::Describe)
+      .def_property_readonly("launches", &mmrt::KernelProgram::launches);
+  m.def("selftest_kernel_address", [] { return reinterpret_cast<uintptr_t>(&mmrt::mmrt_selftest_axpy); });
 
   py::class_<mmrt::MockContext>(m, "MockContext")
       .def(py::init<int>())

@@ -39,6 +39,15 @@ _SIGS = {
     "mm_adamw": (c_int, [_P, _P, _P, _P, _P, c_int64, c_float, c_float, c_float, c_float,
                          c_float, c_int, c_float, _P, _P]),
     "mm_sumsq_f32": (c_int, [_P, c_int64, _P, _P]),
+    "mm_memcpy_d2d": (c_int, [_P, _P, c_int64, _P]),
+    "mm_zero": (c_int, [_P, c_int64, _P]),
+    "mm_f32_to_bf16": (c_int, [_P, _P, c_int64, _P]),
+    "mm_bf16_to_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
+    "mm_accumulate_f32": (c_int, [_P, _P, c_int64, _P]),
+    "mm_fill_f32": (c_int, [_P, c_float, c_int64, _P]),
+    "mm_sum_scale_f32": (c_int, [_P, c_int64, c_float, _P, _P]),
+    "mm_scale_bf16": (c_int, [_P, _P, _P, c_int64, _P]),
+    "mm_add_i64": (c_int, [_P, c_int64, _P, c_int64, _P]),
 }
 
 
