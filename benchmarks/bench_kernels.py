@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m multimesh_jax_b200.ops.bench_kernels [gemm|elementwise|all]``.
+"""Kernel micro-benchmarks: ``python benchmarks/bench_kernels.py [gemm|elementwise|all]``.
 
 Each kernel is timed with CUDA events on the launching stream after warm-up,
 with an L2 flush (a write larger than the 126 MB L2) between timed iterations.
@@ -12,9 +12,11 @@ import json
 import os
 import sys
 
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 import torch
 
-from . import kernels as K
+from multimesh_jax_b200.ops import kernels as K
 
 
 def _peaks():

@@ -1,7 +1,7 @@
 """Cross-submesh reshard micro-benchmark.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
-        -m multimesh_jax_b200.parallel.bench_reshard [--max-mb 4096] [--pairs 1-1,2-2]
+        benchmarks/bench_reshard.py [--max-mb 4096] [--pairs 1-1,2-2]
 
 Tensors are bf16 ``[B, S, 8192]`` of N(0,1) values from 1 MB to 4 GB in powers of 4. For a
 pair ``M-N`` the source submesh is ranks ``[0, M)`` and the destination submesh ranks
@@ -21,6 +21,9 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 import torch.distributed as dist

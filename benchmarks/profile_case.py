@@ -1,6 +1,6 @@
 """One kernel, one small case, three launches - the program to put under a profiler.
 
-    python -m multimesh_jax_b200.ops.profile_case gemm|gemm_dgrad|gemm_wgrad (each also as <case>_pair)|gemm_allreduce_loopback|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
+    python benchmarks/profile_case.py gemm|gemm_dgrad|gemm_wgrad (each also as <case>_pair)|gemm_allreduce_loopback|flash_fwd|flash_bwd|rmsnorm_bwd|swiglu|adamw|cross_entropy
 
 Inputs are larger than the 126 MB L2 where the kernel is memory bound and a few hundred MB at
 most, so a full-metric capture of one launch finishes in seconds. Each case prints its
@@ -10,12 +10,15 @@ numbers in a profile can be checked against an unprofiled run of the same comman
 from __future__ import annotations
 
 import json
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 
-from . import attention
-from . import kernels as K
+from multimesh_jax_b200.ops import attention
+from multimesh_jax_b200.ops import kernels as K
 
 
 def _time(fn, launches=2):

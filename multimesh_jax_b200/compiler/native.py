@@ -138,6 +138,7 @@ class NativeProgram:
         self.out_block_bytes = 0
         self.scratch_bytes = 0
         # per template output: ("block", offset, shape, dtype) | ("input", index, shape) | ("acc", position)
+        # | ("slice", index, shape): rows [scalar, scalar + shape[0]) of input `index`
         self.outputs: List[tuple] = []
         self.acc_positions: List[int] = []      # output positions whose accumulator tile is a slot of the launch
         self.num_calls = 0
@@ -165,8 +166,7 @@ class _Builder:
     def new_value(self, vid: int, shape, dtype) -> Sym:
         """Storage for IR value ``vid``: inside the output block when it is a (non-accumulated)
         task output, else in the scratch tile."""
-        pos = self.out_pos.get(vid)
-        if pos is not None and self.accumulate[pos] == 0:
+        if vid in self.reaches_output:
             sym = Sym(self.SLOT_OUT, self.out_cursor, shape, dtype)
             self.out_cursor += _round(sym.nbytes)
             return sym
@@ -616,6 +616,15 @@ EMITTERS = {
 }
 
 
+# operators that may write a result over a dead operand: (tensor operand position, result position)
+_MAY_WRITE_OVER = {
+    "mm_ops.attention.default": ((0, 2),),
+    "mm_ops.add_rmsnorm_bwd.default": ((2, 0),),
+    "mm_ops.cross_entropy.default": ((0, 1),),
+    "mm_ops.adamw.default": ((0, 0), (1, 1), (2, 2), (3, 3)),
+}
+
+
 def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumulate: Sequence[int], have_acc: bool
                  ) -> NativeProgram:
     """The kernel program of one variant of ``template``: ``accumulate[k]`` is the accumulate
@@ -637,6 +646,26 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
         sh = val.get("sharding")
         shape = sh["shard_size"] if sh else val["shape"]
         b.env[v] = Sym(i, 0, shape, DTYPE_FROM_NAME[val["dtype"]])
+    # Values whose storage a task output ends up naming - directly, through view-like operators
+    # (autograd hands saved tensors on as detached aliases) or because an operator may write its
+    # result over them - are placed in the output block from the start, so no output is copied.
+    alias_parent: Dict[int, int] = {}
+    for ins in prog.instrs:
+        if ins.kind == 1 and isinstance(ins.args, int):
+            alias_parent[ins.outs[0]] = ins.args
+        elif ins.kind in (0, 6):
+            opn = g.node(ins.node_id)["op"]
+            ids_ = _tensor_ids_in_order(ins.args, ins.kwargs)
+            if EMITTERS.get(opn) in (_emit_view, _emit_alias) and ids_:
+                alias_parent[ins.outs[0]] = ids_[0]
+            for operand, result in _MAY_WRITE_OVER.get(opn, ()):
+                if operand < len(ids_) and result < len(ins.outs):
+                    alias_parent[ins.outs[result]] = ids_[operand]
+    b.reaches_output = {v for k, v in enumerate(prog.outputs) if accumulate[k] == 0}
+    for ins in reversed(prog.instrs):
+        for o in ins.outs or ():
+            if o in b.reaches_output and o in alias_parent:
+                b.reaches_output.add(alias_parent[o])
     # operand liveness inside the program, and operands other tasks still need
     last: Dict[int, int] = {}
     for idx, ins in enumerate(prog.instrs):
@@ -690,7 +719,13 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
             b.drop(v)
     # outputs
     for k, v in enumerate(prog.outputs):
-        sym = b.sym_of(v)          # raises for a microbatch slice: such an output keeps the interpreted program
+        if v in b.scaled:          # a microbatch slice of an input handed on as it is (token ids kept for the backward task)
+            sym = b.slice_sym(v)
+            if sym.slot >= b.n_in or sym.off != 0 or accumulate[k]:
+                raise NativeUnsupported("a microbatch slice of an intermediate is a task output")
+            b.np.outputs.append(("slice", sym.slot, sym.shape))
+            continue
+        sym = b.sym_of(v)
         mode = accumulate[k]
         if mode:
             fused = prog.fused_acc.get(k)

@@ -237,7 +237,66 @@ class Executable:
             st = plan["stores"][sid]
             if sid not in unsafe and st["kind"] == "TEMP" and st["alias_of"] < 0:
                 self._dying_inputs.setdefault(k, set()).add(sid)
+        self._build_native_programs()
         live_executables.add(self)
+
+    def _build_native_programs(self) -> None:
+        """Kernel programs for the templates that are nothing but calls into the kernel library
+        (see :mod:`multimesh_jax_b200.compiler.native`): their task bodies then run as one call into
+        the C++ launcher over memory planned ahead of time - task outputs carved from one block
+        per launch, intermediates at fixed offsets of the runtime context's scratch tile.
+        Templates with collectives, and anything on CPU devices, keep the interpreted program.
+        MM_NATIVE_TASKS=0 switches the native path off."""
+        import os
+        self._native: Dict[Tuple[int, bool], Any] = {}
+        self._native_why: Dict[int, str] = {}
+        self._scratch_base: Dict[int, int] = {}
+        self.native_launches = 0
+        if not self._cuda_ctx or os.environ.get("MM_NATIVE_TASKS", "1") == "0":
+            return
+        from ..compiler.native import NativeUnsupported, build_native
+        patterns: Dict[int, set] = {}
+        for op in self.plan["ops"]:
+            if op["kind"] == "task" and op["template"] in self.programs:
+                modes = tuple(op["accumulate"])
+                if any(m == 1 for m in modes) and any(m == 2 for m in modes):
+                    self._native_why[op["template"]] = "mixed first-write / accumulate outputs"
+                    patterns[op["template"]] = None
+                    continue
+                if patterns.get(op["template"], set()) is not None:
+                    patterns.setdefault(op["template"], set()).add((tuple(1 if m else 0 for m in modes), any(m == 2 for m in modes)))
+        scratch = 0
+        for t in self.plan["templates"]:
+            pats = patterns.get(t["id"])
+            if not pats:
+                continue
+            built = {}
+            try:
+                for classes, have_acc in pats:
+                    built[(t["id"], have_acc)] = build_native(self.cap, self.plan, t, self.programs[t["id"]], classes, have_acc)
+            except NativeUnsupported as e:
+                self._native_why[t["id"]] = str(e)
+                continue
+            self._native.update(built)
+            scratch = max([scratch] + [n.scratch_bytes for n in built.values()])
+        self.native_scratch_bytes = scratch
+        if self._native:
+            for d in self.topology.local_devices:
+                base = self.context.reserve_scratch(d, max(scratch, 1 << 20))
+                if not base:
+                    raise MemoryError(f"cannot reserve {scratch} bytes of task scratch on device {d}")
+                self._scratch_base[d] = base
+
+    def native_report(self) -> Dict[str, str]:
+        """Per template: ``native (<n> kernel calls)`` or why it keeps the interpreted program."""
+        out = {}
+        for t in self.plan["templates"]:
+            progs = [n for (tid, _), n in self._native.items() if tid == t["id"]]
+            if progs:
+                out[t["name"]] = f"native ({max(n.num_calls for n in progs)} kernel calls)"
+            else:
+                out[t["name"]] = "interpreted: " + self._native_why.get(t["id"], "not on a CUDA context")
+        return out
 
     def _setup_fused_tp(self) -> None:
         """One-process-per-GPU CUDA jobs get a peer-mapped (IPC) arena, created here,
@@ -534,6 +593,8 @@ class Executable:
                 if tuple(t_in.shape) != want:
                     raise RuntimeError(f"task {name}: store {s} ({stores[s]['shape']['key']}) holds a tile of shape "
                                        f"{tuple(t_in.shape)} on device {d}, expected {want}")
+            if native is not None:
+                return run_native(ins)
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
             outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
@@ -550,6 +611,42 @@ class Executable:
                                               else self._compute_stream)
                 if s in root_tiles:
                     root_tiles[s][d] = tiles[s][d]
+
+        native = self._native.get((op["template"], any(m == 2 for m in modes)))
+        scratch_base = self._scratch_base.get(d, 0)
+
+        def run_native(ins):
+            """The task as one call into the C++ launcher: slots = input tiles, the output block,
+            the scratch tile, the accumulators this launch adds into."""
+            block = None
+            if native.out_block_bytes:
+                block = torch.empty(native.out_block_bytes, dtype=torch.uint8, device=dctx.torch_device)
+            bases = [t.data_ptr() for t in ins]
+            bases.append(block.data_ptr() if block is not None else 0)
+            bases.append(scratch_base)
+            for pos in native.acc_positions:
+                bases.append(tiles[out_ids[pos]][d].data_ptr())
+            native.kernel.launch(bases, scalars, torch.cuda.current_stream().cuda_stream)
+            K._count(native.num_calls)
+            self.native_launches += 1
+            for pos, (spec, s) in enumerate(zip(native.outputs, out_ids)):
+                if spec[0] == "acc":
+                    o = tiles[s][d]
+                elif spec[0] == "block":
+                    _, off, shape, dtype = spec
+                    n = dtype.itemsize
+                    for e in shape:
+                        n *= e
+                    o = block[off:off + n].view(dtype).view(shape)
+                elif spec[0] == "slice":
+                    o = ins[spec[1]].narrow(0, scalars[0], spec[2][0]).view(spec[2])
+                else:
+                    o = ins[spec[1]].view(spec[2])
+                tiles[s][d] = o
+                if side is not None and o.is_cuda and self._compute_stream is not None:
+                    o.record_stream(self._compute_stream)
+                if s in root_tiles:
+                    root_tiles[s][d] = o
 
         self.launches += 1
         if self._cuda_ctx:

@@ -86,3 +86,46 @@ def test_expired_kernel_wait_fails_the_step_and_the_next_step_runs():
     assert torch.isfinite(loss2.full_tensor()).all()
     arena.close()
     exe.shutdown()
+
+
+def test_transformer_tasks_run_as_native_kernel_programs_and_match_the_interpreted_path(monkeypatch):
+    """On a CUDA device the forward, backward and optimizer tasks of the model are kernel programs
+    replayed by the C++ launcher (one call per task, memory planned ahead); the results are those
+    of the interpreted programs."""
+    torch.manual_seed(3)
+    cfg = llama.LlamaConfig.tiny(n_layers=2, d_model=256, n_heads=2, n_kv_heads=2, d_ff=512, vocab=512)
+    B, S, MB = 4, 128, 2
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-3), seq_len=S, global_batch=B, microbatch_size=MB)
+    params = llama.init_params(cfg, device="cuda")
+    state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S), device="cuda")
+    labels = torch.randint(0, cfg.vocab, (B, S), device="cuda")
+    cos, sin = llama.rope_tables(cfg, S, "cuda")
+    args = (params, state, tokens, labels, cos, sin)
+
+    def run(native: bool):
+        monkeypatch.setenv("MM_NATIVE_TASKS", "1" if native else "0")
+        mesh = mm.MultiMesh((1, 1), ("stage", "model"))
+        llama.register_pipeline_tasks(cfg, mesh, num_stages=1)
+        with mesh:
+            exe = mm.compile_function(step, args, mesh=mesh, backend="cuda")
+        loss, p1, s1 = exe(*args)
+        loss2, p2, s2 = exe(p1, s1, tokens, labels, cos, sin)       # second step: accumulators exist, tiles are re-bound
+        out = (loss.full_tensor().clone(), loss2.full_tensor().clone(),
+               [t.full_tensor().clone() for t in pytree.tree_leaves(p2)],
+               [t.full_tensor().clone() for t in pytree.tree_leaves(s2["m"])])
+        report, launches, scratch = exe.native_report(), exe.native_launches, getattr(exe, "native_scratch_bytes", 0)
+        exe.wait()
+        exe.shutdown()
+        return out, report, launches, scratch
+
+    nat, report, launches, scratch = run(True)
+    assert all(v.startswith("native") for k, v in report.items()), report
+    assert launches >= 2 * (2 * (B // MB) + 1) and scratch > 0
+    ref, report0, launches0, _ = run(False)
+    assert launches0 == 0 and all(v.startswith("interpreted") for v in report0.values())
+    torch.testing.assert_close(nat[0], ref[0], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(nat[1], ref[1], rtol=1e-5, atol=1e-6)
+    for a, b in zip(nat[2] + nat[3], ref[2] + ref[3]):
+        torch.testing.assert_close(a.float(), b.float(), rtol=1e-3, atol=1e-5)
+    assert K.read_status() == 0
