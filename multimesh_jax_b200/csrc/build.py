@@ -62,8 +62,8 @@ def _run(cmd, log: Path | None = None):
     return proc.stdout
 
 
-def kernels_lib_path() -> Path:
-    return PKG / "_mm_kernels.so"
+def kernels_lib_path(checked: bool = False) -> Path:
+    return PKG / ("_mm_kernels_checked.so" if checked else "_mm_kernels.so")
 
 
 def host_lib_path() -> Path:
@@ -71,21 +71,26 @@ def host_lib_path() -> Path:
     return PKG / f"_mm_C{suffix}"
 
 
-def build_kernels(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu file for sm_100a and link ``_mm_kernels.so``."""
-    BUILD_DIR.mkdir(exist_ok=True)
+def build_kernels(force: bool = False, verbose: bool = False, checked: bool = False) -> Path:
+    """Compile every .cu file for sm_100a and link ``_mm_kernels.so``. ``checked`` builds the
+    variant with ``-DMM_CHECKED`` (``_mm_kernels_checked.so``): indices derived from run-time data
+    are verified before use and violations are recorded in the status word instead of trapping;
+    ``MM_CHECKED=1`` makes the package load that library."""
+    out_dir = BUILD_DIR / "checked" if checked else BUILD_DIR
+    out_dir.mkdir(parents=True, exist_ok=True)
     cus = sorted(KERNEL_DIR.glob("*.cu"))
     hdrs = sorted(KERNEL_DIR.glob("*.cuh")) + sorted(KERNEL_DIR.glob("*.h"))
-    target = kernels_lib_path()
+    target = kernels_lib_path(checked)
     if not force and not _newer(cus + hdrs, target):
         return target
     nvcc = _nvcc()
+    extra = ["-DMM_CHECKED"] if checked else []
 
     def compile_one(cu: Path) -> Path:
-        obj = BUILD_DIR / (cu.stem + ".o")
+        obj = out_dir / (cu.stem + ".o")
         if force or _newer([cu] + hdrs, obj):
-            out = _run([nvcc, *NVCC_FLAGS, "-I", str(KERNEL_DIR), "-c", str(cu), "-o", str(obj)],
-                       log=BUILD_DIR / (cu.stem + ".ptxas.log"))
+            out = _run([nvcc, *NVCC_FLAGS, *extra, "-I", str(KERNEL_DIR), "-c", str(cu), "-o", str(obj)],
+                       log=out_dir / (cu.stem + ".ptxas.log"))
             if verbose:
                 print(out)
         return obj
@@ -192,6 +197,7 @@ def build_selftest(sanitizer: str = "address", force: bool = False) -> Path:
 
 def build_all(force: bool = False) -> None:
     build_kernels(force=force)
+    build_kernels(force=force, checked=True)
     build_host(force=force)
 
 

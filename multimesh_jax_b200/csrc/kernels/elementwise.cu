@@ -462,12 +462,14 @@ __global__ void __launch_bounds__(CE_THREADS)
 // ---------------------------------------------------------------- embedding
 __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
                                      const int64_t* __restrict__ ids, __nv_bfloat16* __restrict__ out,
-                                     int64_t T, int D, int vocab_start, int vocab_size) {
+                                     int64_t T, int D, int vocab_start, int vocab_size, int* __restrict__ err) {
   const int dv = D / 8;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * dv) return;
   const int64_t t = idx / dv;
   const int v = static_cast<int>(idx - t * dv);
+  (void)err;
+  MM_CHECK_OR(ids[t] >= 0, err, (void)0);     // ids of other vocabulary shards are legal, negative ones never are
   const int64_t id = ids[t] - vocab_start;
   uint4 val = make_uint4(0, 0, 0, 0);
   if (id >= 0 && id < vocab_size) val = reinterpret_cast<const uint4*>(table + id * D)[v];
@@ -476,12 +478,14 @@ __global__ void embedding_fwd_kernel(const __nv_bfloat16* __restrict__ table,
 // grad_table (fp32) [V, D] += scatter of dout rows.
 __global__ void embedding_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
                                      const int64_t* __restrict__ ids, float* __restrict__ grad,
-                                     int64_t T, int D, int vocab_start, int vocab_size) {
+                                     int64_t T, int D, int vocab_start, int vocab_size, int* __restrict__ err) {
   const int dv = D / 2;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * dv) return;
   const int64_t t = idx / dv;
   const int v = static_cast<int>(idx - t * dv);
+  (void)err;
+  MM_CHECK_OR(ids[t] >= 0, err, return);
   const int64_t id = ids[t] - vocab_start;
   if (id < 0 || id >= vocab_size) return;
   const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dout + t * D)[v]);
@@ -709,7 +713,7 @@ int mm_embedding_fwd(const void* table, const int64_t* ids, void* out, int64_t T
   if (total == 0) return 0;
   embedding_fwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), T, D,
-      vocab_start, vocab_size);
+      vocab_start, vocab_size, device_state() ? device_state()->status : nullptr);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }
@@ -719,7 +723,8 @@ int mm_embedding_bwd(const void* dout, const int64_t* ids, float* grad, int64_t 
   const int64_t total = T * (D / 2);
   if (total == 0) return 0;
   embedding_bwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(dout), ids, grad, T, D, vocab_start, vocab_size);
+      static_cast<const __nv_bfloat16*>(dout), ids, grad, T, D, vocab_start, vocab_size,
+      device_state() ? device_state()->status : nullptr);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }

@@ -113,7 +113,7 @@ struct AllGatherHook {
   // with up to eight 16-byte loads in flight per lane, so a round costs about one NVLink round
   // trip whatever the block size, and `workers_per_block` warps signal each block.
   __device__ __forceinline__ void aux(int w, int lane, int M, int K, int* err) const {
-    (void)err; (void)M;
+    (void)err; (void)M;   // err is used by the checked build only
     const int wid = blockIdx.x * kAuxWarps + w;
     if (wid >= workers_per_block * AG_ROUND) return;
     const int slot = wid % AG_ROUND, sub = wid / AG_ROUND;
@@ -127,6 +127,7 @@ struct AllGatherHook {
       const int hop = i / blocks_per_shard;
       int owner = me + hop;
       if (owner >= nranks) owner -= nranks;
+      MM_CHECK_OR(blk >= 0 && blk < num_m && owner >= 0 && owner < nranks && hop < nranks, err, continue);
       const uint4* src = a_src[owner] + static_cast<int64_t>(i - hop * blocks_per_shard) * vec_per_block;
       uint4* dst = gathered + static_cast<int64_t>(blk) * vec_per_block;
       for (int64_t v = lo + lane; v < hi; v += 256) {

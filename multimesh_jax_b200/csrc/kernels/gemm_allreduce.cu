@@ -127,6 +127,12 @@ struct AllReduceHook {
     uint8_t* ws = stage + q * AR_WARP_STAGE;          // this warp's 32 rows x 256 B
     const int row0 = m_blk * GEMM_BM + q * 32;
     const int tile = m_blk * num_n + n_blk;
+    MM_CHECK_OR(m_blk >= 0 && n_blk >= 0 && n_blk < num_n && npeers >= 1 && npeers <= AR_MAX_PEERS, err, {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) rel.arrive();
+      return;
+    });
 #pragma unroll 1
     for (int h = 0; h < GEMM_BN / AR_HALF_COLS; ++h) {
       const int hcol0 = n_blk * GEMM_BN + h * AR_HALF_COLS;
@@ -295,6 +301,12 @@ struct ReduceScatterHook {
     const int owner = chunk % g;
     const int local_row0 = (chunk / g) * chunk_rows + (grow0 - chunk * chunk_rows);
     const int local_m = local_row0 / GEMM_BM;
+    MM_CHECK_OR(owner >= 0 && owner < g && local_row0 >= 0 && local_row0 + GEMM_BM <= Ms && n_blk < num_n, err, {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) rel.arrive();
+      return;
+    });
     const bool mine = owner == me;
     __nv_bfloat16* dst = mine ? out : recv_peer[owner];
     const int64_t ld = mine ? ldo : static_cast<int64_t>(N);

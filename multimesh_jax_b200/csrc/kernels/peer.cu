@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(256)
           so += i * ch.src_stride[d];
           dof += i * ch.dst_stride[d];
         }
+        // the index must decode completely inside the chunk's box
+        MM_CHECK_OR(rem == 0 && c < args.num_chunks, err, continue);
         v[u] = *reinterpret_cast<const uint4*>(ch.src + so);
         dptr[u] = reinterpret_cast<uint4*>(ch.dst + dof);
       }

@@ -36,6 +36,23 @@ enum : int {
   MM_ERR_BOUNDS = 6,         // a checked index was out of range
 };
 
+// Checked build (-DMM_CHECKED, the stand-in for a memory checker on machines where none may
+// run): indices that come from run-time data - row blocks and owners of the fused collectives,
+// chunk decoding of the reshard kernel, token ids - are verified before the access that uses
+// them. A violation records MM_ERR_BOUNDS in the status word and *skips* the access; nothing
+// traps. In the normal build the macros vanish.
+#ifdef MM_CHECKED
+#define MM_CHECK_OR(cond, err, action)                                     \
+  do {                                                                     \
+    if (!(cond)) {                                                         \
+      if (err) atomicCAS((err), 0, static_cast<int>(mm::MM_ERR_BOUNDS));   \
+      action;                                                              \
+    }                                                                      \
+  } while (0)
+#else
+#define MM_CHECK_OR(cond, err, action) ((void)0)
+#endif
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -52,7 +52,10 @@ _SIGS = {
 
 
 def lib_path() -> Path:
-    return _PKG / "_mm_kernels.so"
+    """The kernel library this process uses: the checked build (index checks that record
+    MM_ERR_BOUNDS instead of trapping) when MM_CHECKED=1, else the normal one."""
+    import os
+    return _PKG / ("_mm_kernels_checked.so" if os.environ.get("MM_CHECKED", "0") == "1" else "_mm_kernels.so")
 
 
 def load():

@@ -238,7 +238,41 @@ class Executable:
             if sid not in unsafe and st["kind"] == "TEMP" and st["alias_of"] < 0:
                 self._dying_inputs.setdefault(k, set()).add(sid)
         self._build_native_programs()
+        # Debug aid for the compiler's buffer plan (MM_CHECK_LIFETIMES=1): stores that share a
+        # physical buffer must never be alive at the same time. With the knob on, every tile
+        # remembers which store wrote it last; a task or reshard that reads a store whose buffer
+        # has meanwhile been handed to another store fails the step with both names, and the
+        # tile that loses its buffer is filled with NaN first, so that a kernel still holding the
+        # old address produces visibly wrong numbers instead of plausible ones.
+        import os as _os2
+        self._lifetimes = _os2.environ.get("MM_CHECK_LIFETIMES", "0") == "1"
+        self._owner: Dict[Tuple[int, int], int] = {}
+        self._alias_root: Dict[int, int] = {}
+        for st in plan["stores"]:
+            root = st
+            while root["alias_of"] >= 0:
+                root = plan["stores"][root["alias_of"]]
+            self._alias_root[st["id"]] = root["id"]
         live_executables.add(self)
+
+    def _took_buffer(self, sid: int, d: int, old: Optional[torch.Tensor], new: torch.Tensor) -> None:
+        """Store ``sid`` has just been written on device ``d`` (lifetime checking only)."""
+        key = (self.buffer_of[sid], d)
+        me = self._alias_root[sid]
+        prev = self._owner.get(key)
+        if prev is not None and prev != me and old is not None and old is not new and old.is_floating_point() \
+                and old.untyped_storage().data_ptr() != new.untyped_storage().data_ptr():
+            old.fill_(float("nan"))
+        self._owner[key] = me
+
+    def _check_owner(self, sid: int, d: int, reader: str) -> None:
+        key = (self.buffer_of[sid], d)
+        owner = self._owner.get(key)
+        if owner is not None and owner != self._alias_root[sid]:
+            a, b = self.plan["stores"][sid], self.plan["stores"][owner]
+            raise RuntimeError(f"{reader} reads store {sid} ({a['name']}, {a['shape']['key']}) on device {d}, but its buffer "
+                               f"was handed to store {owner} ({b['name']}) in the meantime: the buffer plan lets two live "
+                               "stores share a buffer")
 
     def _build_native_programs(self) -> None:
         """Kernel programs for the templates that are nothing but calls into the kernel library
@@ -473,6 +507,9 @@ class Executable:
                 new_tiles = shard_tensor(a, want, topo, private=i not in self.donated).local_tiles()
             self.tiles[sid].clear()
             self.tiles[sid].update(new_tiles)
+            if self._lifetimes:
+                for d_ in new_tiles:
+                    self._owner[(self.buffer_of[sid], d_)] = self._alias_root[sid]
         root_tiles: Dict[int, Dict[int, torch.Tensor]] = {sid: {} for sid in plan["root_stores"]}
         # dispatch loop
         for k, op in enumerate(plan["ops"]):
@@ -585,6 +622,9 @@ class Executable:
                         torch.cuda.current_stream().wait_event(ev)
             # inputs read for the last time here are handed over: the program frees each one
             # right after its last use instead of keeping it alive for the whole task
+            if self._lifetimes:
+                for s in in_ids:
+                    self._check_owner(s, d, f"task {name}")
             ins = [tiles[s].pop(d) if s in dying else tiles[s][d] for s in in_ids]
             if side is not None:
                 for t_in in ins:            # allocated on another stream: keep its memory until this one is done
@@ -598,6 +638,7 @@ class Executable:
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
             outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
+                old_tile = tiles[s].get(d) if self._lifetimes else None
                 if m and fused.get(oi):
                     tiles[s][d] = o          # the kernel wrote / accumulated into the accumulator itself
                 elif m == 2:
@@ -606,6 +647,8 @@ class Executable:
                     tiles[s][d] = o.to(acc_dtypes[oi], copy=True)
                 else:
                     tiles[s][d] = o
+                if self._lifetimes:
+                    self._took_buffer(s, d, old_tile, tiles[s][d])
                 if side is not None and isinstance(tiles[s][d], torch.Tensor) and tiles[s][d].is_cuda:
                     tiles[s][d].record_stream(torch.cuda.default_stream(dctx.torch_device) if self._compute_stream is None
                                               else self._compute_stream)
@@ -642,6 +685,8 @@ class Executable:
                     o = ins[spec[1]].narrow(0, scalars[0], spec[2][0]).view(spec[2])
                 else:
                     o = ins[spec[1]].view(spec[2])
+                if self._lifetimes:
+                    self._took_buffer(s, d, tiles[s].get(d), o)
                 tiles[s][d] = o
                 if side is not None and o.is_cuda and self._compute_stream is not None:
                     o.record_stream(self._compute_stream)
@@ -697,6 +742,8 @@ class Executable:
                         torch.cuda.current_stream().wait_event(prev)
                     pr = self._peer_reshard
                     key = (self.buffer_of[src_sid], self.buffer_of[dst_sid])
+                    if self._lifetimes and mine_src:
+                        self._check_owner(src_sid, d, f"reshard S{src_sid}->S{dst_sid}")
                     src_tile = tiles[src_sid].get(d)
                     if side is not None and src_tile is not None and src_tile.is_cuda:
                         src_tile.record_stream(side)
@@ -711,6 +758,8 @@ class Executable:
                     if out is not None:
                         if side is not None and self._compute_stream is not None:
                             out.record_stream(self._compute_stream)   # allocated here, read by tasks of the compute stream
+                        if self._lifetimes:
+                            self._took_buffer(dst_sid, d, tiles[dst_sid].get(d), out)
                         tiles[dst_sid][d] = out
                         if dst_sid in root_tiles:
                             root_tiles[dst_sid][d] = out
@@ -721,7 +770,12 @@ class Executable:
                 writes = [(buf[dst_sid], d)]
 
                 def body(d=d, mine_dst=mine_dst):
+                    if self._lifetimes:
+                        for c in mine_dst:
+                            self._check_owner(src_sid, c["src_device"], f"reshard S{src_sid}->S{dst_sid}")
                     out = run_reshard_local(topo, d, tiles[src_sid], mine_dst, dst_shape)
+                    if self._lifetimes:
+                        self._took_buffer(dst_sid, d, tiles[dst_sid].get(d), out)
                     tiles[dst_sid][d] = out
                     if dst_sid in root_tiles:
                         root_tiles[dst_sid][d] = out

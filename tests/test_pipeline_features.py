@@ -231,3 +231,47 @@ def test_zero_arguments_option_zeroes_hoisted_parameter_casts():
     with mm.ignore_transforms():
         ref = float(step(w, x))
     assert abs(results[False] - ref) < 1e-6 * abs(ref) and results[True] == 0.0
+
+
+def test_lifetime_checking_catches_two_live_stores_in_one_buffer(monkeypatch):
+    """MM_CHECK_LIFETIMES=1: the compiler's buffer plan passes on a real pipeline; a plan that is
+    corrupted so that a stage-boundary activation shares its buffer with a later store is caught
+    when the overwritten store is read, naming both stores."""
+    monkeypatch.setenv("MM_CHECK_LIFETIMES", "1")
+    exe = _compile_and_check(_step("1f1b"), _two_stage(), _loss_task())      # numerics checked with the knob on
+    assert exe._lifetimes and exe._owner
+    plan = exe.plan
+    # find two TEMP stores of equal layout that are alive at the same time: an input of some task
+    # and a store written between that input's definition and the task
+    ops = [op for op in plan["ops"] if op["kind"] == "task"]
+    victim = None
+    for k, op in enumerate(ops):
+        for sid in op["inputs"]:
+            st = plan["stores"][sid]
+            if st["kind"] != "TEMP":
+                continue
+            first_def = next((j for j, o in enumerate(ops) if sid in o["outputs"]), None)
+            if first_def is None:
+                continue
+            for j in range(first_def + 1, k):
+                for other in ops[j]["outputs"]:
+                    so = plan["stores"][other]
+                    if (so["kind"] == "TEMP" and other != sid and so["shape"]["key"] == st["shape"]["key"]
+                            and exe.buffer_of[other] != exe.buffer_of[sid]):
+                        victim = (sid, other)
+                        break
+                if victim:
+                    break
+            if victim:
+                break
+        if victim:
+            break
+    assert victim is not None
+    sid, other = victim
+    exe.buffer_of[other] = exe.buffer_of[sid]                  # the corrupted plan: both stores in one buffer
+    exe.tiles[other] = exe.tiles[sid]
+    with pytest.raises(mm.StepFailed, match="buffer plan lets two live stores share a buffer"):
+        loss, grads = exe(_params(), _data())
+        loss.wait()
+        exe.wait()
+    exe.shutdown()
