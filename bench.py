@@ -262,6 +262,7 @@ def main():
     dev_lab = [t.to(dev) for t in host_lab]
 
     counter = [0]
+    host_s = [0.0]      # wall-clock seconds the host spends inside the step call (submission only: the call does not wait for the GPU)
 
     def run_step(_i, e2e: bool):
         nonlocal params, state
@@ -272,7 +273,9 @@ def main():
             lab = host_lab[i % pool].to(dev, non_blocking=True)
         else:
             tok, lab = dev_tok[i % pool], dev_lab[i % pool]
+        t0 = time.perf_counter()
         loss, params, state = exe(params, state, tok, lab, cos, sin)
+        host_s[0] += time.perf_counter() - t0
         if e2e:
             return float(loss.full_tensor().item())
         return loss
@@ -305,7 +308,9 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     launches0, lib0 = K.launch_count, K.library_call_count
+    host_s[0] = 0.0
     ms, last = timed(args.steps, False)
+    host_ms = host_s[0] * 1e3 / args.steps
     launches = K.launch_count - launches0
     lib_calls = K.library_call_count - lib0
     clocks = sampler.stop()
@@ -346,8 +351,12 @@ def main():
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
                     "h2d_bytes_per_step": 2 * global_batch * seq * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "library_kernel_calls": lib_calls,
+            "host_ms_per_step": round(host_ms, 2),
+            "native_task_launches": getattr(exe, "native_launches", 0),
             "tflops_per_gpu": round(flops / (ms / args.steps / 1e3) / n / 1e12, 1),
             "loss": round(loss_val, 4), "compile_s": round(compile_s, 1), "kernel_status": status,
+            "reshard_sources_in_place_vs_copied": [getattr(getattr(exe, "_peer_reshard", None), "direct_uses", 0),
+                                                   getattr(getattr(exe, "_peer_reshard", None), "copied_uses", 0)],
             "fused_gemm_collective_calls": sum(o.calls for o in getattr(getattr(exe, "_fused_tp", None), "_ops", {}).values()),
             "impl": "ours",
         }

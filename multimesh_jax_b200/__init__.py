@@ -30,7 +30,7 @@ from .no_op import mark_gradient, mark_loss, no_op  # noqa: E402
 from .task import (Context, MultiMesh, Task, TaskMesh, clear_tasks, microbatch, module_scopes, named_scope,  # noqa: E402
                    parallelize, register_task, slice_global_mesh, task, value_and_grad)
 from .runtime.executable import Executable, ShardedTensor, StepFailed  # noqa: E402
-from .compiler.api import compile_function  # noqa: E402
+from .compiler.api import compile_function, compile_program_file  # noqa: E402
 from .init import detect_cluster, init, init_test, shutdown  # noqa: E402
 
 __all__ = [
@@ -38,6 +38,6 @@ __all__ = [
     "MultiMesh", "autoshard", "context", "enable_fast_path", "enable_recomputation", "ignore_transforms",
     "with_sharding_constraint", "relayout", "tasks", "mjit", "shutdown", "replicate_parameters_smaller_than_num_elements",
     "recompute_from_arguments_if_cost_less_than", "clear_tasks", "no_op", "mark_gradient", "mark_loss",
-    "value_and_grad", "named_scope", "module_scopes", "compile_function", "Executable", "ShardedTensor",
+    "value_and_grad", "named_scope", "module_scopes", "compile_function", "compile_program_file", "Executable", "ShardedTensor",
     "StepFailed", "init", "init_test", "custom_partitioning", "index_class", "shard_map", "detect_cluster",
 ]

@@ -61,7 +61,11 @@ def _apply_shardings(cap: Captured, in_shardings, example_args) -> None:
 def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optional[MultiMesh] = None,
                      num_devices: Optional[int] = None, donate_argnums: Sequence[int] = (),
                      backend: Optional[str] = None, in_shardings=None, context=None, topology: Optional[Topology] = None,
-                     name: Optional[str] = None, config_overrides: Optional[Dict[str, Any]] = None):
+                     name: Optional[str] = None, config_overrides: Optional[Dict[str, Any]] = None,
+                     save_program: Optional[str] = None):
+    """Captures ``fn``, partitions it and returns the executable. ``save_program``: also write
+    the captured step, before partitioning, to this path as a stored program that
+    :func:`compile_program_file` can compile again without the model, its tensors or a device."""
     from .. import _mm_C
     mesh = mesh or MultiMesh.current()
     if num_devices is None:
@@ -92,6 +96,9 @@ def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optiona
     nmb = cap.loop_configs[0]["num_microbatches"] if cap.loop_configs else 0
     part = make_partition(num_devices, mesh, nmb)
     cfg = _partition_config(**(config_overrides or {}))
+    if save_program is not None:
+        # before partitioning: the pipeline rewrites the graph in place
+        _mm_C.save_program(cap.graph, part, cfg, str(save_program))
     plan = _mm_C.mpmd_partition(cap.graph, part, cfg)
     name = name or getattr(fn, "__name__", "step")
     reason = bypass_reason(cap, plan, num_devices, donate_argnums, context)
@@ -101,6 +108,17 @@ def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optiona
         exe = Executable(cap, plan, topology, context=context, name=name)
     exe.partition = part
     return exe
+
+
+def compile_program_file(path: str, device_memory_bytes: int = 0, want_plan: bool = False) -> Dict[str, Any]:
+    """Offline compile of a stored program (``compile_function(..., save_program=path)``): the
+    whole MPMD pipeline in C++ plus a replay of the plan on the mock runtime. Returns the number
+    of templates / tasks / reshards, the plan and operation hashes, per-device memory
+    high-water marks, ``fits`` (high-water mark within ``device_memory_bytes``; 0 = no limit),
+    the hazard report of the submission log and, with ``want_plan``, the plan itself.
+    Counterpart of ``CompileHloModuleFromFile`` (src/pjrt_client/mm_pjrt_client.cc:702-771)."""
+    from .. import _mm_C
+    return _mm_C.compile_program_file(str(path), int(device_memory_bytes), bool(want_plan))
 
 
 def bypass_reason(cap: Captured, plan: dict, num_devices: int, donate_argnums, context) -> Optional[str]:

@@ -135,11 +135,15 @@ class NativeProgram:
     def __init__(self):
         from .. import _mm_C
         self.kernel = _mm_C.KernelProgram()
-        self.out_block_bytes = 0
+        self.out_block_bytes = 0                # all chunks together
+        self.out_chunks: List[int] = []         # bytes of each allocation the launch's fresh outputs are carved from
         self.scratch_bytes = 0
-        # per template output: ("block", offset, shape, dtype) | ("input", index, shape) | ("acc", position)
+        # per template output: ("block", chunk, offset, shape, dtype) | ("input", index, shape) | ("acc", position)
         # | ("slice", index, shape): rows [scalar, scalar + shape[0]) of input `index`
+        # | ("ext", j, shape, dtype): the whole of external tile j, a slot of its own that the caller
+        #   points at memory of its choosing (the peer-mapped tile a cross-submesh reshard reads)
         self.outputs: List[tuple] = []
+        self.external: List[int] = []           # output positions with an external tile, in slot order
         self.acc_positions: List[int] = []      # output positions whose accumulator tile is a slot of the launch
         self.num_calls = 0
 
@@ -157,7 +161,8 @@ class _Builder:
         self.scratch = _Scratch()
         self.env: Dict[int, Sym] = {}
         self.out_pos = {v: k for k, v in enumerate(prog.outputs)}
-        self.out_cursor = 0
+        self.out_chunks: List[int] = []
+        self.out_base = None                    # first slot of output chunks 1, 2, ... (chunk 0 is SLOT_OUT)
         self.acc_slot: Dict[int, int] = {}
         self.refs: Dict[int, int] = {}          # scratch allocation id -> number of live values in it
         self.scaled: Dict[int, int] = {}        # microbatch slices: value -> bytes per unit of the launch's scalar
@@ -166,10 +171,14 @@ class _Builder:
     def new_value(self, vid: int, shape, dtype) -> Sym:
         """Storage for IR value ``vid``: inside the output block when it is a (non-accumulated)
         task output, else in the scratch tile."""
+        j = self.reaches_ext.get(vid)
+        if j is not None and j not in self.ext_taken:
+            probe = Sym(self.ext_slot[j], 0, shape, dtype)
+            if probe.nbytes == self.ext_bytes[j]:
+                self.ext_taken.add(j)
+                return probe
         if vid in self.reaches_output:
-            sym = Sym(self.SLOT_OUT, self.out_cursor, shape, dtype)
-            self.out_cursor += _round(sym.nbytes)
-            return sym
+            return self.out_region(shape, dtype)
         return self.temp(shape, dtype)
 
     def temp(self, shape, dtype) -> Sym:
@@ -178,10 +187,29 @@ class _Builder:
         self.refs[ident] = 0
         return Sym(self.SLOT_SCRATCH, off, shape, dtype, root=ident)
 
+    # Fresh outputs are carved from a few allocations of at most OUT_CHUNK bytes each (one of its
+    # own for anything larger) instead of one block: a task that saves tens of GB of activations
+    # would otherwise need that much contiguous free memory.
+    OUT_CHUNK = 256 << 20
+
     def out_region(self, shape, dtype) -> Sym:
-        sym = Sym(self.SLOT_OUT, self.out_cursor, shape, dtype)
-        self.out_cursor += _round(sym.nbytes)
-        return sym
+        nb = _round(Sym(0, 0, shape, dtype).nbytes)
+        if self.out_chunks and self.out_chunks[-1] + nb <= self.OUT_CHUNK:
+            off = self.out_chunks[-1]
+            self.out_chunks[-1] += nb
+        else:
+            self.out_chunks.append(nb)
+            off = 0
+        c = len(self.out_chunks) - 1
+        return Sym(self.SLOT_OUT if c == 0 else self.out_base + c - 1, off, shape, dtype)
+
+    def out_chunk_of(self, slot: int):
+        """Index of the output chunk that ``slot`` names, or None."""
+        if slot == self.SLOT_OUT:
+            return 0
+        if self.out_base is not None and slot >= self.out_base:
+            return slot - self.out_base + 1
+        return None
 
     def bind(self, vid: int, sym: Sym) -> None:
         self.env[vid] = sym
@@ -625,12 +653,16 @@ _MAY_WRITE_OVER = {
 }
 
 
-def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumulate: Sequence[int], have_acc: bool
-                 ) -> NativeProgram:
+def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumulate: Sequence[int], have_acc: bool,
+                 external: Sequence[int] = (), protected_inputs: Sequence[int] = ()) -> NativeProgram:
     """The kernel program of one variant of ``template``: ``accumulate[k]`` is the accumulate
     mode class of output ``k`` (0 plain, else accumulated) and ``have_acc`` says whether the
     accumulator tiles already exist (they then are slots of the launch) or are created by this
-    launch. Raises :class:`NativeUnsupported`."""
+    launch. ``external``: positions of plain outputs that are written into a tile the caller
+    supplies per launch (slots after the accumulators, in the order given).
+    ``protected_inputs``: positions of inputs whose storage must never take a result (someone
+    outside the task graph of this device - a pull from another GPU - may still read them).
+    Raises :class:`NativeUnsupported`."""
     if template["num_devices"] != 1:
         raise NativeUnsupported("templates on more than one device run collectives")
     g = cap.graph
@@ -640,6 +672,16 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
     b.np.acc_positions = acc_positions if have_acc else []
     slot_of_acc = {pos: b.n_in + 2 + j for j, pos in enumerate(acc_positions)}
     b.acc_slot_for = lambda pos: slot_of_acc[pos]
+    external = [k for k in external if accumulate[k] == 0]
+    b.np.external = list(external)
+    b.ext_slot = {j: b.n_in + 2 + len(b.np.acc_positions) + j for j in range(len(external))}
+    b.out_base = b.n_in + 2 + len(b.np.acc_positions) + len(external)
+    b.ext_bytes, b.ext_taken, b.reaches_ext = {}, set(), {}
+    for j, k in enumerate(external):
+        val = g.value(prog.outputs[k])
+        sh = val.get("sharding")
+        b.ext_bytes[j] = Sym(0, 0, sh["shard_size"] if sh else val["shape"], DTYPE_FROM_NAME[val["dtype"]]).nbytes
+        b.reaches_ext[prog.outputs[k]] = j
     input_index = {v: i for i, v in enumerate(prog.inputs)}
     for v, i in input_index.items():
         val = g.value(v)
@@ -666,6 +708,8 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
         for o in ins.outs or ():
             if o in b.reaches_output and o in alias_parent:
                 b.reaches_output.add(alias_parent[o])
+                if o in b.reaches_ext:
+                    b.reaches_ext.setdefault(alias_parent[o], b.reaches_ext[o])
     # operand liveness inside the program, and operands other tasks still need
     last: Dict[int, int] = {}
     for idx, ins in enumerate(prog.instrs):
@@ -675,6 +719,7 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
     mine = set(prog.inputs)
     shared_inputs = {v for t in plan["templates"] if t is not template and t["name"] != template["name"]
                      for v in t["inputs"] if v in mine}
+    shared_inputs |= {prog.inputs[i] for i in protected_inputs}
 
     def may_overwrite(ins: Instr, vid: int) -> bool:
         """The operand dies with this instruction and its storage may take the result (the rule
@@ -727,6 +772,13 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
             continue
         sym = b.sym_of(v)
         mode = accumulate[k]
+        if k in external:
+            j = external.index(k)
+            if not (sym.slot == b.ext_slot[j] and sym.off == 0):
+                dst = Sym(b.ext_slot[j], 0, sym.shape, sym.dtype)
+                b.copy(dst, sym)
+            b.np.outputs.append(("ext", j, sym.shape, sym.dtype))
+            continue
         if mode:
             fused = prog.fused_acc.get(k)
             if fused:
@@ -734,7 +786,7 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
                     b.np.outputs.append(("acc", k))
                 else:
                     fr = b.fresh_acc[k]
-                    b.np.outputs.append(("block", fr.off, fr.shape, fr.dtype))
+                    b.np.outputs.append(("block", b.out_chunk_of(fr.slot), fr.off, fr.shape, fr.dtype))
                 continue
             acc_dtype = DTYPE_FROM_NAME[plan_store_dtype(plan, template, k)]
             if acc_dtype != torch.float32:
@@ -756,10 +808,10 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
                     b.copy(dst, sym)
                 else:
                     raise NativeUnsupported("accumulation of this dtype")
-                b.np.outputs.append(("block", dst.off, dst.shape, dst.dtype))
+                b.np.outputs.append(("block", b.out_chunk_of(dst.slot), dst.off, dst.shape, dst.dtype))
             continue
-        if sym.slot == b.SLOT_OUT:
-            b.np.outputs.append(("block", sym.off, sym.shape, sym.dtype))
+        if b.out_chunk_of(sym.slot) is not None:
+            b.np.outputs.append(("block", b.out_chunk_of(sym.slot), sym.off, sym.shape, sym.dtype))
         elif sym.slot < b.n_in:
             if sym.off != 0:
                 raise NativeUnsupported("task output is a slice of a task input")
@@ -768,8 +820,9 @@ def build_native(cap, plan: dict, template: dict, prog: TemplateProgram, accumul
             # an output that ended up in scratch (it aliases an intermediate): give it its own region
             dst = b.out_region(sym.shape, sym.dtype)
             b.copy(dst, sym)
-            b.np.outputs.append(("block", dst.off, dst.shape, dst.dtype))
-    b.np.out_block_bytes = b.out_cursor
+            b.np.outputs.append(("block", b.out_chunk_of(dst.slot), dst.off, dst.shape, dst.dtype))
+    b.np.out_chunks = list(b.out_chunks)
+    b.np.out_block_bytes = sum(b.out_chunks)
     b.np.scratch_bytes = b.scratch.peak
     return b.np
 

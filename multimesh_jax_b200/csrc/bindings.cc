@@ -8,6 +8,7 @@
 
 #include "mmgraph/graph.h"
 #include "mmgraph/passes.h"
+#include "mmgraph/program_file.h"
 #include "mmgraph/schedule.h"
 #include "mmgraph/sharding.h"
 #include "mmrt/cuda_context.h"
@@ -391,6 +392,52 @@ PYBIND11_MODULE(_mm_C, m) {
           return d;
         },
         "Runs the whole MPMD pipeline on a captured step and returns the execution plan.");
+
+  m.def("save_program",
+        [](std::shared_ptr<Graph> g, std::shared_ptr<Partition> p, const PartitionConfig& cfg, const std::string& path) {
+          SaveProgram(path, *g, *p, cfg);
+        },
+        "Writes a captured, not yet partitioned step (graph, resolved task table, loop settings, partition "
+        "options) to one JSON file.");
+  m.def("load_program",
+        [](const std::string& path) {
+          StoredProgram sp = LoadProgram(path);
+          return py::make_tuple(sp.graph, sp.partition, sp.config);
+        },
+        "Reads a stored program back: (Graph, Partition, PartitionConfig).");
+  m.def("compile_program_file",
+        [](const std::string& path, int64_t device_memory_bytes, bool want_plan) {
+          Plan plan;
+          std::vector<std::string> log;
+          OfflineResult r;
+          {
+            py::gil_scoped_release rel;
+            r = CompileProgramFile(path, device_memory_bytes, &plan, &log);
+          }
+          py::dict d;
+          d["status"] = r.status;
+          d["message"] = r.message;
+          d["hazards"] = r.hazards;
+          d["plan_hash"] = r.plan_hash;
+          d["operation_hash"] = r.operation_hash;
+          d["templates"] = r.templates;
+          d["template_names"] = r.template_names;
+          d["stores"] = r.stores;
+          d["tasks"] = r.tasks;
+          d["reshards"] = r.reshards;
+          d["reshard_bytes"] = r.reshard_bytes;
+          d["temp_bytes_per_device_max"] = r.temp_bytes_per_device_max;
+          d["device_high_water_max"] = r.device_high_water_max;
+          d["device_high_water"] = r.device_high_water;
+          d["fits"] = r.fits;
+          d["stats"] = r.stats;
+          d["log"] = log;
+          if (want_plan) d["plan"] = PlanToDict(plan);
+          return d;
+        },
+        py::arg("path"), py::arg("device_memory_bytes") = 0, py::arg("want_plan") = false,
+        "Offline compile: loads a stored program, runs the MPMD pipeline and replays the plan on the mock "
+        "runtime against a made-up device-memory size. No tensor is allocated and no device is needed.");
 
   py::class_<Compiler>(m, "Compiler")
       .def(py::init<std::shared_ptr<Graph>, std::shared_ptr<Partition>, const PartitionConfig&>())

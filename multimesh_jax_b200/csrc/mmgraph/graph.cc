@@ -216,6 +216,16 @@ Json TaskOptions::ToJson() const {
     la.push(e);
   }
   j.set("logical_axes", la);
+  Json sb = Json::array();
+  for (auto& x : split_backprop) sb.push(Json::string(x));
+  j.set("split_backprop", sb);
+  Json ld = Json::array();
+  for (auto& row : loop_dependent_devices) {
+    Json r = Json::array();
+    for (int v : row) r.push(Json::number(v));
+    ld.push(r);
+  }
+  j.set("loop_dependent_devices", ld);
   return j;
 }
 
@@ -288,6 +298,8 @@ void Partition::RegisterFactory(const std::string& regex, TaskFactory factory) {
 
 std::string Partition::ComputeScopeColor(const std::string& scope, bool backprop) {
   if (scope.empty()) return "";
+  auto pin = pinned_.find({scope, backprop});
+  if (pin != pinned_.end()) return pin->second;
   for (auto& f : factories_) {
     std::smatch m;
     std::regex re(f.first);

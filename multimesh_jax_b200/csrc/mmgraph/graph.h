@@ -169,6 +169,11 @@ class Partition {
   void ClearFactories() { factories_.clear(); cache_.clear(); }
   // Resolves the colour of an operator from its name stack; "" when nothing matches.
   std::string ComputeScopeColor(const std::string& scope, bool backprop);
+  // Fixes the colour of one name stack (stored programs carry the resolved table instead of
+  // the regex contexts, which are callbacks of the process that captured the step).
+  void PinScopeColor(const std::string& scope, bool backprop, const std::string& color) {
+    pinned_[{scope, backprop}] = color;
+  }
   const std::map<std::string, ColorConfig>& colors() const { return colors_; }
 
  private:
@@ -176,6 +181,7 @@ class Partition {
   std::map<std::string, ColorConfig> colors_;
   std::vector<std::pair<std::string, TaskFactory>> factories_;
   std::map<std::pair<std::string, bool>, std::string> cache_;
+  std::map<std::pair<std::string, bool>, std::string> pinned_;
 };
 
 // ---------------------------------------------------------------------------

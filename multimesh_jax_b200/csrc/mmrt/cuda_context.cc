@@ -31,11 +31,30 @@ class RuntimeApi : public GpuApi {
   void PriorityRange(int* least, int* greatest) override {
     if (!Ok(cudaDeviceGetStreamPriorityRange(least, greatest))) *least = *greatest = 0;
   }
+  // Streams are cached for the life of the process (the reference keeps a stream cache too,
+  // src/pjrt_client/mm_utils.cc:44-70): a context that shuts down parks its side streams here
+  // and the next context on that device takes them over. They are never destroyed, because
+  // memory blocks of the caching allocator may still carry them as "used on this stream"
+  // marks and would record an event on them when they are freed.
   void* CreateStream(int priority) override {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto& parked = parked_[{dev, priority}];
+    if (!parked.empty()) {
+      void* s = parked.back();
+      parked.pop_back();
+      where_[s] = {dev, priority};
+      return s;
+    }
     cudaStream_t s = nullptr;
-    return Ok(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, priority)) ? s : nullptr;
+    if (!Ok(cudaStreamCreateWithPriority(&s, cudaStreamNonBlocking, priority))) return nullptr;
+    where_[s] = {dev, priority};
+    return s;
   }
-  void DestroyStream(void* stream) override { cudaStreamDestroy(static_cast<cudaStream_t>(stream)); }
+  void DestroyStream(void* stream) override {
+    auto it = where_.find(stream);
+    if (it != where_.end()) parked_[it->second].push_back(stream);
+  }
   void* CreateEvent(bool timing) override {
     cudaEvent_t e = nullptr;
     return Ok(cudaEventCreateWithFlags(&e, timing ? cudaEventDefault : cudaEventDisableTiming)) ? e : nullptr;
@@ -76,6 +95,8 @@ class RuntimeApi : public GpuApi {
     return false;
   }
   std::string last_;
+  std::map<std::pair<int, int>, std::vector<void*>> parked_;   // (device, priority) -> idle streams
+  std::map<void*, std::pair<int, int>> where_;
   int (*push_)(const char*) = nullptr;
   int (*pop_)() = nullptr;
   void (*mark_)(const char*) = nullptr;

@@ -126,14 +126,19 @@ def run_reshard_dist(topo, device: int, src_tile: Optional[torch.Tensor], send_c
 class PeerReshard:
     """Cross-submesh reshards of a one-process-per-GPU job through peer-mapped memory.
 
-    Every distinct (source buffer, destination buffer) pair of the plan owns two staging
-    tiles in the symmetric arena plus ready / done flags. A source rank copies its tile into
-    the staging tile of the use's parity and raises the ready flags of the ranks that read
-    from it; a destination rank waits for its sources' flags and runs the pull kernel, which
-    reads the source tiles straight from peer HBM over NVLink and writes the destination
-    layout in one pass (no NCCL call, no intermediate receive buffer), then raises the done
-    flags that let the sources reuse the staging tile two uses later. Everything runs on the
-    side stream; waits are bounded by wall-clock time and report through the status word."""
+    Every distinct (source buffer, destination buffer) pair of the plan owns two source tiles
+    in the symmetric arena (alternating by use) plus ready / done flags. The task that produces
+    the source store writes its output straight into the tile of the coming use
+    (:meth:`claim_source`: the store's tile *is* the arena tile, nothing is copied); a source
+    rank then only raises the ready flags of the ranks that read from it. A destination rank
+    waits for its sources' flags and runs the pull kernel, which reads the source tiles
+    straight from peer HBM over NVLink and writes the destination layout in one pass (no NCCL
+    call, no intermediate receive buffer), then raises the done flags that let the sources
+    reuse the tile two uses later. Producers that cannot write into a given tile (interpreted
+    task bodies, parameters, a source buffer read by several reshards) have their tile copied
+    into the arena first. Waits are bounded by wall-clock time and report through the status
+    word. The reference moves cross-submesh data with one call into its task runtime
+    (src/pjrt_client/zuku_execute_context_impl.cc:437-452)."""
 
     MIN_BYTES = 64 << 10
 
@@ -144,6 +149,8 @@ class PeerReshard:
         self.bytes = 0
         # every pull of this object runs on the side stream, one after the other: one counter word
         self.counter = arena.alloc_counter("PeerReshard")
+        self.direct_uses = 0          # uses whose producer wrote into the arena tile itself
+        self.copied_uses = 0          # uses that needed the copy into the arena
         for op in plan["ops"]:
             if op["kind"] != "reshard":
                 continue
@@ -158,15 +165,34 @@ class PeerReshard:
             dtype = DTYPE_FROM_NAME[src["dtype"]]
             srcs = list(range(src["device_start"], src["device_start"] + src["num_devices"]))
             dsts = list(range(dst["device_start"], dst["device_start"] + dst["num_devices"]))
+            readers: Dict[int, List[int]] = {}
+            for c in rplan["chunks"]:
+                readers.setdefault(c["src_device"], set()).add(c["dst_device"])
             slot = {"stage": [arena.alloc(src["shard_size"], dtype) for _ in range(2)],
                     "ready": [[arena.alloc_flag() for _ in srcs] for _ in range(2)],
                     "done": [[arena.alloc_flag() for _ in dsts] for _ in range(2)],
-                    "srcs": srcs, "dsts": dsts, "uses": 0}
+                    "srcs": srcs, "dsts": dsts, "uses": 0, "claimed": {},
+                    "readers": {d: sorted(r) for d, r in readers.items()}}
             self.slots[key] = slot
             n = 1
             for s in src["shard_size"]:
                 n *= s
             self.bytes += 2 * n * dtype.itemsize
+
+    def claim_source(self, key, d: int) -> torch.Tensor:
+        """The arena tile that the coming use of ``key`` will read on device ``d``, for the
+        producer to write its output into. Queues, on the current stream, the wait for the
+        readers of the use two back (the last ones to read this tile)."""
+        slot = self.slots[key]
+        e = slot["uses"] + 1
+        par = e & 1
+        if slot["claimed"].get(d) != e:
+            readers = slot["readers"].get(d, ())
+            if e > 2 and readers:
+                self.symm.wait_flags(self.arena, [self.arena.flag_ptr(d, slot["done"][par][slot["dsts"].index(r)])
+                                                  for r in readers], e - 2)
+            slot["claimed"][d] = e
+        return slot["stage"][par].peer(d)
 
     @classmethod
     def required_bytes(cls, plan: dict, buffer_of: Dict[int, int]) -> int:
@@ -240,10 +266,15 @@ class PeerReshard:
         with scope:
             if mine_src:
                 readers = sorted({c["dst_device"] for c in mine_src})
-                if e > 2:   # the staging tile of this parity was last read in use e - 2
-                    symm.wait_flags(arena, [arena.flag_ptr(d, slot["done"][par][slot["dsts"].index(r)]) for r in readers],
-                                    e - 2)
-                slot["stage"][par].peer(d).copy_(src_tile)
+                mine = slot["stage"][par].peer(d)
+                if slot["claimed"].get(d) == e and src_tile.data_ptr() == mine.data_ptr():
+                    self.direct_uses += 1       # the producer wrote into the arena tile: nothing to move
+                else:
+                    if e > 2:   # the tile of this parity was last read in use e - 2
+                        symm.wait_flags(arena, [arena.flag_ptr(d, slot["done"][par][slot["dsts"].index(r)])
+                                                for r in readers], e - 2)
+                    mine.copy_(src_tile.view(mine.shape))
+                    self.copied_uses += 1
                 symm.set_flags(arena, [arena.flag_ptr(r, slot["ready"][par][slot["srcs"].index(d)]) for r in readers], e)
             if mine_dst:
                 writers = sorted({c["src_device"] for c in mine_dst})

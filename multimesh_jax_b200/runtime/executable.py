@@ -285,6 +285,7 @@ class Executable:
         self._native: Dict[Tuple[int, bool], Any] = {}
         self._native_why: Dict[int, str] = {}
         self._scratch_base: Dict[int, int] = {}
+        self._native_off: set = set()
         self.native_launches = 0
         if not self._cuda_ctx or os.environ.get("MM_NATIVE_TASKS", "1") == "0":
             return
@@ -299,6 +300,34 @@ class Executable:
                     continue
                 if patterns.get(op["template"], set()) is not None:
                     patterns.setdefault(op["template"], set()).add((tuple(1 if m else 0 for m in modes), any(m == 2 for m in modes)))
+        # Outputs that a pull-kernel reshard reads are written straight into the reshard's
+        # peer-mapped tile (every launch of the template must agree on it), and inputs that a
+        # reshard reads are never overwritten in place: the pull runs on another GPU, outside
+        # this device's ordering.
+        pr = self._peer_reshard
+        reshard_src = {op["src_store"] for op in self.plan["ops"] if op["kind"] == "reshard"}
+        readers: Dict[int, set] = {}
+        for op in self.plan["ops"]:
+            if op["kind"] == "reshard":
+                readers.setdefault(op["src_store"], set()).add((self.buffer_of[op["src_store"]], self.buffer_of[op["dst_store"]]))
+        # store -> the one reshard slot that reads it (stores read by several reshards, or by one
+        # that goes through NCCL, keep tiles of their own and are copied)
+        self._direct_key: Dict[int, tuple] = {}
+        if pr is not None and os.environ.get("MM_RESHARD_DIRECT", "1") != "0":
+            for sid, keys in readers.items():
+                if len(keys) == 1 and pr.slots.get(next(iter(keys))) is not None:
+                    self._direct_key[sid] = next(iter(keys))
+        ext: Dict[int, set] = {}
+        protect: Dict[int, set] = {}
+        for op in self.plan["ops"]:
+            if op["kind"] != "task":
+                continue
+            direct = {k for k, (sid, m) in enumerate(zip(op["outputs"], op["accumulate"]))
+                      if m == 0 and sid in self._direct_key}
+            tid = op["template"]
+            ext[tid] = direct if tid not in ext else ext[tid] & direct
+            protect.setdefault(tid, set()).update(i for i, sid in enumerate(op["inputs"]) if sid in reshard_src)
+        self._native_ext = {tid: sorted(v) for tid, v in ext.items()}
         scratch = 0
         for t in self.plan["templates"]:
             pats = patterns.get(t["id"])
@@ -307,7 +336,9 @@ class Executable:
             built = {}
             try:
                 for classes, have_acc in pats:
-                    built[(t["id"], have_acc)] = build_native(self.cap, self.plan, t, self.programs[t["id"]], classes, have_acc)
+                    built[(t["id"], have_acc)] = build_native(self.cap, self.plan, t, self.programs[t["id"]], classes, have_acc,
+                                                              self._native_ext.get(t["id"], ()),
+                                                              sorted(protect.get(t["id"], ())))
             except NativeUnsupported as e:
                 self._native_why[t["id"]] = str(e)
                 continue
@@ -326,7 +357,7 @@ class Executable:
         out = {}
         for t in self.plan["templates"]:
             progs = [n for (tid, _), n in self._native.items() if tid == t["id"]]
-            if progs:
+            if progs and not any(tid == t["id"] for tid, _ in self._native_off):
                 out[t["name"]] = f"native ({max(n.num_calls for n in progs)} kernel calls)"
             else:
                 out[t["name"]] = "interpreted: " + self._native_why.get(t["id"], "not on a CUDA context")
@@ -633,8 +664,17 @@ class Executable:
                 if tuple(t_in.shape) != want:
                     raise RuntimeError(f"task {name}: store {s} ({stores[s]['shape']['key']}) holds a tile of shape "
                                        f"{tuple(t_in.shape)} on device {d}, expected {want}")
-            if native is not None:
-                return run_native(ins)
+            if native is not None and (op["template"], d) not in self._native_off:
+                try:
+                    return run_native(ins)
+                except torch.cuda.OutOfMemoryError:
+                    # The outputs are allocated before anything is launched; when the device
+                    # cannot supply them, this template goes back to the interpreted program,
+                    # which allocates one output at a time as the task proceeds.
+                    self._native_off.add((op["template"], d))
+                    self._native_why[op["template"]] = (f"{native.out_block_bytes >> 20} MiB of outputs could not be "
+                                                        "allocated")
+                    torch.cuda.empty_cache()
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
             outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
@@ -661,14 +701,15 @@ class Executable:
         def run_native(ins):
             """The task as one call into the C++ launcher: slots = input tiles, the output block,
             the scratch tile, the accumulators this launch adds into."""
-            block = None
-            if native.out_block_bytes:
-                block = torch.empty(native.out_block_bytes, dtype=torch.uint8, device=dctx.torch_device)
+            blocks = [torch.empty(nb, dtype=torch.uint8, device=dctx.torch_device) for nb in native.out_chunks]
             bases = [t.data_ptr() for t in ins]
-            bases.append(block.data_ptr() if block is not None else 0)
+            bases.append(blocks[0].data_ptr() if blocks else 0)
             bases.append(scratch_base)
             for pos in native.acc_positions:
                 bases.append(tiles[out_ids[pos]][d].data_ptr())
+            ext_tiles = [self._peer_reshard.claim_source(self._direct_key[out_ids[pos]], d) for pos in native.external]
+            bases.extend(t.data_ptr() for t in ext_tiles)
+            bases.extend(b_.data_ptr() for b_ in blocks[1:])
             native.kernel.launch(bases, scalars, torch.cuda.current_stream().cuda_stream)
             K._count(native.num_calls)
             self.native_launches += 1
@@ -676,11 +717,13 @@ class Executable:
                 if spec[0] == "acc":
                     o = tiles[s][d]
                 elif spec[0] == "block":
-                    _, off, shape, dtype = spec
+                    _, chunk, off, shape, dtype = spec
                     n = dtype.itemsize
                     for e in shape:
                         n *= e
-                    o = block[off:off + n].view(dtype).view(shape)
+                    o = blocks[chunk][off:off + n].view(dtype).view(shape)
+                elif spec[0] == "ext":
+                    o = ext_tiles[spec[1]].view(spec[2])
                 elif spec[0] == "slice":
                     o = ins[spec[1]].narrow(0, scalars[0], spec[2][0]).view(spec[2])
                 else:

@@ -80,11 +80,13 @@ def main():
     peer_uses = sum(s["uses"] for s in pr.slots.values() if s) if pr is not None else 0
     flag = torch.tensor([1 if (ok and status == 0) else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    direct = torch.tensor([pr.direct_uses if pr is not None else 0, pr.copied_uses if pr is not None else 0], device=dev)
+    dist.all_reduce(direct, op=dist.ReduceOp.SUM)
     uses = torch.tensor([peer_uses], device=dev)
     dist.all_reduce(uses, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "peer_moe_calls": moe_calls, "peer_collective_calls": comm_calls, "fused_calls": fused,
-                          "status": status, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
+        print(json.dumps({"STEP_OK": bool(flag.item()), "worst_err_over_limit_rank0": worst, "peer_reshard_uses": int(uses.item()), "reshard_sources_written_in_place": int(direct[0].item()), "reshard_sources_copied": int(direct[1].item()), "peer_moe_calls": moe_calls, "peer_collective_calls": comm_calls, "fused_calls": fused,
+                          "status": status, "native": exe.native_report() if hasattr(exe, "native_report") else {}, "loss": float(loss2.full_tensor().item()) if pp == 1 else None}), flush=True)
     dist.barrier()
     exe.shutdown()
     dist.destroy_process_group()
