@@ -103,6 +103,27 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// Plain copy with 16-byte loads and stores, eight loads in flight per thread. With `src` a peer
+// address this is the bandwidth probe that the reshard benchmark reports its fractions against:
+// the rate at which this GPU can pull from one peer with nothing else in the way.
+__global__ void __launch_bounds__(256) peer_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t nvec) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  constexpr int UNROLL = 8;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; base < nvec; base += stride * UNROLL) {
+    uint4 v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < nvec) v[u] = src[i];
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t i = base + u * stride;
+      if (i < nvec) dst[i] = v[u];
+    }
+  }
+}
+
 // Sets a flag in (peer or local) memory after all prior work of the stream.
 __global__ void set_flag_kernel(int* flag, int value) {
   __threadfence_system();
@@ -292,6 +313,21 @@ int mm_wait_flag(const void* flag, int value, cudaStream_t stream) {
 // bytes); sources may be peer addresses. elem_size 4 = fp32, 2 = bf16.
 int mm_reduce_pull_chunked(const int64_t* srcs, int nsrc, void* out, int64_t chunk_bytes, int64_t nchunks,
                            int64_t src_stride_bytes, int elem_size, float scale, cudaStream_t stream);
+
+// dst[0, bytes) = src[0, bytes): both 16-byte aligned, bytes a multiple of 16; src may be a peer address.
+int mm_peer_copy(void* dst, const void* src, int64_t bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  if ((bytes % 16) || (reinterpret_cast<uintptr_t>(dst) % 16) || (reinterpret_cast<uintptr_t>(src) % 16)) return -2;
+  DeviceState* ds = device_state();
+  if (!ds) return -1;
+  const int64_t nvec = bytes / 16;
+  int64_t want = (nvec + 256 * 8 - 1) / (256 * 8);
+  const int cap = ds->sm_count * 8;
+  const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+  peer_copy_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(src), static_cast<uint4*>(dst), nvec);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
 
 int mm_reduce_pull(const int64_t* srcs, int nsrc, void* out, int64_t nbytes, int elem_size, float scale,
                    cudaStream_t stream) {

@@ -40,6 +40,7 @@ _SIGS = {
                          c_float, c_int, c_float, _P, _P]),
     "mm_sumsq_f32": (c_int, [_P, c_int64, _P, _P]),
     "mm_memcpy_d2d": (c_int, [_P, _P, c_int64, _P]),
+    "mm_peer_copy": (c_int, [_P, _P, c_int64, _P]),
     "mm_zero": (c_int, [_P, c_int64, _P]),
     "mm_f32_to_bf16": (c_int, [_P, _P, c_int64, _P]),
     "mm_bf16_to_f32": (c_int, [_P, _P, c_int64, c_int, _P]),
