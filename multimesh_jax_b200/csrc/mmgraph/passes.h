@@ -84,6 +84,7 @@ bool ShardingPropagation(CompileState& s, PropagationMode mode);
 bool SpmdLowering(CompileState& s);         // contracting-dim dots -> local op + collective
 bool HoistShardMapReduce(CompileState& s);  // gradient reductions once per step, after the loop
 bool ReduceScatterCreator(CompileState& s); // all-reduce + slice -> reduce-scatter; tags all-gathers
+bool SplitUpdateByReduction(CompileState& s);  // optimizer task cut into pieces behind the hoisted reductions
 bool UnusedParamOutputRemover(CompileState& s);
 
 // Final stage: unroll + schedule + reshard + buffers -> Plan.

@@ -1034,4 +1034,118 @@ bool HoistShardMapReduce(CompileState& s) {
   return changed;
 }
 
+// ---------------------------------------------------------------------------
+// Update splitting: the task that consumes the once-per-step gradient reductions (the
+// optimizer) is cut into pieces, each holding the update operators of one bucket of
+// reduced gradients, in the order in which the reductions are issued. The reductions run
+// on the communication stream; with one update task the optimizer waits for the last of
+// them, with pieces the update of bucket i runs under the reduction of bucket i + 1.
+// Only tasks whose operators are independent of one another are cut (an optimizer whose
+// per-tensor updates share an intermediate, e.g. a global gradient norm, is left whole).
+// The reference gets the same overlap from its runtime's data-flow scheduling of the
+// operations XLA emits per parameter (src/pjrt_client/mpmd_hoist_shard_map_reduce.cc:70-189
+// hoists the reductions; nothing forces the update into one region).
+// ---------------------------------------------------------------------------
+bool SplitUpdateByReduction(CompileState& s) {
+  Graph& g = *s.graph;
+  Partition& part = *s.partition;
+  // bucket size: MULTIMESH_UPDATE_BUCKET_MB (default 256; 0 keeps the update in one task), or in
+  // bytes with MULTIMESH_UPDATE_BUCKET_BYTES (small models, tests)
+  const int64_t bucket_bytes = GetEnvInt("MULTIMESH_UPDATE_BUCKET_BYTES", GetEnvInt("MULTIMESH_UPDATE_BUCKET_MB", 256) << 20);
+  if (bucket_bytes <= 0) return false;
+  bool changed = false;
+  std::map<int, size_t> group_pos;
+  for (size_t i = 0; i < s.groups.size(); ++i) group_pos[s.groups[i].id] = i;
+  auto is_reduce_node = [&](const Node& n) { return !n.dead && n.Attr("hoisted") == "1"; };
+  std::vector<TaskGroup> result;
+  int next_id = 0;
+  for (auto& grp : s.groups) next_id = std::max(next_id, grp.id + 1);
+  for (const TaskGroup& grp : s.groups) {
+    bool cut = grp.region == 2 && grp.nodes.size() >= 2;
+    // every node: no operand produced inside the group; at most one reduced operand, its own
+    std::vector<std::pair<size_t, int>> keyed;   // (position of the feeding reduction, node)
+    std::vector<int> free_nodes;                 // nodes without a reduced operand
+    std::set<int> produced;
+    if (cut) for (int id : grp.nodes) for (int v : g.node(id).outputs) produced.insert(v);
+    for (int id : grp.nodes) {
+      if (!cut) break;
+      const Node& n = g.node(id);
+      if (is_reduce_node(n)) { cut = false; break; }
+      size_t latest = 0;
+      bool fed = false;
+      for (int v : n.inputs) {
+        if (produced.count(v)) { cut = false; break; }
+        const int p = g.value(v).producer;
+        if (p >= 0 && is_reduce_node(g.node(p))) {
+          fed = true;
+          latest = std::max(latest, group_pos[g.node(p).task]);
+        }
+      }
+      if (!cut) break;
+      if (fed) keyed.emplace_back(latest, id); else free_nodes.push_back(id);
+    }
+    if (!cut || keyed.size() < 2) { result.push_back(grp); continue; }
+    std::stable_sort(keyed.begin(), keyed.end(), [](const std::pair<size_t, int>& a, const std::pair<size_t, int>& b) {
+      return a.first < b.first;
+    });
+    // buckets by bytes of reduced input
+    std::vector<std::vector<int>> pieces(1);
+    int64_t filled = 0;
+    for (auto& kn : keyed) {
+      int64_t bytes = 0;
+      for (int v : g.node(kn.second).inputs) {
+        const int p = g.value(v).producer;
+        if (p >= 0 && is_reduce_node(g.node(p))) {
+          const Value& val = g.value(v);
+          int64_t b = static_cast<int64_t>(DTypeSize(val.dtype));
+          for (auto e : (val.has_sharding ? val.sharding.ShardSize() : val.shape)) b *= e;
+          bytes += b;
+        }
+      }
+      if (filled > 0 && filled + bytes > bucket_bytes) { pieces.emplace_back(); filled = 0; }
+      pieces.back().push_back(kn.second);
+      filled += bytes;
+    }
+    if (pieces.size() < 2) { result.push_back(grp); continue; }
+    pieces.back().insert(pieces.back().end(), free_nodes.begin(), free_nodes.end());
+    const ColorConfig& cc = part.Get(grp.color);
+    const std::string base = cc.original.empty() ? grp.color : cc.original;
+    // inputs with a layout on record for the whole task keep it in the piece that reads them
+    std::vector<std::pair<int, ShardedShape>> layouts;
+    for (auto& kv : TablesOf(s).input_sharding) if (kv.first.first == grp.id) layouts.emplace_back(kv.first.second, kv.second);
+    for (size_t k = 0; k < pieces.size(); ++k) {
+      TaskGroup piece = grp;
+      piece.nodes = pieces[k];
+      std::sort(piece.nodes.begin(), piece.nodes.end(), [&](int a, int b) {
+        return std::find(grp.nodes.begin(), grp.nodes.end(), a) < std::find(grp.nodes.begin(), grp.nodes.end(), b);
+      });
+      if (k > 0) {
+        piece.id = next_id++;
+        piece.color = part.Clone(grp.color, std::to_string(piece.id) + "." + base + "_update", cc.devices);
+        part.GetMutable(piece.color).original = base;
+        part.GetMutable(piece.color).backprop = cc.backprop;
+        part.GetMutable(piece.color).noncritical = cc.noncritical;
+        std::set<int> reads;
+        for (int id : piece.nodes) for (int v : g.node(id).inputs) reads.insert(v);
+        for (auto& lv : layouts) if (reads.count(lv.first)) SetInputSharding(s, piece.id, lv.first, lv.second);
+      }
+      for (int id : piece.nodes) {
+        g.node(id).task = piece.id;
+        g.node(id).color = piece.color;
+      }
+      result.push_back(std::move(piece));
+    }
+    s.Note("update task " + grp.color + " cut into " + std::to_string(pieces.size()) + " pieces behind its gradient reductions");
+    changed = true;
+  }
+  if (changed) {
+    s.groups = std::move(result);
+    std::vector<int> order;
+    for (auto& grp : s.groups) order.insert(order.end(), grp.nodes.begin(), grp.nodes.end());
+    g.order = order;
+    g.Toposort();
+  }
+  return changed;
+}
+
 }  // namespace mmg

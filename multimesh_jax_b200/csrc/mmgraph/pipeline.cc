@@ -119,6 +119,7 @@ Plan MpmdPartition(Graph& g, Partition& part, const PartitionConfig& cfg, std::v
     return c;
   }, &counter);
   RunPass(s, "reduce_scatter_creator", [&] { return ReduceScatterCreator(s); }, &counter);
+  RunPass(s, "split_update_by_reduction", [&] { return SplitUpdateByReduction(s); }, &counter);
   RunPass(s, "unused_param_output_remover", [&] { return UnusedParamOutputRemover(s); }, &counter);
   Dump(s, "after_mpmd_partitioning", &counter);
 

@@ -227,6 +227,56 @@ def test_data_parallel_and_fsdp_steps_match_eager(axes, fsdp):
     exe.shutdown()
 
 
+@pytest.mark.parametrize("fsdp", [False, True])
+def test_optimizer_task_is_cut_into_pieces_behind_the_gradient_reductions(fsdp, monkeypatch):
+    """With a bucket size below the gradient volume the post-loop update task becomes several
+    `_update` tasks, each reading only the reductions of its own bucket (so that it can run
+    while later reductions are still on the wire); the step still equals the eager one."""
+    monkeypatch.setenv("MULTIMESH_UPDATE_BUCKET_BYTES", "40000")
+    cfg = _cfg(n_layers=2, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128)
+    B, S, MB = 8, 16, 4
+    params = llama.init_params(cfg)
+    opt_state = llama.init_opt_state(params)
+    tokens = torch.randint(0, cfg.vocab, (B, S))
+    labels = torch.randint(0, cfg.vocab, (B, S))
+    cos, sin = llama.rope_tables(cfg, S, "cpu")
+    step = llama.make_train_step(cfg, llama.AdamWConfig(lr=1e-2), seq_len=S, global_batch=B, microbatch_size=MB,
+                                 fsdp=fsdp)
+    mesh = mm.MultiMesh((1, 2, 1), ("stage", "data", "model"))
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=1)
+    with mesh:
+        exe = mm.compile_function(step, (params, opt_state, tokens, labels, cos, sin), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        loss_ref, p_ref, s_ref = step(params, opt_state, tokens, labels, cos, sin)
+    loss, p_mm, s_mm = exe(params, opt_state, tokens, labels, cos, sin)
+    torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-4, atol=1e-5)
+    for a, b in zip(pytree.tree_leaves(p_mm), pytree.tree_leaves(p_ref)):
+        _adam_close(a.full_tensor(), b, 1e-2)
+    for a, b in zip(pytree.tree_leaves(s_mm["v"]), pytree.tree_leaves(s_ref["v"])):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-3, atol=1e-6)
+    g = exe.cap.graph
+    updates = [t for t in exe.plan["templates"] if t["name"].endswith("_update")]
+    reduces = {t["id"] for t in exe.plan["templates"] if t["name"].endswith("_reduce")}
+    assert len(updates) >= 3
+    producer_template = {}
+    for t in exe.plan["templates"]:
+        for v in t["outputs"]:
+            producer_template[v] = t["id"]
+    seen = set()
+    for t in updates:
+        fed_by = {producer_template[v] for v in t["inputs"] if producer_template.get(v) in reduces}
+        assert fed_by and not (fed_by & seen)        # its own reductions, nobody else's
+        seen |= fed_by
+        assert all(g.node(n)["op"].startswith("mm_ops.adamw") for n in t["nodes"])
+    # the pieces are submitted in the order of the reductions that feed them
+    order = [op["template"] for op in exe.plan["ops"] if op["kind"] == "task"]
+    first_reduce_of = {t["id"]: min(order.index(producer_template[v]) for v in t["inputs"] if producer_template.get(v) in reduces)
+                       for t in updates}
+    by_submission = sorted(updates, key=lambda t: order.index(t["id"]))
+    assert [first_reduce_of[t["id"]] for t in by_submission] == sorted(first_reduce_of.values())
+    exe.shutdown()
+
+
 def test_forced_layout_change_at_the_stage_boundary():
     """Two stages of (data 2 x model 2) devices with parameters stored FSDP-style; the first
     stage hands its output over sharded on the hidden dimension, the second takes it sharded on
