@@ -12,6 +12,8 @@
 // source tile and permission to overwrite it again are exchanged through
 // epoch counters in the arenas' flag areas, with bounded waits that record an
 // error in the status word instead of spinning forever.
+#include <cstdlib>
+
 #include "host_common.h"
 #include "ptx.cuh"
 
@@ -359,7 +361,17 @@ int mm_reduce_pull_chunked(const int64_t* srcs, int nsrc, void* out, int64_t chu
   a.src_stride_vecs = src_stride_bytes / 16;
   a.scale = scale;
   int64_t want = (a.nvec + 256 * 4 - 1) / (256 * 4);
-  const int cap = ds->sm_count * 8;
+  // The kernel is bound by NVLink latency x bandwidth, not by SM count: two CTAs per SM keep
+  // about 4.8 MB of loads in flight (three times what 770 GB/s x 2 us needs) and leave the
+  // other thread slots to the kernels it overlaps with (the optimizer pieces that run on the
+  // compute stream while later gradients are still being reduced). MM_REDUCE_PULL_CTAS_PER_SM
+  // changes the share (1..8).
+  static const int per_sm = [] {
+    const char* v = std::getenv("MM_REDUCE_PULL_CTAS_PER_SM");
+    const int n = v && *v ? std::atoi(v) : 2;
+    return n < 1 ? 1 : (n > 8 ? 8 : n);
+  }();
+  const int cap = ds->sm_count * per_sm;
   const int grid = static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
   reduce_pull_kernel<<<grid, 256, 0, stream>>>(a);
   MM_CUDA_TRY(cudaGetLastError());
