@@ -322,7 +322,7 @@ def main():
         os.makedirs(args.trace, exist_ok=True)
         res = {}
         barrier()
-        with timeline.profile(res, device=local_rank):
+        with timeline.profile(res, device=local_rank, context=getattr(exe, "context", None)):
             t_last = run_step(0, False)
             t_last.wait() if hasattr(t_last, "wait") else None
             torch.cuda.synchronize()

@@ -66,6 +66,10 @@ class Breakdown:
     classes: Dict[str, float] = field(default_factory=dict)
     per_task: Dict[str, Dict[str, float]] = field(default_factory=dict)
     top_kernels: List[Tuple[str, float, int]] = field(default_factory=list)
+    # cross-stream ordering of the step: edges the runtime context enforced with an event wait
+    # (from its dependence analysis) and the event calls the profiler saw on the host
+    event_edges: List[dict] = field(default_factory=list)
+    host_event_calls: Dict[str, int] = field(default_factory=dict)
 
     def speed_of_light_us(self) -> float:
         return self.classes.get("Compute", 0.0)
@@ -77,7 +81,21 @@ class Breakdown:
                                 for k, v in self.classes.items()},
                 "speed_of_light_us": round(self.speed_of_light_us(), 1),
                 "per_task_us": {t: {k: round(v, 1) for k, v in c.items()} for t, c in self.per_task.items()},
-                "top_kernels": [{"name": n[:96], "us": round(u, 1), "count": c} for n, u, c in self.top_kernels]}
+                "top_kernels": [{"name": n[:96], "us": round(u, 1), "count": c} for n, u, c in self.top_kernels],
+                "event_edges": self.edge_summary(), "host_event_calls": dict(self.host_event_calls)}
+
+    STREAMS = ("compute", "communication", "auxiliary")
+
+    def edge_summary(self) -> dict:
+        """Event edges by (stream of the earlier task -> stream of the waiting task), with examples."""
+        out: Dict[str, dict] = {}
+        for e in self.event_edges:
+            key = f"{self.STREAMS[e['from_stream']]}->{self.STREAMS[e['to_stream']]}"
+            d = out.setdefault(key, {"count": 0, "examples": []})
+            d["count"] += 1
+            if len(d["examples"]) < 3:
+                d["examples"].append(f"{e['from_name']} -> {e['to_name']}")
+        return out
 
     def format(self) -> str:
         lines = [f"device {self.device}: wall {self.wall_us / 1e3:.2f} ms", f"{'class':<16}{'current ms':>12}{'%':>8}{'SoL ms':>10}"]
@@ -85,6 +103,11 @@ class Breakdown:
             v = self.classes.get(c, 0.0)
             sol = v if c == "Compute" else 0.0
             lines.append(f"{c:<16}{v / 1e3:>12.3f}{100 * v / self.wall_us if self.wall_us else 0:>8.1f}{sol / 1e3:>10.3f}")
+        if self.event_edges or self.host_event_calls:
+            lines.append(f"event edges between streams: {len(self.event_edges)}  (host calls: "
+                         + ", ".join(f"{k} x{v}" for k, v in sorted(self.host_event_calls.items())) + ")")
+            for key, d in self.edge_summary().items():
+                lines.append(f"  {key:<28} x{d['count']:<5} e.g. {d['examples'][0][:90]}")
         lines.append("top kernels:")
         for n, u, cnt in self.top_kernels:
             lines.append(f"  {u / 1e3:>10.3f} ms  x{cnt:<6} {n[:100]}")
@@ -207,16 +230,30 @@ def spans_from_profiler(prof) -> List[Span]:
     return out
 
 
+def host_event_calls(prof) -> Dict[str, int]:
+    """How often the profiled region called the CUDA event API on the host."""
+    out: Dict[str, int] = {}
+    for ev in prof.events():
+        if ev.name in ("cudaStreamWaitEvent", "cudaEventRecord", "cudaEventRecordWithFlags", "cudaEventSynchronize",
+                       "cudaStreamSynchronize", "cudaDeviceSynchronize"):
+            out[ev.name] = out.get(ev.name, 0) + 1
+    return out
+
+
 @contextlib.contextmanager
-def profile(result: dict, device: int = 0):
+def profile(result: dict, device: int = 0, context=None):
     """Runs the body under ``torch.profiler`` and stores the :class:`Breakdown` of ``device`` in
-    ``result['breakdown']``. Timings taken inside the body are perturbed by the profiler and
-    must not be reported as benchmark values."""
+    ``result['breakdown']``. ``context``: the executable's runtime context; when it records
+    cross-stream event edges (``CudaContext``) the edges of the profiled region are attached to
+    the breakdown. Timings taken inside the body are perturbed by the profiler and must not be
+    reported as benchmark values."""
     import torch
     from torch.profiler import ProfilerActivity, profile as _profile
     from .. import state
     old = state.knobs["task_ranges"]
     state.knobs["task_ranges"] = True
+    if context is not None and hasattr(context, "edges"):
+        context.clear_event_log()
     try:
         with _profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
             yield
@@ -225,6 +262,9 @@ def profile(result: dict, device: int = 0):
     finally:
         state.knobs["task_ranges"] = old
     result["breakdown"] = breakdown(spans_from_profiler(prof), device)
+    result["breakdown"].host_event_calls = host_event_calls(prof)
+    if context is not None and hasattr(context, "edges"):
+        result["breakdown"].event_edges = list(context.edges())
     result["profiler"] = prof
 
 

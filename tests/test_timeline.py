@@ -44,3 +44,26 @@ def test_chrome_trace_reader(tmp_path):
     p.write_text(json.dumps(doc))
     spans = spans_from_chrome_trace(str(p))
     assert [(s.name, s.kind) for s in spans] == [("gemm", "kernel"), ("mm.task:t", "range")]
+
+
+def test_event_edges_of_the_runtime_context_appear_in_the_breakdown():
+    """A context that records cross-stream event edges (the fake-API form of the CUDA context
+    here) hands them to the breakdown, which lists them by stream pair."""
+    from multimesh_jax_b200 import _mm_C
+    from multimesh_jax_b200.utils import timeline
+    ctx = _mm_C.CudaContext([0], [0], [0], fake=True)
+    ctx.open_window()
+    ctx.create_execute_task(0, [], [(1, 0)], lambda: None, "produce", False, 0, 0, 0)      # compute stream writes buffer 1
+    ctx.reshard(0, [(1, 0)], [(2, 0)], lambda: None, "reshard S1->S2", 0, 1)                # communication stream reads it
+    ctx.create_execute_task(0, [(2, 0)], [(3, 0)], lambda: None, "consume", False, 0, 0, 0)
+    ctx.close_window()
+    b = timeline.Breakdown(0, 1000.0)
+    b.event_edges = list(ctx.edges())
+    summary = b.edge_summary()
+    assert summary["compute->communication"]["count"] == 1
+    assert summary["communication->compute"]["count"] == 1
+    assert "produce -> reshard S1->S2" in summary["compute->communication"]["examples"][0]
+    text = b.format()
+    assert "event edges between streams: 2" in text
+    assert b.to_dict()["event_edges"] == summary
+    ctx.shutdown()
