@@ -451,7 +451,8 @@ bool CutSizeMinimizer(CompileState& s) {
     int64_t operand_bytes = 0;
     for (int v : n.inputs) operand_bytes += g.value(v).Bytes();
     if (g.value(g.node(tail).outputs[0]).Bytes() <= operand_bytes) continue;
-    if (IsDot(n)) continue;  // keep heavy math where the user put it
+    // a contraction qualifies like anything else: with an output larger than both operands
+    // together its contracted extent is tiny, so it is the result, not the math, that is heavy
     for (int c : chain) g.node(c).color = consumer_color;
     changed = true;
   }

@@ -378,6 +378,47 @@ def test_cut_size_minimizer_moves_expanding_ops_to_the_consumer():
     assert b.color_of(big) == "B" and b.color_of(small) == "A"
 
 
+def test_cut_size_minimizer_moves_a_contraction_that_is_larger_than_its_operands():
+    """[1024, 8] x [8, 1024] -> [1024, 1024]: the product is 64 times the size of its operands
+    together, so it moves to the only task that reads it and the two small operands cross the
+    cut instead - alone, and through a chain of unary operators behind it
+    (src/pjrt_client/mpmd_cut_size_minimizer_test.cc: LargeDotWithSmallOperands, UnaryOperandMove)."""
+    for chain in (False, True):
+        b = G()
+        x = b.inp("x", [1024, 8])
+        y = b.inp("y", [1024, 1024])
+        c0 = b.op("aten.cos.default", [x], [1024, 8], task=task_json("red", [0]))
+        a0 = b.op("aten.add.Tensor", [c0, x], [1024, 8], task=task_json("red", [0]))
+        c0t = b.op("aten.t.default", [c0], [8, 1024], task=task_json("red", [0]))
+        dot = b.op("aten.mm.default", [a0, c0t], [1024, 1024], task=task_json("red", [0]))
+        last = dot
+        if chain:
+            tr = b.op("aten.t.default", [dot], [1024, 1024], task=task_json("red", [0]))
+            last = b.op("aten.neg.default", [tr], [1024, 1024], task=task_json("red", [0]))
+        c1 = b.op("aten.cos.default", [last], [1024, 1024], task=task_json("blue", [1]))
+        a1 = b.op("aten.add.Tensor", [c1, y], [1024, 1024], task=task_json("blue", [1]))
+        b.g.set_outputs([a1])
+        c = b.compiler()
+        for p in ("coloring", "computation_grouper"):
+            c.run(p)
+        assert b.color_of(dot) == "red"
+        assert c.run("cut_size_minimizer")
+        assert b.color_of(dot) == "blue" and b.color_of(last) == "blue"
+        assert b.color_of(a0) == "red" and b.color_of(c0) == "red"
+    # a contraction whose result is smaller than its operands stays where it is
+    b = G()
+    x = b.inp("x", [64, 512])
+    w = b.inp("w", [512, 64])
+    dot = b.op("aten.mm.default", [x, w], [64, 64], task=task_json("red", [0]))
+    use = b.op("aten.neg.default", [dot], [64, 64], task=task_json("blue", [1]))
+    b.g.set_outputs([use])
+    c = b.compiler()
+    for p in ("coloring", "computation_grouper"):
+        c.run(p)
+    c.run("cut_size_minimizer")
+    assert b.color_of(dot) == "red"
+
+
 def test_split_critical_path_separates_weight_gradients():
     b = G()
     x = b.inp("x", [4, 4])
