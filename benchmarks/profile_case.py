@@ -233,7 +233,11 @@ def main(argv=None) -> int:
         raise SystemExit(f"unknown case {case}")
     out["kernel_status"] = K.read_status()
     print(json.dumps(out), flush=True)
-    return 0
+    # a recorded expiry of a bounded wait or a wrong result fails the run, so that a profiler
+    # capture chained behind it with && never replays a kernel that does not finish cleanly
+    bad = out["kernel_status"] != 0 or out.get("ok") is False or out.get("gathered_ok") is False \
+        or out.get("max_rel_err", 0.0) > 2e-2
+    return 1 if bad else 0
 
 
 if __name__ == "__main__":

@@ -129,3 +129,15 @@ def test_transformer_tasks_run_as_native_kernel_programs_and_match_the_interpret
     for a, b in zip(nat[2] + nat[3], ref[2] + ref[3]):
         torch.testing.assert_close(a.float(), b.float(), rtol=1e-3, atol=1e-5)
     assert K.read_status() == 0
+
+
+def test_smoke_entry_point_runs():
+    """The repository's smoke entry (one tiny training step through the MPMD compiler, native
+    task programs and the CUDA runtime context) finishes with a finite loss and a clean status."""
+    import importlib.util
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("graft_entry", os.path.join(root, "__graft_entry__.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.smoke()
