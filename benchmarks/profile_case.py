@@ -145,7 +145,7 @@ def main(argv=None) -> int:
             srcs = (c_int64 * 2)(a0.data_ptr(), a1.data_ptr())
             rc = lib.mm_allgather_gemm_bf16(srcs, 2, 0, gathered.data_ptr(), ready.data_ptr(), ctypes.byref(target),
                                             b.data_ptr(), 0, b.stride(0), res.data_ptr(), res.stride(0), M, N, Kd, 0,
-                                            torch.cuda.current_stream().cuda_stream)
+                                            None, 0, None, torch.cuda.current_stream().cuda_stream)
             _lib.check(rc, "mm_allgather_gemm_bf16")
         ms = _time(fn)
         ref = torch.cat([a0, a1]).float() @ b.float().t()

@@ -19,7 +19,9 @@
 //
 // Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, the
 // others = softmax / epilogue (TMEM lane quarter = warp % 4; four warps forward, eight - two per
-// quarter, splitting the columns - backward). All waits are bounded.
+// quarter, splitting the columns - backward; sixteen backward warps of 16 columns each were
+// measured and are not faster: 0.315 ms against 0.306 ms on B2 H16 S2048). The backward TMA warp
+// also stages the step's log-sum-exp and delta rows in shared memory. All waits are bounded.
 #include <math.h>
 
 #include "host_common.h"

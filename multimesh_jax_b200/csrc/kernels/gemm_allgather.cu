@@ -42,6 +42,9 @@ struct AllGatherHook {
   int chunk_blocks;                  // 128-row blocks per chunk
   int num_m;
   int workers_per_block;             // helper warps that copy (and signal) each row block
+  const int* shard_ready[AG_MAX_RANKS];  // local flag per rank: reaches `epoch` once that rank's shard may be
+                                         // pulled (null: the caller has synchronised the group already)
+  int epoch;
 
   static constexpr int kStageBytes = 0;
   static constexpr int kAuxWarps = 6;
@@ -113,13 +116,14 @@ struct AllGatherHook {
   // with up to eight 16-byte loads in flight per lane, so a round costs about one NVLink round
   // trip whatever the block size, and `workers_per_block` warps signal each block.
   __device__ __forceinline__ void aux(int w, int lane, int M, int K, int* err) const {
-    (void)err; (void)M;   // err is used by the checked build only
+    (void)M;
     const int wid = blockIdx.x * kAuxWarps + w;
     if (wid >= workers_per_block * AG_ROUND) return;
     const int slot = wid % AG_ROUND, sub = wid / AG_ROUND;
     const int64_t vec_per_block = static_cast<int64_t>(GEMM_BM) * K / 8;
     const int64_t per = (vec_per_block + workers_per_block - 1) / workers_per_block;
     const int64_t lo = sub * per, hi = min(vec_per_block, lo + per);
+    unsigned waited = 0;   // owners whose shard this warp has already seen published
     for (int k = slot; k < num_m; k += AG_ROUND) {
       int i = k + blocks_per_shard;                    // scheduler index: remote blocks, then own ones
       if (i >= num_m) i -= num_m;
@@ -128,6 +132,15 @@ struct AllGatherHook {
       int owner = me + hop;
       if (owner >= nranks) owner -= nranks;
       MM_CHECK_OR(blk >= 0 && blk < num_m && owner >= 0 && owner < nranks && hop < nranks, err, continue);
+      if (hop != 0 && shard_ready[owner] != nullptr && !((waited >> owner) & 1u)) {
+        // the owner raises this flag behind the write of its shard; waiting here instead of in a
+        // barrier ahead of the kernel lets the tensor cores start on this rank's own rows meanwhile
+        int ok = 1;
+        if (lane == 0) ok = wait_flag_ge(shard_ready[owner], epoch, err) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return;    // status word is set; the blocks' counters never arrive, the main loop gives up too
+        waited |= 1u << owner;
+      }
       const uint4* src = a_src[owner] + static_cast<int64_t>(i - hop * blocks_per_shard) * vec_per_block;
       uint4* dst = gathered + static_cast<int64_t>(blk) * vec_per_block;
       for (int64_t v = lo + lane; v < hi; v += 256) {
@@ -179,10 +192,14 @@ extern "C" {
 // ready: local int counters, one per 128-row block, zero before the first call and never
 // reset; *target (host memory, 0 before the first call) carries the value the counters reach
 // after this call and is updated here. chunk_rows (0: M / nranks) must be a multiple of 128 and
-// M a multiple of nranks * chunk_rows; K a multiple of 8.
+// M a multiple of nranks * chunk_rows; K a multiple of 8. shard_ready (may be null): `nranks`
+// local flag addresses; the helper warps pull rank r's shard only once *shard_ready[r] >= epoch
+// (entry `me` is ignored) - null when the caller has already synchronised the group. own_rows
+// (may be null): where this rank's shard is read from instead of a_src[me].
 int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathered, int* ready, int* target,
                            const void* B, int b_mn, int64_t ldb, void* C, int64_t ldc, int M, int N, int K,
-                           int chunk_rows, cudaStream_t stream) {
+                           int chunk_rows, const int64_t* shard_ready, int epoch, const void* own_rows,
+                           cudaStream_t stream) {
   using namespace mm;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (nranks < 1 || nranks > AG_MAX_RANKS || (K % 8) || (ldb % 8) || (ldc % 8)) return -2;
@@ -215,13 +232,19 @@ int mm_allgather_gemm_bf16(const int64_t* a_src, int nranks, int me, void* gathe
   }
   AllGatherHook hook;
   // this rank's own rows are read where they are: same box as the map of the gathered matrix
-  rc = encode_tmap_2d_bf16(&hook.tm_own, reinterpret_cast<const void*>(a_src[me]), K, M / nranks,
+  const void* own = own_rows ? own_rows : reinterpret_cast<const void*>(a_src[me]);
+  if (reinterpret_cast<uintptr_t>(own) % 16) return -2;
+  rc = encode_tmap_2d_bf16(&hook.tm_own, own, K, M / nranks,
                            static_cast<uint64_t>(K) * 2, GEMM_BK, GEMM_BM);
   if (rc) return rc;
   hook.C = C;
   hook.ldc = ldc;
   hook.vec_ok = (reinterpret_cast<uintptr_t>(C) % 16 == 0) && (ldc % 8 == 0);
-  for (int r = 0; r < nranks; ++r) hook.a_src[r] = reinterpret_cast<const uint4*>(a_src[r]);
+  for (int r = 0; r < nranks; ++r) {
+    hook.a_src[r] = reinterpret_cast<const uint4*>(r == me ? own : reinterpret_cast<const void*>(a_src[r]));
+    hook.shard_ready[r] = (shard_ready && r != me) ? reinterpret_cast<const int*>(shard_ready[r]) : nullptr;
+  }
+  hook.epoch = epoch;
   hook.gathered = static_cast<uint4*>(gathered);
   hook.ready = ready;
   hook.workers_per_block = grid * AllGatherHook::kAuxWarps / AG_ROUND;

@@ -153,7 +153,8 @@ class FusedLinearReduceScatter:
 
 
 _lib.register("mm_allgather_gemm_bf16", c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
-                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p])
+                                                c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                                c_void_p])
 
 
 class FusedAllGatherLinear:
@@ -161,8 +162,13 @@ class FusedAllGatherLinear:
     the peers' row shards over NVLink while its tensor-core main loop already works on the rows
     that have arrived (``mm_allgather_gemm_bf16``). One instance per tensor-parallel group.
 
-    Every rank first copies its shard into a peer-visible staging tile (double-buffered by call
-    parity) and the group passes a flag barrier; nothing else runs before the fused kernel."""
+    Every rank copies its shard into a peer-visible tile (double-buffered by call parity) and
+    raises its flag at the peers behind the copy; there is no barrier ahead of the kernel: its
+    helper warps wait for a peer's flag right before they pull that peer's rows, while the
+    tensor cores already work on this rank's own rows (read from the caller's tensor, not from
+    the copy). A tile is overwritten two calls later; by then this rank has seen the peers'
+    flags of the call in between, which they raise only after their kernel of the earlier call
+    has finished reading the tile."""
 
     def __init__(self, arena: symm.SymmetricArena, ranks: Sequence[int]):
         self.arena, self.ranks = arena, list(ranks)
@@ -203,14 +209,20 @@ class FusedAllGatherLinear:
         st["calls"] += 1
         par = st["calls"] & 1
         stage = st["stage"][par]
-        stage.peer(self.arena.rank).copy_(a_shard)
-        self._barrier()
+        a_shard = a_shard.contiguous()
+        a = self.arena
+        stage.peer(a.rank).copy_(a_shard)
+        self.epoch += 1
+        peers = [r for r in self.ranks if r != a.rank]
+        symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
         gathered = torch.empty((M, Kd), dtype=torch.bfloat16, device=a_shard.device)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
         srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
+        shard_ready = (c_int64 * self.g)(*[a.flag_ptr(a.rank, self.flag_off[j]) for j in range(self.g)])
         rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), ctypes.byref(st["target"]),
                                              b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
-                                             Ms // outer, torch.cuda.current_stream().cuda_stream)
+                                             Ms // outer, shard_ready, self.epoch, a_shard.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "mm_allgather_gemm_bf16")
         K._count()
         self.calls += 1
