@@ -191,6 +191,9 @@ def main(argv=None) -> int:
         out.update(shape=[T, D, E, k], ms=ms, gbs=(T * D * 2 * (1 + k)) / ms / 1e6)
     elif case in ("flash_fwd", "flash_bwd"):
         B, S, H, D = 2, 2048, 16, 128
+        extra = (argv or sys.argv[1:])[1:]
+        if len(extra) >= 2:          # flash_fwd / flash_bwd <batch> <heads>: the training step's shape is 4 32
+            B, H = int(extra[0]), int(extra[1])
         qkv = (torch.randn(B, S, 3 * H, D, device=dev) * 0.5).bfloat16()
         o, lse = attention.attention_fwd_packed(qkv, 1)
         if case == "flash_fwd":

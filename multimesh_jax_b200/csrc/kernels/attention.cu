@@ -19,9 +19,7 @@
 //
 // Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, the
 // others = softmax / epilogue (TMEM lane quarter = warp % 4; four warps forward, eight - two per
-// quarter, splitting the columns - backward; sixteen backward warps of 16 columns each were
-// measured and are not faster: 0.315 ms against 0.306 ms on B2 H16 S2048). The backward TMA warp
-// also stages the step's log-sum-exp and delta rows in shared memory. All waits are bounded.
+// quarter, splitting the columns - backward). All waits are bounded.
 #include <math.h>
 
 #include "host_common.h"
@@ -295,8 +293,7 @@ constexpr int FB_BQ = 64;
 constexpr int FB_SKV = 2 * FB_BKV * 128;  // K or V: 32 KiB
 constexpr int FB_SQ = 2 * FB_BQ * 128;    // Q or dO stage: 16 KiB
 constexpr int FB_SPT = FB_BKV * 128;      // P^T or dS^T: 16 KiB
-constexpr int FB_SROW = 2 * FB_BQ * 4;    // per stage: log-sum-exp and delta of the step's 64 query rows
-constexpr int FB_SMEM = 2 * FB_SKV + 4 * FB_SQ + 2 * FB_SPT + 256 + 2 * FB_SROW;
+constexpr int FB_SMEM = 2 * FB_SKV + 4 * FB_SQ + 2 * FB_SPT + 256;
 
 struct FaBwdParams {
   const float* lse;    // [B, Hq, S]
@@ -334,10 +331,6 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
   uint64_t* dqt_full = bars + 12;   // [1]
   uint64_t* dqt_free = bars + 13;   // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
-  // per stage [lse of the 64 query rows | delta of the 64 query rows]: fetched by the TMA warp
-  // with the step's Q / dO tiles, so the compute warps read them from shared memory instead of
-  // issuing sixteen global loads per thread and step
-  float* sRow = reinterpret_cast<float*>(sDST + FB_SPT + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x;  // key block; block 0 has the most query blocks and starts first
@@ -393,10 +386,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         const int r = n / nq, i = i0 + (n - r * nq);
         const int hq = g * p.rep + r, hp_q = g * (p.rep + 2) + r;
         if (!mbar_wait(&qdo_empty[st], ((n >> 1) & 1) ^ 1, err, MM_ERR_ATTN_WAIT)) { ok = false; break; }
-        mbar_expect_tx(&qdo_full[st], 2 * FB_SQ + FB_SROW);
-        const int64_t row_off = (static_cast<int64_t>(b) * Hq + hq) * p.S + i * FB_BQ;
-        bulk_load_1d(sRow + st * (2 * FB_BQ), p.lse + row_off, FB_BQ * 4, &qdo_full[st]);
-        bulk_load_1d(sRow + st * (2 * FB_BQ) + FB_BQ, p.delta + row_off, FB_BQ * 4, &qdo_full[st]);
+        mbar_expect_tx(&qdo_full[st], 2 * FB_SQ);
         tma_load_4d(sQ + st * FB_SQ, &tmQ, &qdo_full[st], 0, hp_q, i * FB_BQ, b);
         tma_load_4d(sQ + st * FB_SQ + FB_BQ * 128, &tmQ, &qdo_full[st], 64, hp_q, i * FB_BQ, b);
         tma_load_4d(sDO + st * FB_SQ, &tmDO, &qdo_full[st], 0, hq, i * FB_BQ, b);
@@ -496,11 +486,10 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
       const int r = n / nq, i = i0 + (n - r * nq);
       const int hq = g * p.rep + r;
       const int qcol0 = i * FB_BQ + half * 32;   // first query row (global) of this warp's columns
-      const float* lse_row = sRow + sb * (2 * FB_BQ) + half * 32;
-      const float* delta_row = lse_row + FB_BQ;
+      const float* lse_row = p.lse + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
+      const float* delta_row = p.delta + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
       const bool diag = i < i0 + FB_BKV / FB_BQ;
-      // ---- P^T (the stage's rows of lse / delta arrived with its Q and dO tiles)
-      if (ok && !mbar_wait(&qdo_full[sb], (n >> 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
+      // ---- P^T
       if (ok && !mbar_wait(&st_full[sb], (n >> 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
       tc_fence_after();
       uint32_t pk[16], dsk[16];
@@ -513,7 +502,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         if (lane == 0) mbar_arrive(&st_free[sb]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 ls = *(reinterpret_cast<const float4*>(lse_row) + c4);
+          const float4 ls = __ldg(reinterpret_cast<const float4*>(lse_row) + c4);
           const float lv[4] = {ls.x, ls.y, ls.z, ls.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -534,7 +523,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         if (lane == 0) mbar_arrive(dpt_free);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 dl = *(reinterpret_cast<const float4*>(delta_row) + c4);
+          const float4 dl = __ldg(reinterpret_cast<const float4*>(delta_row) + c4);
           const float dv[4] = {dl.x, dl.y, dl.z, dl.w};
           float pe[4], de[4];
 #pragma unroll

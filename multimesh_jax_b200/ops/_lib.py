@@ -56,6 +56,9 @@ def lib_path() -> Path:
     """The kernel library this process uses: the checked build (index checks that record
     MM_ERR_BOUNDS instead of trapping) when MM_CHECKED=1, else the normal one."""
     import os
+    alt = os.environ.get("MM_KERNEL_LIB")      # another build of the library inside the package directory (experiments)
+    if alt:
+        return _PKG / os.path.basename(alt)
     return _PKG / ("_mm_kernels_checked.so" if os.environ.get("MM_CHECKED", "0") == "1" else "_mm_kernels.so")
 
 

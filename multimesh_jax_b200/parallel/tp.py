@@ -10,6 +10,7 @@ flags carry an epoch, so nothing is ever reset between calls.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_int64, c_void_p
 from typing import Dict, Sequence, Tuple
 
@@ -179,6 +180,7 @@ class FusedAllGatherLinear:
         self.sets: Dict[Tuple[int, int], dict] = {}
         self.lib = _lib.load()
         self.calls = 0
+        self.barrier_first = os.environ.get("MM_AG_BARRIER", "0") == "1"
 
     def _barrier(self) -> None:
         self.epoch += 1
@@ -212,13 +214,17 @@ class FusedAllGatherLinear:
         a_shard = a_shard.contiguous()
         a = self.arena
         stage.peer(a.rank).copy_(a_shard)
-        self.epoch += 1
-        peers = [r for r in self.ranks if r != a.rank]
-        symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
         gathered = torch.empty((M, Kd), dtype=torch.bfloat16, device=a_shard.device)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
         srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
-        shard_ready = (c_int64 * self.g)(*[a.flag_ptr(a.rank, self.flag_off[j]) for j in range(self.g)])
+        if self.barrier_first:       # MM_AG_BARRIER=1: a flag barrier of the group ahead of the kernel (for comparisons)
+            self._barrier()
+            shard_ready = None
+        else:
+            self.epoch += 1
+            peers = [r for r in self.ranks if r != a.rank]
+            symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
+            shard_ready = (c_int64 * self.g)(*[a.flag_ptr(a.rank, self.flag_off[j]) for j in range(self.g)])
         rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), ctypes.byref(st["target"]),
                                              b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
                                              Ms // outer, shard_ready, self.epoch, a_shard.data_ptr(),
