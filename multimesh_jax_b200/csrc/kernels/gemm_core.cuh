@@ -41,6 +41,23 @@ enum GemmOut : int {
 
 struct GemmShape {
   int M, N, K;
+  // Optional run-time extents in device memory (null: the static ones). The kernel computes
+  // min(M, *m_dev) row and min(K, *k_dev) contraction elements: the tensor maps and the grid are
+  // made for the static upper bounds, the roles only walk the tiles that exist. This is how the
+  // expert GEMMs of a mixture-of-experts layer run on however many rows were routed to the expert
+  // without the host ever reading the count. An extent of zero makes the launch a no-op.
+  const int* m_dev = nullptr;
+  const int* k_dev = nullptr;
+  __device__ __forceinline__ int rows() const {
+    if (!m_dev) return M;
+    const int v = *m_dev;
+    return v < 0 ? 0 : (v < M ? v : M);
+  }
+  __device__ __forceinline__ int depth() const {
+    if (!k_dev) return K;
+    const int v = *k_dev;
+    return v < 0 ? 0 : (v < K ? v : K);
+  }
 };
 
 __device__ __forceinline__ void gemm_tile_coords(int tile, int num_m, int num_n, int& m_blk,
@@ -186,7 +203,8 @@ __global__ void __launch_bounds__(GEMM_THREADS + 32 * Hook::kAuxWarps, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int M = shape.M, N = shape.N, K = shape.K;
+  const int K = shape.depth(), N = shape.N;
+  const int M = K > 0 ? shape.rows() : 0;     // nothing to contract: no tile is visited, the output is left alone
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
   const int num_n = (N + GEMM_BN - 1) / GEMM_BN;
   const int num_tiles = num_m * num_n;

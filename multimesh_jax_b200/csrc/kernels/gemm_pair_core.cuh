@@ -120,7 +120,8 @@ __global__ void __launch_bounds__(G2_THREADS + 32 * Hook::kAuxWarps, 1)
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
-  const int M = shape.M, N = shape.N, K = shape.K;
+  const int K = shape.depth(), N = shape.N;
+  const int M = K > 0 ? shape.rows() : 0;     // nothing to contract: no tile is visited, the output is left alone
   const int num_m = (M + 2 * G2_BM - 1) / (2 * G2_BM);
   const int num_n = (N + G2_BN - 1) / G2_BN;
   const int num_tiles = num_m * num_n;
@@ -303,7 +304,8 @@ static int pair_kernel_pairs(int M, int N, int sm_count) {
 // Launches the pair kernel: clusters of two CTAs, at most as many as are resident together.
 template <bool A_MN, bool B_MN, class Hook>
 static int launch_pair_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const Hook& hook, int M, int N, int K,
-                              int sm_count, int* status, cudaStream_t stream) {
+                              int sm_count, int* status, cudaStream_t stream, const int* m_dev = nullptr,
+                              const int* k_dev = nullptr) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, Hook>;
   constexpr int smem_bytes = G2_SMEM_BYTES + Hook::kStageBytes;
   const int pairs = pair_kernel_pairs<A_MN, B_MN, Hook>(M, N, sm_count);
@@ -320,7 +322,7 @@ static int launch_pair_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, co
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  GemmShape shape{M, N, K};
+  GemmShape shape{M, N, K, m_dev, k_dev};
   if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, shape, hook, status) != cudaSuccess) {
     fprintf(stderr, "[mm_kernels] paired GEMM launch failed: %s\n", cudaGetErrorString(cudaGetLastError()));
     return -1;

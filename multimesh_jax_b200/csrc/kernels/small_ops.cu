@@ -80,8 +80,37 @@ static inline unsigned grid_for(int64_t n, int threads, int cap) {
 
 }  // namespace mm
 
+namespace mm {
+// blockIdx.y = which of the (at most `multiple` - 1) tail rows; see mm_zero_row_tail
+__global__ void zero_row_tail_kernel(uint4* __restrict__ base, int64_t vecs_per_row, const int* __restrict__ count,
+                                     int multiple, int capacity) {
+  int c = *count;
+  if (c < 0) c = 0;
+  const int64_t row = static_cast<int64_t>(c) + blockIdx.y;
+  const int64_t end = (static_cast<int64_t>(c) + multiple - 1) / multiple * multiple;
+  if (row >= end || row >= capacity) return;
+  const int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (v < vecs_per_row) base[row * vecs_per_row + v] = make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace mm
+
 extern "C" {
 using namespace mm;
+
+// Zeroes rows [*count, round_up(*count, multiple)) of a row-major matrix with `row_bytes` bytes per
+// row (a multiple of 16) and `capacity` rows: the rows a GEMM with a run-time contraction extent
+// still reads in its last k-block.
+int mm_zero_row_tail(void* base, int64_t row_bytes, const int* count, int multiple, int capacity, cudaStream_t stream) {
+  if (row_bytes <= 0 || (row_bytes & 15) || multiple < 1 || multiple > 1024) return -2;
+  const int64_t vecs = row_bytes / 16;
+  const int threads = 256;
+  const int blocks = static_cast<int>((vecs + threads - 1) / threads);
+  zero_row_tail_kernel<<<dim3(blocks, multiple), threads, 0, stream>>>(static_cast<uint4*>(base), vecs, count, multiple,
+                                                                       capacity);
+  MM_CUDA_TRY(cudaGetLastError());
+  return 0;
+}
 
 int mm_memcpy_d2d(void* dst, const void* src, int64_t bytes, cudaStream_t stream) {
   if (bytes <= 0) return 0;

@@ -23,6 +23,9 @@ _SIGS = {
                              c_int, c_int, c_int, _P]),
     "mm_gemm_pair_bf16": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int, c_int64,
                                   c_int, c_int, c_int, _P]),
+    "mm_gemm_pair_dyn_bf16": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int, c_int64,
+                                      c_int, c_int, c_int, _P, _P, _P]),
+    "mm_zero_row_tail": (c_int, [_P, c_int64, _P, c_int, c_int, _P]),
     "mm_rmsnorm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int, c_float, _P]),
     "mm_rmsnorm_bwd_parts": (c_int, [c_int64]),
     "mm_rmsnorm_bwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int, c_int, c_int, _P]),

@@ -116,13 +116,20 @@ PAIR_MIN_M = int(os.environ.get("MM_GEMM_PAIR_MIN_M", "256"))
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         accumulate: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
+         accumulate: bool = False, pair: Optional[bool] = None, m_dev: Optional[torch.Tensor] = None,
+         k_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``C[M,N] (+)= A[M,K] @ B[N,K]^T`` with bf16 inputs and fp32 accumulation.
 
     ``a_mn`` / ``b_mn`` say that the operand is stored transposed (``[K, M]`` /
     ``[K, N]`` in memory, i.e. contiguous along M / N). Operands must be 2-D
     with unit stride in the last dimension. ``pair`` selects the CTA-pair kernel
     (None: by ``PAIR_MIN_M``).
+
+    ``m_dev`` / ``k_dev``: one-element int32 device tensors with the number of rows / of
+    contraction elements that actually hold data; the shapes of the operands are then upper
+    bounds and the kernel reads the extents when it starts, so the host never needs to know
+    them (rows of ``out`` beyond ``m_dev`` are left alone; with ``k_dev`` the operands' rows up
+    to the next multiple of 64 must be zero, see :func:`zero_row_tail`).
     """
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -145,6 +152,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     assert a.dtype == bf16 and b.dtype == bf16
     mode = _OUT_MODE[(out.dtype, accumulate)]
     lib = _lib.load()
+    if m_dev is not None or k_dev is not None:
+        for t in (m_dev, k_dev):
+            assert t is None or (t.dtype == torch.int32 and t.is_cuda and t.numel() >= 1)
+        rc = lib.mm_gemm_pair_dyn_bf16(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
+                                       out.data_ptr(), mode, out.stride(0), M, N, K,
+                                       m_dev.data_ptr() if m_dev is not None else None,
+                                       k_dev.data_ptr() if k_dev is not None else None, _stream())
+        _lib.check(rc, "mm_gemm_pair_dyn_bf16")
+        _count()
+        return out
     if pair is None:
         pair = PAIR_MIN_M > 0 and M >= PAIR_MIN_M
     fn = lib.mm_gemm_pair_bf16 if pair else lib.mm_gemm_bf16
@@ -155,21 +172,38 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
-def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[T, N] = x[T, K] @ w[N, K]^T."""
-    return gemm(x, w, out=out)
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[T, N] = x[T, K] @ w[N, K]^T. ``rows``: device-side count of the rows of x that hold data."""
+    return gemm(x, w, out=out, m_dev=rows)
 
 
 def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 accumulate: bool = False) -> torch.Tensor:
+                 accumulate: bool = False, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """dx[T, K] = dy[T, N] @ w[N, K]."""
-    return gemm(dy, w, b_mn=True, out=out, accumulate=accumulate)
+    return gemm(dy, w, b_mn=True, out=out, accumulate=accumulate, m_dev=rows)
 
 
 def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
-                 accumulate: bool = False, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """dw[N, K] (+)= dy[T, N]^T @ x[T, K]."""
-    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+                 accumulate: bool = False, out_dtype: Optional[torch.dtype] = None,
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dw[N, K] (+)= dy[T, N]^T @ x[T, K]. With ``rows`` (device-side count of the rows that hold
+    data) the tails of dy and x up to the next multiple of 64 rows must be zero, and a count of
+    zero leaves ``out`` as it is."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype, k_dev=rows)
+
+
+def zero_row_tail(x: torch.Tensor, rows: torch.Tensor, multiple: int = 64) -> None:
+    """Zeroes rows [rows, round_up(rows, multiple)) of the 2-D tensor ``x`` (``rows``: int32 on the device)."""
+    assert x.dim() == 2 and x.is_contiguous() and rows.dtype == torch.int32
+    if not x.is_cuda:
+        c = int(rows[0])
+        x[c:min(x.shape[0], -(-c // multiple) * multiple)] = 0
+        return
+    rc = _lib.load().mm_zero_row_tail(x.data_ptr(), x.shape[1] * x.element_size(), rows.data_ptr(), multiple, x.shape[0],
+                                      _stream())
+    _lib.check(rc, "mm_zero_row_tail")
+    _count()
 
 
 # ------------------------------------------------------------------ RMSNorm

@@ -64,24 +64,43 @@ def select_experts(logits: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torc
     return idx, val
 
 
-def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor, out=None):
-    """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D]); ``out`` may be preallocated."""
+def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor, out=None, count=None):
+    """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D]); ``out`` may be preallocated.
+    ``count`` (one int32 on the device): only that many leading rows hold tokens - M is then the
+    capacity of the expert's receive region, the GEMMs read the count on the device and skip the
+    rest (the element-wise SwiGLU runs over the whole region; rows beyond the count hold
+    whatever the region held before and are never read back)."""
     F = wgu_e.shape[1]
-    gu = K.linear_fwd(rows, wgu_e.reshape(2 * F, -1))
+    gu = K.linear_fwd(rows, wgu_e.reshape(2 * F, -1), rows=count)
     h = K.swiglu_fwd(gu)
-    out = K.linear_fwd(h, wdown_e, out=out)
+    out = K.linear_fwd(h, wdown_e, out=out, rows=count)
     return gu, h, out
 
 
-def _expert_bwd(rows, d_out, wgu_e, wdown_e, dx_out=None, out=None):
-    """Gradients of one expert for the rows routed to it. Returns (dx_rows, dwgu_e, dwdown_e, out)."""
+def _expert_bwd(rows, d_out, wgu_e, wdown_e, dx_out=None, out=None, count=None, dwgu_out=None, dwdown_out=None):
+    """Gradients of one expert for the rows routed to it. Returns (dx_rows, dwgu_e, dwdown_e, out).
+    With ``count`` (see :func:`_expert_fwd`) the weight gradients are written into the
+    preallocated, zero-initialised ``dwgu_out`` [2, F, D] / ``dwdown_out`` [D, F] (fp32); an
+    expert that received nothing leaves them zero."""
     F = wgu_e.shape[1]
-    gu, h, out = _expert_fwd(rows, wgu_e, wdown_e, out=out)
-    dwdown = K.linear_wgrad(d_out, h, out_dtype=torch.float32)              # [D, F]
-    dh = K.linear_dgrad(d_out, wdown_e)                                      # [M, F]
-    dgu2 = K.swiglu_bwd(gu, dh)                                              # [M, 2F]
-    dwgu = K.linear_wgrad(dgu2, rows, out_dtype=torch.float32).view(2, F, -1)
-    dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1), out=dx_out)
+    gu, h, out = _expert_fwd(rows, wgu_e, wdown_e, out=out, count=count)
+    if count is None:
+        dwdown = K.linear_wgrad(d_out, h, out_dtype=torch.float32)              # [D, F]
+        dh = K.linear_dgrad(d_out, wdown_e)                                      # [M, F]
+        dgu2 = K.swiglu_bwd(gu, dh)                                              # [M, 2F]
+        dwgu = K.linear_wgrad(dgu2, rows, out_dtype=torch.float32).view(2, F, -1)
+        dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1), out=dx_out)
+        return dx, dwgu, dwdown, out
+    # the contraction of a weight gradient runs over the rows: its last 64-row block must not
+    # pick up what lies behind the count
+    for t in (d_out, h, rows):
+        K.zero_row_tail(t, count)
+    dwdown = K.linear_wgrad(d_out, h, out=dwdown_out, rows=count)
+    dh = K.linear_dgrad(d_out, wdown_e, rows=count)
+    dgu2 = K.swiglu_bwd(gu, dh)
+    K.zero_row_tail(dgu2, count)
+    dwgu = K.linear_wgrad(dgu2, rows, out=dwgu_out.view(2 * F, -1), rows=count).view(2, F, -1)
+    dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1), out=dx_out, rows=count)
     return dx, dwgu, dwdown, out
 
 

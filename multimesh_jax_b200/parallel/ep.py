@@ -6,7 +6,8 @@ that routes them into the receive region of the GPU that owns the chosen expert 
 collective, no permuted staging copy), the local experts run on the tcgen05 GEMM kernels over
 the rows that arrived, and every token pulls its results back from the owners' buffers while
 weighting them with its gates. Three flag barriers per call order the phases between the GPUs
-(bounded waits); the only host synchronisation is the read of the per-expert row counts.
+(bounded waits); the row counts of the local experts stay on the device (the expert GEMMs read them when
+they start), so a call has no host synchronisation.
 """
 from __future__ import annotations
 
@@ -50,6 +51,11 @@ class PeerMoE:
         self.epoch = 0
         self.lib = arena.lib
         self.calls = 0
+        # MM_MOE_HOST_COUNTS=1: read the per-expert row counts on the host and launch exact-size
+        # GEMMs (one host synchronisation per call); default: the GEMMs read the counts themselves.
+        # The device-side form needs receive regions whose row count suits the CTA-pair kernel.
+        import os
+        self.host_counts = os.environ.get("MM_MOE_HOST_COUNTS", "0") == "1" or self.capacity < 256
         torch.cuda.synchronize()
 
     @staticmethod
@@ -86,11 +92,21 @@ class PeerMoE:
 
     def _counts(self) -> List[int]:
         local = self.counter.peer(self.arena.rank)
-        counts = [int(c) for c in local[:self.E_l].tolist()]      # the call's only host synchronisation
+        counts = [int(c) for c in local[:self.E_l].tolist()]      # host synchronisation (MM_MOE_HOST_COUNTS=1 only)
         local.zero_()
         if max(counts) > self.capacity:
             raise RuntimeError("expert receive region overflowed")
         return counts
+
+    def _device_counts(self) -> torch.Tensor:
+        """Row counts of the local experts as a device tensor of their own (the counter words
+        are reset for the next call): the expert GEMMs read them when they start, the host
+        never does. An overflow of a receive region cannot happen (capacity = every token of
+        every member) and would be reported by the dispatch kernel through the status word."""
+        local = self.counter.peer(self.arena.rank)
+        snap = local[:max(self.E_l, 1)].clone()
+        local.zero_()
+        return snap
 
     def _combine(self, buf, idx, slot, gates, other, dots, y, T):
         rc = self.lib.mm_moe_combine(self._ptrs(buf), self.n, idx.data_ptr(), slot.data_ptr(),
@@ -110,11 +126,15 @@ class PeerMoE:
         T, me = x2.shape[0], self.arena.rank
         idx, gates, slot = self._route_dispatch(x2.contiguous(), wr.contiguous(), None)
         self.barrier()
-        counts = self._counts()
         rx, out = self.recv_x.peer(me), self.out.peer(me)
-        for e, m in enumerate(counts):
-            if m:
-                _expert_fwd(rx[e, :m], wgu[e], wdown[e], out=out[e, :m])
+        if self.host_counts:
+            for e, m in enumerate(self._counts()):
+                if m:
+                    _expert_fwd(rx[e, :m], wgu[e], wdown[e], out=out[e, :m])
+        else:
+            counts = self._device_counts()
+            for e in range(self.E_l):
+                _expert_fwd(rx[e], wgu[e], wdown[e], out=out[e], count=counts[e:e + 1])
         self.barrier()
         y = torch.empty_like(x2)
         self._combine(self.out, idx, slot, gates, None, None, y, T)
@@ -129,15 +149,20 @@ class PeerMoE:
         dy2 = dy2.contiguous()
         idx, gates, slot = self._route_dispatch(x2.contiguous(), wr.contiguous(), dy2)
         self.barrier()
-        counts = self._counts()
         rx, ro, out, dxb = (t.peer(me) for t in (self.recv_x, self.recv_o, self.out, self.dx))
         dwgu = torch.zeros(wgu.shape, dtype=torch.float32, device=x2.device)
         dwdown = torch.zeros(wdown.shape, dtype=torch.float32, device=x2.device)
-        for e, m in enumerate(counts):
-            if m:
-                _, dwgu_e, dwdown_e, _ = _expert_bwd(rx[e, :m], ro[e, :m], wgu[e], wdown[e], dx_out=dxb[e, :m], out=out[e, :m])
-                dwgu[e] = dwgu_e
-                dwdown[e] = dwdown_e
+        if self.host_counts:
+            for e, m in enumerate(self._counts()):
+                if m:
+                    _, dwgu_e, dwdown_e, _ = _expert_bwd(rx[e, :m], ro[e, :m], wgu[e], wdown[e], dx_out=dxb[e, :m], out=out[e, :m])
+                    dwgu[e] = dwgu_e
+                    dwdown[e] = dwdown_e
+        else:
+            counts = self._device_counts()
+            for e in range(self.E_l):
+                _expert_bwd(rx[e], ro[e], wgu[e], wdown[e], dx_out=dxb[e], out=out[e], count=counts[e:e + 1],
+                            dwgu_out=dwgu[e], dwdown_out=dwdown[e])
         self.barrier()
         dx = torch.empty_like(x2)
         self._combine(self.dx, idx, slot, None, None, None, dx, T)

@@ -59,6 +59,47 @@ def test_gemm_pair_layouts(M, N, K_, a_mn, b_mn):
     _close(out, ref)
 
 
+@pytest.mark.parametrize("count", [0, 1, 100, 256, 300, 1000, 1024, 5000])
+def test_gemm_with_row_and_contraction_extents_read_on_the_device(count):
+    """The GEMMs of a mixture-of-experts expert run over a receive region of fixed capacity and
+    read how many of its rows hold tokens from device memory: forward / input-gradient form
+    (the count limits M; rows of the output beyond it are left alone) and weight-gradient form
+    (the count limits the contraction; the operands' rows up to the next multiple of 64 are
+    zeroed first; a count of zero leaves the output untouched)."""
+    torch.manual_seed(count)
+    cap, D, F = 1024, 256, 384
+    x = _rand(cap, D)
+    w = _rand(F, D, scale=0.1)
+    n = torch.tensor([count], dtype=torch.int32, device=DEV)
+    live = min(count, cap)
+    # forward form: y[:live] = x[:live] w^T, the rest keeps its sentinel
+    y = torch.full((cap, F), 7.0, dtype=torch.bfloat16, device=DEV)
+    K.linear_fwd(x, w, out=y, rows=n)
+    if live:
+        _close(y[:live], x[:live].float() @ w.float().t())
+    assert bool((y[live:] == 7.0).all())
+    # input-gradient form
+    dy = _rand(cap, F)
+    dx = torch.full((cap, D), 7.0, dtype=torch.bfloat16, device=DEV)
+    K.linear_dgrad(dy, w, out=dx, rows=n)
+    if live:
+        _close(dx[:live], dy[:live].float() @ w.float())
+    assert bool((dx[live:] == 7.0).all())
+    # weight-gradient form: rows behind the count hold NaN until their tails are zeroed
+    dy2, x2 = dy.clone(), x.clone()
+    dy2[live:] = float("nan")
+    x2[live:] = float("nan")
+    K.zero_row_tail(dy2, n)
+    K.zero_row_tail(x2, n)
+    dw = torch.full((F, D), 3.0, dtype=torch.float32, device=DEV)
+    K.linear_wgrad(dy2, x2, out=dw, rows=n)
+    if live:
+        _close(dw, dy[:live].float().t() @ x[:live].float())
+    else:
+        assert bool((dw == 3.0).all())
+    assert K.read_status() == 0
+
+
 def test_gemm_pair_accumulates_into_fp32():
     torch.manual_seed(1)
     T, Kd, N = 2048, 512, 768
