@@ -143,11 +143,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if not a.is_cuda:
         af = (a.t() if a_mn else a).float()
         bf = (b.t() if b_mn else b).float()
-        res = af @ bf.t()
+        rows = min(M, max(0, int(m_dev[0]))) if m_dev is not None else M
+        depth = min(K, max(0, int(k_dev[0]))) if k_dev is not None else K
+        if depth == 0:
+            return out
+        res = af[:rows, :depth] @ bf[:, :depth].t()
         if accumulate:
-            out.add_(res.to(out.dtype))
+            out[:rows].add_(res.to(out.dtype))
         else:
-            out.copy_(res.to(out.dtype))
+            out[:rows].copy_(res.to(out.dtype))
         return out
     assert a.dtype == bf16 and b.dtype == bf16
     mode = _OUT_MODE[(out.dtype, accumulate)]
