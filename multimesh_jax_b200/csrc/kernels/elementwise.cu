@@ -287,9 +287,14 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float* __restr
 
 // ------------------------------------------------------------------- SwiGLU
 // gu is [T, 2F]: gate in columns [0,F), up in [F,2F).  h = silu(gate) * up.
+// rows_dev (may be null): device-side count of the rows that hold data; rows behind it are skipped.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ h, int64_t T, int F) {
+                                  __nv_bfloat16* __restrict__ h, int64_t T, int F, const int* __restrict__ rows_dev) {
   // two 8-element groups per thread (half the array apart), all four loads issued first
+  if (rows_dev) {
+    const int64_t live = *rows_dev;
+    T = live < 0 ? 0 : (live < T ? live : T);
+  }
   const int fv = F / 8;
   const int64_t total = T * fv;
   const int64_t half = (total + 1) / 2;
@@ -325,7 +330,11 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu,
 // dgu[:, :F] = dh * up * silu'(gate),  dgu[:, F:] = dh * silu(gate)
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu,
                                   const __nv_bfloat16* __restrict__ dh,
-                                  __nv_bfloat16* __restrict__ dgu, int64_t T, int F) {
+                                  __nv_bfloat16* __restrict__ dgu, int64_t T, int F, const int* __restrict__ rows_dev) {
+  if (rows_dev) {
+    const int64_t live = *rows_dev;
+    T = live < 0 ? 0 : (live < T ? live : T);
+  }
   const int fv = F / 8;
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= T * fv) return;
@@ -658,24 +667,33 @@ int mm_rope(void* qk, const float* cos_t, const float* sin_t, int64_t T, int S, 
   return 0;
 }
 
-int mm_swiglu_fwd(const void* gu, void* h, int64_t T, int F, cudaStream_t stream) {
+// rows_dev (may be null): one int in device memory, the number of leading rows that hold data
+// (T is then the capacity the launch is sized for).
+int mm_swiglu_fwd_rows(const void* gu, void* h, int64_t T, int F, const int* rows_dev, cudaStream_t stream) {
   if (F % 8) return -2;
   const int64_t total = T * (F / 8);
   if (total == 0) return 0;
   swiglu_fwd_kernel<<<blocks_for((total + 1) / 2, 256), 256, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), T, F);
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(h), T, F, rows_dev);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
 }
-int mm_swiglu_bwd(const void* gu, const void* dh, void* dgu, int64_t T, int F, cudaStream_t stream) {
+int mm_swiglu_fwd(const void* gu, void* h, int64_t T, int F, cudaStream_t stream) {
+  return mm_swiglu_fwd_rows(gu, h, T, F, nullptr, stream);
+}
+int mm_swiglu_bwd_rows(const void* gu, const void* dh, void* dgu, int64_t T, int F, const int* rows_dev,
+                       cudaStream_t stream) {
   if (F % 8) return -2;
   const int64_t total = T * (F / 8);
   if (total == 0) return 0;
   swiglu_bwd_kernel<<<blocks_for(total, 256), 256, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(dh),
-      static_cast<__nv_bfloat16*>(dgu), T, F);
+      static_cast<__nv_bfloat16*>(dgu), T, F, rows_dev);
   MM_CUDA_TRY(cudaGetLastError());
   return 0;
+}
+int mm_swiglu_bwd(const void* gu, const void* dh, void* dgu, int64_t T, int F, cudaStream_t stream) {
+  return mm_swiglu_bwd_rows(gu, dh, dgu, T, F, nullptr, stream);
 }
 
 int mm_cross_entropy(void* logits, const int64_t* targets, float* loss, float* stats_out,

@@ -32,6 +32,8 @@ _SIGS = {
     "mm_rope": (c_int, [_P, _P, _P, c_int64, c_int, c_int, c_int, c_int64, c_int, c_int, c_int, _P]),
     "mm_swiglu_fwd": (c_int, [_P, _P, c_int64, c_int, _P]),
     "mm_swiglu_bwd": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
+    "mm_swiglu_fwd_rows": (c_int, [_P, _P, c_int64, c_int, _P, _P]),
+    "mm_swiglu_bwd_rows": (c_int, [_P, _P, _P, c_int64, c_int, _P, _P]),
     "mm_cross_entropy": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int, c_int64, c_int, c_float,
                                  c_int, _P]),
     "mm_ce_combine": (c_int, [_P, c_int, _P, _P, _P, c_int64, _P]),

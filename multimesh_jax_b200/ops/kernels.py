@@ -319,20 +319,23 @@ def rope_(qk: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, backward: bool
 
 
 # ------------------------------------------------------------------- SwiGLU
-def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+def swiglu_fwd(gu: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h = silu(gate) * up. ``rows`` (one int32 on the device): only that many leading rows hold
+    data; the others are skipped and their part of the result stays uninitialised."""
     T, F2 = gu.shape
     F = F2 // 2
     if not gu.is_cuda:
         g, u = gu[:, :F].float(), gu[:, F:].float()
         return (torch.nn.functional.silu(g) * u).to(gu.dtype)
     h = torch.empty((T, F), dtype=gu.dtype, device=gu.device)
-    rc = _lib.load().mm_swiglu_fwd(gu.data_ptr(), h.data_ptr(), T, F, _stream())
+    rc = _lib.load().mm_swiglu_fwd_rows(gu.data_ptr(), h.data_ptr(), T, F, rows.data_ptr() if rows is not None else None,
+                                        _stream())
     _lib.check(rc, "mm_swiglu_fwd")
     _count()
     return h
 
 
-def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
+def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     T, F2 = gu.shape
     F = F2 // 2
     if not gu.is_cuda:
@@ -342,7 +345,8 @@ def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
         du = d * g * sg
         return torch.cat([dg, du], dim=1).to(gu.dtype)
     dgu = torch.empty_like(gu)
-    rc = _lib.load().mm_swiglu_bwd(gu.data_ptr(), dh.contiguous().data_ptr(), dgu.data_ptr(), T, F, _stream())
+    rc = _lib.load().mm_swiglu_bwd_rows(gu.data_ptr(), dh.contiguous().data_ptr(), dgu.data_ptr(), T, F,
+                                        rows.data_ptr() if rows is not None else None, _stream())
     _lib.check(rc, "mm_swiglu_bwd")
     _count()
     return dgu

@@ -67,12 +67,12 @@ def select_experts(logits: torch.Tensor, top_k: int) -> Tuple[torch.Tensor, torc
 def _expert_fwd(rows: torch.Tensor, wgu_e: torch.Tensor, wdown_e: torch.Tensor, out=None, count=None):
     """rows [M, D] -> (gu [M, 2F] (gate | up), h [M, F], out [M, D]); ``out`` may be preallocated.
     ``count`` (one int32 on the device): only that many leading rows hold tokens - M is then the
-    capacity of the expert's receive region, the GEMMs read the count on the device and skip the
-    rest (the element-wise SwiGLU runs over the whole region; rows beyond the count hold
-    whatever the region held before and are never read back)."""
+    capacity of the expert's receive region; the GEMMs and the SwiGLU kernel read the count on
+    the device and skip the rest (rows beyond the count hold whatever the buffers held before
+    and are never read back)."""
     F = wgu_e.shape[1]
     gu = K.linear_fwd(rows, wgu_e.reshape(2 * F, -1), rows=count)
-    h = K.swiglu_fwd(gu)
+    h = K.swiglu_fwd(gu, rows=count)
     out = K.linear_fwd(h, wdown_e, out=out, rows=count)
     return gu, h, out
 
@@ -97,7 +97,7 @@ def _expert_bwd(rows, d_out, wgu_e, wdown_e, dx_out=None, out=None, count=None, 
         K.zero_row_tail(t, count)
     dwdown = K.linear_wgrad(d_out, h, out=dwdown_out, rows=count)
     dh = K.linear_dgrad(d_out, wdown_e, rows=count)
-    dgu2 = K.swiglu_bwd(gu, dh)
+    dgu2 = K.swiglu_bwd(gu, dh, rows=count)
     K.zero_row_tail(dgu2, count)
     dwgu = K.linear_wgrad(dgu2, rows, out=dwgu_out.view(2 * F, -1), rows=count).view(2, F, -1)
     dx = K.linear_dgrad(dgu2, wgu_e.reshape(2 * F, -1), out=dx_out, rows=count)

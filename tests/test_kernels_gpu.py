@@ -97,6 +97,15 @@ def test_gemm_with_row_and_contraction_extents_read_on_the_device(count):
         _close(dw, dy[:live].float().t() @ x[:live].float())
     else:
         assert bool((dw == 3.0).all())
+    # the element-wise kernels between the expert GEMMs honour the same count
+    gu = _rand(cap, 2 * F)
+    h = K.swiglu_fwd(gu, rows=n)
+    if live:
+        _close(h[:live], K.swiglu_fwd(gu[:live].contiguous()))
+    dh = _rand(cap, F)
+    dgu = K.swiglu_bwd(gu, dh, rows=n)
+    if live:
+        _close(dgu[:live], K.swiglu_bwd(gu[:live].contiguous(), dh[:live].contiguous()))
     assert K.read_status() == 0
 
 
