@@ -5,8 +5,8 @@
 that routes them into the receive region of the GPU that owns the chosen expert (no all-to-all
 collective, no permuted staging copy), the local experts run on the tcgen05 GEMM kernels over
 the rows that arrived, and every token pulls its results back from the owners' buffers while
-weighting them with its gates. Three flag barriers per call order the phases between the GPUs
-(bounded waits); the row counts of the local experts stay on the device (the expert GEMMs read them when
+weighting them with its gates. Two flag barriers per call order the phases between the GPUs
+(bounded waits; the regions are double-buffered by call, which makes a third one unnecessary); the row counts of the local experts stay on the device (the expert GEMMs read them when
 they start), so a call has no host synchronisation.
 """
 from __future__ import annotations
@@ -41,10 +41,12 @@ class PeerMoE:
         self.E_l = n_experts // self.n
         self.capacity = self.n * tokens            # a token picks an expert at most once
         shape = (self.E_l, self.capacity, d_model)
-        self.recv_x = arena.alloc(shape, torch.bfloat16)
-        self.recv_o = arena.alloc(shape, torch.bfloat16)
-        self.out = arena.alloc(shape, torch.bfloat16)
-        self.dx = arena.alloc(shape, torch.bfloat16)
+        # Two sets of regions, used alternately: the dispatch of call c+1 writes into the set that
+        # nobody reads any more (its last readers, the combines of call c-1, lie behind two barriers
+        # of call c), so no barrier is needed between the combine of one call and the dispatch of
+        # the next - two barriers per call instead of three.
+        self._sets = [{name: arena.alloc(shape, torch.bfloat16) for name in ("recv_x", "recv_o", "out", "dx")}
+                      for _ in range(2)]
         self.counter = arena.alloc((max(self.E_l, 4),), torch.int32)
         self.counter.peer(arena.rank).zero_()
         self.flag_off = [arena.alloc_flag() for _ in self.ranks]   # one flag per group member
@@ -60,7 +62,13 @@ class PeerMoE:
 
     @staticmethod
     def required_bytes(tokens: int, d_model: int, n_experts: int) -> int:
-        return 4 * n_experts * tokens * d_model * 2 + (1 << 20)
+        return 2 * 4 * n_experts * tokens * d_model * 2 + (1 << 20)
+
+    # the regions of the current call
+    recv_x = property(lambda self: self._sets[self.calls & 1]["recv_x"])
+    recv_o = property(lambda self: self._sets[self.calls & 1]["recv_o"])
+    out = property(lambda self: self._sets[self.calls & 1]["out"])
+    dx = property(lambda self: self._sets[self.calls & 1]["dx"])
 
     # ------------------------------------------------------------------
     def _ptrs(self, t: symm.SymmetricTensor):
@@ -138,7 +146,6 @@ class PeerMoE:
         self.barrier()
         y = torch.empty_like(x2)
         self._combine(self.out, idx, slot, gates, None, None, y, T)
-        self.barrier()
         return y
 
     def backward(self, dy2, x2, wr, wgu, wdown, top_k: int):
@@ -168,7 +175,6 @@ class PeerMoE:
         self._combine(self.dx, idx, slot, None, None, None, dx, T)
         dgates = torch.empty((T, top_k), dtype=torch.float32, device=x2.device)
         self._combine(self.out, idx, slot, None, dy2, dgates, None, T)
-        self.barrier()
         dx_r, dwr = _router_bwd(x2, wr, idx.long(), gates, dgates)
         dx = (dx.float() + dx_r).to(x2.dtype)
         return dx, dwr.to(wr.dtype), dwgu.to(wgu.dtype), dwdown.to(wdown.dtype)
