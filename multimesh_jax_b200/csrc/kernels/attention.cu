@@ -19,16 +19,21 @@
 //
 // Warp roles (both kernels): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, the
 // others = softmax / epilogue (TMEM lane quarter = warp % 4; four warps forward, eight - two per
-// quarter, splitting the columns - backward). All waits are bounded.
+// quarter, splitting the columns - backward). The backward TMA warp also brings the step's
+// log-sum-exp and delta rows into shared memory with the step's Q / dO tiles, two steps ahead of
+// their use: as global loads of the compute warps they queued in the load/store unit behind the
+// 32 dQ reductions every thread issues per step. All waits are bounded.
 //
 // Measured on the backward call (B4 H32 S2048, one GPU, alternating runs; 0.816 ms before): a
-// three-stage Q / dO ring 0.793 ms and ex2.approx instead of exp2f 0.780 ms (both kept; forward
-// 0.252 -> 0.233 ms); the step's log-sum-exp / delta rows staged in shared memory 0.940 ms, sixteen
-// compute warps of 16 columns 3 % slower, dQ through shared memory and cp.reduce.async.bulk
-// 0.92 ms, dQ atomics interleaved with the next step's exponentials 0.86 ms (none kept). A
-// cycle-stamped trace of one CTA shows a step of 64 queries x 128 keys taking 5,200 cycles: the
-// eight compute warps are busy for 4,500 of them (exponentials 1,280, dS 970, the 32 dQ
-// reductions per thread 1,320) and the MMA lane issues 32 small (N = 64) instructions in 2,300.
+// three-stage Q / dO ring 0.793 ms, ex2.approx instead of exp2f 0.780 ms, the staged rows on top
+// of the ring 0.700 ms (all kept; forward 0.252 -> 0.233 ms with ex2.approx). The same staging
+// with a two-stage ring was slower (0.940 ms: the rows arrived with the tiles, one step ahead,
+// and the compute warps waited for them). Also not kept: sixteen compute warps of 16 columns
+// (3 % slower), dQ through shared memory and cp.reduce.async.bulk (0.92 ms), dQ reductions
+// interleaved with the next step's exponentials (0.86 ms). A cycle-stamped trace of one CTA
+// before these changes: 5,200 cycles per 64-query step, the eight compute warps busy for 4,500
+// of them (exponentials 1,280, dS 970, the dQ reductions 1,320), the MMA lane issuing its 32
+// small (N = 64) instructions in 2,300.
 #include <math.h>
 
 #include "host_common.h"
@@ -315,7 +320,8 @@ constexpr int FB_SPT = FB_BKV * 128;      // P^T or dS^T: 16 KiB
 // products of step n, so with two stages every step also paid the latency of a TMA load that
 // could only be issued when step n - 1 had released its stage (0.816 -> 0.793 ms on B4 H32 S2048).
 constexpr int FB_QST = 3;
-constexpr int FB_SMEM = 2 * FB_SKV + 2 * FB_QST * FB_SQ + 2 * FB_SPT + 256;
+constexpr int FB_SROW = 2 * FB_BQ * 4;    // per stage: log-sum-exp and delta of the step's 64 query rows
+constexpr int FB_SMEM = 2 * FB_SKV + 2 * FB_QST * FB_SQ + 2 * FB_SPT + 256 + FB_QST * FB_SROW;
 
 struct FaBwdParams {
   const float* lse;    // [B, Hq, S]
@@ -353,6 +359,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
   uint64_t* dqt_full = ps_ready + 1;             // [1]
   uint64_t* dqt_free = dqt_full + 1;             // [1]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dqt_free + 1);
+  float* sRow = reinterpret_cast<float*>(sDST + FB_SPT + 256);   // [FB_QST][lse 64 | delta 64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x;  // key block; block 0 has the most query blocks and starts first
@@ -410,7 +417,18 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         const int r = n / nq, i = i0 + (n - r * nq);
         const int hq = g * p.rep + r, hp_q = g * (p.rep + 2) + r;
         if (!mbar_wait(&qdo_empty[st], ((n / FB_QST) & 1) ^ 1, err, MM_ERR_ATTN_WAIT)) { ok = false; break; }
-        mbar_expect_tx(&qdo_full[st], 2 * FB_SQ);
+        mbar_expect_tx(&qdo_full[st], 2 * FB_SQ + FB_SROW);
+        {
+          const int64_t row_off = (static_cast<int64_t>(b) * Hq + hq) * p.S + i * FB_BQ;
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           smem_u32(sRow + st * (2 * FB_BQ))),
+                       "l"(p.lse + row_off), "r"(FB_BQ * 4), "r"(smem_u32(&qdo_full[st]))
+                       : "memory");
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                           smem_u32(sRow + st * (2 * FB_BQ) + FB_BQ)),
+                       "l"(p.delta + row_off), "r"(FB_BQ * 4), "r"(smem_u32(&qdo_full[st]))
+                       : "memory");
+        }
         tma_load_4d(sQ + st * FB_SQ, &tmQ, &qdo_full[st], 0, hp_q, i * FB_BQ, b);
         tma_load_4d(sQ + st * FB_SQ + FB_BQ * 128, &tmQ, &qdo_full[st], 64, hp_q, i * FB_BQ, b);
         tma_load_4d(sDO + st * FB_SQ, &tmDO, &qdo_full[st], 0, hq, i * FB_BQ, b);
@@ -510,10 +528,11 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
       const int r = n / nq, i = i0 + (n - r * nq);
       const int hq = g * p.rep + r;
       const int qcol0 = i * FB_BQ + half * 32;   // first query row (global) of this warp's columns
-      const float* lse_row = p.lse + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
-      const float* delta_row = p.delta + (static_cast<int64_t>(b) * Hq + hq) * p.S + qcol0;
+      const float* lse_row = sRow + (n % FB_QST) * (2 * FB_BQ) + half * 32;
+      const float* delta_row = lse_row + FB_BQ;
       const bool diag = i < i0 + FB_BKV / FB_BQ;
-      // ---- P^T
+      // ---- P^T (st_full follows the MMA lane's wait for the stage's qdo_full, which also covers the rows)
+      if (ok && !mbar_wait(&qdo_full[n % FB_QST], (n / FB_QST) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
       if (ok && !mbar_wait(&st_full[sb], (n >> 1) & 1, err, MM_ERR_ATTN_WAIT)) ok = false;
       tc_fence_after();
       uint32_t pk[16], dsk[16];
@@ -526,7 +545,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         if (lane == 0) mbar_arrive(&st_free[sb]);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 ls = __ldg(reinterpret_cast<const float4*>(lse_row) + c4);
+          const float4 ls = *(reinterpret_cast<const float4*>(lse_row) + c4);
           const float lv[4] = {ls.x, ls.y, ls.z, ls.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
@@ -547,7 +566,7 @@ __global__ void __launch_bounds__(FB_THREADS, 1)
         if (lane == 0) mbar_arrive(dpt_free);
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 dl = __ldg(reinterpret_cast<const float4*>(delta_row) + c4);
+          const float4 dl = *(reinterpret_cast<const float4*>(delta_row) + c4);
           const float dv[4] = {dl.x, dl.y, dl.z, dl.w};
           float pe[4], de[4];
 #pragma unroll
