@@ -95,6 +95,7 @@ class _ScatterBufferSet:
         self.recv = [arena.alloc((g - 1, Ms, N), torch.bfloat16) for _ in range(2)]
         self.flags = [arena.alloc((g - 1, self.tiles), torch.int32) for _ in range(2)]
         self.epoch = 0
+        self.args = [None, None]      # per parity: the four address arrays of a call (they never change)
 
 
 class FusedLinearReduceScatter:
@@ -133,15 +134,18 @@ class FusedLinearReduceScatter:
             bs = self.sets[(Ms, N)] = _ScatterBufferSet(self.arena, Ms, N, g)
         bs.epoch += 1
         par = bs.epoch & 1
-        recv, flags = bs.recv[par], bs.flags[par]
-        slot_bytes, flag_bytes = Ms * N * 2, bs.tiles * 4
-        my_rank = self.arena.rank
-        recv_local = (c_int64 * (g - 1))(*[recv.ptr(my_rank) + p * slot_bytes for p in range(g - 1)])
-        flag_local = (c_int64 * (g - 1))(*[flags.ptr(my_rank) + p * flag_bytes for p in range(g - 1)])
-        recv_peer = (c_int64 * g)(*[0 if r == me else recv.ptr(self.ranks[r]) + self._sender_slot(me, r) * slot_bytes
-                                   for r in range(g)])
-        flag_peer = (c_int64 * g)(*[0 if r == me else flags.ptr(self.ranks[r]) + self._sender_slot(me, r) * flag_bytes
-                                   for r in range(g)])
+        if bs.args[par] is None:
+            recv, flags = bs.recv[par], bs.flags[par]
+            slot_bytes, flag_bytes = Ms * N * 2, bs.tiles * 4
+            my_rank = self.arena.rank
+            bs.args[par] = (
+                (c_int64 * (g - 1))(*[recv.ptr(my_rank) + p * slot_bytes for p in range(g - 1)]),
+                (c_int64 * g)(*[0 if r == me else recv.ptr(self.ranks[r]) + self._sender_slot(me, r) * slot_bytes
+                                for r in range(g)]),
+                (c_int64 * (g - 1))(*[flags.ptr(my_rank) + p * flag_bytes for p in range(g - 1)]),
+                (c_int64 * g)(*[0 if r == me else flags.ptr(self.ranks[r]) + self._sender_slot(me, r) * flag_bytes
+                                for r in range(g)]))
+        recv_local, recv_peer, flag_local, flag_peer = bs.args[par]
         out = torch.empty((Ms, N), dtype=torch.bfloat16, device=a.device)
         rc = self.lib.mm_gemm_reducescatter_bf16(a.data_ptr(), int(a_mn), a.stride(0), b.data_ptr(), int(b_mn), b.stride(0),
                                                  out.data_ptr(), out.stride(0), M, N, Kd, recv_local, recv_peer,
@@ -181,6 +185,8 @@ class FusedAllGatherLinear:
         self.lib = _lib.load()
         self.calls = 0
         self.barrier_first = os.environ.get("MM_AG_BARRIER", "0") == "1"
+        self._peer_flags = None
+        self._shard_ready = None
 
     def _barrier(self) -> None:
         self.epoch += 1
@@ -207,7 +213,7 @@ class FusedAllGatherLinear:
             st = self.sets[(Ms, Kd)] = {
                 "stage": [self.arena.alloc((Ms, Kd), torch.bfloat16) for _ in range(2)],
                 "ready": torch.zeros(M // BM, dtype=torch.int32, device=a_shard.device), "calls": 0,
-                "target": c_int(0)}
+                "target": c_int(0), "srcs": [None, None]}
         st["calls"] += 1
         par = st["calls"] & 1
         stage = st["stage"][par]
@@ -216,15 +222,19 @@ class FusedAllGatherLinear:
         stage.peer(a.rank).copy_(a_shard)
         gathered = torch.empty((M, Kd), dtype=torch.bfloat16, device=a_shard.device)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
-        srcs = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
+        if st["srcs"][par] is None:
+            st["srcs"][par] = (c_int64 * self.g)(*[stage.ptr(r) for r in self.ranks])
+        srcs = st["srcs"][par]
         if self.barrier_first:       # MM_AG_BARRIER=1: a flag barrier of the group ahead of the kernel (for comparisons)
             self._barrier()
             shard_ready = None
         else:
             self.epoch += 1
-            peers = [r for r in self.ranks if r != a.rank]
-            symm.set_flags(a, [a.flag_ptr(r, self.flag_off[self.me]) for r in peers], self.epoch)
-            shard_ready = (c_int64 * self.g)(*[a.flag_ptr(a.rank, self.flag_off[j]) for j in range(self.g)])
+            if self._peer_flags is None:
+                self._peer_flags = [a.flag_ptr(r, self.flag_off[self.me]) for r in self.ranks if r != a.rank]
+                self._shard_ready = (c_int64 * self.g)(*[a.flag_ptr(a.rank, self.flag_off[j]) for j in range(self.g)])
+            symm.set_flags(a, self._peer_flags, self.epoch)
+            shard_ready = self._shard_ready
         rc = self.lib.mm_allgather_gemm_bf16(srcs, self.g, self.me, gathered.data_ptr(), st["ready"].data_ptr(), ctypes.byref(st["target"]),
                                              b.data_ptr(), int(b_mn), b.stride(0), out.data_ptr(), out.stride(0), M, N, Kd,
                                              Ms // outer, shard_ready, self.epoch, a_shard.data_ptr(),
