@@ -304,6 +304,12 @@ def main():
     last = None
     for i in range(args.warmup):
         last = run_step(i, False)
+    # The compiled program (captured graph, plan, per-task programs) is a large, long-lived object
+    # graph: a full collection that walks it takes a few hundred milliseconds of host time, longer
+    # than the launch queue can cover. Everything alive now is moved out of the collector's reach.
+    import gc
+    gc.collect()
+    gc.freeze()
     barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
