@@ -103,3 +103,37 @@ def test_expert_selection_is_total_for_nan_and_infinite_logits():
     idx, val = moe.select_experts(rnd, 2)
     topv, topi = rnd.topk(2, dim=-1)
     assert torch.equal(idx, topi) and torch.equal(val, topv)
+
+
+@pytest.mark.parametrize("count", [0, 5, 64, 100])
+def test_expert_functions_with_a_row_count_equal_the_exact_size_call(count):
+    """The expert forward / backward over a receive region of fixed capacity with the number of
+    live rows given as a tensor (the form the GPU path uses so that the host never reads the
+    count) equals the same functions on exactly the live rows; rows behind the count may hold
+    anything, including NaN."""
+    from multimesh_jax_b200.ops.moe import _expert_bwd, _expert_fwd
+    torch.manual_seed(count)
+    cap, D, F = 128, 32, 48
+    rows = torch.randn(cap, D)
+    d_out = torch.randn(cap, D)
+    wgu = torch.randn(2, F, D) * 0.2
+    wdown = torch.randn(D, F) * 0.2
+    rows[count:] = float("nan")
+    d_out[count:] = float("nan")
+    n = torch.tensor([count], dtype=torch.int32)
+    out = torch.zeros(cap, D)
+    _, _, out = _expert_fwd(rows.clone(), wgu, wdown, out=out, count=n)
+    dwgu = torch.zeros(2, F, D)
+    dwdown = torch.zeros(D, F)
+    dx = torch.zeros(cap, D)
+    _expert_bwd(rows.clone(), d_out.clone(), wgu, wdown, dx_out=dx, out=torch.zeros(cap, D), count=n, dwgu_out=dwgu,
+                dwdown_out=dwdown)
+    if count == 0:
+        assert bool((dwgu == 0).all()) and bool((dwdown == 0).all())
+        return
+    _, _, ref_out = _expert_fwd(rows[:count].contiguous(), wgu, wdown)
+    ref_dx, ref_dwgu, ref_dwdown, _ = _expert_bwd(rows[:count].contiguous(), d_out[:count].contiguous(), wgu, wdown)
+    torch.testing.assert_close(out[:count], ref_out, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dx[:count], ref_dx, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dwgu, ref_dwgu, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(dwdown, ref_dwdown, rtol=1e-4, atol=1e-5)
