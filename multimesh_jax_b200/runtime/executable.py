@@ -261,9 +261,17 @@ class Executable:
         me = self._alias_root[sid]
         prev = self._owner.get(key)
         if prev is not None and prev != me and old is not None and old is not new and old.is_floating_point() \
-                and old.untyped_storage().data_ptr() != new.untyped_storage().data_ptr():
+                and old.untyped_storage().data_ptr() != new.untyped_storage().data_ptr() and not self._in_arena(old):
+            # (tiles inside the peer-mapped arena are left alone: another GPU may still be pulling them)
             old.fill_(float("nan"))
         self._owner[key] = me
+
+    def _in_arena(self, t: torch.Tensor) -> bool:
+        pr = getattr(self, "_peer_reshard", None)
+        if pr is None or not t.is_cuda:
+            return False
+        a = pr.arena
+        return a.base <= t.data_ptr() < a.base + a.nbytes
 
     def _check_owner(self, sid: int, d: int, reader: str) -> None:
         key = (self.buffer_of[sid], d)
