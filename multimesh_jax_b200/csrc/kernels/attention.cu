@@ -29,7 +29,7 @@
 // of the ring 0.700 ms (all kept; forward 0.252 -> 0.233 ms with ex2.approx). The same staging
 // with a two-stage ring was slower (0.940 ms: the rows arrived with the tiles, one step ahead,
 // and the compute warps waited for them). Also not kept: sixteen compute warps of 16 columns
-// (3 % slower), dQ through shared memory and cp.reduce.async.bulk (0.92 ms; 0.86 ms against 0.70
+// (3 % slower before the staging, 0.6 % faster after it), dQ through shared memory and cp.reduce.async.bulk (0.92 ms; 0.86 ms against 0.70
 // with a reducer warp of its own), dQ reductions
 // interleaved with the next step's exponentials (0.86 ms). A cycle-stamped trace of one CTA
 // before these changes: 5,200 cycles per 64-query step, the eight compute warps busy for 4,500
