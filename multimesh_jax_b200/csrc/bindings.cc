@@ -160,6 +160,7 @@ struct Compiler {
     else if (name == "spmd_lowering") changed = SpmdLowering(s);
     else if (name == "hoist_shard_map_reduce") changed = HoistShardMapReduce(s);
     else if (name == "reduce_scatter_creator") changed = ReduceScatterCreator(s);
+    else if (name == "split_update_by_reduction") changed = SplitUpdateByReduction(s);
     else if (name == "unused_param_output_remover") changed = UnusedParamOutputRemover(s);
     else throw std::runtime_error("unknown pass '" + name + "'");
     ValidateCircularDependencies(s, name);

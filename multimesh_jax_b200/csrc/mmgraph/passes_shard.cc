@@ -1030,6 +1030,31 @@ bool HoistShardMapReduce(CompileState& s) {
     g.order = keep;
     g.Toposort();
     s.Note("hoisted gradient reductions out of the microbatch loop");
+    // hoisted reductions live after the loop: each gets a task of its own, with the colour and
+    // devices of the accumulator it reduces, placed right after the last loop task
+    Partition& part = *s.partition;
+    for (auto& n : g.nodes) {
+      if (n.dead || n.Attr("hoisted") != "1" || n.task >= 0) continue;
+      const Node& src = g.node(g.value(n.inputs[0]).producer);
+      TaskGroup grp;
+      int max_id = 0;
+      for (auto& x : s.groups) max_id = std::max(max_id, x.id + 1);
+      grp.id = max_id;
+      const ColorConfig& cc = part.Get(src.color);
+      grp.color = part.Recolor(src.color, std::to_string(grp.id) + "." + (cc.original.empty() ? src.color : cc.original) + "_reduce");
+      grp.region = 2;
+      grp.nodes = {n.id};
+      n.task = grp.id;
+      n.color = grp.color;
+      // the reduction reads the accumulator in the layout the loop tasks left it in
+      if (g.value(n.inputs[0]).has_sharding) SetInputSharding(s, grp.id, n.inputs[0], g.value(n.inputs[0]).sharding);
+      size_t pos = s.groups.size();
+      for (size_t i = 0; i < s.groups.size(); ++i) if (s.groups[i].region == 2) { pos = i; break; }
+      s.groups.insert(s.groups.begin() + pos, grp);
+    }
+    std::vector<int> order;
+    for (auto& grp : s.groups) order.insert(order.end(), grp.nodes.begin(), grp.nodes.end());
+    g.order = order;
   }
   return changed;
 }

@@ -9,7 +9,6 @@
 namespace mmg {
 
 void ReleaseShardingTables(const CompileState& s);
-void SetInputSharding(const CompileState& s, int group, int value, const ShardedShape& sh);
 
 namespace {
 
@@ -88,36 +87,7 @@ Plan MpmdPartition(Graph& g, Partition& part, const PartitionConfig& cfg, std::v
   RunPass(s, "sharding_propagation_backward_io", [&] { return ShardingPropagation(s, PropagationMode::kBackwardInputOutput); }, &counter);
   RunPass(s, "sharding_propagation_forward_full", [&] { return ShardingPropagation(s, PropagationMode::kForwardFull); }, &counter);
   RunPass(s, "spmd_lowering", [&] { return SpmdLowering(s); }, &counter);
-  RunPass(s, "hoist_shard_map_reduce", [&] {
-    const bool c = HoistShardMapReduce(s);
-    if (c) {
-      // hoisted reductions live after the loop: give them a task of their own colour/devices
-      for (auto& n : g.nodes) {
-        if (n.dead || n.Attr("hoisted") != "1" || n.task >= 0) continue;
-        const Node& src = g.node(g.value(n.inputs[0]).producer);
-        TaskGroup grp;
-        int max_id = 0;
-        for (auto& x : s.groups) max_id = std::max(max_id, x.id + 1);
-        grp.id = max_id;
-        const ColorConfig& cc = part.Get(src.color);
-        grp.color = part.Recolor(src.color, std::to_string(grp.id) + "." + (cc.original.empty() ? src.color : cc.original) + "_reduce");
-        grp.region = 2;
-        grp.nodes = {n.id};
-        n.task = grp.id;
-        n.color = grp.color;
-        // the reduction reads the accumulator in the layout the loop tasks left it in
-        if (g.value(n.inputs[0]).has_sharding) SetInputSharding(s, grp.id, n.inputs[0], g.value(n.inputs[0]).sharding);
-        // place right after the last loop group
-        size_t pos = s.groups.size();
-        for (size_t i = 0; i < s.groups.size(); ++i) if (s.groups[i].region == 2) { pos = i; break; }
-        s.groups.insert(s.groups.begin() + pos, grp);
-      }
-      std::vector<int> order;
-      for (auto& grp : s.groups) order.insert(order.end(), grp.nodes.begin(), grp.nodes.end());
-      g.order = order;
-    }
-    return c;
-  }, &counter);
+  RunPass(s, "hoist_shard_map_reduce", [&] { return HoistShardMapReduce(s); }, &counter);
   RunPass(s, "reduce_scatter_creator", [&] { return ReduceScatterCreator(s); }, &counter);
   RunPass(s, "split_update_by_reduction", [&] { return SplitUpdateByReduction(s); }, &counter);
   RunPass(s, "unused_param_output_remover", [&] { return UnusedParamOutputRemover(s); }, &counter);
