@@ -33,6 +33,10 @@ FIXTURES = {
     "llama_tp2_sequence_parallel": ((1, 1, 2), "1f1b", {"sequence_parallel": True, "vocab_parallel": True}, {}),
     "llama_pp2_dp2_tp2_gpipe": ((2, 2, 2), "gpipe", {}, {}),
     "mixtral_ep2_pp2": ((2, 2, 1), "1f1b", {"n_experts": 4, "top_k": 2}, {}),
+    "llama_tp2_all_reduce": ((1, 1, 2), "1f1b", {}, {}),
+    "llama_pp2_dp2_fsdp_zero_bubble": ((2, 2, 1), "zero-bubble-h2", {}, {"fsdp": True}),
+    "llama_pp4_uneven_stages_1f1b": ((4, 1, 1), "1f1b", {"n_layers": 6, "layers_per_stage": [2, 2, 1, 1]}, {}),
+    "llama_one_device_microbatched": ((1, 1, 1), "1f1b", {}, {}),
 }
 SUMMARY_KEYS = ("status", "message", "hazards", "plan_hash", "templates", "template_names", "stores", "tasks", "reshards",
                 "reshard_bytes", "temp_bytes_per_device_max", "device_high_water_max", "device_high_water", "stats")
@@ -43,7 +47,7 @@ def capture(name: str, path: str) -> None:
     n = pp * dp * tp
     torch.manual_seed(0)
     moe = {k: model_opts[k] for k in ("n_experts", "top_k") if k in model_opts}
-    cfg = llama.LlamaConfig.tiny(n_layers=2 * pp, n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128, **moe)
+    cfg = llama.LlamaConfig.tiny(n_layers=model_opts.get("n_layers", 2 * pp), n_heads=4, n_kv_heads=2, d_model=64, d_ff=96, vocab=128, **moe)
     cfg.dtype = torch.float32
     cfg.sequence_parallel = model_opts.get("sequence_parallel", False)
     cfg.vocab_parallel = model_opts.get("vocab_parallel", False)
@@ -56,7 +60,8 @@ def capture(name: str, path: str) -> None:
                                  schedule=schedule, **step_opts)
     mesh = mm.MultiMesh((pp, dp, tp), ("stage", "data", "model"))
     split = ("_act", "_wgt") if schedule == "zero-bubble-h2" else None
-    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, split_backprop=split)
+    llama.register_pipeline_tasks(cfg, mesh, num_stages=pp, split_backprop=split,
+                                  layers_per_stage=model_opts.get("layers_per_stage"))
     with mesh:
         exe = mm.compile_function(step, (params, opt_state, tokens, tokens, cos, sin), mesh=mesh,
                                   context=_mm_C.MockContext(n), topology=Topology("cpu", n), donate_argnums=(0, 1),
