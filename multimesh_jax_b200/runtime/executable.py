@@ -203,6 +203,11 @@ class Executable:
         self._step = 0
         self._created = False
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
+        # per-step invariants of the dispatch loop, built at first submission and reused
+        self._task_entries: Dict[Tuple[int, int], tuple] = {}
+        self._reshard_entries: Dict[int, list] = {}
+        self._cur_step = 0
+        self._cur_roots: Dict[int, Dict[int, torch.Tensor]] = {}
         self._setup_fused_tp()
         # one-process-per-GPU jobs: side stream for stage-boundary messages, and the events
         # that mark the arrival of a received tile, keyed by (buffer, device)
@@ -550,6 +555,10 @@ class Executable:
                 for d_ in new_tiles:
                     self._owner[(self.buffer_of[sid], d_)] = self._alias_root[sid]
         root_tiles: Dict[int, Dict[int, torch.Tensor]] = {sid: {} for sid in plan["root_stores"]}
+        # the task bodies are built once per (operation, device) and kept; what changes from step to
+        # step reaches them through these two fields (the previous step's bodies have all run: the
+        # wait above, or inline submission)
+        self._cur_step, self._cur_roots = step, root_tiles
         # dispatch loop
         for k, op in enumerate(plan["ops"]):
             kind = op["kind"]
@@ -599,6 +608,20 @@ class Executable:
 
     # ------------------------------------------------------------------ tasks
     def _submit_task(self, k: int, op: dict, d: int, step: int, root_tiles):
+        entry = self._task_entries.get((k, d))
+        if entry is None:
+            entry = self._task_entries[(k, d)] = self._make_task_entry(k, op, d)
+        reads, writes, body, kind = entry
+        self.launches += 1
+        if self._cuda_ctx:
+            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step,
+                                             kind)
+        else:
+            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step)
+
+    def _make_task_entry(self, k: int, op: dict, d: int):
+        """Read / write tile lists, stream kind and body of operation ``k`` on device ``d``: everything
+        about a task launch that does not change between steps, built at its first submission."""
         prog = self.programs[op["template"]]
         tiles = self.tiles
         dctx = self.dev_ctx[d]
@@ -649,7 +672,8 @@ class Executable:
         def run_on_current_stream():
             dctx.device_start = dev_start
             dctx.mesh_dims = mesh_dims
-            dctx.key_prefix = (step, k)
+            dctx.key_prefix = (self._cur_step, k)
+            root_tiles = self._cur_roots
             dctx.stream_kind = kind
             if dctx.torch_device.type == "cuda":
                 torch.cuda.set_device(dctx.torch_device)
@@ -709,6 +733,7 @@ class Executable:
         def run_native(ins):
             """The task as one call into the C++ launcher: slots = input tiles, the output block,
             the scratch tile, the accumulators this launch adds into."""
+            root_tiles = self._cur_roots
             blocks = [torch.empty(nb, dtype=torch.uint8, device=dctx.torch_device) for nb in native.out_chunks]
             bases = [t.data_ptr() for t in ins]
             bases.append(blocks[0].data_ptr() if blocks else 0)
@@ -744,12 +769,7 @@ class Executable:
                 if s in root_tiles:
                     root_tiles[s][d] = o
 
-        self.launches += 1
-        if self._cuda_ctx:
-            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step,
-                                             kind)
-        else:
-            self.context.create_execute_task(d, reads, writes, body, op["name"], op["strict_ordering"], op["priority"], step)
+        return reads, writes, body, kind
 
     # ------------------------------------------------------------------ reshards
     def _reshard_plan(self, src_sid: int, dst_sid: int) -> dict:
@@ -761,6 +781,19 @@ class Executable:
         return self._reshard_plans[key]
 
     def _submit_reshard(self, k: int, op: dict, step: int, root_tiles):
+        entries = self._reshard_entries.get(k)
+        if entries is None:
+            entries = self._reshard_entries[k] = self._make_reshard_entries(op)
+        for d, reads, writes, body, label in entries:
+            self.launches += 1
+            if self._cuda_ctx:
+                self.context.reshard(d, reads, writes, body, label, step, 1)
+            else:
+                self.context.reshard(d, reads, writes, body, label, step)
+
+    def _make_reshard_entries(self, op: dict) -> list:
+        """One (device, reads, writes, body, label) per local device that sends or receives a part
+        of this reshard; built at the first submission, the same in every step."""
         from ..parallel.reshard import run_reshard_local, run_reshard_dist
         topo = self.topology
         src_sid, dst_sid = op["src_store"], op["dst_store"]
@@ -769,6 +802,8 @@ class Executable:
         dst_shape = self.plan["stores"][dst_sid]["shape"]
         buf = self.buffer_of
         tiles = self.tiles
+        label = f"reshard S{src_sid}->S{dst_sid}"
+        entries = []
         for d in range(op["device_start"], op["device_start"] + op["num_devices"]):
             if not topo.is_local(d):
                 continue
@@ -779,33 +814,27 @@ class Executable:
             if topo.kind == "dist":
                 reads = [(buf[src_sid], d)] if mine_src else []
                 writes = [(buf[dst_sid], d)] if mine_dst else []
+                both = mine_src + [c for c in mine_dst if c not in mine_src]
 
-                def body(d=d, mine_dst=mine_dst, mine_src=mine_src):
-                    side = self._streams.get(1) if self._cuda_ctx else None
-                    if side is None:
-                        return move(d, mine_dst, mine_src, None)
-                    with torch.cuda.stream(side):       # the context ordered this stream behind the producer
-                        return move(d, mine_dst, mine_src, side)
-
-                def move(d, mine_dst, mine_src, side):
-                    prev = self._arrival.get((self.buffer_of[src_sid], d))
+                def move(side, d=d, mine_dst=mine_dst, mine_src=mine_src, both=both):
+                    root_tiles = self._cur_roots
+                    prev = self._arrival.get((buf[src_sid], d))
                     if prev is not None:     # the source itself arrived by message
                         torch.cuda.current_stream().wait_event(prev)
                     pr = self._peer_reshard
-                    key = (self.buffer_of[src_sid], self.buffer_of[dst_sid])
+                    key = (buf[src_sid], buf[dst_sid])
                     if self._lifetimes and mine_src:
-                        self._check_owner(src_sid, d, f"reshard S{src_sid}->S{dst_sid}")
+                        self._check_owner(src_sid, d, label)
                     src_tile = tiles[src_sid].get(d)
                     if side is not None and src_tile is not None and src_tile.is_cuda:
                         src_tile.record_stream(side)
                     if pr is not None and pr.slots.get(key) is not None:
-                        out, ev = pr.run(key, d, src_tile, mine_src + [c for c in mine_dst if c not in mine_src],
-                                         src_shape, dst_shape, self._comm_stream(d))
+                        out, ev = pr.run(key, d, src_tile, both, src_shape, dst_shape, self._comm_stream(d))
                     else:
                         out, ev = run_reshard_dist(topo, d, src_tile, mine_src, mine_dst, dst_shape,
                                                    self._comm_stream(d))
                     if ev is not None and out is not None:
-                        self._arrival[(self.buffer_of[dst_sid], d)] = ev
+                        self._arrival[(buf[dst_sid], d)] = ev
                     if out is not None:
                         if side is not None and self._compute_stream is not None:
                             out.record_stream(self._compute_stream)   # allocated here, read by tasks of the compute stream
@@ -814,16 +843,24 @@ class Executable:
                         tiles[dst_sid][d] = out
                         if dst_sid in root_tiles:
                             root_tiles[dst_sid][d] = out
+
+                def inner(move=move):
+                    side = self._streams.get(1) if self._cuda_ctx else None
+                    if side is None:
+                        return move(None)
+                    with torch.cuda.stream(side):       # the context ordered this stream behind the producer
+                        return move(side)
             else:
                 if not mine_dst:
                     continue
                 reads = sorted({(buf[src_sid], c["src_device"]) for c in mine_dst})
                 writes = [(buf[dst_sid], d)]
 
-                def body(d=d, mine_dst=mine_dst):
+                def inner(d=d, mine_dst=mine_dst):
+                    root_tiles = self._cur_roots
                     if self._lifetimes:
                         for c in mine_dst:
-                            self._check_owner(src_sid, c["src_device"], f"reshard S{src_sid}->S{dst_sid}")
+                            self._check_owner(src_sid, c["src_device"], label)
                     out = run_reshard_local(topo, d, tiles[src_sid], mine_dst, dst_shape)
                     if self._lifetimes:
                         self._took_buffer(dst_sid, d, tiles[dst_sid].get(d), out)
@@ -831,15 +868,14 @@ class Executable:
                     if dst_sid in root_tiles:
                         root_tiles[dst_sid][d] = out
 
-            if state.knobs["task_ranges"]:
-                def body(inner=body, label=f"mm.reshard:S{src_sid}->S{dst_sid}"):
-                    with torch.profiler.record_function(label):
-                        inner()
-            self.launches += 1
-            if self._cuda_ctx:
-                self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step, 1)
-            else:
-                self.context.reshard(d, reads, writes, body, f"reshard S{src_sid}->S{dst_sid}", step)
+            def body(inner=inner):
+                if state.knobs["task_ranges"]:
+                    with torch.profiler.record_function("mm." + label.replace(" ", ":", 1)):
+                        return inner()
+                return inner()
+
+            entries.append((d, reads, writes, body, label))
+        return entries
 
     # ------------------------------------------------------------------ misc
     def _check_kernel_status(self, block: bool) -> None:

@@ -275,3 +275,28 @@ def test_lifetime_checking_catches_two_live_stores_in_one_buffer(monkeypatch):
         loss.wait()
         exe.wait()
     exe.shutdown()
+
+
+def test_task_and_reshard_bodies_are_built_once_and_reused_by_later_steps():
+    exe = _compile_and_check(_step("1f1b"), _two_stage(), _loss_task())     # first step ran in the helper
+    ops = exe.plan["ops"]
+    n_tasks = sum(op["num_devices"] for op in ops if op["kind"] == "task")
+    n_reshards = sum(1 for op in ops if op["kind"] == "reshard")
+    assert len(exe._task_entries) == n_tasks and len(exe._reshard_entries) == n_reshards
+    bodies = {key: entry[2] for key, entry in exe._task_entries.items()}
+    moves = {k: [e[3] for e in entries] for k, entries in exe._reshard_entries.items()}
+    params, batch = _params(), _data()
+    with mm.ignore_transforms():
+        loss_ref, grads_ref = _step("1f1b")(params, batch)
+    for _ in range(2):                       # later steps: same closures, fresh results
+        loss, grads = exe(params, batch)
+        torch.testing.assert_close(loss.full_tensor(), loss_ref, rtol=1e-5, atol=1e-5)
+        for a, b in zip(grads, grads_ref):
+            torch.testing.assert_close(a.full_tensor(), b, rtol=1e-5, atol=1e-5)
+    assert all(exe._task_entries[key][2] is body for key, body in bodies.items())
+    assert all([e[3] for e in exe._reshard_entries[k]] == m for k, m in moves.items())
+    # a different input gives a different result through the same bodies
+    x, y = batch
+    loss2, _ = exe(params, (x * 2.0, y))
+    assert abs(float(loss2.full_tensor()) - float(loss_ref)) > 1e-3
+    exe.shutdown()
