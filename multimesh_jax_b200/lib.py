@@ -180,6 +180,12 @@ def shard_map(fun: Callable, in_specs: Sequence[Optional[Sequence[AxisSpec]]],
     return wrapped
 
 
+def optional_kwargs(**kwargs):
+    """The keyword arguments whose value is not ``None``: lets a caller forward only the options a
+    user actually set (multimesh/jax/lib.py:247-252)."""
+    return {k: v for k, v in kwargs.items() if v is not None}
+
+
 @contextlib.contextmanager
 def tasks(configurable: Any):
     """Registers every ``(matcher, Task | factory)`` pair produced by

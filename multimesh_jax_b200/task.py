@@ -239,6 +239,21 @@ class MultiMesh(Context):
         return f"MultiMesh({self.mesh.shape})"
 
 
+def get_global_mesh() -> TaskMesh:
+    """The whole mesh of the innermost active :class:`MultiMesh` (``with mesh:``), devices included
+    (multimesh/jax/task.py:1152-1153: the physical mesh of the enclosing mesh context)."""
+    mesh = MultiMesh.current()
+    if mesh is None:
+        raise RuntimeError("get_global_mesh() needs an active MultiMesh")
+    return mesh.mesh
+
+
+def get_abstract_global_mesh() -> Dict[str, int]:
+    """Axis names and sizes of the active mesh without its devices: what sharding rules and
+    shape-only code may depend on (multimesh/jax/task.py:1156-1157)."""
+    return dict(get_global_mesh().shape)
+
+
 def slice_global_mesh(**axis_idx: int) -> TaskMesh:
     mesh = MultiMesh.current()
     if mesh is None:

@@ -68,11 +68,17 @@ def test_multimesh_slice_and_context_nesting():
     with mesh:
         assert mm.MultiMesh.current() is mesh
         assert list(mm.slice_global_mesh(stage=1).devices) == [4, 5, 6, 7]
+        assert mm.get_global_mesh() is mesh.mesh and mm.get_global_mesh().size == 8
+        assert mm.get_abstract_global_mesh() == {"stage": 2, "data": 2, "model": 2}
         inner = mm.MultiMesh((2,), ("x",))
         with inner:
             assert mm.MultiMesh.current() is inner
+            assert mm.get_abstract_global_mesh() == {"x": 2}
         assert mm.MultiMesh.current() is mesh
     assert mm.MultiMesh.current() is None
+    with pytest.raises(RuntimeError, match="active MultiMesh"):
+        mm.get_global_mesh()
+    assert mm.optional_kwargs(mesh=None, devices=[0, 1], donate=None, name="") == {"devices": [0, 1], "name": ""}
     m2 = mm.TaskMesh((2, 2), ("a", "b")).place([4, 5, 6, 7])
     assert list(m2.devices) == [4, 5, 6, 7] and m2.size == 4
 
