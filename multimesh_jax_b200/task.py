@@ -14,7 +14,7 @@ from __future__ import annotations
 import contextlib
 import re
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple, Union
+from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple, Union
 
 import torch
 from torch.utils import _pytree as pytree
@@ -59,6 +59,11 @@ class TaskMesh:
     def place(self, devices: Sequence[int]) -> "TaskMesh":
         """Same mesh shape on other devices."""
         return TaskMesh(self.axis_sizes, self.axis_names, devices)
+
+    @property
+    def abstract_mesh(self) -> Dict[str, int]:
+        """Axis names and sizes without the devices (multimesh/jax/task.py:108-110)."""
+        return self.shape
 
     def __eq__(self, other):
         return (isinstance(other, TaskMesh) and self.axis_sizes == other.axis_sizes
@@ -133,6 +138,23 @@ class Context:
         Context._stack.pop()
         return False
 
+    def find_matching_slice_in_scope(self) -> Optional[Mapping[str, int]]:
+        """Mesh slice of the task this context registers for the operator name stack at this point
+        of a capture: innermost scope first, and within a scope the registration made last. ``None``
+        outside a capture or when nothing matches; an error when the matching task names a whole
+        mesh instead of a slice (multimesh/jax/task.py:160-182)."""
+        scopes = [e.name for e in state.trace.scopes] if state.trace.active else []
+        for scope in reversed(scopes):
+            for reg in reversed(self.registrations):
+                m = re.search(reg.matcher, scope)
+                if not m:
+                    continue
+                t = reg.factory(m.group(1), False)
+                if t.mesh_slice is None:
+                    raise ValueError(f"task {m.group(1)} does not return a mesh slice: {t}")
+                return t.mesh_slice
+        return None
+
     @staticmethod
     def active_registrations() -> List[_Registration]:
         """Innermost context first."""
@@ -193,6 +215,60 @@ class MultiMesh(Context):
     @property
     def size(self):
         return self.mesh.size
+
+    @property
+    def shape_tuple(self) -> Tuple[Tuple[str, int], ...]:
+        return tuple(zip(self.mesh.axis_names, self.mesh.axis_sizes))
+
+    @property
+    def abstract_mesh(self) -> Dict[str, int]:
+        return self.mesh.abstract_mesh
+
+    @property
+    def empty(self) -> bool:
+        return self.mesh.size == 0
+
+    @property
+    def local_devices(self) -> List[int]:
+        """Device ordinals of the mesh that this process drives: all of them in a one-process job,
+        the rank's own one in a one-process-per-GPU job (``torch.distributed`` initialised)."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            return [d for d in self.mesh.devices if d == dist.get_rank()]
+        return list(self.mesh.devices)
+
+    @property
+    def is_multi_process(self) -> bool:
+        return len(self.local_devices) != self.mesh.size
+
+    def single_slice_devices(self, **axis_idx: int):
+        """The device ordinals with the named axes fixed, as a nested list that keeps every axis of
+        the mesh (fixed axes have extent 1). Unlike :meth:`slice` the result need not be a contiguous
+        range: this is a query, not a task placement (multimesh/jax/task.py:383-390)."""
+        names, sizes = self.mesh.axis_names, self.mesh.axis_sizes
+        for a in axis_idx:
+            if a not in names:
+                raise ValueError(f"unknown mesh axis {a!r}")
+
+        def build(axis: int, flat: int):
+            if axis == len(sizes):
+                return self.mesh.devices[flat]
+            picks = [axis_idx[names[axis]]] if names[axis] in axis_idx else range(sizes[axis])
+            return [build(axis + 1, flat * sizes[axis] + i) for i in picks]
+        return build(0, 0)
+
+    def single_slice_ids(self, **axis_idx: int) -> List[int]:
+        """Flat list of the device ordinals of :meth:`single_slice_devices`."""
+        out: List[int] = []
+
+        def walk(x):
+            if isinstance(x, list):
+                for y in x:
+                    walk(y)
+            else:
+                out.append(x)
+        walk(self.single_slice_devices(**axis_idx))
+        return out
 
     def slice(self, **axis_idx: int) -> TaskMesh:
         """Sub-mesh with the named axes fixed at the given indices. The result

@@ -338,3 +338,41 @@ def test_cluster_detection_reads_the_launchers_environment(monkeypatch):
         mm.detect_cluster("ompi")
     with pytest.raises(ValueError):
         mm.detect_cluster("kubernetes")
+
+
+def test_mesh_queries_and_scope_lookup_during_a_capture():
+    mesh = mm.MultiMesh((2, 2, 2), ("stage", "data", "model"))
+    assert mesh.shape_tuple == (("stage", 2), ("data", 2), ("model", 2))
+    assert mesh.abstract_mesh == {"stage": 2, "data": 2, "model": 2} == mesh.mesh.abstract_mesh
+    assert not mesh.empty and not mesh.is_multi_process and mesh.local_devices == list(range(8))
+    # a query, not a placement: fixing an inner axis gives a strided set that slice() would refuse
+    assert mesh.single_slice_devices(model=1) == [[[1], [3]], [[5], [7]]]
+    assert mesh.single_slice_ids(model=1) == [1, 3, 5, 7]
+    assert mesh.single_slice_ids(stage=1, data=0) == [4, 5]
+    assert mesh.single_slice_ids() == list(range(8))
+    with pytest.raises(ValueError, match="unknown mesh axis"):
+        mesh.single_slice_ids(pipeline=0)
+    with pytest.raises(ValueError, match="contiguous"):
+        mesh.slice(model=1)
+
+    mesh.register_task(r"(blk\.\d+)", factory=lambda m, b: mm.Task(name=m, mesh_slice={"stage": int(m.split(".")[1])}))
+    mesh.register_task("(whole)", task=mm.Task(name="whole", mesh=mesh.mesh))
+    seen = {}
+
+    def fn(x):
+        seen["outside"] = mesh.find_matching_slice_in_scope()
+        with mm.named_scope("blk.0"):
+            seen["blk.0"] = mesh.find_matching_slice_in_scope()
+            y = x * 2.0
+        with mm.named_scope("blk.1"):
+            with mm.named_scope("inner"):
+                seen["blk.1/inner"] = mesh.find_matching_slice_in_scope()
+            y = y + 1.0
+        return y.sum()
+
+    assert mesh.find_matching_slice_in_scope() is None          # not capturing
+    with mesh:
+        exe = mm.compile_function(fn, (torch.ones(4),), mesh=mesh, backend="cpu")
+    assert seen == {"outside": None, "blk.0": {"stage": 0}, "blk.1/inner": {"stage": 1}}
+    assert float(exe(torch.ones(4)).full_tensor()) == 12.0
+    exe.shutdown()
