@@ -123,25 +123,33 @@ class Json {
   static void skip_ws(const std::string& t, size_t& p) {
     while (p < t.size() && (t[p] == ' ' || t[p] == '\n' || t[p] == '\t' || t[p] == '\r')) ++p;
   }
-  static Json parse_value(const std::string& t, size_t& p) {
-    skip_ws(t, p);
+  // The character at `p`; text that ends where a character is needed is an error, never a read
+  // past the end.
+  static char peek(const std::string& t, size_t p) {
     if (p >= t.size()) throw std::runtime_error("json: unexpected end");
-    char c = t[p];
+    return t[p];
+  }
+  static constexpr int kMaxDepth = 256;
+  static Json parse_value(const std::string& t, size_t& p, int depth = 0) {
+    if (depth > kMaxDepth) throw std::runtime_error("json: nested too deeply");
+    skip_ws(t, p);
+    const char c = peek(t, p);
     if (c == '{') {
       Json j = object();
       ++p;
       skip_ws(t, p);
-      if (t[p] == '}') { ++p; return j; }
+      if (peek(t, p) == '}') { ++p; return j; }
       while (true) {
         skip_ws(t, p);
         Json key = parse_string(t, p);
         skip_ws(t, p);
-        if (t[p] != ':') throw std::runtime_error("json: expected ':'");
+        if (peek(t, p) != ':') throw std::runtime_error("json: expected ':'");
         ++p;
-        j.obj.emplace_back(key.str, parse_value(t, p));
+        j.obj.emplace_back(key.str, parse_value(t, p, depth + 1));
         skip_ws(t, p);
-        if (t[p] == ',') { ++p; continue; }
-        if (t[p] == '}') { ++p; break; }
+        const char sep = peek(t, p);
+        if (sep == ',') { ++p; continue; }
+        if (sep == '}') { ++p; break; }
         throw std::runtime_error("json: expected ',' or '}'");
       }
       return j;
@@ -150,12 +158,13 @@ class Json {
       Json j = array();
       ++p;
       skip_ws(t, p);
-      if (t[p] == ']') { ++p; return j; }
+      if (peek(t, p) == ']') { ++p; return j; }
       while (true) {
-        j.arr.push_back(parse_value(t, p));
+        j.arr.push_back(parse_value(t, p, depth + 1));
         skip_ws(t, p);
-        if (t[p] == ',') { ++p; continue; }
-        if (t[p] == ']') { ++p; break; }
+        const char sep = peek(t, p);
+        if (sep == ',') { ++p; continue; }
+        if (sep == ']') { ++p; break; }
         throw std::runtime_error("json: expected ',' or ']'");
       }
       return j;
@@ -165,28 +174,38 @@ class Json {
     if (t.compare(p, 5, "false") == 0) { p += 5; return boolean(false); }
     if (t.compare(p, 4, "null") == 0) { p += 4; return Json(); }
     size_t end = p;
-    while (end < t.size() && (isdigit(t[end]) || t[end] == '-' || t[end] == '+' || t[end] == '.' ||
-                              t[end] == 'e' || t[end] == 'E'))
+    while (end < t.size() && (isdigit(static_cast<unsigned char>(t[end])) || t[end] == '-' || t[end] == '+' ||
+                              t[end] == '.' || t[end] == 'e' || t[end] == 'E'))
       ++end;
     if (end == p) throw std::runtime_error("json: unexpected character");
-    Json j = number(std::stod(t.substr(p, end - p)));
+    double value = 0;
+    try {
+      size_t used = 0;
+      value = std::stod(t.substr(p, end - p), &used);
+      if (used != end - p) throw std::runtime_error("");
+    } catch (const std::exception&) {
+      throw std::runtime_error("json: malformed number '" + t.substr(p, end - p) + "'");
+    }
     p = end;
-    return j;
+    return number(value);
   }
   static Json parse_string(const std::string& t, size_t& p) {
-    if (t[p] != '"') throw std::runtime_error("json: expected string");
+    if (peek(t, p) != '"') throw std::runtime_error("json: expected string");
     ++p;
     std::string out;
-    while (p < t.size() && t[p] != '"') {
-      if (t[p] == '\\' && p + 1 < t.size()) {
+    while (true) {
+      const char c = peek(t, p);      // an unterminated string runs into the end of the text: error
+      if (c == '"') break;
+      if (c == '\\') {
         ++p;
-        switch (t[p]) {
+        const char e = peek(t, p);
+        switch (e) {
           case 'n': out += '\n'; break;
           case 't': out += '\t'; break;
-          default: out += t[p];
+          default: out += e;
         }
       } else {
-        out += t[p];
+        out += c;
       }
       ++p;
     }

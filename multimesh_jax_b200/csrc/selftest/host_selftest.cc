@@ -9,7 +9,14 @@
 //      dependency edge is a data race the thread sanitizer reports and a wrong checksum here;
 //   3. replays the submission log through the hazard checker;
 //   4. injects host-side faults (a task body that throws, a dropped task) and checks that the
-//      error surfaces as a status and that the context stays usable.
+//      error surfaces as a status and that the context stays usable;
+//   5. for every stored-program file named on the command line (real-model training steps with
+//      pipeline, tensor, sequence, data and expert parallelism): loads it, compiles it offline,
+//      replays the plan on the mock runtime, writes the program back to text, reads that again
+//      and compares the plans; then feeds the loader truncated and corrupted copies of the text,
+//      which must be refused with an exception, never read out of bounds.
+//
+//   host_selftest [repeats] [stored-program.json ...]
 //
 // Exit code 0 = all checks passed. The reference gets the same assurance from its ASAN build type
 // (CMakeLists.txt:12-17) over the mock-runtime tests.
@@ -22,6 +29,7 @@
 
 #include "../mmgraph/graph.h"
 #include "../mmgraph/passes.h"
+#include "../mmgraph/program_file.h"
 #include "../mmrt/runtime.h"
 
 using namespace mmg;
@@ -197,6 +205,46 @@ static RunResult Execute(const Plan& plan, int num_devices, bool inject_throw) {
   return res;
 }
 
+static void CheckStoredProgram(const std::string& path) {
+  Plan plan;
+  std::vector<std::string> log;
+  OfflineResult r = CompileProgramFile(path, 0, &plan, &log);
+  CHECK(r.status == 0, ("stored program did not replay cleanly: " + path + ": " + r.message).c_str());
+  CHECK(r.hazards.empty(), r.hazards.c_str());
+  CHECK(r.tasks > 0 && r.templates > 0 && r.device_high_water_max > 0, "degenerate offline result");
+  CHECK(r.fits, "a plan cannot fail to fit without a device-memory size");
+  OfflineResult tight = CompileProgramFile(path, r.device_high_water_max - 1);
+  CHECK(!tight.fits && tight.plan_hash == r.plan_hash, "memory limit below the high-water mark must not fit");
+  // text -> program -> text -> program: the second reading compiles to the same plan
+  StoredProgram first = LoadProgram(path);
+  const std::string text = ProgramToJson(*first.graph, *first.partition, first.config);
+  StoredProgram second = ProgramFromJson(text);
+  std::vector<std::string> log2;
+  Plan plan2 = MpmdPartition(*second.graph, *second.partition, second.config, &log2);
+  CHECK(plan2.Hash() == r.plan_hash, "a program written back and read again compiles to another plan");
+  // damaged text must be refused, not read past its end
+  int refused = 0, tried = 0;
+  for (size_t cut : {text.size() / 7, text.size() / 3, text.size() / 2, text.size() - 2}) {
+    ++tried;
+    try { ProgramFromJson(text.substr(0, cut)); } catch (const std::exception&) { ++refused; }
+  }
+  CHECK(refused == tried, "a truncated program file was accepted");
+  std::string wrong = text;
+  const size_t at = wrong.find("\"inputs\":[");
+  if (at != std::string::npos) {
+    wrong.insert(at + 10, "123456789,");     // an operand id that no value has
+    bool threw = false;
+    try {
+      StoredProgram bad = ProgramFromJson(wrong);
+      MpmdPartition(*bad.graph, *bad.partition, bad.config);
+    } catch (const std::exception&) { threw = true; }
+    CHECK(threw, "an operand id out of range was accepted");
+  }
+  std::printf("%-60s %d templates, %d tasks, %d reshards, high water %lld bytes\n",
+              path.substr(path.find_last_of('/') + 1).c_str(), r.templates, r.tasks, r.reshards,
+              static_cast<long long>(r.device_high_water_max));
+}
+
 int main(int argc, char** argv) {
   const int repeats = argc > 1 ? std::atoi(argv[1]) : 3;
   const char* schedules[] = {"gpipe", "1f1b", "wavefront", "zero-bubble-h2"};
@@ -242,6 +290,7 @@ int main(int argc, char** argv) {
                   microbatches, tasks, reshards, first);
     }
   }
+  for (int a = 2; a < argc; ++a) CheckStoredProgram(argv[a]);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
     return 1;

@@ -2,7 +2,11 @@
 ThreadSanitizer (the reference has an ASAN build type for its host code, CMakeLists.txt:12-17).
 ``csrc/selftest/host_selftest.cc`` compiles pipelines with every schedule and executes the plans on
 worker threads whose task bodies touch unlocked buffers, so a missing dependency edge is a data
-race the thread sanitizer reports. No Python runs inside the instrumented process."""
+race the thread sanitizer reports; it then loads the stored real-model programs of ``tests/testdata``,
+compiles them offline, round-trips them through text and feeds the loader damaged copies. No Python
+runs inside the instrumented process."""
+import glob
+import os
 import subprocess
 from concurrent.futures import ThreadPoolExecutor
 
@@ -29,7 +33,11 @@ def test_host_selftest_is_clean_under(sanitizer, programs):
         pytest.skip(str(programs[sanitizer]))
     env = {"ASAN_OPTIONS": "detect_leaks=1:abort_on_error=0", "UBSAN_OPTIONS": "print_stacktrace=1:halt_on_error=1",
            "TSAN_OPTIONS": "halt_on_error=1", "PATH": "/usr/bin:/bin"}
-    proc = subprocess.run([str(programs[sanitizer]), "3"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+    stored = sorted(glob.glob(os.path.join(os.path.dirname(os.path.abspath(__file__)), "testdata", "*.mmprog.json")))
+    assert len(stored) >= 6
+    if sanitizer == "thread":
+        stored = stored[:2]          # the loader is single-threaded; two files keep the slow build's run short
+    proc = subprocess.run([str(programs[sanitizer]), "3", *stored], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                           timeout=600, env=env)
     out = proc.stdout
     assert proc.returncode == 0, out[-4000:]

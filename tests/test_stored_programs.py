@@ -71,7 +71,12 @@ def test_unknown_format_and_bad_ids_are_rejected(tmp_path):
     bad.write_text(json.dumps({"format": "something else"}))
     with pytest.raises(RuntimeError):
         mm.compile_program_file(str(bad))
-    prog = json.load(open(os.path.join(DATA, "llama_tp2_sequence_parallel.mmprog.json")))
+    text = open(os.path.join(DATA, "llama_tp2_sequence_parallel.mmprog.json")).read()
+    for cut in (len(text) // 7, len(text) // 2, len(text) - 2):      # text that ends early is refused
+        bad.write_text(text[:cut])
+        with pytest.raises(RuntimeError, match="json"):
+            mm.compile_program_file(str(bad))
+    prog = json.loads(text)
     prog["graph"]["nodes"][0]["inputs"] = [10 ** 6]
     bad.write_text(json.dumps(prog))
     with pytest.raises(RuntimeError):
