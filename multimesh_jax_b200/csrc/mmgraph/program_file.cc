@@ -189,23 +189,69 @@ Graph GraphFromJson(const Json& j) {
     n.dead = e.has("dead") && e.at("dead").as_bool();
     g.nodes.push_back(std::move(n));
   }
-  const int nv = static_cast<int>(g.values.size()), nn = static_cast<int>(g.nodes.size());
-  auto check_value = [&](int v) { if (v < 0 || v >= nv) throw std::runtime_error("stored program: value id out of range"); };
-  for (const Node& n : g.nodes) {
-    for (int v : n.inputs) check_value(v);
-    for (int v : n.outputs) check_value(v);
-  }
-  for (const Value& v : g.values)
-    if (v.producer >= nn) throw std::runtime_error("stored program: producer id out of range");
   g.order = ToInts(j.at("order"));
   g.inputs = ToInts(j.at("inputs"));
   g.outputs = ToInts(j.at("outputs"));
-  for (int v : g.inputs) check_value(v);
-  for (int v : g.outputs) check_value(v);
   g.donated_inputs = ToInts(j.at("donated_inputs"));
   for (const Json& l : j.at("loops").arr) g.loops.push_back(LoopConfig::FromJson(l));
+  ValidateStoredGraph(g);
   g.Toposort();
   return g;
+}
+
+// A file is input from outside: every id is checked against the tables it indexes and every
+// producer / result link against its mirror image before a pass follows it.
+void ValidateStoredGraph(const Graph& g) {
+  auto fail = [](const std::string& what) { throw std::runtime_error("stored program: " + what); };
+  const int nv = static_cast<int>(g.values.size()), nn = static_cast<int>(g.nodes.size());
+  auto check_value = [&](int v) { if (v < 0 || v >= nv) fail("value id out of range"); };
+  std::set<int> loop_ids;
+  for (const LoopConfig& l : g.loops) {
+    if (l.num_microbatches < 1 || l.num_microbatches > 65536) fail("number of microbatches out of range");
+    if (l.size < 0 || l.interleave < 1 || l.num_stages < 0 || l.slice_dim < 0 || l.batch_dim < 0)
+      fail("loop setting out of range");
+    if (!loop_ids.insert(l.id).second) fail("loop id used twice");
+  }
+  for (const Node& n : g.nodes) {
+    for (int v : n.inputs) check_value(v);
+    for (size_t i = 0; i < n.outputs.size(); ++i) {
+      check_value(n.outputs[i]);
+      const Value& v = g.values[n.outputs[i]];
+      if (v.producer != n.id || v.out_index != static_cast<int>(i)) fail("result does not name its producer");
+    }
+    if (n.loop != -1 && !loop_ids.count(n.loop)) fail("operator in an unknown loop");
+  }
+  for (const Value& v : g.values) {
+    if (v.producer < -1 || v.producer >= nn) fail("producer id out of range");
+    if (v.producer >= 0) {
+      const Node& n = g.nodes[v.producer];
+      if (v.out_index < 0 || v.out_index >= static_cast<int>(n.outputs.size()) || n.outputs[v.out_index] != v.id)
+        fail("value is not a result of its producer");
+    } else if (v.input_index < 0 || v.input_index >= static_cast<int>(g.inputs.size()) ||
+               g.inputs[v.input_index] != v.id) {
+      fail("value without a producer is not a graph input");
+    }
+    if (v.shape.size() > 8) fail("rank above 8");
+    int64_t elements = 1;
+    for (int64_t d : v.shape) {
+      if (d < 0 || d > (int64_t{1} << 40)) fail("dimension out of range");
+      if (d > 0 && elements > (int64_t{1} << 50) / d) fail("tensor too large");
+      elements *= std::max<int64_t>(d, 1);
+    }
+    if (v.has_axes && v.axes.size() != v.shape.size()) fail("axis annotation does not match the rank");
+  }
+  std::vector<char> seen(nn, 0);
+  for (int id : g.order) {
+    if (id < 0 || id >= nn) fail("operator id out of range");
+    if (seen[id]++) fail("operator listed twice");
+  }
+  for (int v : g.inputs) {
+    check_value(v);
+    if (g.values[v].producer != -1) fail("graph input has a producer");
+  }
+  for (int v : g.outputs) check_value(v);
+  for (int i : g.donated_inputs)
+    if (i < 0 || i >= static_cast<int>(g.inputs.size())) fail("donated input index out of range");
 }
 
 // ------------------------------------------------------------------------------ program
@@ -252,6 +298,9 @@ StoredProgram ProgramFromJson(const std::string& text) {
     throw std::runtime_error("stored program: unknown format");
   StoredProgram p;
   p.graph = std::make_shared<Graph>(GraphFromJson(j.at("graph")));
+  const int64_t dev_start = j.at("device_start").as_int(), dev_count = j.at("num_devices").as_int();
+  if (dev_start < 0 || dev_count < 1 || dev_start + dev_count > 65536)
+    throw std::runtime_error("stored program: device range out of bounds");
   p.partition = std::make_shared<Partition>(
       DeviceRange::Create(static_cast<int>(j.at("device_start").as_int()), static_cast<int>(j.at("num_devices").as_int())));
   p.config = ConfigFromJson(j.at("config"));

@@ -8,6 +8,9 @@ namespace mmg {
 
 Json GraphToJson(const Graph& g);
 Graph GraphFromJson(const Json& j);
+// Throws std::runtime_error when an id, a producer / result link, a loop reference or a shape of
+// a graph read from a file is inconsistent (GraphFromJson calls it before anything follows an id).
+void ValidateStoredGraph(const Graph& g);
 
 struct StoredProgram {
   std::shared_ptr<Graph> graph;

@@ -14,13 +14,15 @@
 //      pipeline, tensor, sequence, data and expert parallelism): loads it, compiles it offline,
 //      replays the plan on the mock runtime, writes the program back to text, reads that again
 //      and compares the plans; then feeds the loader truncated and corrupted copies of the text,
-//      which must be refused with an exception, never read out of bounds.
+//      which must be refused with an exception, never read out of bounds, and 40 randomly damaged
+//      copies of the first file, which must be refused or compile.
 //
 //   host_selftest [repeats] [stored-program.json ...]
 //
 // Exit code 0 = all checks passed. The reference gets the same assurance from its ASAN build type
 // (CMakeLists.txt:12-17) over the mock-runtime tests.
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <map>
@@ -240,9 +242,53 @@ static void CheckStoredProgram(const std::string& path) {
     } catch (const std::exception&) { threw = true; }
     CHECK(threw, "an operand id out of range was accepted");
   }
+  // an operator id that does not exist in the order list, and a result that names another producer
+  for (const char* key : {"\"order\":[", "\"outputs\":["}) {
+    std::string broken = text;
+    const size_t k = broken.find(key);
+    if (k == std::string::npos) continue;
+    broken.insert(k + std::string(key).size(), "7880,");
+    bool threw = false;
+    try { ProgramFromJson(broken); } catch (const std::exception&) { threw = true; }
+    CHECK(threw, "an inconsistent id list was accepted");
+  }
   std::printf("%-60s %d templates, %d tasks, %d reshards, high water %lld bytes\n",
               path.substr(path.find_last_of('/') + 1).c_str(), r.templates, r.tasks, r.reshards,
               static_cast<long long>(r.device_high_water_max));
+}
+
+// Random small damage to the text of a stored program (a digit replaced, a few characters cut,
+// a structural character overwritten): the loader and the compiler either refuse the result with
+// an exception or compile it; under the sanitizers anything else shows up as a report.
+static void MutateStoredProgram(const std::string& path, int rounds) {
+  StoredProgram original = LoadProgram(path);
+  const std::string text = ProgramToJson(*original.graph, *original.partition, original.config);
+  uint64_t state = 0x9E3779B97F4A7C15ull;
+  auto next = [&](uint64_t bound) {
+    state = state * 6364136223846793005ull + 1442695040888963407ull;
+    return static_cast<size_t>((state >> 33) % bound);
+  };
+  int refused = 0, compiled = 0;
+  for (int r = 0; r < rounds; ++r) {
+    std::string t = text;
+    const int edits = 1 + static_cast<int>(next(3));
+    for (int e = 0; e < edits; ++e) {
+      const size_t i = next(t.size());
+      if (t[i] >= '0' && t[i] <= '9') t[i] = static_cast<char>('0' + next(10));
+      else if (next(2)) t.erase(i, 1 + next(6));
+      else t[i] = "{}[]\",:0a-"[next(11)];
+    }
+    try {
+      StoredProgram p = ProgramFromJson(t);
+      Plan plan = MpmdPartition(*p.graph, *p.partition, p.config);
+      MockExecutePlan(plan, p.partition->global().start, p.partition->global().n, 0, 1);
+      ++compiled;
+    } catch (const std::exception&) {
+      ++refused;
+    }
+  }
+  std::printf("%d damaged copies of %s: %d refused, %d still compiled\n", rounds,
+              path.substr(path.find_last_of('/') + 1).c_str(), refused, compiled);
 }
 
 int main(int argc, char** argv) {
@@ -291,6 +337,7 @@ int main(int argc, char** argv) {
     }
   }
   for (int a = 2; a < argc; ++a) CheckStoredProgram(argv[a]);
+  if (argc > 2) MutateStoredProgram(argv[2], 40);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
     return 1;
