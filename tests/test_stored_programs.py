@@ -81,3 +81,22 @@ def test_unknown_format_and_bad_ids_are_rejected(tmp_path):
     bad.write_text(json.dumps(prog))
     with pytest.raises(RuntimeError):
         mm.compile_program_file(str(bad))
+    # every table that holds ids is checked before a pass follows one
+    for damage, message in (
+            (lambda g: g["order"].__setitem__(3, 7880), "operator id out of range"),
+            (lambda g: g["order"].__setitem__(3, g["order"][2]), "operator listed twice"),
+            (lambda g: g["values"][g["nodes"][5]["outputs"][0]].__setitem__("producer", 4), "does not name its producer"),
+            (lambda g: g["nodes"][5].__setitem__("loop", 9), "unknown loop"),
+            (lambda g: g["donated_inputs"].append(10 ** 6), "donated input"),
+            (lambda g: g["values"][0].__setitem__("shape", [-4, 64]), "dimension out of range"),
+            (lambda g: g["loops"][0].__setitem__("num_microbatches", 0), "microbatches")):
+        prog = json.loads(text)
+        damage(prog["graph"])
+        bad.write_text(json.dumps(prog))
+        with pytest.raises(RuntimeError, match=message):
+            mm.compile_program_file(str(bad))
+    prog = json.loads(text)
+    prog["num_devices"] = 0
+    bad.write_text(json.dumps(prog))
+    with pytest.raises(RuntimeError, match="device range"):
+        mm.compile_program_file(str(bad))
