@@ -176,7 +176,9 @@ def build_selftest(sanitizer: str = "address", force: bool = False) -> Path:
     # outside the source tree: the instrumented objects are large and of no use to anyone else
     out_dir = Path(tempfile.gettempdir()) / f"mm_selftest_{os.getuid()}" / sanitizer
     out_dir.mkdir(parents=True, exist_ok=True)
-    srcs = [HERE / "selftest" / "host_selftest.cc"] + sorted((HERE / "mmgraph").glob("*.cc")) + [HERE / "mmrt" / "runtime.cc"]
+    srcs = ([HERE / "selftest" / "host_selftest.cc"] + sorted((HERE / "mmgraph").glob("*.cc"))
+            + [HERE / "mmrt" / "runtime.cc", HERE / "mmrt" / "cuda_context.cc"])
+    cuda = _cuda_home()
     hdrs = sorted((HERE / "mmgraph").glob("*.h")) + sorted((HERE / "mmrt").glob("*.h"))
     target = out_dir / "host_selftest"
     if not force and not _newer(srcs + hdrs, target):
@@ -186,12 +188,16 @@ def build_selftest(sanitizer: str = "address", force: bool = False) -> Path:
     def compile_one(src: Path) -> Path:
         obj = out_dir / (src.stem + ".o")
         if force or _newer([src] + hdrs, obj):
-            _run([cxx, "-std=c++17", "-O0", "-g1", "-pthread", *flags, "-c", str(src), "-o", str(obj)])
+            _run([cxx, "-std=c++17", "-O0", "-g1", "-pthread", *flags, "-I", str(cuda / "include"), "-c", str(src),
+                  "-o", str(obj)])
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    _run([cxx, "-pthread", *flags, "-o", str(target), *map(str, objs)])
+    # the stream context is driven through its recording stand-in here; the CUDA runtime is linked
+    # only because the same source also holds the real adaptor
+    _run([cxx, "-pthread", *flags, "-o", str(target), *map(str, objs), "-L", str(cuda / "lib64"), "-lcudart", "-ldl",
+          "-Wl,-rpath," + str(cuda / "lib64")])
     return target
 
 

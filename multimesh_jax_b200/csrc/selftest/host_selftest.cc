@@ -32,6 +32,7 @@
 #include "../mmgraph/graph.h"
 #include "../mmgraph/passes.h"
 #include "../mmgraph/program_file.h"
+#include "../mmrt/cuda_context.h"
 #include "../mmrt/runtime.h"
 
 using namespace mmg;
@@ -106,11 +107,9 @@ struct RunResult {
   mmrt::Status status = mmrt::Status::kOk;
 };
 
-// Executes the plan's operation list with synthetic bodies over unlocked host buffers.
-static RunResult Execute(const Plan& plan, int num_devices, bool inject_throw) {
-  std::vector<int> devices(num_devices);
-  for (int d = 0; d < num_devices; ++d) devices[d] = d;
-  mmrt::ThreadedContext ctx(devices, /*inline_execution=*/false, /*record_submissions=*/true);
+// Executes the plan's operation list on `ctx` with synthetic bodies over unlocked host buffers.
+template <class Context>
+static RunResult ExecuteOn(Context& ctx, const Plan& plan, bool inject_throw) {
   std::map<std::string, int> buffer_of_name;
   auto buffer_id = [&](const Store& st) {
     const std::string key = std::to_string(static_cast<int>(st.kind)) + ":" + st.name;
@@ -204,6 +203,31 @@ static RunResult Execute(const Plan& plan, int num_devices, bool inject_throw) {
     CHECK(ctx.WaitAll(&m2) == mmrt::Status::kOk && probe == 42.0, "context unusable after an injected fault");
   }
   ctx.Shutdown();
+  return res;
+}
+
+static RunResult Execute(const Plan& plan, int num_devices, bool inject_throw) {
+  std::vector<int> devices(num_devices);
+  for (int d = 0; d < num_devices; ++d) devices[d] = d;
+  mmrt::ThreadedContext ctx(devices, /*inline_execution=*/false, /*record_submissions=*/true);
+  return ExecuteOn(ctx, plan, inject_throw);
+}
+
+// The same plan on the stream-and-event context over the recording stand-in for the CUDA runtime:
+// bodies run at submission, reshards are given the communication stream, and every conflicting
+// pair of accesses on different streams must have become an event wait.
+static RunResult ExecuteOnStreams(const Plan& plan, int num_devices, bool inject_throw, size_t* edges, size_t* waits) {
+  std::vector<int> devices(num_devices);
+  for (int d = 0; d < num_devices; ++d) devices[d] = d;
+  mmrt::FakeGpuApi api;
+  RunResult res;
+  {
+    mmrt::CudaContext ctx(devices, devices, std::vector<uintptr_t>(num_devices, 0), &api, /*record_submissions=*/true);
+    res = ExecuteOn(ctx, plan, inject_throw);
+    *edges = ctx.Edges().size();
+  }
+  *waits = 0;
+  for (const std::string& line : api.trace) *waits += line.rfind("wait ", 0) == 0;
   return res;
 }
 
@@ -332,6 +356,14 @@ int main(int argc, char** argv) {
       }
       RunResult failed = Execute(plan, stages, true);
       CHECK(failed.status != mmrt::Status::kOk, "an injected fault did not surface as a status");
+      size_t edges = 0, waits = 0;
+      RunResult streams = ExecuteOnStreams(plan, stages, false, &edges, &waits);
+      CHECK(streams.status == mmrt::Status::kOk, "stream context reported an error");
+      CHECK(streams.hazards.empty(), streams.hazards.c_str());
+      CHECK(std::fabs(streams.checksum - first) < 1e-12, "stream context computed another result");
+      CHECK(edges > 0 && waits >= edges, "cross-stream conflicts did not become event waits");
+      RunResult streams_failed = ExecuteOnStreams(plan, stages, true, &edges, &waits);
+      CHECK(streams_failed.status != mmrt::Status::kOk, "stream context: an injected fault did not surface");
       std::printf("%-15s stages=%d microbatches=%d: %d tasks, %d reshards, checksum %.9f\n", schedule, stages,
                   microbatches, tasks, reshards, first);
     }
