@@ -7,7 +7,9 @@
 //      and reshard bodies read and write plain host buffers (one per physical buffer and device,
 //      shared by every store with the same scheduling name) WITHOUT locks, so a missing
 //      dependency edge is a data race the thread sanitizer reports and a wrong checksum here;
-//   3. replays the submission log through the hazard checker;
+//   3. replays the submission log through the hazard checker; runs the same plan on the
+//      stream-and-event context (CudaContext over the recording stand-in for the CUDA runtime) and
+//      checks that it computes the same result and that its cross-stream conflicts became waits;
 //   4. injects host-side faults (a task body that throws, a dropped task) and checks that the
 //      error surfaces as a status and that the context stays usable;
 //   5. for every stored-program file named on the command line (real-model training steps with
