@@ -227,3 +227,38 @@ def test_zero_bubble_interleaved_keeps_dependencies_and_defers_weight_gradients(
             if s > 0:
                 assert pos[(it, idx[f"fwd{s}"])] > pos[(it, idx[f"fwd{s - 1}"])]
                 assert pos[(it, idx[f"bwd{s - 1}"])] > pos[(it, idx[f"bwd{s}"])]
+
+
+def test_random_pipelines_are_scheduled_validly_or_refused():
+    """400 seeded random cases over every schedule name, split backward halves, a full-mesh
+    prefetch task, interleaving, unrolling and random custom schedules: the scheduler either
+    refuses the request with an error or returns an order that keeps every dependency."""
+    import random
+    rng = random.Random(1234)
+    valid = refused = 0
+    for _ in range(400):
+        stages, n = rng.randint(1, 6), rng.randint(1, 12)
+        schedule = rng.choice(["gpipe", "1f1b", "wavefront", "zero-bubble-h2", "prefetch-wavefront", "custom"])
+        split = schedule == "zero-bubble-h2" or rng.random() < 0.2
+        rows, names = pipeline(stages, n, split_bwd=split, embeddings=rng.random() < 0.3,
+                               devices_per_stage=rng.randint(1, 2))
+        extra = {}
+        if rng.random() < 0.3:
+            extra["interleave"] = rng.randint(1, 3)
+        if rng.random() < 0.2:
+            extra["unrolling"] = rng.randint(0, 3)
+        if schedule == "custom":
+            extra["custom_schedule"] = []
+            for s in range(stages):
+                entries = [(it, rng.choice([f"fwd{s}", f"bwd{s}", f"wgrad{s}", "fwd", "x"])) for it in range(n) for _ in range(2)]
+                rng.shuffle(entries)
+                extra["custom_schedule"].append(entries[:rng.randint(0, len(entries))])
+        try:
+            out = run(schedule, rows, n, **extra)
+        except (RuntimeError, ValueError):
+            refused += 1
+            continue
+        if len(out["orders"]) == 1:
+            check_valid([tuple(e) for e in out["orders"][0]], names, n, stages)
+        valid += 1
+    assert valid > 250 and refused > 10, (valid, refused)
