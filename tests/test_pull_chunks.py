@@ -36,6 +36,39 @@ EXTRA = [
 
 @pytest.mark.parametrize("src,dst", list(CASES) + EXTRA)
 def test_records_move_every_element_to_its_place(src, dst):
+    _check_case(src, dst)
+
+
+def _random_layout(rng, sizes, start):
+    """A random valid layout of `sizes`: a mesh of one to three axes of extent 1-4, each axis either
+    unused (replication) or tiling a dimension it divides; several axes may tile one dimension."""
+    mesh = [rng.choice([1, 2, 2, 3, 4]) for _ in range(rng.randint(1, 3))]
+    dim_axes = [[] for _ in sizes]
+    left = list(sizes)
+    for axis, extent in enumerate(mesh):
+        fits = [d for d in range(len(sizes)) if left[d] % extent == 0 and left[d] >= extent]
+        if not fits or rng.random() < 0.25:
+            continue
+        d = rng.choice(fits)
+        dim_axes[d].append(axis)
+        left[d] //= extent
+    return shape("bfloat16", list(sizes), dim_axes, mesh, start)
+
+
+def test_random_layout_pairs_move_every_element_to_its_place():
+    import random
+    rng = random.Random(99)
+    done = 0
+    for _ in range(120):
+        sizes = [rng.choice([2, 4, 6, 8, 12]) for _ in range(rng.randint(1, 4))]
+        src = _random_layout(rng, sizes, rng.randint(0, 3))
+        dst = _random_layout(rng, sizes, rng.randint(0, 9))
+        _check_case(src, dst)
+        done += 1
+    assert done == 120
+
+
+def _check_case(src, dst):
     sizes = src["sizes"]
     total = int(np.prod(sizes)) if sizes else 1
     glob = np.arange(1, total + 1, dtype=np.uint16).reshape(sizes)
