@@ -250,9 +250,16 @@ Rule GetRule(const Graph& g, const Node& n) {
   }
   if (n.op == "mm.dynamic_slice" || n.op == "mm.copy" || n.op == "mm.accumulate") {
     // same rank, dimension by dimension; a sliced dimension keeps its sharding (every
-    // shard contributes its own rows to each microbatch)
+    // shard contributes its own rows to each microbatch) unless the slices of the loop would
+    // be cut differently (`exact_rows`, see MarkExactMicrobatchSlices): then the sliced
+    // dimension stays whole and microbatch i is rows [i * size, (i + 1) * size) exactly
     const int rank = in_rank(0);
-    for (int d = 0; d < rank; ++d) r.classes.push_back(Cls({{0, d}, {nin, d}}));
+    const int exact = n.op == "mm.dynamic_slice" && n.Attr("exact_rows") == "1" ? std::atoi(n.Attr("dim", "0").c_str()) : -1;
+    for (int d = 0; d < rank; ++d) {
+      IndexClass c = Cls({{0, d}, {nin, d}});
+      c.no_shard = d == exact;
+      r.classes.push_back(c);
+    }
     return r;
   }
   r.known = false;
@@ -596,10 +603,59 @@ bool ShardingPropagation(CompileState& s, PropagationMode mode) {
 // ---------------------------------------------------------------------------
 // SPMD lowering
 // ---------------------------------------------------------------------------
+namespace {
+
+// Number of ways the sliced dimension of every microbatch slice is cut, per loop.
+std::map<int, std::vector<std::pair<int, int>>> MicrobatchSliceCuts(CompileState& s, bool skip_exact) {
+  Graph& g = *s.graph;
+  std::map<int, std::vector<std::pair<int, int>>> cuts;   // loop -> (node, parts)
+  for (auto& grp : s.groups) {
+    const TaskMeshInfo mesh = MeshOf(*s.partition, grp.color);
+    for (int id : grp.nodes) {
+      const Node& n = g.node(id);
+      if (n.dead || n.op != "mm.dynamic_slice" || n.loop < 0 || n.inputs.empty()) continue;
+      if (skip_exact && n.Attr("exact_rows") == "1") continue;
+      int parts = 1;
+      if (mesh.devices.n > 1) {
+        const Value& out = g.value(n.outputs[0]);
+        const ShardedShape* sh = out.has_sharding ? &out.sharding : Available(s, grp, n.inputs[0]);
+        const int dim = std::atoi(n.Attr("dim", "0").c_str());
+        if (sh && dim >= 0 && dim < sh->rank()) parts = AxesProduct(sh->dim_axes[dim], mesh.dims);
+      }
+      cuts[n.loop].emplace_back(id, parts);
+    }
+  }
+  return cuts;
+}
+
+// A microbatch slice along a sharded dimension is taken shard by shard: with the batch cut p
+// ways, microbatch i is made of every shard's own rows [i * size / p, (i + 1) * size / p), not of
+// the global rows [i * size, (i + 1) * size). That regrouping of rows is harmless - results of the
+// loop are sums over all microbatches - as long as every sliced value of the loop is regrouped the
+// same way. Where the slices of one loop would be cut differently (the samples split over two
+// devices, the labels replicated; stages with different data-parallel widths), all of them are
+// marked `exact_rows`: the sliced dimension stays whole, each device slices the global rows and a
+// consumer that wants them split takes its part afterwards.
+bool MarkExactMicrobatchSlices(CompileState& s) {
+  bool marked = false;
+  for (auto& kv : MicrobatchSliceCuts(s, false)) {
+    bool same = true;
+    for (auto& e : kv.second) same = same && e.second == kv.second.front().second;
+    if (same) continue;
+    for (auto& e : kv.second) s.graph->node(e.first).attrs["exact_rows"] = "1";
+    s.Note("microbatch slices of loop " + std::to_string(kv.first) + " are cut differently: exact rows for all " +
+           std::to_string(kv.second.size()) + " of them");
+    marked = true;
+  }
+  return marked;
+}
+
+}  // namespace
+
 bool SpmdLowering(CompileState& s) {
   Graph& g = *s.graph;
   Partition& part = *s.partition;
-  bool changed = false;
+  bool changed = MarkExactMicrobatchSlices(s);
   for (auto& grp : s.groups) {
     const TaskMeshInfo mesh = MeshOf(part, grp.color);
     if (mesh.devices.n == 1) continue;
@@ -768,6 +824,13 @@ bool SpmdLowering(CompileState& s) {
     }
     g.order = order;
   }
+  // the layouts are final now: slices that regroup rows must all regroup them alike
+  for (auto& kv : MicrobatchSliceCuts(s, true))
+    for (auto& e : kv.second)
+      if (e.second != kv.second.front().second)
+        throw std::runtime_error("spmd_lowering: microbatch slices of loop " + std::to_string(kv.first) + " are cut " +
+                                 std::to_string(kv.second.front().second) + " and " + std::to_string(e.second) +
+                                 " ways; their rows would be paired wrongly");
   return changed;
 }
 

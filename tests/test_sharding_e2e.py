@@ -165,3 +165,40 @@ def test_layout_change_made_of_local_pieces_needs_no_exchange(monkeypatch):
             torch.testing.assert_close(out, full[lo[0]:hi[0], lo[1]:hi[1]])
     assert not exchanged
     assert col._local_only_chunks(rows, rep) is None                  # the gather direction is not local
+
+
+def test_microbatch_slices_of_one_loop_pair_the_same_rows():
+    """Samples split over the data axis, labels left replicated: sliced shard by shard, microbatch 0
+    would hold sample rows {0, 2} but label rows {0, 1}. The compiler then slices exact rows for
+    every value of the loop (found by a randomised differential run; 11 % loss error before)."""
+    mm.init(cpus=2)
+
+    def fwd(params, batch):
+        xb, yb = batch
+        with mm.named_scope("net"):
+            h = mm.with_sharding_constraint(xb, ("batch", None))
+            h = h * params[0]
+            h = mm.with_sharding_constraint(h, (None, None))          # gathered again: the labels stay whole
+            h = h * params[1]
+            return ((h - yb) ** 2).sum()
+
+    def step(params, batch):
+        return mm.microbatch(mm.value_and_grad(fwd), size=2, argnum=1, schedule="gpipe")(params, batch)
+
+    g = torch.Generator().manual_seed(0)
+    params = [torch.randn(12, generator=g) for _ in range(2)]
+    batch = (torch.randn(4, 12, generator=g), torch.randn(4, 12, generator=g))
+    mesh = mm.MultiMesh((1, 2), ("stage", "data"))
+    with mesh:
+        mesh.register_task("net", task=mm.Task(mesh_slice={"stage": 0}, logical_axes=[("batch", "data")]))
+        exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="cpu")
+    loss, grads = exe(params, batch)
+    with mm.ignore_transforms():
+        ref_loss, ref_grads = step(params, batch)
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-4)
+    for a, b in zip(grads, ref_grads):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-4, atol=1e-4)
+    slices = [n for _, n in _node_dicts(exe, "mm.dynamic_slice")]
+    assert len(slices) == 2 and all(n["attrs"].get("exact_rows") == "1" for n in slices)
+    assert any("cut differently" in line for line in exe.plan["log"])
+    exe.shutdown()
