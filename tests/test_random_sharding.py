@@ -1,0 +1,150 @@
+"""Randomised differential test of sharding propagation, SPMD lowering, reshard insertion and the
+pipeline runtime: seeded random networks (MLP and attention blocks, norms, softmax, reductions over
+the sequence, biases) with random layout constraints on activations and weights, random logical ->
+mesh axis tables (optionally a different priority order on odd stages), random three-axis meshes
+and random microbatching, compiled for virtual CPU devices and compared with the eager step. The
+method of the reference's Python end-to-end tests (tests/python/jax_task_test.py: same function with and
+without the transformations), with the cases drawn instead of written. Longer runs of the same
+generator found the microbatch-slice pairing error that ``test_sharding_e2e.py`` pins."""
+import random
+
+import pytest
+import torch
+from torch.utils import _pytree as pytree
+
+import multimesh_jax_b200 as mm
+
+OPS = ["mlp", "mlp", "tanh", "resid", "scale", "norm", "attn", "softmax", "meanseq", "gelu", "bias"]
+MESHES = [(1, 2, 2), (2, 2, 1), (1, 4, 1), (2, 1, 2), (1, 2, 1), (2, 2, 2), (1, 1, 2)]
+AXES = [("batch", "x"), ("hid", "y"), ("feat", "y"), ("seq", "y"), ("batch", "y"), ("hid", "x"), ("heads", "y"),
+        ("heads", "x")]
+
+
+def _draw(rng):
+    mesh_shape = rng.choice(MESHES)
+    B, S, D, F, H = rng.choice([4, 8]), rng.choice([2, 4]), rng.choice([8, 16]), rng.choice([8, 16]), rng.choice([2, 4])
+    blocks = []
+    for b in range(mesh_shape[0] * rng.randint(1, 2)):
+        ops = [rng.choice(OPS) for _ in range(rng.randint(1, 4))]
+        if b == 0 and not any(o in ("mlp", "scale", "attn", "bias") for o in ops):
+            ops.append("mlp")
+        constraints = [(rng.randint(0, len(ops)), (rng.choice([None, "batch"]), rng.choice([None, None, "seq"]),
+                                                   rng.choice([None, None, "feat"]))) for _ in range(rng.randint(0, 2))]
+        blocks.append((ops, constraints, rng.random() < 0.5))
+    axes = list(AXES)
+    rng.shuffle(axes)
+    return dict(mesh_shape=mesh_shape, B=B, S=S, D=D, F=F, H=H, blocks=blocks, logical=axes[:rng.randint(1, 4)],
+                microbatch=rng.choice([None, B // 2, B // 4 if B >= 8 else B // 2]),
+                schedule=rng.choice(["gpipe", "1f1b"]), other_order_on_odd_stages=rng.random() < 0.2)
+
+
+def _build(case):
+    B, S, D, F, H = (case[k] for k in "BSDFH")
+    g = torch.Generator().manual_seed(0)
+    params = []
+    for ops, _, _ in case["blocks"]:
+        blk = []
+        for op in ops:
+            if op == "mlp":
+                blk.append((torch.randn(D, F, generator=g) / D ** 0.5, torch.randn(F, D, generator=g) / F ** 0.5))
+            elif op == "attn":
+                blk.append((torch.randn(D, 3 * D, generator=g) / D ** 0.5, torch.randn(D, D, generator=g) / D ** 0.5))
+            elif op in ("scale", "bias"):
+                blk.append((torch.randn(D, generator=g),))
+            else:
+                blk.append(())
+        params.append(blk)
+    batch = (torch.randn(B, S, D, generator=g), torch.randn(B, S, D, generator=g))
+
+    def loss_fn(params, batch):
+        h, target = batch
+        for bi, ((ops, constraints, shard_weights), blk) in enumerate(zip(case["blocks"], params)):
+            with mm.named_scope(f"blk.{bi}"):
+                for oi, (op, p) in enumerate(zip(ops, blk)):
+                    for at, spec in constraints:
+                        if at == oi:
+                            h = mm.with_sharding_constraint(h, spec)
+                    if op == "mlp":
+                        w1, w2 = p
+                        if shard_weights:
+                            w1 = mm.with_sharding_constraint(w1, (None, "hid"))
+                            w2 = mm.with_sharding_constraint(w2, ("hid", None))
+                        h = h + torch.tanh(h @ w1) @ w2
+                    elif op == "attn":
+                        wqkv, wo = p
+                        if shard_weights:
+                            wqkv = mm.with_sharding_constraint(wqkv, (None, "heads"))
+                            wo = mm.with_sharding_constraint(wo, ("heads", None))
+                        b_, s_, _ = h.shape
+                        qkv = (h @ wqkv).view(b_, s_, 3, H, D // H)
+                        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+                        att = torch.softmax((q @ k.transpose(-1, -2)) / (D // H) ** 0.5, dim=-1)
+                        h = h + (att @ v).transpose(1, 2).reshape(b_, s_, D) @ wo
+                    elif op == "tanh":
+                        h = torch.tanh(h)
+                    elif op == "gelu":
+                        h = torch.nn.functional.gelu(h)
+                    elif op == "resid":
+                        h = h + h * 0.5
+                    elif op == "scale":
+                        h = h * p[0]
+                    elif op == "bias":
+                        h = h + p[0]
+                    elif op == "norm":
+                        h = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-5)
+                    elif op == "softmax":
+                        h = torch.softmax(h, dim=-1) * h.shape[-1] ** 0.5
+                    elif op == "meanseq":
+                        h = h - h.mean(1, keepdim=True)
+        with mm.named_scope("lossfn"):
+            return ((h - target) ** 2).sum()
+
+    def step(params, batch):
+        vg = mm.value_and_grad(loss_fn)
+        if case["microbatch"]:
+            vg = mm.microbatch(vg, size=case["microbatch"], argnum=1, schedule=case["schedule"])
+        return vg(params, batch)
+    return step, params, batch
+
+
+def _mesh(case):
+    stages = case["mesh_shape"][0]
+    per_stage = len(case["blocks"]) // stages
+
+    def axes_of(stage):
+        if case["other_order_on_odd_stages"] and stage % 2:
+            return list(reversed(case["logical"]))
+        return case["logical"]
+
+    def block_task(matched, backprop):
+        stage = int(matched.split(".")[1]) // per_stage
+        return mm.Task(name=f"s{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage},
+                       logical_axes=axes_of(stage))
+
+    mesh = mm.MultiMesh(case["mesh_shape"], ("stage", "x", "y"))
+    mesh.register_task(r"(blk\.\d+)", factory=block_task)
+    mesh.register_task("(lossfn)", factory=lambda m, b: mm.Task(name=f"s{stages - 1}" + ("_bwd" if b else ""),
+                                                                 mesh_slice={"stage": stages - 1},
+                                                                 logical_axes=axes_of(stages - 1)))
+    return mesh
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_network_and_layouts_match_the_eager_step(seed):
+    mm.init(cpus=8)
+    case = _draw(random.Random(1000 + seed))
+    step, params, batch = _build(case)
+    with mm.ignore_transforms():
+        ref_loss, ref_grads = step(params, batch)
+    mesh = _mesh(case)
+    with mesh:
+        exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="cpu")
+    try:
+        loss, grads = exe(params, batch)
+        scale = float(ref_loss.abs())
+        assert abs(float(loss.full_tensor()) - float(ref_loss)) <= 1e-4 * scale + 1e-5, case
+        for got, want in zip(pytree.tree_leaves(grads), pytree.tree_leaves(ref_grads)):
+            err = float((got.full_tensor() - want).abs().max())
+            assert err <= 2e-3 * (float(want.abs().max()) + 1e-3 * scale), (err, case)
+    finally:
+        exe.shutdown()
