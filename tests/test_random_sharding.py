@@ -1,11 +1,14 @@
 """Randomised differential test of sharding propagation, SPMD lowering, reshard insertion and the
 pipeline runtime: seeded random networks (MLP and attention blocks, norms, softmax, reductions over
 the sequence, biases) with random layout constraints on activations and weights, random logical ->
-mesh axis tables (optionally a different priority order on odd stages), random three-axis meshes
+mesh axis tables (optionally a different priority order on odd stages), random three-axis meshes of
+one to four stages, every pipeline schedule (zero-bubble with split backward tasks), interleaved
+block placement, a first block that moves between stages per microbatch, recomputation on or off
 and random microbatching, compiled for virtual CPU devices and compared with the eager step. The
 method of the reference's Python end-to-end tests (tests/python/jax_task_test.py: same function with and
 without the transformations), with the cases drawn instead of written. Longer runs of the same
 generator found the microbatch-slice pairing error that ``test_sharding_e2e.py`` pins."""
+import contextlib
 import random
 
 import pytest
@@ -15,7 +18,8 @@ from torch.utils import _pytree as pytree
 import multimesh_jax_b200 as mm
 
 OPS = ["mlp", "mlp", "tanh", "resid", "scale", "norm", "attn", "softmax", "meanseq", "gelu", "bias"]
-MESHES = [(1, 2, 2), (2, 2, 1), (1, 4, 1), (2, 1, 2), (1, 2, 1), (2, 2, 2), (1, 1, 2)]
+MESHES = [(1, 2, 2), (2, 2, 1), (1, 4, 1), (2, 1, 2), (1, 2, 1), (2, 2, 2), (1, 1, 2), (4, 2, 1), (4, 1, 1), (3, 1, 2),
+          (2, 1, 1)]
 AXES = [("batch", "x"), ("hid", "y"), ("feat", "y"), ("seq", "y"), ("batch", "y"), ("hid", "x"), ("heads", "y"),
         ("heads", "x")]
 
@@ -24,7 +28,7 @@ def _draw(rng):
     mesh_shape = rng.choice(MESHES)
     B, S, D, F, H = rng.choice([4, 8]), rng.choice([2, 4]), rng.choice([8, 16]), rng.choice([8, 16]), rng.choice([2, 4])
     blocks = []
-    for b in range(mesh_shape[0] * rng.randint(1, 2)):
+    for b in range(mesh_shape[0] * rng.randint(1, 3)):
         ops = [rng.choice(OPS) for _ in range(rng.randint(1, 4))]
         if b == 0 and not any(o in ("mlp", "scale", "attn", "bias") for o in ops):
             ops.append("mlp")
@@ -35,7 +39,9 @@ def _draw(rng):
     rng.shuffle(axes)
     return dict(mesh_shape=mesh_shape, B=B, S=S, D=D, F=F, H=H, blocks=blocks, logical=axes[:rng.randint(1, 4)],
                 microbatch=rng.choice([None, B // 2, B // 4 if B >= 8 else B // 2]),
-                schedule=rng.choice(["gpipe", "1f1b"]), other_order_on_odd_stages=rng.random() < 0.2)
+                schedule=rng.choice(["gpipe", "1f1b", "zero-bubble-h2", "wavefront"]),
+                other_order_on_odd_stages=rng.random() < 0.2, interleaved=rng.random() < 0.3,
+                recompute=rng.choice([None, True, False]), moving_first_block=rng.random() < 0.15)
 
 
 def _build(case):
@@ -109,27 +115,40 @@ def _build(case):
 
 def _mesh(case):
     stages = case["mesh_shape"][0]
-    per_stage = len(case["blocks"]) // stages
+    blocks = len(case["blocks"])
+    per_stage = blocks // stages
+    split = ("_act", "_wgt") if case["schedule"] == "zero-bubble-h2" else None
 
     def axes_of(stage):
         if case["other_order_on_odd_stages"] and stage % 2:
             return list(reversed(case["logical"]))
         return case["logical"]
 
-    def block_task(matched, backprop):
-        stage = int(matched.split(".")[1]) // per_stage
-        return mm.Task(name=f"s{stage}" + ("_bwd" if backprop else ""), mesh_slice={"stage": stage},
-                       logical_axes=axes_of(stage))
+    def stage_of(block):       # interleaved: every microbatch visits each stage several times
+        return block % stages if case["interleaved"] else block // per_stage
 
+    def name_of(block, backprop):
+        return (f"v{block}" if case["interleaved"] else f"s{stage_of(block)}") + ("_bwd" if backprop else "")
+
+    def block_task(matched, backprop):
+        block = int(matched.split(".")[1])
+        if case["moving_first_block"] and block == 0 and not backprop and stages > 1 and not case["interleaved"]:
+            # the first block's forward task runs on another stage's devices every microbatch
+            return mm.Task(name="moving", mesh_slice={"stage": 0}, logical_axes=case["logical"],
+                           loop_dependent_mesh_slice=lambda i: {"stage": i % stages})
+        stage = stage_of(block)
+        return mm.Task(name=name_of(block, backprop), mesh_slice={"stage": stage}, logical_axes=axes_of(stage),
+                       split_backprop=split)
+
+    last = stage_of(blocks - 1)
     mesh = mm.MultiMesh(case["mesh_shape"], ("stage", "x", "y"))
     mesh.register_task(r"(blk\.\d+)", factory=block_task)
-    mesh.register_task("(lossfn)", factory=lambda m, b: mm.Task(name=f"s{stages - 1}" + ("_bwd" if b else ""),
-                                                                 mesh_slice={"stage": stages - 1},
-                                                                 logical_axes=axes_of(stages - 1)))
+    mesh.register_task("(lossfn)", factory=lambda m, b: mm.Task(name=name_of(blocks - 1, b), mesh_slice={"stage": last},
+                                                                 logical_axes=axes_of(last), split_backprop=split))
     return mesh
 
 
-@pytest.mark.parametrize("seed", range(16))
+@pytest.mark.parametrize("seed", range(24))
 def test_random_network_and_layouts_match_the_eager_step(seed):
     mm.init(cpus=8)
     case = _draw(random.Random(1000 + seed))
@@ -137,7 +156,8 @@ def test_random_network_and_layouts_match_the_eager_step(seed):
     with mm.ignore_transforms():
         ref_loss, ref_grads = step(params, batch)
     mesh = _mesh(case)
-    with mesh:
+    recompute = mm.enable_recomputation(case["recompute"]) if case["recompute"] is not None else contextlib.nullcontext()
+    with mesh, recompute:
         exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="cpu")
     try:
         loss, grads = exe(params, batch)
