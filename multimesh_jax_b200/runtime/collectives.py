@@ -329,8 +329,12 @@ class DeviceCtx:
         local = _local_only_chunks(src, dst)
         if local is None:
             raise RuntimeError("reduce-scatter target is not a refinement of the source layout")
+        # by position in the task's sub-mesh: the layouts name the devices the template was compiled for
+        mine = local.get(src["device_start"] + self.device - self.device_start)
+        if mine is None:
+            raise RuntimeError(f"reduce-scatter: device {self.device} has no part in {src['key']} -> {dst['key']}")
         out = torch.empty(dst["shard_size"], dtype=full.dtype, device=full.device)
-        for c in local.get(self.device, ()):
+        for c in mine:
             ext = [h - l for l, h in zip(c["lo"], c["hi"])]
             s_box = tuple(slice(o, o + e) for o, e in zip(c["src_offset"], ext))
             d_box = tuple(slice(o, o + e) for o, e in zip(c["dst_offset"], ext))
@@ -429,8 +433,14 @@ class DeviceCtx:
             # every destination tile is made of pieces of the same device's source tile (replicated
             # -> sharded, or a coarser -> finer split): a slice, no exchange. All members take this
             # branch together because the plan depends on the two layouts only.
+            # The layouts name the devices the task's template was compiled for; a task that moves
+            # between sub-meshes per microbatch runs the same template elsewhere, so the chunks are
+            # looked up by this device's position in the task's sub-mesh.
+            mine = local.get(src["device_start"] + me)
+            if mine is None:
+                raise RuntimeError(f"spmd_reshard: device {self.device} (position {me}) has no part in {src['key']} -> {dst['key']}")
             out = torch.empty(dst["shard_size"], dtype=x.dtype, device=x.device)
-            for c in local.get(self.device, ()):
+            for c in mine:
                 ext = [h - l for l, h in zip(c["lo"], c["hi"])]
                 s_box = tuple(slice(o, o + e) for o, e in zip(c["src_offset"], ext))
                 d_box = tuple(slice(o, o + e) for o, e in zip(c["dst_offset"], ext))

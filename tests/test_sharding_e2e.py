@@ -202,3 +202,51 @@ def test_microbatch_slices_of_one_loop_pair_the_same_rows():
     assert len(slices) == 2 and all(n["attrs"].get("exact_rows") == "1" for n in slices)
     assert any("cut differently" in line for line in exe.plan["log"])
     exe.shutdown()
+
+
+def test_task_that_moves_between_submeshes_changes_layouts_by_its_position_in_the_submesh():
+    """A forward task that runs on another stage's devices every microbatch and changes a layout
+    inside (gather for the projection, slice back to the sequence-split residual): the slice is
+    looked up by the device's position in whichever sub-mesh the task runs on. Before the fix the
+    instances on the second sub-mesh returned uninitialised memory (found by a randomised run)."""
+    mm.init(cpus=4)
+    g = torch.Generator().manual_seed(0)
+    B, S, D, F = 8, 4, 16, 8
+    params = [torch.randn(D, F, generator=g) / 4, torch.randn(F, D, generator=g) / 3, torch.randn(D, generator=g)]
+    batch = (torch.randn(B, S, D, generator=g), torch.randn(B, S, D, generator=g))
+
+    def loss_fn(params, batch):
+        (w1, w2, scale), (x, y) = params, batch
+        with mm.named_scope("blk.0"):
+            h = mm.with_sharding_constraint(x, (None, "seq", None))
+            h = h + torch.tanh(h @ w1) @ w2
+        with mm.named_scope("blk.1"):
+            h = h * scale
+            return ((h - y) ** 2).sum()
+
+    def step(params, batch):
+        return mm.microbatch(mm.value_and_grad(loss_fn), size=2, argnum=1, schedule="1f1b")(params, batch)
+
+    axes = [("seq", "model")]
+
+    def factory(matched, backprop):
+        i = int(matched.split(".")[1])
+        if i == 0 and not backprop:
+            return mm.Task(name="moving", mesh_slice={"stage": 0}, logical_axes=axes,
+                           loop_dependent_mesh_slice=lambda k: {"stage": k % 2})
+        return mm.Task(name=f"s{i}" + ("_bwd" if backprop else ""), mesh_slice={"stage": i}, logical_axes=axes)
+
+    mesh = mm.MultiMesh((2, 2), ("stage", "model"))
+    mesh.register_task(r"(blk\.\d+)", factory=factory)
+    with mesh:
+        exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="cpu")
+    starts = sorted({op["device_start"] for op in exe.plan["ops"] if op["kind"] == "task" and op["name"].endswith("moving_loop")})
+    assert starts == [0, 2]
+    assert _node_dicts(exe, "mm.spmd_reshard")                    # the layout does change inside the task
+    loss, grads = exe(params, batch)
+    with mm.ignore_transforms():
+        ref_loss, ref_grads = step(params, batch)
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-4)
+    for a, b in zip(grads, ref_grads):
+        torch.testing.assert_close(a.full_tensor(), b, rtol=1e-4, atol=1e-4)
+    exe.shutdown()
