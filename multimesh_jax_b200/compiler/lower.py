@@ -125,7 +125,10 @@ class TemplateProgram:
             elif kind == 3:  # dynamic slice at a host-provided offset
                 dim, size, shards = ins.extra
                 x = env[ins.args]
-                env[ins.outs[0]] = x.narrow(dim, scalars[0] // shards, size // shards)
+                piece = x.narrow(dim, scalars[0] // shards, size // shards)
+                # rows of the leading dimension are one block of memory; a slice of an inner
+                # dimension is not, and the captured operators (views) expect a dense operand
+                env[ins.outs[0]] = piece if piece.is_contiguous() else piece.contiguous()
             elif kind == 4:  # all-reduce over mesh axes
                 axes, scale, in_place = ins.extra
                 y = ctx.all_reduce(env[ins.args], axes, ins.node_id, in_place=in_place)

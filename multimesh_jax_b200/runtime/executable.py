@@ -149,8 +149,13 @@ class Executable:
         self.topology = topology
         self.name = name
         self.programs: Dict[int, TemplateProgram] = {}
+        # a process builds the programs of the templates it will run: those compiled for its devices
+        # and those that some operation of the plan places there (a task that moves between
+        # sub-meshes per microbatch runs one template on several device ranges)
+        runs_here = {op["template"] for op in plan["ops"] if op["kind"] == "task" and
+                     any(topology.is_local(d) for d in range(op["device_start"], op["device_start"] + op["num_devices"]))}
         for t in plan["templates"]:
-            local = any(topology.is_local(d) for d in self._template_devices(t))
+            local = t["id"] in runs_here or any(topology.is_local(d) for d in self._template_devices(t))
             if local or topology.kind != "dist":
                 self.programs[t["id"]] = build_program(cap, plan, t, fast_ops, acc_fusable)
         # A process that drives exactly one CUDA device gets the context that owns the device's

@@ -5,6 +5,8 @@ Modes:
            checks its tiles of the loss and of the updated parameters against the eager step.
   leave  - the last rank exits cleanly between steps; the others see their next collective
            end with an error within the process-group timeout and report it as a status.
+  moving - a forward task that runs on another stage's devices every microbatch (one template on two
+           device ranges) with a layout change inside; every rank checks its tiles against eager.
   ckpt   - every rank saves its tiles of the updated parameters, the job reloads them (stored layout
            and the compiled step's layout) and compares; the manifest names only complete tiles.
 """
@@ -61,6 +63,60 @@ def mode_step(pp, tp, dp=1):
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
         print(json.dumps({"DIST_STEP_OK": bool(ok.item()), "tiles_checked_rank0": checked}), flush=True)
+    exe.shutdown()
+
+
+def mode_moving():
+    import multimesh_jax_b200 as mm
+    from multimesh_jax_b200.runtime.collectives import tile_box
+    rank = dist.get_rank()
+    g = torch.Generator().manual_seed(0)
+    B, S, D, F = 8, 4, 16, 8
+    params = [torch.randn(D, F, generator=g) / 4, torch.randn(F, D, generator=g) / 3, torch.randn(D, generator=g)]
+    batch = (torch.randn(B, S, D, generator=g), torch.randn(B, S, D, generator=g))
+
+    def loss_fn(params, batch):
+        (w1, w2, scale), (x, y) = params, batch
+        with mm.named_scope("blk.0"):
+            h = mm.with_sharding_constraint(x, (None, "seq", None))
+            h = h + torch.tanh(h @ w1) @ w2
+        with mm.named_scope("blk.1"):
+            h = h * scale
+            return ((h - y) ** 2).sum()
+
+    def step(params, batch):
+        return mm.microbatch(mm.value_and_grad(loss_fn), size=2, argnum=1, schedule="1f1b")(params, batch)
+
+    axes = [("seq", "model")]
+
+    def factory(matched, backprop):
+        i = int(matched.split(".")[1])
+        if i == 0 and not backprop:
+            return mm.Task(name="moving", mesh_slice={"stage": 0}, logical_axes=axes,
+                           loop_dependent_mesh_slice=lambda k: {"stage": k % 2})
+        return mm.Task(name=f"s{i}" + ("_bwd" if backprop else ""), mesh_slice={"stage": i}, logical_axes=axes)
+
+    mesh = mm.MultiMesh((2, 2), ("stage", "model"))
+    mesh.register_task(r"(blk\.\d+)", factory=factory)
+    with mesh:
+        exe = mm.compile_function(step, (params, batch), mesh=mesh, backend="dist")
+    with mm.ignore_transforms():
+        ref_loss, ref_grads = step(params, batch)
+    loss, grads = exe(params, batch)
+    checked = 0
+    for got, want in [(loss, ref_loss)] + list(zip(grads, ref_grads)):
+        got.wait()
+        for d, tile in got.local_tiles().items():
+            lo, hi = tile_box(got.sharding, d - got.sharding["device_start"])
+            ref = want[tuple(slice(a, b) for a, b in zip(lo, hi))] if want.dim() else want
+            torch.testing.assert_close(tile, ref, rtol=1e-4, atol=1e-4)
+            checked += 1
+    moved_here = sum(1 for op in exe.plan["ops"] if op["kind"] == "task" and op["name"].endswith("moving_loop")
+                     and op["device_start"] <= rank < op["device_start"] + op["num_devices"])
+    ok = torch.tensor([1 if moved_here == 2 else 0])      # four microbatches: two on each stage's devices
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(json.dumps({"DIST_MOVING_OK": bool(ok.item()), "tiles_checked_rank0": checked}), flush=True)
     exe.shutdown()
 
 
@@ -128,6 +184,8 @@ if __name__ == "__main__":
         mode_step(pp, tp, dp)
     elif mode == "ckpt":
         mode_ckpt(pp, tp, sys.argv[4])
+    elif mode == "moving":
+        mode_moving()
     else:
         mode_leave(pp, tp)
     dist.destroy_process_group()

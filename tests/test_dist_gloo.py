@@ -35,6 +35,13 @@ def test_dist_topology_step_matches_eager(pp, tp, dp):
     assert json.loads(line)["DIST_STEP_OK"] is True
 
 
+def test_task_that_moves_between_stages_runs_on_ranks_its_template_was_not_compiled_for():
+    r = _run(4, "moving", 2, 2)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    line = next(l for l in r.stdout.splitlines() if "DIST_MOVING_OK" in l)
+    assert json.loads(line)["DIST_MOVING_OK"] is True
+
+
 def test_rank_leaving_between_steps_is_reported_on_the_host():
     r = _run(2, "leave", 2, 1, timeout=240)
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]

@@ -300,3 +300,35 @@ def test_task_and_reshard_bodies_are_built_once_and_reused_by_later_steps():
     loss2, _ = exe(params, (x * 2.0, y))
     assert abs(float(loss2.full_tensor()) - float(loss_ref)) > 1e-3
     exe.shutdown()
+
+
+def test_microbatches_cut_along_an_inner_dimension_feed_views():
+    """Microbatches taken along dimension 1: the slice is not one block of memory, the projection
+    behind it flattens its operand with a view (found by a randomised run)."""
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(D, D, generator=g) / D ** 0.5
+    x, y = torch.randn(4, 6, D, generator=g), torch.randn(4, 6, D, generator=g)
+
+    def loss_fn(w, batch):
+        xb, yb = batch
+        with mm.named_scope("blk.0"):
+            h = torch.tanh(xb @ w)
+        with mm.named_scope("lossfn"):
+            return ((h - yb) ** 2).sum()
+
+    def step(w, batch):
+        return mm.microbatch(mm.value_and_grad(loss_fn), dim=1, size=2, argnum=1, schedule="gpipe")(w, batch)
+
+    mesh = mm.MultiMesh((2,), ("stage",))
+    mesh.register_task(r"(blk\.\d+)", task=mm.Task(name="s0", mesh_slice={"stage": 0}))
+    mesh.register_task("(lossfn)", factory=lambda m, b: mm.Task(name="s1" + ("_bwd" if b else ""), mesh_slice={"stage": 1}))
+    with mesh:
+        exe = mm.compile_function(step, (w, (x, y)), mesh=mesh, backend="cpu")
+    loss, grad = exe(w, (x, y))
+    with mm.ignore_transforms():
+        ref_loss, ref_grad = step(w, (x, y))
+    torch.testing.assert_close(loss.full_tensor(), ref_loss, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(grad.full_tensor(), ref_grad, rtol=1e-4, atol=1e-5)
+    offsets = {op["scalars"][0] for op in exe.plan["ops"] if op["kind"] == "task" and op["scalars"]}
+    assert offsets == {0, 2, 4}                                   # three microbatches of two columns of dimension 1
+    exe.shutdown()
