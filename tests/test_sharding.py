@@ -172,3 +172,66 @@ def test_planner_prefers_the_local_replica_and_spreads_the_rest():
     assert by_dst[2] == 2 and by_dst[3] == 3                     # overlap: no link traffic
     assert len({by_dst[4], by_dst[5]}) == 2                      # different sources serve the others
     assert plan["bytes_over_links"] == 2 * 2 * 16 * 2
+
+
+def test_layout_predicates_hold_on_random_layout_pairs():
+    """2,000 seeded random pairs of layouts (one to three mesh axes, several axes on one dimension,
+    any device offsets): mesh-equivalent layouts have the same tiles; where no reshard is asked for,
+    every destination device already holds its tile of the source; equal tiles on equal devices never
+    ask for one; text round trips keep the tiles; a resized layout has the requested device count and
+    covers every element once per replica."""
+    import random
+
+    def layout(rng, sizes, start):
+        mesh = [rng.choice([1, 2, 2, 3, 4]) for _ in range(rng.randint(1, 3))]
+        dim_axes, left = [[] for _ in sizes], list(sizes)
+        order = list(range(len(mesh)))
+        rng.shuffle(order)
+        for axis in order:
+            fits = [d for d in range(len(sizes)) if left[d] % mesh[axis] == 0 and left[d] >= mesh[axis]]
+            if fits and rng.random() > 0.25:
+                d = rng.choice(fits)
+                dim_axes[d].append(axis)
+                left[d] //= mesh[axis]
+        return C.sharded_shape("float32", list(sizes), dim_axes, mesh, start)
+
+    def boxes(s):
+        return [C.tile_box(s, o) for o in range(s["num_devices"])]
+
+    def volume(box):
+        v = 1
+        for lo, hi in zip(*box):
+            v *= hi - lo
+        return v
+
+    equivalent = in_place = 0
+    for seed in range(2000):
+        rng = random.Random(seed)
+        sizes = [rng.choice([2, 4, 6, 8, 12]) for _ in range(rng.randint(1, 3))]
+        a, b = layout(rng, sizes, rng.randint(0, 2)), layout(rng, sizes, rng.randint(0, 2))
+        same_tiles = a["num_devices"] == b["num_devices"] and boxes(a) == boxes(b)
+        if C.mesh_equivalent(a, b):
+            equivalent += 1
+            assert same_tiles, (a["key"], b["key"])
+        if not C.needs_reshard(a, b):
+            in_place += 1
+            for o in range(b["num_devices"]):
+                pos = b["device_start"] + o - a["device_start"]
+                assert 0 <= pos < a["num_devices"] and C.tile_box(a, pos) == C.tile_box(b, o), (a["key"], b["key"])
+        if same_tiles and a["device_start"] == b["device_start"]:
+            assert not C.needs_reshard(a, b), (a["key"], b["key"])
+        again = C.sharded_shape_from_json(C.sharded_shape_to_json(a))
+        assert again["key"] == a["key"] and boxes(again) == boxes(a)
+        count = rng.choice([1, 2, 3, 4, 6, 8])
+        resized, _ = C.resize_sharding(a, rng.randint(0, 4), count)
+        assert resized["num_devices"] == count
+        used = {axis for dim in resized["dim_axes"] for axis in dim}
+        replicas = 1
+        for axis, extent in enumerate(resized["mesh_dims"]):
+            if axis not in used:
+                replicas *= extent
+        total = 1
+        for s_ in sizes:
+            total *= s_
+        assert sum(volume(bx) for bx in boxes(resized)) == total * replicas, (a["key"], resized["key"])
+    assert equivalent > 10 and in_place > 30
