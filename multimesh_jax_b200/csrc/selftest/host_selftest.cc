@@ -12,7 +12,9 @@
 //      checks that it computes the same result and that its cross-stream conflicts became waits;
 //   4. injects host-side faults (a task body that throws, a dropped task) and checks that the
 //      error surfaces as a status and that the context stays usable;
-//   5. for every stored-program file named on the command line (real-model training steps with
+//   5. runs 20 random task graphs (random devices, tiles, priorities, strict-order flags) on the
+//      threaded runtime and compares each with the same tasks run one after the other;
+//   6. for every stored-program file named on the command line (real-model training steps with
 //      pipeline, tensor, sequence, data and expert parallelism): loads it, compiles it offline,
 //      replays the plan on the mock runtime, writes the program back to text, reads that again
 //      and compares the plans; then feeds the loader truncated and corrupted copies of the text,
@@ -233,6 +235,63 @@ static RunResult ExecuteOnStreams(const Plan& plan, int num_devices, bool inject
   return res;
 }
 
+// Random task graphs straight on the runtime: tasks on random devices read and write random tiles
+// (their own device's and other devices'), with random priorities and strict-order flags. The
+// bodies update unlocked cells, so the result equals the one of running the tasks one after the other
+// in submission order only if every read-after-write, write-after-read and write-after-write pair
+// was ordered - and an unordered pair is a data race for the thread sanitizer.
+static void RandomTaskGraphs(int rounds) {
+  uint64_t state = 0x2545F4914F6CDD1Dull;
+  auto next = [&](uint64_t bound) {
+    state ^= state << 13; state ^= state >> 7; state ^= state << 17;
+    return static_cast<int>(state % bound);
+  };
+  for (int round = 0; round < rounds; ++round) {
+    const int devices = 2 + next(5), buffers = 3 + next(10), tasks = 50 + next(200);
+    std::vector<int> ids(devices);
+    for (int d = 0; d < devices; ++d) ids[d] = d;
+    std::map<std::pair<int, int>, double> cells, expect;
+    for (int b = 0; b < buffers; ++b)
+      for (int d = 0; d < devices; ++d) cells[{b, d}] = expect[{b, d}] = 1.0 + 0.01 * b + 0.1 * d;
+    mmrt::ThreadedContext ctx(ids, /*inline_execution=*/false, /*record_submissions=*/true);
+    ctx.OpenWindow();
+    for (int k = 0; k < tasks; ++k) {
+      const int device = next(devices);
+      std::vector<mmrt::TileRef> reads, writes;
+      for (int r = 1 + next(3); r > 0; --r) reads.push_back({next(buffers), next(4) ? device : next(devices)});
+      for (int w = 1 + next(2); w > 0; --w) {
+        mmrt::TileRef t{next(buffers), next(6) ? device : next(devices)};
+        bool dup = false;
+        for (auto& x : writes) dup = dup || (x.buffer == t.buffer && x.device == t.device);
+        if (!dup) writes.push_back(t);
+      }
+      auto apply = [reads, writes, k](std::map<std::pair<int, int>, double>& m) {
+        double v = 0.001 * k;
+        for (auto& r : reads) v += 0.5 * m.at({r.buffer, r.device});
+        for (auto& w : writes) m.at({w.buffer, w.device}) = std::tanh(v + 0.25 * m.at({w.buffer, w.device}));
+      };
+      apply(expect);                       // the sequential answer
+      std::vector<mmrt::TileRef> all_reads = reads;
+      for (auto& w : writes) all_reads.push_back(w);   // a written cell is also read
+      mmrt::ExecuteOptions eo;
+      eo.name = "t" + std::to_string(k);
+      eo.priority = next(3) - 1;
+      eo.strict_ordering = next(8) == 0;
+      if (next(5) == 0) ctx.Reshard(device, all_reads, writes, [&cells, apply] { apply(cells); }, eo);
+      else ctx.CreateExecuteTask(device, all_reads, writes, [&cells, apply] { apply(cells); }, eo);
+    }
+    ctx.CloseWindow();
+    std::string message;
+    CHECK(ctx.WaitAll(&message) == mmrt::Status::kOk, "random task graph reported an error");
+    CHECK(mmrt::CheckHazards(ctx.Submissions()).empty(), "random task graph: unordered conflicting accesses");
+    bool same = true;
+    for (auto& kv : expect) same = same && cells.at(kv.first) == kv.second;
+    CHECK(same, "random task graph: result differs from the sequential run");
+    ctx.Shutdown();
+  }
+  std::printf("%d random task graphs match their sequential runs\n", rounds);
+}
+
 static void CheckStoredProgram(const std::string& path) {
   Plan plan;
   std::vector<std::string> log;
@@ -370,6 +429,7 @@ int main(int argc, char** argv) {
                   microbatches, tasks, reshards, first);
     }
   }
+  RandomTaskGraphs(20);
   for (int a = 2; a < argc; ++a) CheckStoredProgram(argv[a]);
   if (argc > 2) MutateStoredProgram(argv[2], 40);
   if (g_failures) {
