@@ -1,6 +1,6 @@
 """Randomised differential test of sharding propagation, SPMD lowering, reshard insertion and the
 pipeline runtime: seeded random networks (MLP and attention blocks, norms, softmax, reductions over
-the sequence, biases) with random layout constraints on activations and weights, random logical ->
+the sequence, biases, concatenation, chunks, permutes, cumulative sums, flips, einsum, stack, expand) with random layout constraints on activations and weights, random logical ->
 mesh axis tables (optionally a different priority order on odd stages), random three-axis meshes of
 one to four stages, every pipeline schedule (zero-bubble with split backward tasks), interleaved
 block placement, a first block that moves between stages per microbatch, recomputation on or off
@@ -17,7 +17,8 @@ from torch.utils import _pytree as pytree
 
 import multimesh_jax_b200 as mm
 
-OPS = ["mlp", "mlp", "tanh", "resid", "scale", "norm", "attn", "softmax", "meanseq", "gelu", "bias"]
+OPS = ["mlp", "mlp", "tanh", "resid", "scale", "norm", "attn", "softmax", "meanseq", "gelu", "bias", "cat", "chunk",
+       "permute", "cumsum", "max", "where", "clamp", "layernorm", "flip", "einsum", "stack", "expand", "sq_sum", "outer"]
 MESHES = [(1, 2, 2), (2, 2, 1), (1, 4, 1), (2, 1, 2), (1, 2, 1), (2, 2, 2), (1, 1, 2), (4, 2, 1), (4, 1, 1), (3, 1, 2),
           (2, 1, 1)]
 AXES = [("batch", "x"), ("hid", "y"), ("feat", "y"), ("seq", "y"), ("batch", "y"), ("hid", "x"), ("heads", "y"),
@@ -102,6 +103,35 @@ def _build(case):
                         h = torch.softmax(h, dim=-1) * h.shape[-1] ** 0.5
                     elif op == "meanseq":
                         h = h - h.mean(1, keepdim=True)
+                    elif op == "cat":
+                        h = torch.cat([h[..., h.shape[-1] // 2:] * 2.0, h[..., : h.shape[-1] // 2]], dim=-1)
+                    elif op == "chunk":
+                        lo, hi = h.chunk(2, dim=-1)
+                        h = torch.cat([lo + hi, lo - hi], dim=-1)
+                    elif op == "permute":
+                        h = (h.permute(0, 2, 1).contiguous() * 1.5).permute(0, 2, 1)
+                    elif op == "cumsum":
+                        h = h + 0.1 * torch.cumsum(h, dim=1)
+                    elif op == "max":
+                        h = h - h.max(dim=-1, keepdim=True).values
+                    elif op == "where":
+                        h = torch.where(h > 0, h, 0.2 * h)
+                    elif op == "clamp":
+                        h = h.clamp(-1.5, 1.5)
+                    elif op == "layernorm":
+                        h = torch.nn.functional.layer_norm(h, (h.shape[-1],))
+                    elif op == "flip":
+                        h = h + 0.3 * h.flip(1)
+                    elif op == "einsum":
+                        h = h + 0.1 * torch.einsum("bsd,btd->bsd", h, h) / h.shape[1]
+                    elif op == "stack":
+                        h = torch.stack([h, 2.0 * h], dim=0).sum(0)
+                    elif op == "expand":
+                        h = h + h.mean(-1, keepdim=True).expand_as(h)
+                    elif op == "sq_sum":
+                        h = h / (1.0 + (h * h).sum((1, 2), keepdim=True)).sqrt()
+                    elif op == "outer":
+                        h = h + 0.05 * (h.unsqueeze(-1) * h.unsqueeze(-2)).sum(-1)
         with mm.named_scope("lossfn"):
             return ((h - target) ** 2).sum()
 
@@ -148,7 +178,7 @@ def _mesh(case):
     return mesh
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(32))
 def test_random_network_and_layouts_match_the_eager_step(seed):
     mm.init(cpus=8)
     case = _draw(random.Random(1000 + seed))
