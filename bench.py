@@ -248,7 +248,7 @@ def main():
                           "tasks": sum(1 for op in plan["ops"] if op["kind"] == "task"),
                           "reshards": sum(1 for op in plan["ops"] if op["kind"] == "reshard"),
                           "temp_gb_per_device": round(plan["temp_bytes_per_device_max"] / 2 ** 30, 1),
-                          "plan_hash": plan["hash"], "stats": plan["stats"]}))
+                          "plan_hash": plan["hash"], "stats": plan["stats"], "compiler_notes": plan.get("log", [])}))
         exe.shutdown()
         return 0
 
