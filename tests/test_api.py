@@ -376,3 +376,67 @@ def test_mesh_queries_and_scope_lookup_during_a_capture():
     assert seen == {"outside": None, "blk.0": {"stage": 0}, "blk.1/inner": {"stage": 1}}
     assert float(exe(torch.ones(4)).full_tensor()) == 12.0
     exe.shutdown()
+
+
+def _grid(*shape):
+    n = 1
+    for s in shape:
+        n *= s
+    return torch.arange(n, dtype=torch.float32).reshape(*shape)
+
+
+def _same_as_eager(fn, args, setup=None):
+    mm.clear_tasks()
+    if setup:
+        setup()
+    try:
+        with mm.ignore_transforms():
+            want = fn(*args)
+        exe = mm.compile_function(fn, args, num_devices=2, backend="cpu")
+        got = exe(*args)
+        from torch.utils import _pytree as pytree
+        for a, b in zip(pytree.tree_leaves(got), pytree.tree_leaves(want)):
+            torch.testing.assert_close(a.full_tensor() if hasattr(a, "full_tensor") else a, b)
+        exe.shutdown()
+    finally:
+        mm.clear_tasks()
+
+
+def test_microbatch_loop_without_any_task():
+    """tests/python/jax_microbatch_test.py: test_microbatch_no_tasks, test_multiple_microbatch_slices."""
+    def step(args):
+        return mm.microbatch(lambda a: (a[0] * a[1] * a[2]).sum(), dim=0, size=2)(args)
+    _same_as_eager(step, ((_grid(4, 4), _grid(4, 1), _grid(4, 1)),))
+
+
+def test_scopes_around_a_microbatch_loop_become_its_pre_and_post_tasks():
+    """tests/python/jax_microbatch_test.py: test_microbatch_implicit_pre_post_task - the same two
+    scope names match operators before, inside and after the loop."""
+    def setup():
+        for name in ("layer0", "layer1"):
+            mm.register_task(name, task=mm.Task(name=name, mesh=mm.TaskMesh((1, 1), ("x", "y"), [0]),
+                                                logical_axes=[("batch", "x"), ("model", "y")]))
+
+    def step(args):
+        def body(a):
+            x, y, z = a
+            with mm.named_scope("layer0"):
+                s = x + y
+            with mm.named_scope("layer1"):
+                return (s + z).sum(0)
+        x, y, z = args
+        with mm.named_scope("layer0"):
+            x, y, z = 2 * x, 2 * y, 2 * z
+        s = mm.microbatch(body, dim=0, size=2)((x, y, z))
+        with mm.named_scope("layer1"):
+            return s.sum()
+    _same_as_eager(step, ((_grid(4, 4), _grid(4, 1), _grid(4, 1)),), setup)
+
+
+def test_two_explicit_tasks_in_one_microbatch_loop_with_gradients():
+    """tests/python/jax_microbatch_test.py: test_multiple_microbatch, test_multiple_microbatch_grad."""
+    def step(params, x):
+        f = mm.task(lambda x, p: x * p, name="f", devices=[0])
+        g = mm.task(lambda x, p: (x * p).sum(), name="g", devices=[1])
+        return mm.microbatch(mm.value_and_grad(lambda params, x: g(f(x, params[0]), params[1])), argnum=1, dim=0, size=2)(params, x)
+    _same_as_eager(step, ([_grid(4), _grid(4)], _grid(4, 4)))
