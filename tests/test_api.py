@@ -440,3 +440,43 @@ def test_two_explicit_tasks_in_one_microbatch_loop_with_gradients():
         g = mm.task(lambda x, p: (x * p).sum(), name="g", devices=[1])
         return mm.microbatch(mm.value_and_grad(lambda params, x: g(f(x, params[0]), params[1])), argnum=1, dim=0, size=2)(params, x)
     _same_as_eager(step, ([_grid(4), _grid(4)], _grid(4, 4)))
+
+
+def test_activation_checkpointing_inside_tasks_recomputes_in_the_backward_task():
+    """tests/python/jax_task_test.py: test_rematerialization, test_multiple_layer_rematerialization -
+    ``torch.utils.checkpoint`` inside a task: the recomputed forward operators are captured as part
+    of the task's backward task, results equal the eager ones."""
+    from torch.utils import _pytree as pytree
+    from torch.utils.checkpoint import checkpoint
+
+    def square_twice(x):
+        def loss(x):
+            sq = mm.task(lambda t: checkpoint(lambda u: u * u, t, use_reentrant=False), name="sq", devices=[0])
+            return sq(sq(x)).sum()
+        return mm.value_and_grad(loss)(x)
+
+    def three_layers(params, x):
+        def net(params, x):
+            y, z = params
+            layer = lambda x, y, z: x * x + x * y + x * z      # noqa: E731
+            for _ in range(3):
+                x = checkpoint(layer, x, y, z, use_reentrant=False)
+            return x.sum()
+        return mm.value_and_grad(mm.task(net, name="net", devices=[0, 1]))(params, x)
+
+    cases = [(square_twice, (_grid(4, 4) / 8,), "sq"),
+             (three_layers, ([torch.full((4, 4), 0.3), torch.full((4, 4), 0.2)], _grid(4, 4) / 16), "net")]
+    for fn, args, name in cases:
+        with mm.ignore_transforms():
+            want = fn(*args)
+        exe = mm.compile_function(fn, args, num_devices=2, backend="cpu")
+        got = exe(*args)
+        for a, b in zip(pytree.tree_leaves(got), pytree.tree_leaves(want)):
+            torch.testing.assert_close(a.full_tensor(), b)
+        g = exe.cap.graph
+        ops = {t["name"].split(".", 1)[1]: [g.node(n)["op"] for n in t["nodes"]] for t in exe.plan["templates"]}
+        assert set(ops) == {name, name + "_bwd"}
+        forward_muls = ops[name].count("aten.mul.Tensor")
+        # the backward task holds the recomputed forward products beside the gradient products
+        assert ops[name + "_bwd"].count("aten.mul.Tensor") > forward_muls >= 2
+        exe.shutdown()
