@@ -39,23 +39,44 @@ def _partition_config(**overrides):
     return cfg
 
 
+def _is_spec(x) -> bool:
+    """One layout: a tuple / list with one entry per dimension, each None, an axis name or a tuple
+    of axis names."""
+    return isinstance(x, (tuple, list)) and all(
+        e is None or isinstance(e, str) or (isinstance(e, (tuple, list)) and e and all(isinstance(a, str) for a in e))
+        for e in x)
+
+
 def _apply_shardings(cap: Captured, in_shardings, example_args) -> None:
-    """Attaches user-given axis names to graph inputs (mesh-axis names unless autoshard)."""
+    """Attaches user-given axis names to graph inputs (mesh-axis names unless autoshard).
+    ``in_shardings`` has one entry per positional argument: ``None`` (the compiler's choice), one
+    layout - applied to every tensor of that argument - or a container shaped like the argument
+    that holds a layout or ``None`` per tensor."""
     if in_shardings is None:
         return
-    flat_args, _ = pytree.tree_flatten(tuple(example_args))
-    specs = pytree.tree_leaves(in_shardings, is_leaf=lambda x: x is None or (
-        isinstance(x, (tuple, list)) and all(e is None or isinstance(e, (str, tuple, list)) for e in x)))
-    tensor_pos = [i for i, a in enumerate(flat_args) if isinstance(a, torch.Tensor)]
-    if len(specs) != len(tensor_pos):
-        return
+    example_args = tuple(example_args)
+    if not isinstance(in_shardings, (tuple, list)) or len(in_shardings) != len(example_args):
+        raise ValueError(f"in_shardings needs one entry per positional argument ({len(example_args)}), got {in_shardings!r}")
     from ..lib import _canonical_axes
-    for k, spec in enumerate(specs):
-        if spec is None:
-            continue
-        vid = cap.graph.inputs[k]
-        ndim = len(cap.graph.value(vid)["shape"])
-        cap.graph.set_value_axes(vid, _canonical_axes(spec, ndim), bool(state.flags.autoshard))
+    k = 0           # index over the tensor leaves of all arguments = index over graph inputs
+    for pos, (arg, entry) in enumerate(zip(example_args, in_shardings)):
+        leaves = [a for a in pytree.tree_leaves(arg) if isinstance(a, torch.Tensor)]
+        if entry is None:
+            specs = [None] * len(leaves)
+        elif _is_spec(entry) and not (isinstance(arg, (tuple, list)) and len(entry) == len(arg) and
+                                       all(e is None or _is_spec(e) for e in entry) and
+                                       any(_is_spec(e) for e in entry)):
+            specs = [entry] * len(leaves)
+        else:
+            specs = pytree.tree_leaves(entry, is_leaf=lambda x: x is None or _is_spec(x))
+            if len(specs) != len(leaves):
+                raise ValueError(f"in_shardings[{pos}] holds {len(specs)} layouts for {len(leaves)} tensors")
+        for spec in specs:
+            if spec is not None:
+                vid = cap.graph.inputs[k]
+                ndim = len(cap.graph.value(vid)["shape"])
+                cap.graph.set_value_axes(vid, _canonical_axes(spec, ndim), bool(state.flags.autoshard))
+            k += 1
 
 
 def compile_function(fn: Callable, example_args: Sequence[Any], *, mesh: Optional[MultiMesh] = None,

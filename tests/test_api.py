@@ -480,3 +480,65 @@ def test_activation_checkpointing_inside_tasks_recomputes_in_the_backward_task()
         # the backward task holds the recomputed forward products beside the gradient products
         assert ops[name + "_bwd"].count("aten.mul.Tensor") > forward_muls >= 2
         exe.shutdown()
+
+
+def test_donated_arguments_single_multiple_and_sharded():
+    """tests/python/jax_task_test.py: test_donation_single_argument, test_donation_multiple_arguments,
+    test_donation_sharded_arguments - results equal the eager ones, donated buffers back the results
+    where shapes match, and the caller's own tensors are not written."""
+    from multimesh_jax_b200.test_util import check_against_reference
+
+    def single(x):
+        return mm.task(lambda t: t * t, name="f", devices=[0])(x)
+
+    def chained(x, y):
+        f = mm.task(lambda t: t * t, name="f", devices=[0])
+        g = mm.task(lambda t, u: (t * t, t * u), name="g", devices=[0])
+        return g(f(x), y)
+
+    def chained_wide(x, y):
+        f = mm.task(lambda t: t * t, name="f", devices=[0, 1])
+        g = mm.task(lambda t, u: (t * t, t * u), name="g", devices=[0, 1])
+        return g(f(x), y)
+
+    mk = lambda: (_grid(4, 4) / 4,)                      # noqa: E731
+    mk2 = lambda: (_grid(4, 4) / 4, _grid(4, 4) / 8)     # noqa: E731
+    _, _, exe = check_against_reference(single, mk, num_devices=1, donate_argnums=(0,))
+    exe.shutdown()
+    _, _, exe = check_against_reference(chained, mk2, num_devices=1, donate_argnums=(0, 1))
+    exe.shutdown()
+    _, out, exe = check_against_reference(chained_wide, mk2, num_devices=2, donate_argnums=(0, 1),
+                                          arg_shardings=(("x", None), ("x", None)))      # rows over the tasks' axis
+    assert [s["shard_size"] for s in exe.input_shardings()] == [[2, 4], [2, 4]]
+    # a second call with fresh arguments still works after the first call's buffers were given away
+    x, y = mk2()
+    keep_x, keep_y = x.clone(), y.clone()
+    a, b = exe(x, y)
+    torch.testing.assert_close(a.full_tensor(), (keep_x * keep_x) ** 2)
+    torch.testing.assert_close(b.full_tensor(), keep_x * keep_x * keep_y)
+    assert torch.equal(x, keep_x) and torch.equal(y, keep_y)      # host tensors are copied in, never written
+    exe.shutdown()
+
+
+def test_in_shardings_take_one_entry_per_argument():
+    mm.init(cpus=2)
+    wide = mm.task(lambda w, pair: (pair[0] @ w + pair[1]).sum(-1), name="net", devices=[0, 1])
+    w, a, b = torch.randn(4, 4), torch.randn(6, 4), torch.randn(6, 4)
+
+    def layouts(in_shardings):
+        exe = mm.compile_function(lambda w, pair: wide(w, pair), (w, (a, b)), num_devices=2, backend="cpu",
+                                  in_shardings=in_shardings)
+        try:
+            torch.testing.assert_close(exe(w, (a, b)).full_tensor(), (a @ w + b).sum(-1))
+            return [s["shard_size"] for s in exe.input_shardings()]
+        finally:
+            exe.shutdown()
+
+    assert layouts((None, ("x", None))) == [[4, 4], [3, 4], [3, 4]]            # one layout for every tensor of the argument
+    assert layouts((None, (("x", None), None)))[:2] == [[4, 4], [3, 4]]        # a layout per tensor of the argument
+    assert layouts(((None, "x"), None))[0] == [4, 2]                            # columns of the weight
+    assert layouts((None, None)) is not None
+    with pytest.raises(ValueError, match="one entry per positional argument"):
+        layouts((("x", None),))
+    with pytest.raises(ValueError, match="layouts for 2 tensors"):
+        layouts((None, [("x", None), None, None]))
