@@ -250,3 +250,48 @@ def test_task_that_moves_between_submeshes_changes_layouts_by_its_position_in_th
     for a, b in zip(grads, ref_grads):
         torch.testing.assert_close(a.full_tensor(), b, rtol=1e-4, atol=1e-4)
     exe.shutdown()
+
+
+def test_several_mesh_axes_on_one_dimension_and_tasks_on_unequal_meshes():
+    """tests/python/jax_auto_task_test.py: test_auto_shard_multiple_axes - an embedding task on a
+    4 x 2 mesh of eight devices feeds a layer on a 2 x 2 mesh of four; the batch dimension carries
+    two logical names. The weight of the second task lives on its four devices, split over one
+    mesh axis and replicated over the other; the token batch is split eight ways; the result stays
+    on the second task's devices."""
+    mm.init(cpus=8)
+    axes = [("batch", "x"), ("embed", "x"), ("model", "y")]
+    mesh = mm.MultiMesh((8, 1, 1), ("batch", "model", "embed"))
+    mesh.register_task("embeddings", task=mm.Task(name="embeddings", logical_axes=axes,
+                                                  mesh=mm.TaskMesh((4, 2), ("x", "y"), list(range(8)))))
+    mesh.register_task("layer0", task=mm.Task(name="layer0", logical_axes=axes,
+                                              mesh=mm.TaskMesh((2, 2), ("x", "y"), [0, 1, 2, 3])))
+    vocab, B, S, E = 2, 8, 4, 16
+
+    def f(params, batch):
+        embed, fc = params
+        with mm.named_scope("embeddings"):
+            batch = mm.with_sharding_constraint(batch, (("batch", "model"), "seq"))
+            embed = mm.with_sharding_constraint(embed, ("vocab", "embed"))
+            x = torch.einsum("bsv,ve->bse", torch.nn.functional.one_hot(batch, num_classes=vocab).to(embed.dtype), embed)
+        with mm.named_scope("layer0"):
+            x = mm.with_sharding_constraint(x, (("batch", "model"), "seq", "embed"))
+            fc = mm.with_sharding_constraint(fc, ("hidden", "embed"))
+            x = torch.einsum("bsh,eh->bsh", x, fc)
+            return mm.with_sharding_constraint(x, ("batch", "seq", "embed"))
+
+    g = torch.Generator().manual_seed(0)
+    params = (torch.randn(vocab, E, generator=g), torch.randn(E, E, generator=g))
+    batch = torch.randint(0, vocab, (B, S), generator=g)
+    with mesh:
+        exe = mm.compile_function(f, (params, batch), mesh=mesh, backend="cpu")
+    with mm.ignore_transforms():
+        want = f(params, batch)
+    torch.testing.assert_close(exe(params, batch).full_tensor(), want)
+    embed_in, fc_in, batch_in = exe.input_shardings()
+    assert (fc_in["device_start"], fc_in["num_devices"]) == (0, 4)
+    assert fc_in["dim_axes"] == [[], [0]] and fc_in["mesh_dims"] == [2, 2]      # split over x, replicated over y
+    assert (batch_in["device_start"], batch_in["num_devices"]) == (0, 8)
+    assert batch_in["dim_axes"][0] == [0, 1] and batch_in["shard_size"] == [1, 4]
+    out = exe.output_shardings()[0]
+    assert (out["device_start"], out["num_devices"]) == (0, 4)
+    exe.shutdown()
