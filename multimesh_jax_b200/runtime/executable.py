@@ -271,10 +271,21 @@ class Executable:
         me = self._alias_root[sid]
         prev = self._owner.get(key)
         if prev is not None and prev != me and old is not None and old is not new and old.is_floating_point() \
-                and old.untyped_storage().data_ptr() != new.untyped_storage().data_ptr() and not self._in_arena(old):
-            # (tiles inside the peer-mapped arena are left alone: another GPU may still be pulling them)
+                and old.untyped_storage().data_ptr() != new.untyped_storage().data_ptr() and not self._in_arena(old) \
+                and not self._storage_shared(old):
+            # (tiles inside the peer-mapped arena are left alone: another GPU may still be pulling them;
+            # so is memory that another store's tile is a view of - two results of one task, a detached
+            # copy - since that store may be read long after this buffer's name was handed on)
             old.fill_(float("nan"))
         self._owner[key] = me
+
+    def _storage_shared(self, t: torch.Tensor) -> bool:
+        ptr = t.untyped_storage().data_ptr()
+        for tiles in self.tiles.values():
+            for other in tiles.values():
+                if other is not t and isinstance(other, torch.Tensor) and other.untyped_storage().data_ptr() == ptr:
+                    return True
+        return False
 
     def _in_arena(self, t: torch.Tensor) -> bool:
         pr = getattr(self, "_peer_reshard", None)
