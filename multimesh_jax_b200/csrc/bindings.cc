@@ -619,6 +619,7 @@ PYBIND11_MODULE(_mm_C, m) {
            },
            py::arg("kind"), py::arg("name"), py::arg("device") = -1, py::arg("count") = 1, py::arg("delay_ms") = 0)
       .def("hazard_report", [](const mmrt::ThreadedContext& c) { return mmrt::CheckHazards(c.Submissions()); })
+      .def("pending_report", &mmrt::ThreadedContext::PendingReport)
       .def_property_readonly("device_bytes_high_water", &mmrt::ThreadedContext::device_bytes_high_water);
 
   // CUDA streams, events and the scratch tile behind the same submission interface. With

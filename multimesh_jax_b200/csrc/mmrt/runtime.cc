@@ -81,9 +81,22 @@ ThreadedContext::ThreadedContext(std::vector<int> local_devices, bool inline_exe
   if (!inline_) {
     for (int d : local_devices_) {
       workers_[d] = std::make_unique<Worker>();
+      comm_workers_[d] = std::make_unique<Worker>();
     }
-    for (int d : local_devices_) workers_[d]->thread = std::thread([this, d] { WorkerLoop(d); });
+    for (int d : local_devices_) {
+      workers_[d]->thread = std::thread([this, d] { WorkerLoop(*workers_[d]); });
+      comm_workers_[d]->thread = std::thread([this, d] { WorkerLoop(*comm_workers_[d]); });
+    }
   }
+}
+
+// Reshards run on a thread of their own per device (the counterpart of the communication stream
+// of the CUDA context). A task body may block in a collective until its partners on other devices
+// reach it, and a partner may be unable to start before a reshard has read the tile it is about
+// to overwrite; with reshards queued behind the blocked task on the same thread, two such chains
+// close into a cycle (seen with interleaved stages whose tasks exchange data inside).
+ThreadedContext::Worker& ThreadedContext::WorkerOf(const Task& task) {
+  return task.options.kind == 1 ? *comm_workers_[task.device] : *workers_[task.device];
 }
 
 ThreadedContext::~ThreadedContext() { Shutdown(); }
@@ -99,8 +112,10 @@ void ThreadedContext::Shutdown() {
     done_cv_.wait(lock, [&] { return outstanding_ == 0; });
     shutdown_ = true;
     for (auto& kv : workers_) kv.second->cv.notify_all();
+    for (auto& kv : comm_workers_) kv.second->cv.notify_all();
   }
   for (auto& kv : workers_) if (kv.second->thread.joinable()) kv.second->thread.join();
+  for (auto& kv : comm_workers_) if (kv.second->thread.joinable()) kv.second->thread.join();
 }
 
 uint64_t ThreadedContext::CreateExecuteTask(int device, const std::vector<TileRef>& reads,
@@ -141,7 +156,7 @@ uint64_t ThreadedContext::Submit(int device, const std::vector<TileRef>& reads, 
     if (task->pending == 0) {
       if (inline_) run_now = true;
       else {
-        Worker& w = *workers_[device];
+        Worker& w = WorkerOf(*task);
         w.ready.emplace(task->options.priority, -static_cast<int64_t>(task->id));
         w.cv.notify_one();
       }
@@ -151,8 +166,7 @@ uint64_t ThreadedContext::Submit(int device, const std::vector<TileRef>& reads, 
   return task->id;
 }
 
-void ThreadedContext::WorkerLoop(int device) {
-  Worker& w = *workers_[device];
+void ThreadedContext::WorkerLoop(Worker& w) {
   while (true) {
     std::shared_ptr<Task> task;
     {
@@ -234,7 +248,7 @@ void ThreadedContext::Finish(const std::shared_ptr<Task>& task, bool skipped, bo
       if (--it->second->pending == 0) {
         if (inline_) run_inline.push_back(it->second);
         else {
-          Worker& w = *workers_[it->second->device];
+          Worker& w = WorkerOf(*it->second);
           w.ready.emplace(it->second->options.priority, -static_cast<int64_t>(sid));
           w.cv.notify_one();
         }
@@ -245,6 +259,31 @@ void ThreadedContext::Finish(const std::shared_ptr<Task>& task, bool skipped, bo
     done_cv_.notify_all();
   }
   for (auto& t : run_inline) RunTask(t);
+}
+
+std::vector<std::string> ThreadedContext::PendingReport() const {
+  std::unique_lock<std::mutex> lock(mu_);
+  std::map<uint64_t, std::vector<uint64_t>> waits_for;
+  for (auto& kv : tasks_)
+    if (!kv.second->done)
+      for (uint64_t succ : kv.second->successors) waits_for[succ].push_back(kv.first);
+  std::vector<std::string> out;
+  for (auto& kv : tasks_) {
+    const Task& t = *kv.second;
+    if (t.done) continue;
+    std::string line = std::to_string(t.id) + " " + t.options.name + " dev " + std::to_string(t.device) + " ";
+    if (t.pending == 0) {
+      line += "running or ready";
+    } else {
+      line += "waits for:";
+      for (uint64_t p : waits_for[t.id]) {
+        auto it = tasks_.find(p);
+        line += " " + std::to_string(p) + (it != tasks_.end() ? "(" + it->second->options.name + "@" + std::to_string(it->second->device) + ")" : "");
+      }
+    }
+    out.push_back(line);
+  }
+  return out;
 }
 
 void ThreadedContext::CreateStore(int buffer, int device, int64_t bytes, bool host) {

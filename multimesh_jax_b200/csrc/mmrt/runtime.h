@@ -172,6 +172,10 @@ class ThreadedContext : public ExecuteContext {
   Status WaitTask(uint64_t id, std::string* message) override;
   void Shutdown() override;
   std::vector<TaskRecord> EventLog() const override;
+  // One line per task that has been submitted and not finished: "id name device state" where
+  // state is "running or ready" or "waits for: <unfinished predecessors>". For diagnosing a step
+  // that does not end (a task body blocked in a collective its partners never reach).
+  std::vector<std::string> PendingReport() const;
   void ClearEventLog() override;
 
   void InjectFault(const FaultSpec& spec);
@@ -197,9 +201,10 @@ class ThreadedContext : public ExecuteContext {
     std::priority_queue<std::pair<int, int64_t>> ready;
     std::condition_variable cv;
   };
+  Worker& WorkerOf(const Task& task);
   uint64_t Submit(int device, const std::vector<TileRef>& reads, const std::vector<TileRef>& writes, Body body,
                   ExecuteOptions options);
-  void WorkerLoop(int device);
+  void WorkerLoop(Worker& worker);
   void RunTask(std::shared_ptr<Task> task);
   void Finish(const std::shared_ptr<Task>& task, bool skipped, bool failed, double start_us);
   double NowUs() const;
@@ -209,7 +214,8 @@ class ThreadedContext : public ExecuteContext {
   bool record_;
   mutable std::mutex mu_;
   std::condition_variable done_cv_;
-  std::map<int, std::unique_ptr<Worker>> workers_;
+  std::map<int, std::unique_ptr<Worker>> workers_;        // task bodies, one thread per device
+  std::map<int, std::unique_ptr<Worker>> comm_workers_;   // reshard bodies, one thread per device
   std::map<uint64_t, std::shared_ptr<Task>> tasks_;  // live (unfinished) tasks
   DependenceTracker deps_;
   uint64_t next_id_ = 1;
