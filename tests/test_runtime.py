@@ -374,3 +374,30 @@ def test_cuda_context_windows_scratch_and_status():
     c.create_execute_task(0, [], [(1, 0)], lambda: ran.append(3), "victim", False, 0, 101, 0)
     assert c.wait_all()[0] == C.Status.INJECTED_FAULT
     c.shutdown()
+
+
+def test_a_reshard_is_not_held_up_by_a_task_that_waits_for_its_partner():
+    """Two devices run one collective task each (the bodies wait for one another, as an exchange
+    inside a task does). Device 1's half may only start once a reshard queued on device 0 has read
+    the tile it overwrites - and device 0's task thread is already inside its half. Reshards run on
+    a thread of their own per device, so the step ends; with one thread per device it could not."""
+    ctx = C.ThreadedContext([0, 1], False, True)
+    arrived = [threading.Event(), threading.Event()]
+    outcome = {}
+
+    def half(me):
+        def body():
+            arrived[me].set()
+            outcome[me] = arrived[1 - me].wait(timeout=20.0)       # the partner must get here too
+        return body
+
+    X, Y = 0, 1
+    ctx.create_execute_task(1, [], [(X, 1)], lambda: None, "produce")                    # tile X on device 1
+    ctx.create_execute_task(0, [], [(Y, 0)], half(0), "collective", True)                # device 0 enters first ...
+    ctx.reshard(0, [(X, 1)], [(Y + 1, 0)], lambda: time.sleep(0.05), "move X to device 0", 0)   # ... with this queued behind it
+    ctx.create_execute_task(1, [], [(X, 1)], half(1), "collective", True)                # overwrites X: waits for the reshard
+    status, message = ctx.wait_all()
+    assert int(status) == 0, message
+    assert outcome == {0: True, 1: True}
+    assert ctx.hazard_report() == "" and ctx.pending_report() == []
+    ctx.shutdown()
