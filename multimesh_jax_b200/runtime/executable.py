@@ -13,6 +13,8 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional, Tuple
 
+import threading
+
 import torch
 from torch.utils import _pytree as pytree
 
@@ -210,6 +212,8 @@ class Executable:
         self._reshard_plans: Dict[Tuple[int, int], dict] = {}
         # per-step invariants of the dispatch loop, built at first submission and reused
         self._task_entries: Dict[Tuple[int, int], tuple] = {}
+        self._in_use: Dict[int, int] = {}          # lifetime checking: storages of tiles handed to running tasks
+        self._in_use_lock = threading.Lock()
         self._reshard_entries: Dict[int, list] = {}
         self._cur_step = 0
         self._cur_roots: Dict[int, Dict[int, torch.Tensor]] = {}
@@ -281,6 +285,9 @@ class Executable:
 
     def _storage_shared(self, t: torch.Tensor) -> bool:
         ptr = t.untyped_storage().data_ptr()
+        with self._in_use_lock:
+            if ptr in self._in_use:          # a running task of another thread still reads a view of it
+                return True
         for tiles in self.tiles.values():
             for other in tiles.values():
                 if other is not t and isinstance(other, torch.Tensor) and other.untyped_storage().data_ptr() == ptr:
@@ -724,7 +731,23 @@ class Executable:
                                                         "allocated")
                     torch.cuda.empty_cache()
             accs = [tiles[s].get(d) if m == 2 else None for s, m in zip(out_ids, modes)] if fused else None
-            outs = prog.run(dctx, scalars, ins, accs)
+            if self._lifetimes:
+                # inputs read for the last time leave the tile table while the program still reads them
+                held = [t.untyped_storage().data_ptr() for t in ins if isinstance(t, torch.Tensor)]
+                with self._in_use_lock:
+                    for ptr in held:
+                        self._in_use[ptr] = self._in_use.get(ptr, 0) + 1
+                try:
+                    outs = prog.run(dctx, scalars, ins, accs)
+                finally:
+                    with self._in_use_lock:
+                        for ptr in held:
+                            if self._in_use[ptr] == 1:
+                                del self._in_use[ptr]
+                            else:
+                                self._in_use[ptr] -= 1
+            else:
+                outs = prog.run(dctx, scalars, ins, accs)
             for oi, (s, o, m) in enumerate(zip(out_ids, outs, modes)):
                 old_tile = tiles[s].get(d) if self._lifetimes else None
                 if m and fused.get(oi):
